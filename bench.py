@@ -1,0 +1,458 @@
+"""Benchmark of the spatial-search hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload NAME]
+
+Default workload "sa_fp_pipeline": the PointNet++ SSG set-abstraction / feature-propagation
+stack on B=16 clouds of N=16384 points per GPU (FPS to 4096/1024/256/64, ball query radii
+0.1/0.2/0.4/0.8 with nsample 32, grouping of C=64/128/256/512 features, three_nn +
+three_interpolate back up every level, forward and backward), seeded synthetic data.
+One step = one pass of that stack over one batch.  Prints ONE JSON line (rank 0).
+
+--impl reference times the reference's own CPU implementation (its nanoflann / ATen
+extension compiled from the reference sources into oracle/_ref, or the oracle port when
+that is absent) on the host cores, on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+LEVELS = dict(npoint=[4096, 1024, 256, 64], radius=[0.1, 0.2, 0.4, 0.8], nsample=32, channels=[64, 128, 256, 512])
+B_CLOUDS, N_POINTS = 16, 16384
+METRIC = "sa_fp_pipeline_clouds_per_s"
+
+
+# --------------------------------------------------------------------------- inputs
+
+def make_inputs(B, N, seed):
+    """Host tensors of one batch: unit-ball clouds, per-level features ~N(0,1)."""
+    g = torch.Generator().manual_seed(seed)
+    d = torch.randn(B, N, 3, generator=g)
+    xyz = (d / d.norm(dim=2, keepdim=True) * torch.rand(B, N, 1, generator=g) ** (1.0 / 3.0)).contiguous()
+    n_in = [N] + LEVELS["npoint"][:-1]
+    sa_feat = [torch.randn(B, c, n, generator=g) for c, n in zip(LEVELS["channels"], n_in)]
+    fp_feat = [torch.randn(B, c, m, generator=g) for c, m in zip(LEVELS["channels"], LEVELS["npoint"])]
+    return xyz, sa_feat, fp_feat
+
+
+# ------------------------------------------------------------------ B200 arm: the pipeline
+
+class Pipeline:
+    """SA + FP stack on one GPU.  FPS is a chain of latency-bound launches that occupy at
+    most 128 of the 148 SMs, so it runs on its own stream; everything that only needs a
+    level's centres (ball query, grouping, three_nn, interpolation, the backward passes)
+    is enqueued on a second stream behind an event and overlaps the next level's FPS."""
+
+    def __init__(self, dev, B, N, seed):
+        import torch_points_kernels_b200 as tpk
+
+        self.tpk = tpk
+        self.dev = dev
+        self.B, self.N = B, N
+        self.s_fps = torch.cuda.Stream(dev)
+        self.s_main = torch.cuda.Stream(dev)
+        g = torch.Generator(device=dev).manual_seed(seed + 7)
+        # upstream gradients: produced on the device by the layers above in a real model
+        n_in = [N] + LEVELS["npoint"][:-1]
+        self.g_grouped = [torch.randn(B, c, m, LEVELS["nsample"], device=dev, generator=g)
+                          for c, m in zip(LEVELS["channels"], LEVELS["npoint"])]
+        self.g_up = [torch.randn(B, c, n, device=dev, generator=g) for c, n in zip(LEVELS["channels"], n_in)]
+        self.launches = 0
+
+    def step(self, xyz, sa_feat, fp_feat, overlap=True, timers=None):
+        """xyz (B,N,3), sa_feat[l] (B,C_l,N_l), fp_feat[l] (B,C_l,M_l) on the device.
+        Returns (fps indices of every level, gradients of all features)."""
+        tpk = self.tpk
+        cur = torch.cuda.current_stream(self.dev)
+        s_fps = self.s_fps if overlap else cur
+        s_main = self.s_main if overlap else cur
+        if overlap:
+            s_fps.wait_stream(cur)
+            s_main.wait_stream(cur)
+
+        def timed(name, fn):
+            if timers is None:
+                return fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(torch.cuda.current_stream(self.dev))
+            out = fn()
+            e1.record(torch.cuda.current_stream(self.dev))
+            timers.setdefault(name, []).append((e0, e1))
+            return out
+
+        pts = [xyz]
+        fps_idx, ready = [], []
+        with torch.cuda.stream(s_fps):
+            for l, m in enumerate(LEVELS["npoint"]):
+                idx = timed("fps_l%d" % (l + 1), lambda: tpk.furthest_point_sample(pts[l], m))
+                centres = torch.gather(pts[l], 1, idx.long().unsqueeze(-1).expand(-1, -1, 3)).contiguous()
+                fps_idx.append(idx)
+                pts.append(centres)
+                ev = torch.cuda.Event()
+                ev.record(s_fps)
+                ready.append(ev)
+        self.launches += 4
+
+        grads_sa, grads_fp = [], []
+        with torch.cuda.stream(s_main):
+            for l in range(4):
+                if overlap:
+                    s_main.wait_event(ready[l])
+                r, ns = LEVELS["radius"][l], LEVELS["nsample"]
+                nbr, _ = timed("ball_query_l%d" % (l + 1),
+                               lambda: tpk.ball_query(r, ns, pts[l], pts[l + 1], mode="dense"))
+                f = sa_feat[l].requires_grad_(True)
+                grouped = timed("grouping_fwd_l%d" % (l + 1), lambda: tpk.grouping_operation(f, nbr))
+                timed("grouping_bwd_l%d" % (l + 1), lambda: grouped.backward(self.g_grouped[l]))
+                grads_sa.append(f.grad)
+                f.grad = None
+                # feature propagation of this level: from its centres back to its input points
+                dist, idx3 = timed("three_nn_l%d" % (l + 1), lambda: tpk.three_nn(pts[l], pts[l + 1]))
+                w = 1.0 / (dist + 1e-8)
+                w = (w / w.sum(dim=2, keepdim=True)).contiguous()
+                ff = fp_feat[l].requires_grad_(True)
+                up = timed("interp_fwd_l%d" % (l + 1), lambda: tpk.three_interpolate(ff, idx3, w))
+                timed("interp_bwd_l%d" % (l + 1), lambda: up.backward(self.g_up[l]))
+                grads_fp.append(ff.grad)
+                ff.grad = None
+                self.launches += 6
+        if overlap:
+            cur.wait_stream(s_fps)
+            cur.wait_stream(s_main)
+        return fps_idx, grads_sa, grads_fp
+
+
+def pipeline_work(B, N):
+    """Algorithmic bytes (HBM-bound kernels) or FP32-pipe lane operations (search kernels,
+    6 per point pair: 3 subtractions, 1 multiply, 2 fused multiply-adds) per launch."""
+    n_in = [N] + LEVELS["npoint"][:-1]
+    ns = LEVELS["nsample"]
+    w = {}
+    for l in range(4):
+        n, m, c = n_in[l], LEVELS["npoint"][l], LEVELS["channels"][l]
+        w["grouping_fwd_l%d" % (l + 1)] = ("hbm", 4 * B * c * m * ns + 8 * B * m * ns + 4 * B * c * n)
+        w["grouping_bwd_l%d" % (l + 1)] = ("hbm", 4 * B * c * m * ns + 8 * B * m * ns + 4 * B * c * n)
+        w["interp_fwd_l%d" % (l + 1)] = ("hbm", 4 * B * c * n + 4 * B * c * m + B * n * 3 * 8)
+        w["interp_bwd_l%d" % (l + 1)] = ("hbm", 4 * B * c * n + 4 * B * c * m + B * n * 3 * 8)
+        w["three_nn_l%d" % (l + 1)] = ("fp32", 6 * B * n * m)
+        w["ball_query_l%d" % (l + 1)] = ("fp32", None)  # pairs depend on the data: filled from the oracle
+        w["fps_l%d" % (l + 1)] = ("fp32", 6 * B * (m - 1) * n)
+    return w
+
+
+def sample_clocks(stop, path, dev_index):
+    q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    try:
+        with open(path, "w") as f:
+            p = subprocess.Popen(["nvidia-smi", "-i", str(dev_index), "--query-gpu=" + q,
+                                  "--format=csv,noheader,nounits", "-lms", "100"], stdout=f,
+                                 stderr=subprocess.DEVNULL)
+            stop.wait()
+            p.terminate()
+            p.wait(timeout=5)
+    except Exception:
+        pass
+
+
+def parse_clocks(path):
+    sm, mx, reasons = [], 0, set()
+    try:
+        for line in open(path):
+            c = [x.strip() for x in line.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1]))
+                mx = max(mx, float(c[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+    except OSError:
+        pass
+    sm.sort()
+    return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+            "samples": len(sm)}
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def run_b200(args, rank, world, local_rank):
+    import torch.distributed as dist
+
+    from torch_points_kernels_b200 import _lib
+
+    _lib.lib()  # fail loudly if the CUDA library is missing
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    B, N = B_CLOUDS, N_POINTS
+    xyz_h, sa_h, fp_h = make_inputs(B, N, 2000 + rank)
+    host = [xyz_h] + sa_h + fp_h
+    pinned = [t.pin_memory() for t in host]
+    dev_in = [t.to(dev) for t in host]
+    pipe = Pipeline(dev, B, N, 2000 + rank)
+
+    def split(ts):
+        return ts[0], list(ts[1:5]), list(ts[5:9])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing (inputs already in HBM); > 1 GB moves per step, far beyond L2
+    for _ in range(args.warmup):
+        pipe.step(*split([t.detach() for t in dev_in]))
+    stop = threading.Event()
+    clock_file = os.path.join(tempfile.gettempdir(), "tpk_clocks_%d.csv" % rank)
+    sampler = threading.Thread(target=sample_clocks, args=(stop, clock_file, local_rank), daemon=True)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    pipe.launches = 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        pipe.step(*split([t.detach() for t in dev_in]))
+    e1.record()
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    launches = pipe.launches
+
+    # ---- end to end: pinned host inputs copied in, result (indices + gradient checksums) read back
+    def e2e_step():
+        ins = [p.to(dev, non_blocking=True) for p in pinned]
+        fps_idx, g_sa, g_fp = pipe.step(*split(ins))
+        chk = torch.stack([g.sum() for g in g_sa + g_fp])
+        out = [i.cpu() for i in fps_idx] + [chk.cpu()]
+        return out
+
+    for _ in range(max(1, args.warmup // 2)):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        res = e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1))
+    h2d = sum(t.numel() * t.element_size() for t in pinned)
+    d2h = sum(t.numel() * t.element_size() for t in res)
+    if rank == 0:
+        stop.set()
+        sampler.join(timeout=10)
+    clocks = parse_clocks(clock_file) if rank == 0 else {}
+
+    # ---- per-kernel durations: serialised pass, CUDA events on the launching stream
+    timers = {}
+    for _ in range(max(3, min(args.steps, 10))):
+        pipe.step(*split([t.detach() for t in dev_in]), overlap=False, timers=timers)
+    torch.cuda.synchronize(dev)
+    kms = {k: sum(a.elapsed_time(b) for a, b in v) / len(v) for k, v in timers.items()}
+
+    if rank != 0:
+        return
+    hbm_peak, peak_kind = measured_peaks()
+    work = pipeline_work(B, N)
+    sm_mhz = clocks.get("sm_mhz") or 1965.0
+    fp32_peak_lane_ops = 148 * 128 * sm_mhz * 1e6  # lane-ops / s at the sampled clock
+    kernels = {}
+    for name, ms in sorted(kms.items()):
+        kind, amount = work[name]
+        entry = {"ms": round(ms, 4), "bound": kind}
+        if amount is not None:
+            if kind == "hbm":
+                entry["achieved_gbs"] = round(amount / ms / 1e6, 1)
+                entry["frac"] = round(amount / ms / 1e6 / hbm_peak, 4)
+            else:
+                entry["lane_ops"] = amount
+                entry["frac"] = round(amount / (ms * 1e-3) / fp32_peak_lane_ops, 4)
+        kernels[name] = entry
+    dom = max((k for k in kernels if kernels[k]["bound"] == "hbm"), key=lambda k: kms[k])
+    roof = {"kernel": dom, "bound": "hbm", "achieved": kernels[dom]["achieved_gbs"], "peak": hbm_peak,
+            "peak_source": peak_kind, "unit": "GB/s", "frac": kernels[dom]["frac"], "traffic": None,
+            "time_dominant_kernel": max(kms, key=kms.get)}
+    clouds = B * world
+    line = {
+        "metric": METRIC, "value": round(clouds * args.steps / (ms_total * 1e-3), 2), "unit": "clouds/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_total / args.steps, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "pointnet2_ssg_sa_fp_stack fwd+bwd, B=16 clouds x N=16384 per GPU, "
+                               "npoint 4096/1024/256/64, radius 0.1/0.2/0.4/0.8, nsample 32, C 64/128/256/512",
+                   "clouds_per_gpu": B, "points_per_cloud": N, "parallelism": "batch-sharded x%d" % world,
+                   "l2": "each step moves > 1 GB (inputs larger than L2), no explicit flush"},
+        "e2e": {"value": round(clouds * args.steps / (ms_e2e * 1e-3), 2), "unit": "clouds/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(ms_e2e / args.steps, 4)},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": roof,
+        "kernels": kernels,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline_sample()
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------- reference arm / CPU baseline (host cores)
+
+def load_reference_cpu():
+    """The reference's CPU extension built from its own sources, or None."""
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    if os.path.exists(os.path.join(ref_dir, "points_cpu.so")):
+        sys.path.insert(0, ref_dir)
+        try:
+            import points_cpu
+
+            return points_cpu
+        except Exception:
+            return None
+    return None
+
+
+def cpu_pipeline(xyz, sa_feat, fp_feat, g_grouped, g_up, ref):
+    """The same stack on CPU tensors.  With `ref`: the reference's CPU functions (FPS from
+    cpu/src/fps.cpp with a fixed start, nanoflann ball query and kNN, accessor-loop
+    interpolation, torch.gather grouping as in torchpoints.py:143-146).  Without: the oracle."""
+    pts = [xyz]
+    if ref is None:
+        from oracle import oracle as orc
+    for l, m in enumerate(LEVELS["npoint"]):
+        r, ns = LEVELS["radius"][l], LEVELS["nsample"]
+        if ref is not None:
+            idx = ref.fps(pts[l], m, False)
+            centres = torch.gather(pts[l], 1, idx.unsqueeze(-1).expand(-1, -1, 3)).contiguous()
+            nbr, _ = ref.dense_ball_query(centres, pts[l], r, ns, 0, False)
+            f = sa_feat[l].requires_grad_(True)
+            all_idx = nbr.reshape(nbr.shape[0], -1).unsqueeze(1).repeat(1, f.shape[1], 1)
+            grouped = f.gather(2, all_idx).reshape(nbr.shape[0], f.shape[1], nbr.shape[1], nbr.shape[2])
+            grouped.backward(g_grouped[l])
+            idx3, d2 = ref.dense_knn(centres, pts[l], 3)
+            dist = torch.sqrt(d2)
+            w = 1.0 / (dist + 1e-8)
+            w = (w / w.sum(dim=2, keepdim=True)).contiguous()
+            up = ref.knn_interpolate(fp_feat[l], idx3, w)
+            ref.knn_interpolate_grad(g_up[l].contiguous(), idx3, w, fp_feat[l].shape[2])
+            del up
+        else:
+            idx = torch.from_numpy(orc.fps(pts[l], m)).long()
+            centres = torch.gather(pts[l], 1, idx.unsqueeze(-1).expand(-1, -1, 3)).contiguous()
+            nbr, _ = orc.ball_query_dense(r, ns, pts[l], centres)
+            orc.grouping(sa_feat[l], nbr)
+            orc.grouping_grad(g_grouped[l], nbr, pts[l].shape[1])
+            d2, idx3 = orc.three_nn(pts[l], centres)
+            dist = torch.sqrt(torch.from_numpy(d2))
+            w = 1.0 / (dist + 1e-8)
+            w = (w / w.sum(dim=2, keepdim=True)).contiguous()
+            orc.three_interpolate(fp_feat[l], idx3, w)
+            orc.three_interpolate_grad(g_up[l], idx3, w, fp_feat[l].shape[2])
+        pts.append(centres)
+
+
+def cpu_inputs(sample_clouds):
+    xyz, sa, fp = make_inputs(sample_clouds, N_POINTS, 2000)
+    g = torch.Generator().manual_seed(9)
+    n_in = [N_POINTS] + LEVELS["npoint"][:-1]
+    g_grouped = [torch.randn(sample_clouds, c, m, LEVELS["nsample"], generator=g)
+                 for c, m in zip(LEVELS["channels"], LEVELS["npoint"])]
+    g_up = [torch.randn(sample_clouds, c, n, generator=g) for c, n in zip(LEVELS["channels"], n_in)]
+    return xyz, sa, fp, g_grouped, g_up
+
+
+def cpu_baseline_sample(sample_clouds=1):
+    ref = load_reference_cpu()
+    ins = cpu_inputs(sample_clouds)
+    t0 = time.perf_counter()
+    cpu_pipeline(*ins, ref)
+    dt = time.perf_counter() - t0
+    return {"value": round(sample_clouds / dt, 4), "unit": "clouds/s", "cores": torch.get_num_threads(),
+            "kind": "reference" if ref is not None else "port",
+            "sample": "%d of the 16 clouds of one step (N=16384, all four SA/FP levels, fwd+bwd), one pass, %.1f s"
+                      % (sample_clouds, dt)}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    ref = load_reference_cpu()
+    sample = 1
+    ins = cpu_inputs(sample)
+    for _ in range(min(args.warmup, 1)):  # one warm-up pass is enough for a deterministic CPU loop
+        cpu_pipeline(*ins, ref)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_pipeline(*ins, ref)
+    dt = time.perf_counter() - t0
+    v = round(sample * args.steps / dt, 4)
+    kind = "reference" if ref is not None else "port"
+    desc = "%d of the 16 clouds of one step per timed step (N=16384, all four SA/FP levels, fwd+bwd)" % sample
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "clouds/s", "n_gpus": world,
+        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": round(dt / args.steps * 1e3, 2),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "pointnet2_ssg_sa_fp_stack fwd+bwd, N=16384, npoint 4096/1024/256/64, "
+                               "radius 0.1/0.2/0.4/0.8, nsample 32, C 64/128/256/512; CPU sample of %d cloud" % sample},
+        "cpu_baseline": {"value": v, "unit": "clouds/s", "cores": torch.get_num_threads(), "kind": kind, "sample": desc},
+        "e2e": {"value": v, "unit": "clouds/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_b200(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,212 @@
+/*
+ * tpk_b200 — C ABI of the B200 (sm_100a) spatial-search kernels.
+ *
+ * One shared library, libtpk_b200.so, exports every function below with C linkage.
+ * Conventions shared by all entry points:
+ *   - every pointer is a DEVICE pointer on the current CUDA device unless stated
+ *     otherwise; inputs are borrowed, outputs and scratch are owned by the caller;
+ *   - the library allocates no device memory, keeps no per-call state and never
+ *     synchronises the host: kernels are enqueued on `stream` (a cudaStream_t passed
+ *     as void*, NULL = legacy default stream) and the call returns at once;
+ *   - outputs need no pre-fill: the kernels write every element, including the
+ *     padding values that are part of the contract (dense ball query idx 0 / dist -1,
+ *     partial_dense -1 / -1, FPS 0, gradients start from 0);
+ *   - layouts are dense row-major ("contiguous") with the dimension order given;
+ *   - the return value is a tpk_status; nothing aborts the process.
+ *
+ * Each declaration cites the reference interface it stands in for, by path inside
+ * torch-points-kernels 0.7.1.
+ */
+#ifndef TPK_B200_H
+#define TPK_B200_H
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define TPK_API __attribute__((visibility("default")))
+#else
+#define TPK_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum tpk_status
+{
+    TPK_OK = 0,
+    TPK_ERR_INVALID_ARGUMENT = 1, /* negative size, NULL pointer, k > n, ...            */
+    TPK_ERR_CUDA = 2,             /* a CUDA runtime call or launch failed               */
+    TPK_ERR_UNSUPPORTED = 3,      /* size outside what the kernels are instantiated for */
+    TPK_ERR_SCRATCH = 4           /* scratch pointer missing or too small               */
+} tpk_status;
+
+/* Library version, e.g. 100 = 0.1.0. */
+TPK_API int tpk_version(void);
+
+/* Text of the last error recorded on the calling thread (never NULL). */
+TPK_API const char* tpk_last_error(void);
+
+/*
+ * Sticky device-side status word of the current device: 0, or non-zero after a
+ * kernel gave up a bounded wait (a cluster or grid barrier that did not complete).
+ * Reading it synchronises the device.  `reset` != 0 clears it after reading.
+ */
+TPK_API int tpk_device_status(int* status_out, int reset);
+
+/* ---------------------------------------------------------------- sampling ---- */
+
+/*
+ * Iterative furthest point sampling.  xyz (b,n,3) f32 -> idxs (b,m) int32.
+ * First sample is index 0; squared distances; points with |p|^2 <= 1e-3 are never
+ * candidates; ties resolve as in the reference's 512-thread tree reduction.
+ * Replaces furthest_point_sampling_kernel_wrapper, cuda/src/sampling.cpp:5-6
+ * (kernel cuda/src/sampling_gpu.cu:16-144), including the zero/1e10 fills of
+ * cuda/src/sampling.cpp:14-18.
+ *
+ * scratch: tpk_fps_scratch_bytes(b,n,m) bytes of device memory, or NULL when that
+ * function returns 0 (clouds small enough to keep the running min-distance array
+ * on chip).  Content on entry is irrelevant.
+ */
+TPK_API int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz, void* scratch,
+                                int32_t* idxs, void* stream);
+TPK_API int64_t tpk_fps_scratch_bytes(int b, int n, int m);
+
+/* --------------------------------------------------------------- ball query ---- */
+
+/*
+ * Dense radius search.  new_xyz (b,m,3) centres, xyz (b,n,3) candidates ->
+ * idx (b,m,nsample) int64, dist (b,m,nsample) f32 squared distances.
+ * First nsample candidates in index order with d2 < radius*radius; unused idx slots
+ * repeat the first hit (0 when there is none); unused dist slots are -1.
+ * Replaces query_ball_point_kernel_dense_wrapper, cuda/src/ball_query.cpp:5-7
+ * (kernel cuda/src/ball_query_gpu.cu:9-52) and the fills of ball_query.cpp:26-29.
+ */
+TPK_API int tpk_ball_query_dense(int b, int n, int m, float radius, int nsample, const float* new_xyz,
+                         const float* xyz, int64_t* idx, float* dist, void* stream);
+
+/*
+ * Radius search on packed segments.  x (size_x,3) candidates, y (size_y,3) centres,
+ * batch_x (size_x) / batch_y (size_y) sorted int64 segment ids ->
+ * idx (size_y,nsample) int64 positions in x, dist (size_y,nsample) f32; test is
+ * d2 <= radius*radius; unused slots are -1 in both outputs.
+ * Replaces query_ball_point_kernel_partial_wrapper, cuda/src/ball_query.cpp:9-13
+ * (kernel cuda/src/ball_query_gpu.cu:54-95) together with the host-side offset
+ * construction of cuda/src/ball_query.cpp:64-73: segment ranges are found on the
+ * device by binary search, so no device-to-host copy of batch_x[-1] takes place.
+ */
+TPK_API int tpk_ball_query_partial_dense(int64_t size_x, int64_t size_y, float radius, int nsample,
+                                 const float* x, const float* y, const int64_t* batch_x,
+                                 const int64_t* batch_y, int64_t* idx, float* dist, void* stream);
+
+/* ---------------------------------------------------------- nearest neighbours ---- */
+
+/*
+ * Three nearest known points per unknown point.  unknown (b,n,3), known (b,m,3) ->
+ * dist2 (b,n,3) f32 SQUARED distances ascending, idx (b,n,3) int32.
+ * Fewer than three known points leave +inf / 0 in the missing slots.
+ * Replaces three_nn_kernel_wrapper, cuda/src/interpolate.cpp:5-6
+ * (kernel cuda/src/interpolate_gpu.cu:9-65).
+ */
+TPK_API int tpk_three_nn(int b, int n, int m, const float* unknown, const float* known, float* dist2,
+                 int32_t* idx, void* stream);
+
+/*
+ * k nearest support points per query.  support (b,n,3), query (b,m,3) ->
+ * idx (b,m,k) int64, dist2 (b,m,k) f32, ascending squared distance evaluated
+ * unfused as ((dx*dx)+dy*dy)+dz*dz; equal distances keep index order.
+ * The reference has this on the CPU only: dense_knn, cpu/src/knn.cpp:40-59
+ * (nanoflann knnSearch, cpu/include/nanoflann.hpp:1367-1375); its Python wrapper
+ * raises on CUDA tensors (torch_points_kernels/knn.py:16-17).
+ * k > n returns TPK_ERR_INVALID_ARGUMENT (reference: cpu/src/knn.cpp:12-14).
+ * 1 <= k <= TPK_KNN_MAX_K.
+ */
+#define TPK_KNN_MAX_K 64
+TPK_API int tpk_knn_dense(int b, int n, int m, int k, const float* support, const float* query,
+                  int64_t* idx, float* dist2, void* stream);
+
+/*
+ * The same on packed segments: support (size_s,3) / query (size_q,3) with sorted
+ * int64 segment ids; idx are positions in the packed support array; a query whose
+ * segment holds fewer than k support points gets -1 in the missing idx and dist2
+ * slots.  No counterpart in the reference (its kNN is dense only); semantics are
+ * dense_knn applied to each segment on its own.
+ */
+TPK_API int tpk_knn_partial_dense(int64_t size_s, int64_t size_q, int k, const float* support,
+                          const float* query, const int64_t* batch_s, const int64_t* batch_q,
+                          int64_t* idx, float* dist2, void* stream);
+
+/* ------------------------------------------------------------- interpolation ---- */
+
+/*
+ * out[b,c,j] = sum_k points[b,c,idx[b,j,k]] * weight[b,j,k], k = 0..2.
+ * points (b,c,m) f32, idx (b,n,3) int32, weight (b,n,3) f32 -> out (b,c,n) f32.
+ * Replaces three_interpolate_kernel_wrapper, cuda/src/interpolate.cpp:7-8
+ * (kernel cuda/src/interpolate_gpu.cu:78-107).
+ */
+TPK_API int tpk_three_interpolate(int b, int c, int m, int n, const float* points, const int32_t* idx,
+                          const float* weight, float* out, void* stream);
+
+/*
+ * grad_points[b,c,idx[b,j,k]] += grad_out[b,c,j] * weight[b,j,k]; grad_points (b,c,m)
+ * is fully written (starts from zero inside the call).
+ * Replaces three_interpolate_grad_kernel_wrapper, cuda/src/interpolate.cpp:9-10
+ * (kernel cuda/src/interpolate_gpu.cu:122-152) and the zero fill of interpolate.cpp:69-70.
+ */
+TPK_API int tpk_three_interpolate_grad(int b, int c, int n, int m, const float* grad_out,
+                               const int32_t* idx, const float* weight, float* grad_points,
+                               void* stream);
+
+/* ------------------------------------------------------------------ grouping ---- */
+
+/*
+ * out[b,c,p,s] = features[b,c,idx[b,p,s]].  features (b,c,n) f32, idx
+ * (b,npoint,nsample) int64 -> out (b,c,npoint,nsample) f32.
+ * The reference has no native code here: it expands idx to (b,c,npoint*nsample)
+ * int64 and calls torch.gather, torch_points_kernels/torchpoints.py:129-146.
+ */
+TPK_API int tpk_grouping(int b, int c, int n, int npoint, int nsample, const float* features,
+                 const int64_t* idx, float* out, void* stream);
+
+/*
+ * grad_features[b,c,idx[b,p,s]] += grad_out[b,c,p,s]; grad_features (b,c,n) is fully
+ * written.  Stands in for autograd's scatter-add backward of the gather at
+ * torch_points_kernels/torchpoints.py:145.
+ */
+TPK_API int tpk_grouping_grad(int b, int c, int n, int npoint, int nsample, const float* grad_out,
+                      const int64_t* idx, float* grad_features, void* stream);
+
+/* ------------------------------------------------------------------- chamfer ---- */
+
+/*
+ * Nearest neighbour in the other cloud, both directions.  xyz1 (b,n,3), xyz2 (b,m,3)
+ * -> dist1 (b,n), dist2 (b,m) squared distances, idx1 (b,n), idx2 (b,m) int32;
+ * lowest index wins among equal minima.  f32 and f64 variants, as the reference
+ * dispatches both (cuda/src/chamfer_dist_gpu.cu:167-176).
+ * Replaces chamfer_dist_kernel_wrapper, cuda/include/chamfer_dist.h:10
+ * (kernel cuda/src/chamfer_dist_gpu.cu:8-155).
+ */
+TPK_API int tpk_chamfer_dist_f32(int b, int n, const float* xyz1, int m, const float* xyz2, float* dist1,
+                         float* dist2, int32_t* idx1, int32_t* idx2, void* stream);
+TPK_API int tpk_chamfer_dist_f64(int b, int n, const double* xyz1, int m, const double* xyz2,
+                         double* dist1, double* dist2, int32_t* idx1, int32_t* idx2, void* stream);
+
+/*
+ * Gradient of both directions w.r.t. both clouds; grad_xyz1 (b,n,3) and grad_xyz2
+ * (b,m,3) are fully written.
+ * Replaces chamfer_dist_grad_kernel_wrapper, cuda/include/chamfer_dist.h:12-15
+ * (kernel cuda/src/chamfer_dist_gpu.cu:186-245).
+ */
+TPK_API int tpk_chamfer_dist_grad_f32(int b, int n, const float* xyz1, int m, const float* xyz2,
+                              const int32_t* idx1, const int32_t* idx2, const float* grad_dist1,
+                              const float* grad_dist2, float* grad_xyz1, float* grad_xyz2,
+                              void* stream);
+TPK_API int tpk_chamfer_dist_grad_f64(int b, int n, const double* xyz1, int m, const double* xyz2,
+                              const int32_t* idx1, const int32_t* idx2, const double* grad_dist1,
+                              const double* grad_dist2, double* grad_xyz1, double* grad_xyz2,
+                              void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TPK_B200_H */

@@ -1,0 +1,95 @@
+"""CPU tests of the drop-in boundary: the shared library loads and exports exactly what
+include/tpk_b200.h declares, and the Python surface raises the reference's exceptions
+without touching a GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+import torch_points_kernels_b200 as tpk
+from torch_points_kernels_b200 import _lib, chamfer_dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "tpk_b200.h")).read()
+    return sorted(set(re.findall(r"TPK_API\s+[\w\s\*]+?\b(tpk_\w+)\s*\(", text)))
+
+
+def test_header_symbols_exported():
+    names = _declared()
+    assert len(names) >= 18
+    handle = ctypes.CDLL(_lib.LIB_PATH)
+    for n in names:
+        assert hasattr(handle, n), n
+    assert sorted(_lib.EXPORTS) == names
+
+
+def test_version_and_error_text():
+    l = _lib.lib()
+    assert l.tpk_version() >= 100
+    assert isinstance(l.tpk_last_error(), bytes)
+
+
+def test_invalid_arguments_return_status_without_gpu():
+    l = _lib.lib()
+    # argument validation happens before any CUDA call
+    assert l.tpk_knn_dense(1, 3, 1, 5, None, None, None, None, None) == 1
+    assert b"Not enough points" in l.tpk_last_error()
+    assert l.tpk_ball_query_dense(-1, 1, 1, 0.1, 1, None, None, None, None, None) == 1
+    assert l.tpk_three_nn(1, 4, 4, None, None, None, None, None) == 1
+    assert l.tpk_furthest_point_sampling(1, 0, 2, None, None, None, None) == 1
+    # empty problems are no-ops
+    assert l.tpk_furthest_point_sampling(0, 10, 2, None, None, None, None) == 0
+    assert l.tpk_grouping(0, 4, 4, 4, 4, None, None, None, None) == 0
+
+
+def test_python_surface_matches_reference_names():
+    for name in ("ball_query", "furthest_point_sample", "grouping_operation", "three_interpolate",
+                 "three_nn", "knn"):
+        assert callable(getattr(tpk, name))
+    assert callable(chamfer_dist.chamfer_dist) and hasattr(chamfer_dist, "ChamferFunction")
+
+
+def test_python_level_errors():
+    x = torch.rand(2, 16, 3)
+    with pytest.raises(ValueError):
+        tpk.furthest_point_sample(x, 17)
+    with pytest.raises(ValueError):
+        tpk.three_nn(torch.rand(2, 2, 3), x)
+    with pytest.raises(Exception):
+        tpk.ball_query(0.1, 4, x, x, mode=None)
+    with pytest.raises(Exception):
+        tpk.ball_query(0.1, 4, x, x, mode="sparse")
+    with pytest.raises(Exception):
+        tpk.ball_query(0.1, 4, x, x, mode="dense", batch_x=torch.zeros(2))
+    with pytest.raises(Exception):
+        tpk.ball_query(0.1, 4, x[0], x[0], mode="PARTIAL_DENSE")
+    with pytest.raises(NotImplementedError):
+        tpk.ball_query(0.1, 4, x, x, sort=True)
+    with pytest.raises(ValueError):
+        chamfer_dist.chamfer_dist(torch.rand(2, 3), torch.rand(2, 5, 3))
+    with pytest.raises(AssertionError):
+        tpk.ball_query(0.1, 4, x, x, mode="partial_dense", batch_x=torch.zeros(2, dtype=torch.long),
+                       batch_y=torch.zeros(2, dtype=torch.long))
+
+
+def test_cpu_tensors_are_rejected_not_silently_computed():
+    # no CPU fallback: the reference's CHECK_CUDA message, as a RuntimeError
+    x = torch.rand(2, 16, 3)
+    for fn in (lambda: tpk.furthest_point_sample(x, 4), lambda: tpk.three_nn(x, x),
+               lambda: tpk.ball_query(0.1, 4, x, x), lambda: tpk.knn(x, x, 2),
+               lambda: tpk.grouping_operation(torch.rand(2, 3, 16), torch.zeros(2, 4, 2, dtype=torch.long)),
+               lambda: chamfer_dist.chamfer_dist(x, x)):
+        with pytest.raises(RuntimeError, match="CUDA tensor"):
+            fn()
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libtpk_b200.so")
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.lib()

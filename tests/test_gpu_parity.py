@@ -1,0 +1,377 @@
+"""GPU parity tests: every op, called through the Python surface (which calls the C ABI),
+against the CPU oracle on the same seeded inputs.  Integer outputs and the distances the
+search kernels return are compared bit for bit; interpolated / grouped values to 1e-5
+relative; atomically accumulated gradients to 1e-4."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import torch_points_kernels_b200 as tpk
+from torch_points_kernels_b200 import _lib, chamfer_dist as cd
+from oracle import oracle as orc
+from tests import data
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.int32)
+
+
+def same_bits(got, want):
+    np.testing.assert_array_equal(bits(got), bits(want))
+
+
+def cu(t):
+    return torch.as_tensor(t).to(DEV).contiguous()
+
+
+def npy(t):
+    return t.detach().cpu().numpy()
+
+
+# ------------------------------------------------------------------------------ FPS
+
+@pytest.fixture
+def fps_env():
+    old = os.environ.get("TPK_FPS_CONFIG")
+    yield
+    if old is None:
+        os.environ.pop("TPK_FPS_CONFIG", None)
+    else:
+        os.environ["TPK_FPS_CONFIG"] = old
+
+
+def test_fps_known_answer(known_answers):
+    ka = known_answers["fps_start0"]
+    out = tpk.furthest_point_sample(cu(np.asarray(ka["points"], np.float32)), ka["npoint"])
+    assert out.dtype == torch.int32 and npy(out).tolist() == ka["idx"]
+
+
+@pytest.mark.parametrize("B,N,m", [(3, 1000, 200), (2, 4096, 512), (2, 16384, 700), (1, 40000, 150),
+                                   (1, 100000, 40), (4, 257, 257), (2, 31, 9), (5, 1, 1), (2, 2, 2)])
+def test_fps_matches_oracle(B, N, m):
+    x = data.unit_ball(B, N, seed=2000 + N)
+    got = npy(tpk.furthest_point_sample(cu(x), m))
+    np.testing.assert_array_equal(got, orc.fps(x, m))
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("cfg", ["1,512,16,0", "1,512,16,1", "2,512,8,0", "2,512,8,1", "4,256,8,0",
+                                 "4,256,8,1", "8,128,8,0", "8,128,8,1", "8,512,2,1", "16,512,1,0",
+                                 "16,512,1,1", "4,128,16,1"])
+def test_fps_every_cluster_shape(cfg, fps_env):
+    """Same cloud through every cluster size / block size / exchange mechanism."""
+    x = data.unit_ball(3, 5000, seed=77)
+    want = orc.fps(x, 300)
+    os.environ["TPK_FPS_CONFIG"] = cfg
+    got = npy(tpk.furthest_point_sample(cu(x), 300))
+    np.testing.assert_array_equal(got, want)
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("n", [3, 8, 37, 64, 300, 700, 1500, 5000])
+def test_fps_tie_break_and_skip_rule(n, fps_env):
+    rng = np.random.default_rng(n)
+    pts = np.zeros((2, n, 3), np.float32)
+    pts[:, 0] = (1.0, 1.0, 1.0)
+    pts[:, 1:] = (1.0, 1.0, 1.5)
+    far = rng.choice(np.arange(1, n), size=max(1, (n - 1) // 2), replace=False)
+    pts[0, far] = (5.0, 1.0, 1.0)          # many exact ties for the second sample
+    pts[1, 1:] = rng.integers(0, 3, size=(n - 1, 3)).astype(np.float32)  # lattice: ties and skipped origin points
+    m = min(n, 12)
+    want = orc.fps(pts, m)
+    for cfg in (None, "2,256,16,1", "4,128,16,0"):
+        if cfg:
+            os.environ["TPK_FPS_CONFIG"] = cfg
+        np.testing.assert_array_equal(npy(tpk.furthest_point_sample(cu(pts), m)), want)
+
+
+def test_fps_all_points_skipped():
+    tiny = np.full((2, 40, 3), 0.001, np.float32)
+    assert npy(tpk.furthest_point_sample(cu(tiny), 7)).tolist() == [[0] * 7] * 2
+
+
+# ------------------------------------------------------------------------ ball query
+
+def test_ball_query_known_answers(known_answers):
+    ka = known_answers["ball_query_dense_cuda"]
+    idx, dist = tpk.ball_query(ka["radius"], ka["nsample"], cu(np.asarray(ka["x"], np.float32)),
+                               cu(np.asarray(ka["y"], np.float32)))
+    assert idx.dtype == torch.int64 and npy(idx).tolist() == ka["idx"]
+    np.testing.assert_allclose(npy(dist), np.asarray(ka["dist"], np.float32), atol=1e-6)
+    for name in ("ball_query_partial_cuda", "ball_query_partial_cpu"):
+        ka = known_answers[name]
+        idx, dist = tpk.ball_query(ka["radius"], ka["nsample"], cu(np.asarray(ka["x"], np.float32)),
+                                   cu(np.asarray(ka["y"], np.float32)), mode="PARTIAL_DENSE",
+                                   batch_x=cu(np.asarray(ka["batch_x"])), batch_y=cu(np.asarray(ka["batch_y"])))
+        assert npy(idx).tolist() == ka["idx"]
+        np.testing.assert_allclose(npy(dist), np.asarray(ka["dist"], np.float32), atol=1e-6)
+
+
+@pytest.mark.parametrize("B,N,M,r,ns", [(4, 4096, 1024, 0.2, 32), (2, 1025, 77, 0.1, 32), (3, 5, 9, 0.5, 4),
+                                        (2, 1, 3, 10.0, 3), (2, 3000, 300, 0.8, 32), (1, 2048, 2048, 0.05, 1),
+                                        (2, 1500, 40, 1e-4, 16), (16, 1024, 256, 0.4, 32)])
+def test_ball_query_dense_matches_oracle(B, N, M, r, ns):
+    x = data.unit_ball(B, N, seed=N + M)
+    y = x[:, torch.randperm(N, generator=data.gen(N))[: min(M, N)]].contiguous() if M <= N else data.unit_ball(B, M, seed=5)
+    idx, dist = tpk.ball_query(r, ns, cu(x), cu(y), mode="dense")
+    oi, od = orc.ball_query_dense(r, ns, x, y)
+    np.testing.assert_array_equal(npy(idx), oi)
+    same_bits(npy(dist), od)
+
+
+def test_ball_query_dense_boundary_is_strict_partial_is_inclusive():
+    x = np.array([[[0, 0, 0], [0.5, 0, 0], [0.25, 0, 0]]], np.float32)
+    y = np.array([[[0, 0, 0]]], np.float32)
+    idx, dist = tpk.ball_query(0.5, 3, cu(x), cu(y))
+    assert npy(idx).tolist() == [[[0, 2, 0]]] and npy(dist).tolist() == [[[0.0, 0.0625, -1.0]]]
+    b = torch.zeros(3, dtype=torch.long)
+    idx, dist = tpk.ball_query(0.5, 3, cu(x[0]), cu(y[0]), mode="partial_dense", batch_x=cu(b), batch_y=cu(b[:1]))
+    assert npy(idx).tolist() == [[0, 1, 2]] and npy(dist).tolist() == [[0.0, 0.25, 0.0625]]
+
+
+def test_ball_query_partial_golden_and_oracle(golden_dir):
+    p = np.load(os.path.join(golden_dir, "partial.npz"))
+    r, ns = float(p["radius"]), int(p["nsample"])
+    idx, d2 = tpk.ball_query(r, ns, cu(p["x"]), cu(p["y"]), mode="partial_dense",
+                             batch_x=cu(p["batch_x"]), batch_y=cu(p["batch_y"]))
+    oi, od = orc.ball_query_partial(r, ns, p["x"], p["y"], p["batch_x"], p["batch_y"])
+    np.testing.assert_array_equal(npy(idx), oi)
+    same_bits(npy(d2), od)
+    r2 = np.float32(r) * np.float32(r)
+    for q in range(oi.shape[0]):  # the reference CPU result as a set (strict radius there)
+        got = {int(i) for i, d in zip(npy(idx)[q], npy(d2)[q]) if d >= 0 and d != r2}
+        assert got == {int(i) for i, d in zip(p["idx"][q], p["d2"][q]) if d >= 0}
+
+
+@pytest.mark.parametrize("seed,ns", [(1, 16), (2, 64), (3, 1)])
+def test_ball_query_partial_ragged_segments(seed, ns):
+    g = data.gen(seed)
+    sizes = [1, 700, 3, 0, 1500, 2, 260, 1100]       # id 3 has no support points
+    qsizes = [1, 90, 0, 4, 333, 2, 0, 270]           # ids 2 and 6 have no queries
+    x = torch.cat([torch.rand(s, 3, generator=g) for s in sizes])
+    bx = torch.cat([torch.full((s,), i, dtype=torch.long) for i, s in enumerate(sizes)])
+    y = torch.cat([torch.rand(s, 3, generator=g) for s in qsizes])
+    by = torch.cat([torch.full((s,), i, dtype=torch.long) for i, s in enumerate(qsizes)])
+    idx, d2 = tpk.ball_query(0.12, ns, cu(x), cu(y), mode="partial_dense", batch_x=cu(bx), batch_y=cu(by))
+    oi, od = orc.ball_query_partial(0.12, ns, x, y, bx, by)
+    np.testing.assert_array_equal(npy(idx), oi)
+    same_bits(npy(d2), od)
+
+
+def test_ball_query_partial_scene_scale():
+    x, y, bx, by = data.packed_planes(n_scenes=5, lo=2000, hi=9000, seed=3001)
+    idx, d2 = tpk.ball_query(0.05, 64, cu(x), cu(y), mode="partial_dense", batch_x=cu(bx), batch_y=cu(by))
+    oi, od = orc.ball_query_partial(0.05, 64, x, y, bx, by)
+    np.testing.assert_array_equal(npy(idx), oi)
+    same_bits(npy(d2), od)
+
+
+# ------------------------------------------------------------------ three_nn and kNN
+
+@pytest.mark.parametrize("B,n,m", [(4, 4096, 1024), (2, 1000, 2000), (3, 77, 3), (2, 10, 2), (2, 5, 1), (16, 256, 64)])
+def test_three_nn_matches_oracle(B, n, m):
+    unknown = data.unit_ball(B, n, seed=n)
+    known = data.unit_ball(B, m, seed=m + 1)
+    dist, idx = tpk.three_nn(cu(unknown), cu(known))
+    od2, oi = orc.three_nn(unknown, known)
+    assert idx.dtype == torch.int32
+    np.testing.assert_array_equal(npy(idx), oi)
+    with np.errstate(invalid="ignore"):
+        same_bits(npy(dist), np.sqrt(od2))
+
+
+def test_three_nn_duplicates_keep_lowest_index_first():
+    known = np.zeros((1, 6, 3), np.float32)
+    known[0, :, 0] = [1, 1, 1, 2, 1, 0.5]
+    unknown = np.zeros((1, 3, 3), np.float32)
+    dist, idx = tpk.three_nn(cu(unknown), cu(known))
+    assert npy(idx)[0, 0].tolist() == [5, 0, 1]
+    od2, oi = orc.three_nn(unknown, known)
+    np.testing.assert_array_equal(npy(idx), oi)
+
+
+def test_knn_known_answer(known_answers):
+    ka = known_answers["knn"]
+    s, q = cu(np.asarray(ka["support"], np.float32)), cu(np.asarray(ka["query"], np.float32))
+    idx, d2 = tpk.knn(s, q, 3)
+    assert idx.dtype == torch.int64 and npy(idx).tolist() == ka["k3_idx"]
+    assert npy(d2).tolist() == ka["k3_dist"]
+    assert npy(tpk.knn(s, q, 2)[0]).tolist() == ka["k2_idx"]
+    with pytest.raises(RuntimeError):
+        tpk.knn(s, q, ka["k_too_large"])
+
+
+def test_knn_golden_bit_exact(golden_dir):
+    p = np.load(os.path.join(golden_dir, "plumbing.npz"))
+    for k in (3, 16):
+        idx, d2 = tpk.knn(cu(p["x"]), cu(p["y"]), k)
+        np.testing.assert_array_equal(npy(idx), p["knn%d_idx" % k])
+        same_bits(npy(d2), p["knn%d_d2" % k])
+
+
+@pytest.mark.parametrize("B,N,M,k", [(4, 4096, 1024, 3), (2, 3000, 500, 16), (2, 700, 130, 1), (1, 2500, 300, 64),
+                                     (3, 40, 17, 40), (16, 1500, 64, 8)])
+def test_knn_dense_matches_oracle(B, N, M, k):
+    s = data.unit_ball(B, N, seed=N + k)
+    q = data.unit_ball(B, M, seed=M + k)
+    idx, d2 = tpk.knn(cu(s), cu(q), k)
+    oi, od = orc.knn(s, q, k)
+    np.testing.assert_array_equal(npy(idx), oi)
+    same_bits(npy(d2), od)
+
+
+def test_knn_partial_matches_per_segment_dense():
+    x, y, bx, by = data.packed_planes(n_scenes=4, lo=1500, hi=5000, seed=3002)
+    # a short segment (fewer support points than k) and one without queries
+    x = torch.cat([x, torch.rand(5, 3)]); bx = torch.cat([bx, torch.full((5,), 4)])
+    y = torch.cat([y, torch.rand(2, 3)]); by = torch.cat([by, torch.full((2,), 4)])
+    x = torch.cat([x, torch.rand(30, 3)]); bx = torch.cat([bx, torch.full((30,), 6)])
+    idx, d2 = tpk.knn(cu(x), cu(y), 16, batch_support=cu(bx), batch_pos=cu(by))
+    oi, od = orc.knn_segmented(x, y, bx, by, 16)
+    np.testing.assert_array_equal(npy(idx), oi)
+    same_bits(npy(d2), od)
+
+
+# --------------------------------------------------------- interpolation and grouping
+
+@pytest.mark.parametrize("B,C,m,n", [(4, 64, 1024, 4096), (2, 7, 33, 1001), (3, 30, 100, 500), (2, 130, 64, 256)])
+def test_three_interpolate_forward_backward(B, C, m, n):
+    g = data.gen(n)
+    known = torch.rand(B, m, 3, generator=g)
+    unknown = torch.rand(B, n, 3, generator=g)
+    feat = torch.randn(B, C, m, generator=g)
+    od2, oi = orc.three_nn(unknown, known)
+    dist = torch.from_numpy(np.sqrt(od2))
+    w = 1.0 / (dist + 1e-8)
+    w = (w / w.sum(2, keepdim=True)).contiguous()
+    f = cu(feat).requires_grad_(True)
+    out = tpk.three_interpolate(f, cu(oi), cu(w))
+    want = orc.three_interpolate(feat, oi, w)
+    np.testing.assert_allclose(npy(out), want, rtol=1e-5, atol=1e-6)
+    gout = torch.randn(out.shape, generator=g)
+    out.backward(cu(gout))
+    np.testing.assert_allclose(npy(f.grad), orc.three_interpolate_grad(gout, oi, w, m), rtol=1e-4, atol=1e-4)
+
+
+def test_three_interpolate_golden(golden_dir):
+    p = np.load(os.path.join(golden_dir, "plumbing.npz"))
+    f = cu(p["feat"]).requires_grad_(True)
+    out = tpk.three_interpolate(f, cu(p["nn_idx"].astype(np.int32)), cu(p["weight"]))
+    np.testing.assert_allclose(npy(out), p["interp"], rtol=1e-5, atol=1e-6)
+    out.backward(cu(p["interp_gout"]))
+    np.testing.assert_allclose(npy(f.grad), p["interp_grad"], rtol=1e-4, atol=1e-4)
+
+
+def test_grouping_known_answer(known_answers):
+    ka = known_answers["grouping"]
+    out = tpk.grouping_operation(cu(np.asarray(ka["features"], np.float32)), cu(np.asarray(ka["idx"], np.int64)))
+    np.testing.assert_array_equal(npy(out), np.asarray(ka["expected"], np.float32))
+
+
+@pytest.mark.parametrize("B,C,N,P,S", [(4, 64, 4096, 1024, 32), (2, 5, 100, 33, 3), (3, 130, 257, 64, 32),
+                                       (1, 3, 60000, 500, 16), (2, 17, 1000, 1, 1)])
+def test_grouping_forward_backward(B, C, N, P, S, monkeypatch):
+    g = data.gen(N + P)
+    feat = torch.randn(B, C, N, generator=g)
+    idx = torch.randint(0, N, (B, P, S), generator=g)
+    f = cu(feat).requires_grad_(True)
+    out = tpk.grouping_operation(f, cu(idx))
+    np.testing.assert_array_equal(npy(out), orc.grouping(feat, idx))
+    gout = torch.randn(out.shape, generator=g)
+    out.backward(cu(gout))
+    want = orc.grouping_grad(gout, idx, N)
+    np.testing.assert_allclose(npy(f.grad), want, rtol=1e-4, atol=1e-4)
+    # the global-atomics fallback gives the same sums
+    monkeypatch.setenv("TPK_SCATTER_GLOBAL", "1")
+    f2 = cu(feat).requires_grad_(True)
+    tpk.grouping_operation(f2, cu(idx)).backward(cu(gout))
+    np.testing.assert_allclose(npy(f2.grad), want, rtol=1e-4, atol=1e-4)
+
+
+def test_grouping_golden(golden_dir):
+    p = np.load(os.path.join(golden_dir, "plumbing.npz"))
+    f = cu(p["gfeat"]).requires_grad_(True)
+    out = tpk.grouping_operation(f, cu(p["gidx"]))
+    np.testing.assert_array_equal(npy(out), p["grouped"])
+    out.backward(cu(p["grouped_gout"]))
+    np.testing.assert_allclose(npy(f.grad), p["grouped_grad"], rtol=1e-4, atol=1e-4)
+
+
+# ------------------------------------------------------------------------- chamfer
+
+def test_chamfer_known_answers(known_answers):
+    ka = known_answers["chamfer"]
+    x1, x2 = cu(np.asarray(ka["xyz1"], np.float32)), cu(np.asarray(ka["xyz2"], np.float32))
+    assert abs(cd.chamfer_dist(x1, x2).item() - ka["dist"]) < 10 ** -ka["places"]
+    assert abs(cd.chamfer_dist(x1, x2, True).item() - ka["dist_ignore_zeros"]) < 10 ** -ka["places"]
+
+
+@pytest.mark.parametrize("B,n,m", [(4, 2048, 2048), (2, 1000, 1777), (3, 5, 1), (64, 300, 200)])
+def test_chamfer_forward_backward(B, n, m):
+    c1, c2 = data.chamfer_pair(B, max(n, m), seed=4000 + n)
+    c1, c2 = c1[:, :n].contiguous(), c2[:, :m].contiguous()
+    x1, x2 = cu(c1).requires_grad_(True), cu(c2).requires_grad_(True)
+    d1, d2 = cd.ChamferFunction.apply(x1, x2)
+    o1, o2, i1, i2 = orc.chamfer(c1, c2)
+    same_bits(npy(d1), o1)
+    same_bits(npy(d2), o2)
+    g = data.gen(n)
+    g1, g2 = torch.randn(B, n, generator=g), torch.randn(B, m, generator=g)
+    torch.autograd.backward([d1, d2], [cu(g1), cu(g2)])
+    w1, w2 = orc.chamfer_grad(c1, c2, i1, i2, g1, g2)
+    np.testing.assert_allclose(npy(x1.grad), w1, rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(npy(x2.grad), w2, rtol=1e-4, atol=1e-4)
+
+
+def test_chamfer_indices_bit_exact_with_duplicates():
+    c1 = np.zeros((1, 4, 3), np.float32)
+    c2 = np.tile(np.array([[1, 0, 0]], np.float32), (1, 1500, 1))   # every candidate ties
+    lib = _lib.lib()
+    x1, x2 = cu(c1), cu(c2)
+    d1 = torch.empty(1, 4, device=DEV); d2 = torch.empty(1, 1500, device=DEV)
+    i1 = torch.empty(1, 4, dtype=torch.int32, device=DEV); i2 = torch.empty(1, 1500, dtype=torch.int32, device=DEV)
+    _lib.call("tpk_chamfer_dist_f32", 1, 4, _lib.ptr(x1), 1500, _lib.ptr(x2), _lib.ptr(d1), _lib.ptr(d2),
+              _lib.ptr(i1), _lib.ptr(i2), _lib.stream_of(x1))
+    o1, o2, oi1, oi2 = orc.chamfer(c1, c2)
+    np.testing.assert_array_equal(npy(i1), oi1)
+    np.testing.assert_array_equal(npy(i2), oi2)
+    assert npy(i1).tolist() == [[0, 0, 0, 0]]
+
+
+def test_chamfer_float64_gradcheck():
+    g = data.gen(11)
+    x = torch.rand(4, 64, 3, generator=g).double().to(DEV).requires_grad_(True)
+    y = torch.rand(4, 128, 3, generator=g).double().to(DEV).requires_grad_(True)
+    assert torch.autograd.gradcheck(cd.ChamferFunction.apply, [x, y])
+    o1, o2, _, _ = orc.chamfer(x.detach().cpu(), y.detach().cpu())
+    d1, d2 = cd.ChamferFunction.apply(x, y)
+    np.testing.assert_allclose(npy(d1), o1, rtol=1e-12)
+    np.testing.assert_allclose(npy(d2), o2, rtol=1e-12)
+
+
+# ------------------------------------------------- the CPU-runnable plumbing configuration
+
+def test_config1_plumbing_end_to_end():
+    x, y, feat = data.cfg1_plumbing()
+    xc, yc = cu(x), cu(y)
+    idx, dist = tpk.ball_query(0.2, 32, xc, yc, mode="dense")
+    oi, od = orc.ball_query_dense(0.2, 32, x, y)
+    np.testing.assert_array_equal(npy(idx), oi)
+    same_bits(npy(dist), od)
+    ki, kd = tpk.knn(xc, yc, 3)
+    oki, okd = orc.knn(x, y, 3)
+    np.testing.assert_array_equal(npy(ki), oki)
+    same_bits(npy(kd), okd)
+    d, i3 = tpk.three_nn(xc, yc)
+    od2, oi3 = orc.three_nn(x, y)
+    np.testing.assert_array_equal(npy(i3), oi3)
+    w = 1.0 / (d + 1e-8)
+    w = w / w.sum(2, keepdim=True)
+    out = tpk.three_interpolate(cu(feat), i3, w.contiguous())
+    np.testing.assert_allclose(npy(out), orc.three_interpolate(feat, oi3, npy(w)), rtol=1e-5, atol=1e-6)

@@ -1,0 +1,428 @@
+// Gather / scatter-add kernels for sm_100a: grouping_operation and three_interpolate,
+// forward and backward.  All four are bandwidth problems: the forward passes write a
+// large output from a small, cache-resident feature tensor, the backward passes read a
+// large gradient and reduce it into a small one.
+//
+// Forward: a thread owns four consecutive output positions, loads their indices (and
+// weights) once, then walks a chunk of channels; per channel it gathers from the
+// (L1/L2-resident) feature row and issues one 16-byte streaming store, so a warp
+// writes 512 contiguous bytes per channel.
+//
+// Backward: a CTA owns a few (batch, channel) rows of the small gradient tensor and
+// keeps them in shared memory; it streams the matching rows of the incoming gradient
+// with 16-byte loads, accumulates with shared-memory atomics (no global atomics, no
+// zero-fill pass over the output) and writes each finished row once.  Rows too long
+// for shared memory fall back to global red.add on a zeroed output.
+//
+// grouping          : torch_points_kernels/torchpoints.py:129-146 (torch.gather + autograd)
+// three_interpolate : cuda/src/interpolate_gpu.cu:78-107, :122-152
+#include "tpk_common.cuh"
+
+namespace tpk
+{
+namespace
+{
+
+constexpr int kGatherThreads = 256;
+constexpr int kScatterThreads = 512;
+constexpr int kChanChunk = 16;
+constexpr size_t kRowSmemBudget = 200 * 1024;
+
+// p1*w1 + p2*w2 + p3*w3 as nvcc contracts the reference expression (interpolate_gpu.cu:105)
+__device__ __forceinline__ float interp3(float p1, float w1, float p2, float w2, float p3, float w3)
+{
+    return __fmaf_rn(p3, w3, __fmaf_rn(p1, w1, __fmul_rn(p2, w2)));
+}
+
+// ------------------------------------------------------------------ grouping forward
+
+template <bool VEC>
+__global__ void __launch_bounds__(kGatherThreads)
+    grouping_fwd_kernel(int c, int n, long long ps, const float* __restrict__ features,
+                        const int64_t* __restrict__ idx, float* __restrict__ out)
+{
+    const int bi = blockIdx.z;
+    const int c0 = blockIdx.y * kChanChunk;
+    const int c1 = min(c, c0 + kChanChunk);
+    const long long pos = (static_cast<long long>(blockIdx.x) * kGatherThreads + threadIdx.x) * 4;
+    if (pos >= ps) return;
+    const int64_t* ip = idx + static_cast<size_t>(bi) * ps + pos;
+    int i0, i1 = 0, i2 = 0, i3 = 0;
+    const bool full = VEC || pos + 3 < ps;
+    if (VEC)
+    {
+        const longlong2 a = __ldg(reinterpret_cast<const longlong2*>(ip));
+        const longlong2 b2 = __ldg(reinterpret_cast<const longlong2*>(ip) + 1);
+        i0 = static_cast<int>(a.x);
+        i1 = static_cast<int>(a.y);
+        i2 = static_cast<int>(b2.x);
+        i3 = static_cast<int>(b2.y);
+    }
+    else
+    {
+        i0 = static_cast<int>(__ldg(ip));
+        if (pos + 1 < ps) i1 = static_cast<int>(__ldg(ip + 1));
+        if (pos + 2 < ps) i2 = static_cast<int>(__ldg(ip + 2));
+        if (pos + 3 < ps) i3 = static_cast<int>(__ldg(ip + 3));
+    }
+    const float* f = features + (static_cast<size_t>(bi) * c + c0) * n;
+    float* o = out + (static_cast<size_t>(bi) * c + c0) * ps + pos;
+#pragma unroll 4
+    for (int ch = c0; ch < c1; ++ch, f += n, o += ps)
+    {
+        float4 v;
+        v.x = __ldg(f + i0);
+        v.y = __ldg(f + i1);
+        v.z = __ldg(f + i2);
+        v.w = __ldg(f + i3);
+        if (VEC)
+            __stcs(reinterpret_cast<float4*>(o), v);
+        else if (full)
+        {
+            o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+        }
+        else
+        {
+            o[0] = v.x;
+            if (pos + 1 < ps) o[1] = v.y;
+            if (pos + 2 < ps) o[2] = v.z;
+        }
+    }
+}
+
+// ---------------------------------------------------------- three_interpolate forward
+
+template <bool VEC>
+__global__ void __launch_bounds__(kGatherThreads)
+    interp_fwd_kernel(int c, int m, int n, const float* __restrict__ points,
+                      const int32_t* __restrict__ idx, const float* __restrict__ weight,
+                      float* __restrict__ out)
+{
+    const int bi = blockIdx.z;
+    const int c0 = blockIdx.y * kChanChunk;
+    const int c1 = min(c, c0 + kChanChunk);
+    const int j0 = (blockIdx.x * kGatherThreads + threadIdx.x) * 4;
+    if (j0 >= n) return;
+    int id[4][3];
+    float w[4][3];
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+    {
+        const bool ok = j0 + t < n;
+        const size_t o = (static_cast<size_t>(bi) * n + (ok ? j0 + t : j0)) * 3;
+#pragma unroll
+        for (int k = 0; k < 3; ++k)
+        {
+            id[t][k] = __ldg(idx + o + k);
+            w[t][k] = __ldg(weight + o + k);
+        }
+    }
+    const float* f = points + (static_cast<size_t>(bi) * c + c0) * m;
+    float* o = out + (static_cast<size_t>(bi) * c + c0) * n + j0;
+#pragma unroll 2
+    for (int ch = c0; ch < c1; ++ch, f += m, o += n)
+    {
+        float r[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+            r[t] = interp3(__ldg(f + id[t][0]), w[t][0], __ldg(f + id[t][1]), w[t][1],
+                           __ldg(f + id[t][2]), w[t][2]);
+        if (VEC)
+            __stcs(reinterpret_cast<float4*>(o), make_float4(r[0], r[1], r[2], r[3]));
+        else
+        {
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+                if (j0 + t < n) o[t] = r[t];
+        }
+    }
+}
+
+// ------------------------------------------------------------------ backward, shared rows
+
+// Rows of the small gradient (length row_len) for `rows` consecutive (batch, channel)
+// pairs live in shared memory.  INTERP == false: grouping (src positions ps, one int64
+// index each).  INTERP == true: three_interpolate (src positions n, three int32
+// indices and weights each).
+template <bool INTERP>
+__global__ void __launch_bounds__(kScatterThreads)
+    scatter_rows_kernel(int c, int row_len, long long src_len, int rows,
+                        const float* __restrict__ grad_out, const void* __restrict__ idx_v,
+                        const float* __restrict__ weight, float* __restrict__ grad_small)
+{
+    extern __shared__ __align__(16) float acc[];
+    const int groups_per_batch = (c + rows - 1) / rows;
+    const int bi = blockIdx.x / groups_per_batch;
+    const int c0 = (blockIdx.x - bi * groups_per_batch) * rows;
+    const int nrows = min(rows, c - c0);
+    for (int i = threadIdx.x; i < nrows * row_len; i += kScatterThreads) acc[i] = 0.f;
+    __syncthreads();
+
+    const float* g = grad_out + (static_cast<size_t>(bi) * c + c0) * src_len;
+    const bool vec = (src_len % 4 == 0);
+    if (vec)
+    {
+        for (long long p = static_cast<long long>(threadIdx.x) * 4; p < src_len;
+             p += kScatterThreads * 4)
+        {
+            if (!INTERP)
+            {
+                const int64_t* ip = static_cast<const int64_t*>(idx_v) + static_cast<size_t>(bi) * src_len + p;
+                const longlong2 a = __ldg(reinterpret_cast<const longlong2*>(ip));
+                const longlong2 b2 = __ldg(reinterpret_cast<const longlong2*>(ip) + 1);
+                const int i0 = static_cast<int>(a.x), i1 = static_cast<int>(a.y);
+                const int i2 = static_cast<int>(b2.x), i3 = static_cast<int>(b2.y);
+                for (int r = 0; r < nrows; ++r)
+                {
+                    const float4 v = __ldcs(reinterpret_cast<const float4*>(g + r * src_len + p));
+                    float* a_r = acc + r * row_len;
+                    atomicAdd(a_r + i0, v.x);
+                    atomicAdd(a_r + i1, v.y);
+                    atomicAdd(a_r + i2, v.z);
+                    atomicAdd(a_r + i3, v.w);
+                }
+            }
+            else
+            {
+                const size_t o = (static_cast<size_t>(bi) * src_len + p) * 3;
+                const int32_t* ip = static_cast<const int32_t*>(idx_v) + o;
+                const float* wp = weight + o;
+                int id[12];
+                float w[12];
+                // 12 consecutive values, 16-byte aligned because p is a multiple of 4
+#pragma unroll
+                for (int t = 0; t < 3; ++t)
+                {
+                    const int4 a = __ldg(reinterpret_cast<const int4*>(ip) + t);
+                    const float4 b4 = __ldg(reinterpret_cast<const float4*>(wp) + t);
+                    id[4 * t + 0] = a.x; id[4 * t + 1] = a.y; id[4 * t + 2] = a.z; id[4 * t + 3] = a.w;
+                    w[4 * t + 0] = b4.x; w[4 * t + 1] = b4.y; w[4 * t + 2] = b4.z; w[4 * t + 3] = b4.w;
+                }
+                for (int r = 0; r < nrows; ++r)
+                {
+                    const float4 v = __ldcs(reinterpret_cast<const float4*>(g + r * src_len + p));
+                    const float gv[4] = {v.x, v.y, v.z, v.w};
+                    float* a_r = acc + r * row_len;
+#pragma unroll
+                    for (int t = 0; t < 4; ++t)
+#pragma unroll
+                        for (int k = 0; k < 3; ++k)
+                            atomicAdd(a_r + id[3 * t + k], __fmul_rn(gv[t], w[3 * t + k]));
+                }
+            }
+        }
+    }
+    else
+    {
+        for (long long p = threadIdx.x; p < src_len; p += kScatterThreads)
+        {
+            if (!INTERP)
+            {
+                const int i0 = static_cast<int>(
+                    __ldg(static_cast<const int64_t*>(idx_v) + static_cast<size_t>(bi) * src_len + p));
+                for (int r = 0; r < nrows; ++r) atomicAdd(acc + r * row_len + i0, g[r * src_len + p]);
+            }
+            else
+            {
+                const size_t o = (static_cast<size_t>(bi) * src_len + p) * 3;
+                const int32_t* ip = static_cast<const int32_t*>(idx_v) + o;
+                for (int r = 0; r < nrows; ++r)
+                {
+                    const float gv = g[r * src_len + p];
+#pragma unroll
+                    for (int k = 0; k < 3; ++k)
+                        atomicAdd(acc + r * row_len + __ldg(ip + k), __fmul_rn(gv, __ldg(weight + o + k)));
+                }
+            }
+        }
+    }
+    __syncthreads();
+    float* dst = grad_small + (static_cast<size_t>(bi) * c + c0) * row_len;
+    for (int i = threadIdx.x; i < nrows * row_len; i += kScatterThreads) dst[i] = acc[i];
+}
+
+// ------------------------------------------------------------------ backward, global atomics
+
+template <bool INTERP>
+__global__ void __launch_bounds__(kGatherThreads)
+    scatter_global_kernel(int c, int row_len, long long src_len, const float* __restrict__ grad_out,
+                          const void* __restrict__ idx_v, const float* __restrict__ weight,
+                          float* __restrict__ grad_small)
+{
+    const int bi = blockIdx.z;
+    const int c0 = blockIdx.y * kChanChunk;
+    const int c1 = min(c, c0 + kChanChunk);
+    const long long p = static_cast<long long>(blockIdx.x) * kGatherThreads + threadIdx.x;
+    if (p >= src_len) return;
+    int id[3];
+    float w[3] = {1.f, 1.f, 1.f};
+    if (!INTERP)
+        id[0] = static_cast<int>(__ldg(static_cast<const int64_t*>(idx_v) + static_cast<size_t>(bi) * src_len + p));
+    else
+    {
+        const size_t o = (static_cast<size_t>(bi) * src_len + p) * 3;
+#pragma unroll
+        for (int k = 0; k < 3; ++k)
+        {
+            id[k] = __ldg(static_cast<const int32_t*>(idx_v) + o + k);
+            w[k] = __ldg(weight + o + k);
+        }
+    }
+    for (int ch = c0; ch < c1; ++ch)
+    {
+        const float gv = __ldg(grad_out + (static_cast<size_t>(bi) * c + ch) * src_len + p);
+        float* dst = grad_small + (static_cast<size_t>(bi) * c + ch) * row_len;
+        if (!INTERP)
+            atomicAdd(dst + id[0], gv);
+        else
+        {
+#pragma unroll
+            for (int k = 0; k < 3; ++k) atomicAdd(dst + id[k], __fmul_rn(gv, w[k]));
+        }
+    }
+}
+
+template <bool INTERP>
+int launch_scatter(int b, int c, int row_len, long long src_len, const float* grad_out,
+                   const void* idx, const float* weight, float* grad_small, cudaStream_t s,
+                   const char* what)
+{
+    const size_t row_bytes = static_cast<size_t>(row_len) * sizeof(float);
+    const bool force_global = getenv("TPK_SCATTER_GLOBAL") != nullptr;
+    if (row_bytes <= kRowSmemBudget && !force_global)
+    {
+        int rows = static_cast<int>(kRowSmemBudget / row_bytes);
+        if (rows > 4) rows = 4;
+        if (rows > c) rows = c;
+        // keep at least ~2 CTAs per SM when the problem allows it
+        while (rows > 1 && static_cast<long long>(b) * ((c + rows - 1) / rows) < 2ll * num_sms()) --rows;
+        const size_t smem = static_cast<size_t>(rows) * row_bytes;
+        auto kernel = scatter_rows_kernel<INTERP>;
+        if (smem > 48 * 1024)
+        {
+            cudaError_t err = cudaFuncSetAttribute(
+                kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            if (err != cudaSuccess)
+            {
+                set_error("%s: shared memory attribute: %s", what, cudaGetErrorString(err));
+                return TPK_ERR_CUDA;
+            }
+        }
+        const long long grid = static_cast<long long>(b) * ((c + rows - 1) / rows);
+        TPK_REQUIRE(grid < (1ll << 31), "%s: too many rows", what);
+        kernel<<<static_cast<unsigned>(grid), kScatterThreads, smem, s>>>(
+            c, row_len, src_len, rows, grad_out, idx, weight, grad_small);
+        return check_launch(what);
+    }
+    cudaError_t err = cudaMemsetAsync(grad_small, 0, static_cast<size_t>(b) * c * row_bytes, s);
+    if (err != cudaSuccess)
+    {
+        set_error("%s: memset: %s", what, cudaGetErrorString(err));
+        return TPK_ERR_CUDA;
+    }
+    const long long gx = (src_len + kGatherThreads - 1) / kGatherThreads;
+    TPK_REQUIRE(gx < (1ll << 31) && b <= 65535 && (c + kChanChunk - 1) / kChanChunk <= 65535,
+                "%s: grid too large", what);
+    const dim3 g(static_cast<unsigned>(gx), (c + kChanChunk - 1) / kChanChunk, b);
+    scatter_global_kernel<INTERP><<<g, kGatherThreads, 0, s>>>(c, row_len, src_len, grad_out, idx,
+                                                              weight, grad_small);
+    return check_launch(what);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+}  // namespace tpk
+
+extern "C" int tpk_grouping(int b, int c, int n, int npoint, int nsample, const float* features,
+                            const int64_t* idx, float* out, void* stream)
+{
+    using namespace tpk;
+    TPK_REQUIRE(b >= 0 && c >= 0 && n >= 0 && npoint >= 0 && nsample >= 0, "grouping: negative size");
+    const long long ps = static_cast<long long>(npoint) * nsample;
+    if (b == 0 || c == 0 || ps == 0) return TPK_OK;
+    TPK_REQUIRE(features && idx && out && n > 0, "grouping: NULL pointer or empty feature row");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const long long gx = (ps + kGatherThreads * 4 - 1) / (kGatherThreads * 4);
+    const int gy = (c + kChanChunk - 1) / kChanChunk;
+    TPK_REQUIRE(gx < (1ll << 31) && gy <= 65535 && b <= 65535, "grouping: grid too large");
+    const dim3 g(static_cast<unsigned>(gx), gy, b);
+    if (ps % 4 == 0 && aligned16(idx) && aligned16(out))
+        grouping_fwd_kernel<true><<<g, kGatherThreads, 0, s>>>(c, n, ps, features, idx, out);
+    else
+        grouping_fwd_kernel<false><<<g, kGatherThreads, 0, s>>>(c, n, ps, features, idx, out);
+    return check_launch("grouping");
+}
+
+extern "C" int tpk_grouping_grad(int b, int c, int n, int npoint, int nsample,
+                                 const float* grad_out, const int64_t* idx, float* grad_features,
+                                 void* stream)
+{
+    using namespace tpk;
+    TPK_REQUIRE(b >= 0 && c >= 0 && n >= 0 && npoint >= 0 && nsample >= 0,
+                "grouping_grad: negative size");
+    if (b == 0 || c == 0 || n == 0) return TPK_OK;
+    TPK_REQUIRE(grad_features, "grouping_grad: NULL pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const long long ps = static_cast<long long>(npoint) * nsample;
+    if (ps == 0)
+    {
+        cudaError_t err = cudaMemsetAsync(grad_features, 0, sizeof(float) * static_cast<size_t>(b) * c * n, s);
+        if (err != cudaSuccess)
+        {
+            set_error("grouping_grad: memset: %s", cudaGetErrorString(err));
+            return TPK_ERR_CUDA;
+        }
+        return TPK_OK;
+    }
+    TPK_REQUIRE(grad_out && idx, "grouping_grad: NULL pointer");
+    TPK_REQUIRE(aligned16(grad_out) && aligned16(idx), "grouping_grad: inputs must be 16-byte aligned");
+    return launch_scatter<false>(b, c, n, ps, grad_out, idx, nullptr, grad_features, s, "grouping_grad");
+}
+
+extern "C" int tpk_three_interpolate(int b, int c, int m, int n, const float* points,
+                                     const int32_t* idx, const float* weight, float* out,
+                                     void* stream)
+{
+    using namespace tpk;
+    TPK_REQUIRE(b >= 0 && c >= 0 && m >= 0 && n >= 0, "three_interpolate: negative size");
+    if (b == 0 || c == 0 || n == 0) return TPK_OK;
+    TPK_REQUIRE(points && idx && weight && out && m > 0,
+                "three_interpolate: NULL pointer or empty feature row");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int gx = (n + kGatherThreads * 4 - 1) / (kGatherThreads * 4);
+    const int gy = (c + kChanChunk - 1) / kChanChunk;
+    TPK_REQUIRE(gy <= 65535 && b <= 65535, "three_interpolate: grid too large");
+    const dim3 g(gx, gy, b);
+    if (n % 4 == 0 && aligned16(out))
+        interp_fwd_kernel<true><<<g, kGatherThreads, 0, s>>>(c, m, n, points, idx, weight, out);
+    else
+        interp_fwd_kernel<false><<<g, kGatherThreads, 0, s>>>(c, m, n, points, idx, weight, out);
+    return check_launch("three_interpolate");
+}
+
+extern "C" int tpk_three_interpolate_grad(int b, int c, int n, int m, const float* grad_out,
+                                          const int32_t* idx, const float* weight,
+                                          float* grad_points, void* stream)
+{
+    using namespace tpk;
+    TPK_REQUIRE(b >= 0 && c >= 0 && m >= 0 && n >= 0, "three_interpolate_grad: negative size");
+    if (b == 0 || c == 0 || m == 0) return TPK_OK;
+    TPK_REQUIRE(grad_points, "three_interpolate_grad: NULL pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (n == 0)
+    {
+        cudaError_t err = cudaMemsetAsync(grad_points, 0, sizeof(float) * static_cast<size_t>(b) * c * m, s);
+        if (err != cudaSuccess)
+        {
+            set_error("three_interpolate_grad: memset: %s", cudaGetErrorString(err));
+            return TPK_ERR_CUDA;
+        }
+        return TPK_OK;
+    }
+    TPK_REQUIRE(grad_out && idx && weight, "three_interpolate_grad: NULL pointer");
+    TPK_REQUIRE(aligned16(grad_out) && aligned16(idx) && aligned16(weight),
+                "three_interpolate_grad: inputs must be 16-byte aligned");
+    return launch_scatter<true>(b, c, m, n, grad_out, idx, weight, grad_points, s,
+                                "three_interpolate_grad");
+}

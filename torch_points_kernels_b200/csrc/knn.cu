@@ -1,0 +1,435 @@
+// Nearest-neighbour searches for sm_100a: three_nn (fixed k = 3, int32 indices, the
+// feature-propagation search) and kNN (1 <= k <= 64, int64 indices, dense and packed).
+//
+// Both are brute force over shared-memory candidate tiles (scan.cuh).  A thread keeps
+// the running k-th best distance of each of its queries in a register and touches its
+// sorted result list only when a candidate beats it, which on real clouds happens
+// O(k log(n/k)) times per query out of n candidates.
+//
+// three_nn : cuda/src/interpolate_gpu.cu:9-65 (strict '<' cascade: ascending distance,
+//            lowest index first among equals; missing neighbours are +inf / index 0)
+// kNN      : cpu/src/knn.cpp:40-59 -> nanoflann knnSearch; unfused distance arithmetic,
+//            ascending distance, index order among equals
+#include <math_constants.h>
+
+#include "scan.cuh"
+
+namespace tpk
+{
+namespace
+{
+
+constexpr int kNnTile = 1024;
+constexpr int kNnQ = 2;
+
+template <int Q>
+struct ThreeNnOp
+{
+    float qx[Q], qy[Q], qz[Q];
+    float b1[Q], b2[Q], b3[Q];
+    int i1[Q], i2[Q], i3[Q];
+    long long ncand;
+
+    __device__ __forceinline__ bool group(long long k0, const float (&cx)[4], const float (&cy)[4],
+                                          const float (&cz)[4])
+    {
+        float d[Q][4];
+        bool any = false;
+#pragma unroll
+        for (int q = 0; q < Q; ++q)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+            {
+                d[q][i] = sumsq_abc(qx[q] - cx[i], qy[q] - cy[i], qz[q] - cz[i]);
+                any |= d[q][i] < b3[q];
+            }
+        if (any)
+        {
+#pragma unroll
+            for (int q = 0; q < Q; ++q)
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                {
+                    const float v = d[q][i];
+                    const int k = static_cast<int>(k0) + i;
+                    if (v < b3[q] && k0 + i < ncand)
+                    {
+                        if (v < b1[q])
+                        {
+                            b3[q] = b2[q]; i3[q] = i2[q];
+                            b2[q] = b1[q]; i2[q] = i1[q];
+                            b1[q] = v;     i1[q] = k;
+                        }
+                        else if (v < b2[q])
+                        {
+                            b3[q] = b2[q]; i3[q] = i2[q];
+                            b2[q] = v;     i2[q] = k;
+                        }
+                        else
+                        {
+                            b3[q] = v; i3[q] = k;
+                        }
+                    }
+                }
+        }
+        return false;
+    }
+};
+
+template <int THREADS, int Q>
+__global__ void __launch_bounds__(THREADS)
+    three_nn_kernel(int n, int m, int tiles_per_cloud, const float* __restrict__ unknown,
+                    const float* __restrict__ known, float* __restrict__ dist2,
+                    int32_t* __restrict__ idx)
+{
+    __shared__ __align__(16) float smem[2 * 3 * kNnTile];
+    const int cloud = blockIdx.x / tiles_per_cloud;
+    const int qtile = blockIdx.x - cloud * tiles_per_cloud;
+
+    ThreeNnOp<Q> op;
+    op.ncand = m;
+    bool act[Q];
+    bool done = true;
+#pragma unroll
+    for (int q = 0; q < Q; ++q)
+    {
+        const int j = qtile * (THREADS * Q) + q * THREADS + threadIdx.x;
+        act[q] = j < n;
+        const size_t row = static_cast<size_t>(cloud) * n + (act[q] ? j : 0);
+        op.qx[q] = act[q] ? __ldg(unknown + row * 3 + 0) : 0.f;
+        op.qy[q] = act[q] ? __ldg(unknown + row * 3 + 1) : 0.f;
+        op.qz[q] = act[q] ? __ldg(unknown + row * 3 + 2) : 0.f;
+        op.b1[q] = op.b2[q] = op.b3[q] = CUDART_INF_F;
+        op.i1[q] = op.i2[q] = op.i3[q] = 0;
+        done &= !act[q];
+    }
+    scan_candidates<THREADS, kNnTile>(known + static_cast<size_t>(cloud) * m * 3, m, smem, op, done);
+#pragma unroll
+    for (int q = 0; q < Q; ++q)
+    {
+        if (!act[q]) continue;
+        const int j = qtile * (THREADS * Q) + q * THREADS + threadIdx.x;
+        const size_t o = (static_cast<size_t>(cloud) * n + j) * 3;
+        dist2[o + 0] = op.b1[q];
+        dist2[o + 1] = op.b2[q];
+        dist2[o + 2] = op.b3[q];
+        idx[o + 0] = op.i1[q];
+        idx[o + 1] = op.i2[q];
+        idx[o + 2] = op.i3[q];
+    }
+}
+
+// Sorted lists live in shared memory, slot s of list l at [s * LISTS + l]: consecutive
+// threads hit consecutive banks.
+template <int Q, int LISTS>
+struct KnnOp
+{
+    float qx[Q], qy[Q], qz[Q];
+    float thr[Q];  // current k-th best (the admission threshold), +inf until the list is full
+    int cnt[Q];
+    bool act[Q];
+    float* ldist;  // + list id of q = 0; q-th list is at + q * (LISTS / Q)
+    int* lidx;
+    int k;
+    long long ncand;
+
+    __device__ __forceinline__ void insert(int q, float v, int cand)
+    {
+        float* dl = ldist + q * (LISTS / Q);
+        int* il = lidx + q * (LISTS / Q);
+        int i = cnt[q] < k ? cnt[q] : k - 1;
+        for (; i > 0 && dl[(i - 1) * LISTS] > v; --i)
+        {
+            dl[i * LISTS] = dl[(i - 1) * LISTS];
+            il[i * LISTS] = il[(i - 1) * LISTS];
+        }
+        dl[i * LISTS] = v;
+        il[i * LISTS] = cand;
+        if (cnt[q] < k) ++cnt[q];
+        if (cnt[q] == k) thr[q] = dl[(k - 1) * LISTS];
+    }
+
+    __device__ __forceinline__ bool group(long long k0, const float (&cx)[4], const float (&cy)[4],
+                                          const float (&cz)[4])
+    {
+        float d[Q][4];
+        bool any = false;
+#pragma unroll
+        for (int q = 0; q < Q; ++q)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+            {
+                d[q][i] = sumsq_unfused(qx[q] - cx[i], qy[q] - cy[i], qz[q] - cz[i]);
+                any |= d[q][i] < thr[q];
+            }
+        if (any)
+        {
+#pragma unroll
+            for (int q = 0; q < Q; ++q)
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (act[q] && d[q][i] < thr[q] && k0 + i < ncand)
+                        insert(q, d[q][i], static_cast<int>(k0) + i);
+        }
+        return false;
+    }
+};
+
+template <int THREADS, int Q>
+__device__ __forceinline__ void knn_write(const KnnOp<Q, THREADS * Q>& op, int q, int k,
+                                          long long idx_base, int64_t* orow, float* drow)
+{
+    const float* dl = op.ldist + q * THREADS;
+    const int* il = op.lidx + q * THREADS;
+    for (int s = 0; s < k; ++s)
+    {
+        const bool have = s < op.cnt[q];
+        orow[s] = have ? il[s * THREADS * Q] + idx_base : -1;
+        drow[s] = have ? dl[s * THREADS * Q] : -1.0f;
+    }
+}
+
+template <int THREADS, int Q>
+__global__ void __launch_bounds__(THREADS)
+    knn_dense_kernel(int n, int m, int k, int tiles_per_cloud, const float* __restrict__ support,
+                     const float* __restrict__ query, int64_t* __restrict__ idx,
+                     float* __restrict__ dist2)
+{
+    extern __shared__ __align__(16) float dyn_smem[];
+    float* tile = dyn_smem;
+    float* ldist = dyn_smem + 2 * 3 * kNnTile;
+    int* lidx = reinterpret_cast<int*>(ldist + static_cast<size_t>(k) * THREADS * Q);
+    const int cloud = blockIdx.x / tiles_per_cloud;
+    const int qtile = blockIdx.x - cloud * tiles_per_cloud;
+
+    KnnOp<Q, THREADS * Q> op;
+    op.k = k;
+    op.ncand = n;
+    op.ldist = ldist + threadIdx.x;
+    op.lidx = lidx + threadIdx.x;
+    bool done = true;
+#pragma unroll
+    for (int q = 0; q < Q; ++q)
+    {
+        const int j = qtile * (THREADS * Q) + q * THREADS + threadIdx.x;
+        op.act[q] = j < m;
+        const size_t row = static_cast<size_t>(cloud) * m + (op.act[q] ? j : 0);
+        op.qx[q] = op.act[q] ? __ldg(query + row * 3 + 0) : 0.f;
+        op.qy[q] = op.act[q] ? __ldg(query + row * 3 + 1) : 0.f;
+        op.qz[q] = op.act[q] ? __ldg(query + row * 3 + 2) : 0.f;
+        op.thr[q] = CUDART_INF_F;
+        op.cnt[q] = 0;
+        done &= !op.act[q];
+    }
+    scan_candidates<THREADS, kNnTile>(support + static_cast<size_t>(cloud) * n * 3, n, tile, op, done);
+#pragma unroll
+    for (int q = 0; q < Q; ++q)
+    {
+        if (!op.act[q]) continue;
+        const int j = qtile * (THREADS * Q) + q * THREADS + threadIdx.x;
+        const size_t row = static_cast<size_t>(cloud) * m + j;
+        knn_write<THREADS, Q>(op, q, k, 0, idx + row * k, dist2 + row * k);
+    }
+}
+
+template <int THREADS, int Q>
+__global__ void __launch_bounds__(THREADS)
+    knn_partial_kernel(long long size_s, long long size_q, int k,
+                       const float* __restrict__ support, const float* __restrict__ query,
+                       const int64_t* __restrict__ batch_s, const int64_t* __restrict__ batch_q,
+                       int64_t* __restrict__ idx, float* __restrict__ dist2)
+{
+    extern __shared__ __align__(16) float dyn_smem[];
+    __shared__ long long s_range[2];
+    __shared__ unsigned long long s_next;
+    float* tile = dyn_smem;
+    float* ldist = dyn_smem + 2 * 3 * kNnTile;
+    int* lidx = reinterpret_cast<int*>(ldist + static_cast<size_t>(k) * THREADS * Q);
+
+    KnnOp<Q, THREADS * Q> op;
+    op.k = k;
+    op.ldist = ldist + threadIdx.x;
+    op.lidx = lidx + threadIdx.x;
+    int64_t seg[Q];
+    bool valid[Q];
+    long long base[Q];
+    const long long j0 = static_cast<long long>(blockIdx.x) * (THREADS * Q);
+#pragma unroll
+    for (int q = 0; q < Q; ++q)
+    {
+        const long long j = j0 + q * THREADS + threadIdx.x;
+        valid[q] = j < size_q;
+        const long long row = valid[q] ? j : 0;
+        seg[q] = valid[q] ? __ldg(batch_q + row) : 0;
+        op.qx[q] = valid[q] ? __ldg(query + row * 3 + 0) : 0.f;
+        op.qy[q] = valid[q] ? __ldg(query + row * 3 + 1) : 0.f;
+        op.qz[q] = valid[q] ? __ldg(query + row * 3 + 2) : 0.f;
+        op.thr[q] = CUDART_INF_F;
+        op.cnt[q] = 0;
+        base[q] = 0;
+    }
+    int64_t cur = __ldg(batch_q + j0);
+    const unsigned long long kNone = ~0ull;
+    while (true)
+    {
+        if (threadIdx.x == 0)
+        {
+            s_range[0] = segment_bound(batch_s, size_s, cur, false);
+            s_range[1] = segment_bound(batch_s, size_s, cur, true);
+            s_next = kNone;
+        }
+        __syncthreads();
+        const long long lo = s_range[0], hi = s_range[1];
+        bool done = true;
+#pragma unroll
+        for (int q = 0; q < Q; ++q)
+        {
+            op.act[q] = valid[q] && seg[q] == cur;
+            if (op.act[q]) base[q] = lo;
+            done &= !op.act[q];
+            if (valid[q] && seg[q] > cur)
+                atomicMin(&s_next, static_cast<unsigned long long>(seg[q]));
+        }
+        op.ncand = hi - lo;
+        scan_candidates<THREADS, kNnTile>(support + lo * 3, hi - lo, tile, op, done);
+        const unsigned long long nxt = s_next;
+        __syncthreads();
+        if (nxt == kNone) break;
+        cur = static_cast<int64_t>(nxt);
+    }
+#pragma unroll
+    for (int q = 0; q < Q; ++q)
+    {
+        if (!valid[q]) continue;
+        const long long row = j0 + q * THREADS + threadIdx.x;
+        knn_write<THREADS, Q>(op, q, k, base[q], idx + row * k, dist2 + row * k);
+    }
+}
+
+int pick_threads_nn(long long queries, int q_per_thread)
+{
+    const long long want = 6ll * num_sms();
+    if (queries / (128ll * q_per_thread) >= want) return 128;
+    if (queries / (64ll * q_per_thread) >= want) return 64;
+    return 32;
+}
+
+size_t knn_smem_bytes(int threads, int k)
+{
+    return sizeof(float) * 2 * 3 * kNnTile + static_cast<size_t>(k) * threads * kNnQ * 8;
+}
+
+template <class K>
+int set_smem(K kernel, size_t bytes, const char* what)
+{
+    if (bytes > 48 * 1024)
+    {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(bytes));
+        if (err != cudaSuccess)
+        {
+            set_error("%s: shared memory attribute: %s", what, cudaGetErrorString(err));
+            return TPK_ERR_CUDA;
+        }
+    }
+    return TPK_OK;
+}
+
+}  // namespace
+}  // namespace tpk
+
+extern "C" int tpk_three_nn(int b, int n, int m, const float* unknown, const float* known,
+                            float* dist2, int32_t* idx, void* stream)
+{
+    using namespace tpk;
+    TPK_REQUIRE(b >= 0 && n >= 0 && m >= 0, "three_nn: negative size (b=%d n=%d m=%d)", b, n, m);
+    if (b == 0 || n == 0) return TPK_OK;
+    TPK_REQUIRE(unknown && dist2 && idx && (known || m == 0), "three_nn: NULL pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int threads = pick_threads_nn(static_cast<long long>(b) * n, kNnQ);
+    const int tiles = (n + threads * kNnQ - 1) / (threads * kNnQ);
+    const long long grid = static_cast<long long>(b) * tiles;
+    TPK_REQUIRE(grid < (1ll << 31), "three_nn: too many queries");
+    const dim3 g(static_cast<unsigned>(grid));
+    if (threads == 128)
+        three_nn_kernel<128, kNnQ><<<g, 128, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
+    else if (threads == 64)
+        three_nn_kernel<64, kNnQ><<<g, 64, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
+    else
+        three_nn_kernel<32, kNnQ><<<g, 32, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
+    return check_launch("three_nn");
+}
+
+extern "C" int tpk_knn_dense(int b, int n, int m, int k, const float* support, const float* query,
+                             int64_t* idx, float* dist2, void* stream)
+{
+    using namespace tpk;
+    TPK_REQUIRE(b >= 0 && n >= 0 && m >= 0, "knn: negative size (b=%d n=%d m=%d)", b, n, m);
+    TPK_REQUIRE(k >= 1 && k <= TPK_KNN_MAX_K, "knn: k=%d outside 1..%d", k, TPK_KNN_MAX_K);
+    TPK_REQUIRE(k <= n, "Not enough points in support to find %d neighboors", k);
+    if (b == 0 || m == 0) return TPK_OK;
+    TPK_REQUIRE(support && query && idx && dist2, "knn: NULL pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int threads = pick_threads_nn(static_cast<long long>(b) * m, kNnQ);
+    if (k > 32 && threads > 64) threads = 64;
+    const size_t smem = knn_smem_bytes(threads, k);
+    const int tiles = (m + threads * kNnQ - 1) / (threads * kNnQ);
+    const long long grid = static_cast<long long>(b) * tiles;
+    TPK_REQUIRE(grid < (1ll << 31), "knn: too many queries");
+    const dim3 g(static_cast<unsigned>(grid));
+    int rc;
+    if (threads == 128)
+    {
+        if ((rc = set_smem(knn_dense_kernel<128, kNnQ>, smem, "knn")) != TPK_OK) return rc;
+        knn_dense_kernel<128, kNnQ><<<g, 128, smem, s>>>(n, m, k, tiles, support, query, idx, dist2);
+    }
+    else if (threads == 64)
+    {
+        if ((rc = set_smem(knn_dense_kernel<64, kNnQ>, smem, "knn")) != TPK_OK) return rc;
+        knn_dense_kernel<64, kNnQ><<<g, 64, smem, s>>>(n, m, k, tiles, support, query, idx, dist2);
+    }
+    else
+    {
+        if ((rc = set_smem(knn_dense_kernel<32, kNnQ>, smem, "knn")) != TPK_OK) return rc;
+        knn_dense_kernel<32, kNnQ><<<g, 32, smem, s>>>(n, m, k, tiles, support, query, idx, dist2);
+    }
+    return check_launch("knn_dense");
+}
+
+extern "C" int tpk_knn_partial_dense(int64_t size_s, int64_t size_q, int k, const float* support,
+                                     const float* query, const int64_t* batch_s,
+                                     const int64_t* batch_q, int64_t* idx, float* dist2,
+                                     void* stream)
+{
+    using namespace tpk;
+    TPK_REQUIRE(size_s >= 0 && size_q >= 0, "knn_partial_dense: negative size");
+    TPK_REQUIRE(k >= 1 && k <= TPK_KNN_MAX_K, "knn: k=%d outside 1..%d", k, TPK_KNN_MAX_K);
+    if (size_q == 0) return TPK_OK;
+    TPK_REQUIRE(query && batch_q && idx && dist2 && ((support && batch_s) || size_s == 0),
+                "knn_partial_dense: NULL pointer");
+    TPK_REQUIRE(size_s < (1ll << 31), "knn_partial_dense: support too large");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int threads = pick_threads_nn(size_q, kNnQ);
+    if (k > 32 && threads > 64) threads = 64;
+    const size_t smem = knn_smem_bytes(threads, k);
+    const long long grid = (size_q + threads * kNnQ - 1) / (threads * kNnQ);
+    TPK_REQUIRE(grid < (1ll << 31), "knn_partial_dense: too many queries");
+    const dim3 g(static_cast<unsigned>(grid));
+    int rc;
+    if (threads == 128)
+    {
+        if ((rc = set_smem(knn_partial_kernel<128, kNnQ>, smem, "knn")) != TPK_OK) return rc;
+        knn_partial_kernel<128, kNnQ><<<g, 128, smem, s>>>(size_s, size_q, k, support, query, batch_s, batch_q, idx, dist2);
+    }
+    else if (threads == 64)
+    {
+        if ((rc = set_smem(knn_partial_kernel<64, kNnQ>, smem, "knn")) != TPK_OK) return rc;
+        knn_partial_kernel<64, kNnQ><<<g, 64, smem, s>>>(size_s, size_q, k, support, query, batch_s, batch_q, idx, dist2);
+    }
+    else
+    {
+        if ((rc = set_smem(knn_partial_kernel<32, kNnQ>, smem, "knn")) != TPK_OK) return rc;
+        knn_partial_kernel<32, kNnQ><<<g, 32, smem, s>>>(size_s, size_q, k, support, query, batch_s, batch_q, idx, dist2);
+    }
+    return check_launch("knn_partial_dense");
+}

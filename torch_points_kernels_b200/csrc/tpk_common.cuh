@@ -1,0 +1,85 @@
+// Shared helpers of the tpk_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/tpk_b200.h"
+
+namespace tpk
+{
+
+// Records the text returned by tpk_last_error() for the calling thread.
+void set_error(const char* fmt, ...);
+
+constexpr unsigned kFullMask = 0xffffffffu;
+constexpr int kNumSmsB200 = 148;
+
+inline int num_sms()
+{
+    static int cached = 0;
+    if (cached == 0)
+    {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
+            cached = v;
+        else
+            cached = kNumSmsB200;
+    }
+    return cached;
+}
+
+// Turns the sticky launch error into a status; never exits the process
+// (the reference prints and calls exit(-1), cuda/include/cuda_utils.h:53-63).
+inline int check_launch(const char* what)
+{
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess)
+    {
+        set_error("%s: %s", what, cudaGetErrorString(err));
+        return TPK_ERR_CUDA;
+    }
+    return TPK_OK;
+}
+
+#define TPK_REQUIRE(cond, ...)                                                                     \
+    do                                                                                             \
+    {                                                                                              \
+        if (!(cond))                                                                               \
+        {                                                                                          \
+            ::tpk::set_error(__VA_ARGS__);                                                         \
+            return TPK_ERR_INVALID_ARGUMENT;                                                       \
+        }                                                                                          \
+    } while (0)
+
+// a*a + b*b + c*c exactly as nvcc's default contraction evaluates the reference's
+// left-associated expression: one rounded product, two fused multiply-adds.
+// Used by dense ball query (ball_query_gpu.cu:35-36), three_nn (interpolate_gpu.cu:34),
+// chamfer (chamfer_dist_gpu.cu:41) and FPS (sampling_gpu.cu:52,56).
+__device__ __forceinline__ float sumsq_abc(float a, float b, float c)
+{
+    return __fmaf_rn(c, c, __fmaf_rn(a, a, __fmul_rn(b, b)));
+}
+
+// dist = 0; dist += a*a; dist += b*b; dist += c*c as contracted for the
+// partial_dense loop (ball_query_gpu.cu:78-82): three chained fused multiply-adds.
+__device__ __forceinline__ float sumsq_loop(float a, float b, float c)
+{
+    return __fmaf_rn(c, c, __fmaf_rn(b, b, __fmul_rn(a, a)));
+}
+
+// ((a*a) + b*b) + c*c with every operation rounded: the arithmetic of the reference's
+// CPU kd-tree metric (cpu/include/nanoflann.hpp:488-497, built without FMA).
+__device__ __forceinline__ float sumsq_unfused(float a, float b, float c)
+{
+    return __fadd_rn(__fadd_rn(__fmul_rn(a, a), __fmul_rn(b, b)), __fmul_rn(c, c));
+}
+
+__device__ __forceinline__ double sumsq_abc(double a, double b, double c)
+{
+    return __fma_rn(c, c, __fma_rn(a, a, __dmul_rn(b, b)));
+}
+
+}  // namespace tpk
