@@ -14,6 +14,8 @@
 // reference's strided scan plus shared-memory tree would keep.  That tie rule is
 // encoded as a rank: with bs = largest power of two <= n (at most 512) the reference
 // prefers the smallest bit-reversed (k mod bs), then the smallest (k div bs).
+#include <climits>
+
 #include <cooperative_groups.h>
 
 #include "tpk_common.cuh"
@@ -29,7 +31,7 @@ __device__ int g_dev_status = 0;
 
 constexpr int kFpsMaxThreads = 512;
 constexpr int kFpsMaxRanks = 16;
-constexpr int kFpsMaxPpt = 16;
+constexpr int kFpsMaxPpt = 32;
 constexpr unsigned long long kWaitLimitNs = 1000000000ull;  // give up a wait after one second
 constexpr int kMsgBytes = 20;  // {key_hi, key_lo, x, y} + {z}
 
@@ -133,13 +135,51 @@ __device__ __forceinline__ uint32_t bitrev_low(uint32_t v, int bits)
     return bits == 0 ? 0u : (__brev(v) >> (32 - bits));
 }
 
-// SYNC == 0: messages are plain distributed-shared-memory stores followed by a cluster
-//            barrier (or __syncthreads for a one-CTA cluster).
-// SYNC == 1: messages are st.async stores that complete a transaction count on the
-//            receiver's mbarrier; receivers wait (bounded) on their own barrier and no
-//            CTA-wide or cluster-wide barrier is executed inside the round loop.
+// Winner of one arg-max stage: key = bits of the running minimum (negative: no
+// candidate), k = index of the point in its cloud, (x, y, z) = its coordinates.
+struct Msg
+{
+    int key, k;
+    float x, y, z;
+};
+
+constexpr int fps_max_threads(int ppt) { return ppt <= 16 ? 512 : 128; }
+
+// Tie rank of point k: the reference's strided scan + tree keeps, among equal maxima,
+// the smallest bit-reversed (k mod bs), then the smallest (k div bs).
+__device__ __forceinline__ uint32_t fps_rank(int k, int log2bs)
+{
+    const uint32_t u = static_cast<uint32_t>(k);
+    return (bitrev_low(u & ((1u << log2bs) - 1u), log2bs) << 22) | (u >> log2bs);
+}
+
+// Lane holding the largest key among the lanes of the warp.  One redux and one ballot
+// when that key is unique (the usual case); ranks are only computed and reduced when
+// two lanes carry exactly the same distance.
+__device__ __forceinline__ int warp_argmax(int key, int k, int log2bs)
+{
+    const int wkey = __reduce_max_sync(kFullMask, key);
+    uint32_t ball = __ballot_sync(kFullMask, key == wkey);
+    if (__popc(ball) > 1 && wkey >= 0)
+    {
+        const uint32_t r = key == wkey ? fps_rank(k, log2bs) : 0xFFFFFFFFu;
+        const uint32_t wr = __reduce_min_sync(kFullMask, r);
+        ball = __ballot_sync(kFullMask, key == wkey && r == wr);
+    }
+    return __ffs(ball) - 1;
+}
+
+// One round = three arg-max stages, each a redux over at most 32 lanes:
+//   1. inside every warp, over its lanes' best points;
+//   2. inside the CTA, over its warps' winners (shared memory + one __syncthreads);
+//   3. inside the cluster, over its CTAs' winners.  The winner of every CTA is delivered
+//      to all CTAs of the cluster through distributed shared memory:
+//      SYNC == 1: st.async stores that complete a transaction count on the receiver's
+//                 mbarrier; receivers poll their own barrier with a time limit;
+//      SYNC == 0: plain st.shared::cluster stores followed by a cluster barrier.
+// Stages 2 and 3 are skipped for a one-warp CTA / one-CTA cluster.
 template <int PPT, int SYNC>
-__global__ void __launch_bounds__(kFpsMaxThreads, 1)
+__global__ void __launch_bounds__(fps_max_threads(PPT), 1)
     fps_onchip_kernel(int n, int m, int log2bs, const float* __restrict__ xyz_all,
                       int32_t* __restrict__ idxs_all)
 {
@@ -151,23 +191,38 @@ __global__ void __launch_bounds__(kFpsMaxThreads, 1)
     const int cloud = blockIdx.x / nranks;
     const int total = nranks * nthreads;
     const int gtid = rank * nthreads + tid;
-    const int nslots = nranks * nwarps;
 
-    // shared memory: msg_a[2][nslots] (16 B), msg_z[2][nslots] (4 B), 2 mbarriers, xyz copy
-    uint4* msg_a = reinterpret_cast<uint4*>(smem_raw);
-    float* msg_z = reinterpret_cast<float*>(msg_a + 2 * nslots);
-    uint64_t* mbar = reinterpret_cast<uint64_t*>(smem_raw + 2 * nslots * kMsgBytes +
-                                                 ((2 * nslots * kMsgBytes) & 8));
-    float* sxyz = reinterpret_cast<float*>(mbar + 2);
+    // shared memory: 2 x 32 warp messages, 2 x 32 CTA messages (16 B + 4 B each),
+    // 2 mbarriers, then this CTA's coordinates as float4
+    uint4* wmsg_a = reinterpret_cast<uint4*>(smem_raw);
+    uint4* cmsg_a = wmsg_a + 64;
+    float* wmsg_z = reinterpret_cast<float*>(cmsg_a + 64);
+    float* cmsg_z = wmsg_z + 64;
+    uint64_t* mbar = reinterpret_cast<uint64_t*>(cmsg_z + 64);
+    float4* sxyz = reinterpret_cast<float4*>(mbar + 2);
 
     const float* xyz = xyz_all + static_cast<size_t>(cloud) * n * 3;
     int32_t* idxs = idxs_all + static_cast<size_t>(cloud) * m;
+
+    // Point p of this thread.  The layout makes "lowest p" the winner of the tie rule
+    // among one thread's points: with at least bs threads in the cluster all of a
+    // thread's points share (k mod bs) and ascend in (k div bs); with fewer, a thread
+    // owns bs/total residues, visited in bit-reversed order, each with ascending k div bs.
+    const int bs = 1 << log2bs;
+    const bool wide = total >= bs;
+    const int log2_per_residue = wide ? 0 : (31 - __clz(PPT)) + (31 - __clz(total)) - log2bs;
+    const int residue_bits = wide ? 0 : log2bs - (31 - __clz(total));
+    auto point_index = [&](int p) -> int {
+        if (wide) return p * total + gtid;
+        const int q = p >> log2_per_residue, i = p & ((1 << log2_per_residue) - 1);
+        return (i << log2bs) + static_cast<int>(bitrev_low(static_cast<uint32_t>(q), residue_bits)) * total + gtid;
+    };
 
     float px[PPT], py[PPT], pz[PPT], md[PPT];
 #pragma unroll
     for (int p = 0; p < PPT; ++p)
     {
-        const int k = p * total + gtid;
+        const int k = point_index(p);
         float x = 0.f, y = 0.f, z = 0.f;
         bool valid = false;
         if (k < n)
@@ -183,17 +238,8 @@ __global__ void __launch_bounds__(kFpsMaxThreads, 1)
         pz[p] = z;
         // a negative running minimum marks "never a candidate": fminf keeps it negative
         md[p] = valid ? 1e10f : -1.0f;
-        float* s = sxyz + (static_cast<size_t>(p) * nthreads + tid) * 3;
-        s[0] = x;
-        s[1] = y;
-        s[2] = z;
+        sxyz[p * nthreads + tid] = make_float4(x, y, z, 0.f);
     }
-
-    // tie-break rank of point k = p*total + gtid (total is a multiple of bs)
-    const uint32_t bs_mask = (1u << log2bs) - 1u;
-    const uint32_t rbase = (bitrev_low(static_cast<uint32_t>(gtid) & bs_mask, log2bs) << 22) |
-                           (static_cast<uint32_t>(gtid) >> log2bs);
-    const uint32_t rstep = static_cast<uint32_t>(total) >> log2bs;
 
     float cx = 0.f, cy = 0.f, cz = 0.f;
     if (n > 0)
@@ -204,139 +250,159 @@ __global__ void __launch_bounds__(kFpsMaxThreads, 1)
     }
     if (gtid == 0 && m > 0) idxs[0] = 0;
 
-    if (SYNC == 1)
+    if (SYNC == 1 && tid == 0)
     {
-        if (tid == 0)
-        {
-            mbar_init(smem_u32(mbar + 0), 1);
-            mbar_init(smem_u32(mbar + 1), 1);
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        }
+        mbar_init(smem_u32(mbar + 0), 1);
+        mbar_init(smem_u32(mbar + 1), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (nranks > 1)
         cluster_sync_all();
     else
         __syncthreads();
 
-    const uint32_t my_slot = static_cast<uint32_t>(rank * nwarps + warp);
     bool failed = false;
-
     for (int j = 1; j < m; ++j)
     {
         const int par = j & 1;
         if (SYNC == 1 && nranks > 1 && tid == 0)
-            mbar_arrive_expect_tx(smem_u32(mbar + par), static_cast<uint32_t>(nslots * kMsgBytes));
+            mbar_arrive_expect_tx(smem_u32(mbar + par), static_cast<uint32_t>(nranks * kMsgBytes));
 
-        float best = -1.0f;
+        // ---- every point: distance to the newest sample, running minimum, thread maximum
 #pragma unroll
         for (int p = 0; p < PPT; ++p)
-        {
-            const float d = sumsq_abc(px[p] - cx, py[p] - cy, pz[p] - cz);
-            md[p] = fminf(d, md[p]);
-            best = fmaxf(best, md[p]);
-        }
-        // 64-bit key (hi, lo): hi orders by distance (0 = no candidate), lo by tie rank
-        const uint32_t hi = best >= 0.0f ? __float_as_uint(best) + 1u : 0u;
-        const uint32_t whi = __reduce_max_sync(kFullMask, hi);
-        uint32_t lo = 0;
-        int bp = 0;
-        if (hi == whi && hi != 0u)
-        {
+            md[p] = fminf(sumsq_abc(px[p] - cx, py[p] - cy, pz[p] - cz), md[p]);
+        float red[PPT];
 #pragma unroll
-            for (int p = PPT - 1; p >= 0; --p) bp = (md[p] == best) ? p : bp;
-            lo = ~(rbase + static_cast<uint32_t>(bp) * rstep);
+        for (int p = 0; p < PPT; ++p) red[p] = md[p];
+#pragma unroll
+        for (int w = PPT / 2; w >= 1; w >>= 1)
+#pragma unroll
+            for (int p = 0; p < w; ++p) red[p] = fmaxf(red[p], red[p + w]);
+        const float best = red[0];
+
+        // ---- stage 1: the warp's best point.  Non-negative floats order like their bits.
+        Msg msg;
+        msg.key = __float_as_int(best);
+        msg.k = 0;
+        msg.x = msg.y = msg.z = 0.f;
+        auto own_best = [&]() {  // this thread's best point: lowest p among equal minima
+            uint32_t eq = 0;
+#pragma unroll
+            for (int p = 0; p < PPT; ++p) eq |= (md[p] == best) ? (1u << p) : 0u;
+            return __ffs(eq) - 1;
+        };
+        const int wkey = __reduce_max_sync(kFullMask, msg.key);
+        uint32_t ball = __ballot_sync(kFullMask, msg.key == wkey);
+        int bp = -1;
+        if (__popc(ball) > 1 && wkey >= 0)
+        {
+            uint32_t r = 0xFFFFFFFFu;
+            if (msg.key == wkey)
+            {
+                bp = own_best();
+                r = fps_rank(point_index(bp), log2bs);
+            }
+            const uint32_t wr = __reduce_min_sync(kFullMask, r);
+            ball = __ballot_sync(kFullMask, msg.key == wkey && r == wr);
         }
-        const uint32_t wlo = __reduce_max_sync(kFullMask, lo);
-        const int src = __ffs(__ballot_sync(kFullMask, hi == whi && lo == wlo)) - 1;
-        float wx = 0.f, wy = 0.f, wz = 0.f;
+        int src = __ffs(ball) - 1;
         if (lane == src)
         {
-            const float* s = sxyz + (static_cast<size_t>(bp) * nthreads + tid) * 3;
-            wx = s[0];
-            wy = s[1];
-            wz = s[2];
-        }
-        wx = __shfl_sync(kFullMask, wx, src);
-        wy = __shfl_sync(kFullMask, wy, src);
-        wz = __shfl_sync(kFullMask, wz, src);
-
-        // lane r delivers this warp's message to CTA r of the cluster
-        if (lane < nranks)
-        {
-            const uint32_t a_local = smem_u32(msg_a + par * nslots + my_slot);
-            const uint32_t z_local = smem_u32(msg_z + par * nslots + my_slot);
-            if (nranks == 1)
+            if (bp < 0) bp = wkey >= 0 ? own_best() : 0;
+            msg.k = point_index(bp);
+            const float4 c = sxyz[bp * nthreads + tid];
+            msg.x = c.x;
+            msg.y = c.y;
+            msg.z = c.z;
+            if (nwarps > 1)
             {
-                msg_a[par * nslots + my_slot] =
-                    make_uint4(whi, wlo, __float_as_uint(wx), __float_as_uint(wy));
-                msg_z[par * nslots + my_slot] = wz;
-            }
-            else if (SYNC == 0)
-            {
-                st_cluster_msg(mapa_cluster(a_local, lane), mapa_cluster(z_local, lane), whi, wlo,
-                               wx, wy, wz);
-            }
-            else
-            {
-                st_async_msg(mapa_cluster(a_local, lane), mapa_cluster(z_local, lane),
-                             mapa_cluster(smem_u32(mbar + par), lane), whi, wlo, wx, wy, wz);
+                wmsg_a[par * 32 + warp] = make_uint4(static_cast<uint32_t>(msg.key), static_cast<uint32_t>(msg.k),
+                                                     __float_as_uint(msg.x), __float_as_uint(msg.y));
+                wmsg_z[par * 32 + warp] = msg.z;
             }
         }
 
-        if (SYNC == 1 && nranks > 1)
+        // ---- stage 2: the CTA's best point
+        if (nwarps > 1)
         {
-            const uint32_t parity = static_cast<uint32_t>((j - 1) >> 1) & 1u;
-            const uint32_t bar = smem_u32(mbar + par);
-            if (!mbar_wait_bounded(bar, parity))
+            __syncthreads();
+            int key2 = INT_MIN, k2 = 0;  // below every real key, including "no candidate"
+            if (lane < nwarps)
             {
-                if (lane == 0) atomicExch(&g_dev_status, 1);
-                failed = true;
-                break;
+                const uint2 a = *reinterpret_cast<const uint2*>(wmsg_a + par * 32 + lane);
+                key2 = static_cast<int>(a.x);
+                k2 = static_cast<int>(a.y);
             }
-        }
-        else if (nranks > 1)
-        {
-            cluster_sync_all();
+            src = warp_argmax(key2, k2, log2bs);
+            const uint4 a = wmsg_a[par * 32 + src];  // same address in every lane: a broadcast
+            msg.key = static_cast<int>(a.x);
+            msg.k = static_cast<int>(a.y);
+            msg.x = __uint_as_float(a.z);
+            msg.y = __uint_as_float(a.w);
+            msg.z = wmsg_z[par * 32 + src];
         }
         else
         {
-            __syncthreads();
+            msg.key = wkey;
+            msg.k = __shfl_sync(kFullMask, msg.k, src);
+            msg.x = __shfl_sync(kFullMask, msg.x, src);
+            msg.y = __shfl_sync(kFullMask, msg.y, src);
+            msg.z = __shfl_sync(kFullMask, msg.z, src);
         }
 
-        // every warp reduces all messages of the round to the same winner
-        uint32_t bhi = 0, blo = 0;
-        float bx = 0.f, by = 0.f, bz = 0.f;
-        for (int s = lane; s < nslots; s += 32)
+        // ---- stage 3: the cluster's best point
+        if (nranks > 1)
         {
-            const uint4 a = msg_a[par * nslots + s];
-            const float z = msg_z[par * nslots + s];
-            if (a.x > bhi || (a.x == bhi && a.y > blo))
+            if (warp == 0 && lane < nranks)
             {
-                bhi = a.x;
-                blo = a.y;
-                bx = __uint_as_float(a.z);
-                by = __uint_as_float(a.w);
-                bz = z;
+                const uint32_t a_remote = mapa_cluster(smem_u32(cmsg_a + par * 32 + rank), lane);
+                const uint32_t z_remote = mapa_cluster(smem_u32(cmsg_z + par * 32 + rank), lane);
+                if (SYNC == 1)
+                    st_async_msg(a_remote, z_remote, mapa_cluster(smem_u32(mbar + par), lane),
+                                 static_cast<uint32_t>(msg.key), static_cast<uint32_t>(msg.k), msg.x,
+                                 msg.y, msg.z);
+                else
+                    st_cluster_msg(a_remote, z_remote, static_cast<uint32_t>(msg.key),
+                                   static_cast<uint32_t>(msg.k), msg.x, msg.y, msg.z);
             }
-        }
-        const uint32_t ghi = __reduce_max_sync(kFullMask, bhi);
-        const uint32_t glo = __reduce_max_sync(kFullMask, bhi == ghi ? blo : 0u);
-        const int gsrc = __ffs(__ballot_sync(kFullMask, bhi == ghi && blo == glo)) - 1;
-        cx = __shfl_sync(kFullMask, bx, gsrc);
-        cy = __shfl_sync(kFullMask, by, gsrc);
-        cz = __shfl_sync(kFullMask, bz, gsrc);
-        if (gtid == 0)
-        {
-            int k = 0;
-            if (ghi != 0u)
+            if (SYNC == 1)
             {
-                const uint32_t r = ~glo;
-                k = static_cast<int>(((r & 0x3FFFFFu) << log2bs) | bitrev_low(r >> 22, log2bs));
+                // a warp whose wait ran out records it and stops waiting, but keeps taking
+                // part in every barrier and exchange so that no other warp or CTA is left
+                // behind at one; the results are then meaningless and the status word says so
+                const uint32_t parity = static_cast<uint32_t>((j - 1) >> 1) & 1u;
+                if (!failed && !mbar_wait_bounded(smem_u32(mbar + par), parity))
+                {
+                    if (lane == 0) atomicExch(&g_dev_status, 1);
+                    failed = true;
+                }
             }
-            idxs[j] = k;
+            else
+            {
+                cluster_sync_all();
+            }
+            int key3 = INT_MIN, k3 = 0;
+            if (lane < nranks)
+            {
+                const uint2 a = *reinterpret_cast<const uint2*>(cmsg_a + par * 32 + lane);
+                key3 = static_cast<int>(a.x);
+                k3 = static_cast<int>(a.y);
+            }
+            src = warp_argmax(key3, k3, log2bs);
+            const uint4 a = cmsg_a[par * 32 + src];
+            msg.key = static_cast<int>(a.x);
+            msg.k = static_cast<int>(a.y);
+            msg.x = __uint_as_float(a.z);
+            msg.y = __uint_as_float(a.w);
+            msg.z = cmsg_z[par * 32 + src];
         }
+
+        cx = msg.x;
+        cy = msg.y;
+        cz = msg.z;
+        if (gtid == 0) idxs[j] = msg.key >= 0 ? msg.k : 0;
     }
-    (void)failed;
     // no CTA may leave while a peer can still write into its shared memory
     if (nranks > 1) cluster_sync_all();
 }
@@ -348,12 +414,8 @@ struct FpsConfig
 
 size_t fps_smem_bytes(const FpsConfig& c)
 {
-    const size_t nslots = static_cast<size_t>(c.nranks) * (c.nthreads / 32);
-    size_t off = 2 * nslots * kMsgBytes;
-    off += off & 8;
-    off += 16;
-    off += static_cast<size_t>(c.ppt) * c.nthreads * 3 * sizeof(float);
-    return off;
+    // 128 x 16 B + 128 x 4 B messages, 2 mbarriers, coordinates
+    return 128 * 16 + 128 * 4 + 16 + static_cast<size_t>(c.ppt) * c.nthreads * 4 * sizeof(float);
 }
 
 int floor_log2(int v)
@@ -370,38 +432,42 @@ int round_up_pow2(int v)
     return p;
 }
 
-// Picks cluster size, block size and points per thread for n points per cloud.
+bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+bool fps_config_ok(const FpsConfig& e, int n)
+{
+    return (e.nranks >= 1 && e.nranks <= kFpsMaxRanks && is_pow2(e.nranks)) &&
+           (e.nthreads >= 32 && e.nthreads <= kFpsMaxThreads && is_pow2(e.nthreads)) &&
+           (e.ppt >= 1 && e.ppt <= kFpsMaxPpt && is_pow2(e.ppt)) && e.nthreads <= fps_max_threads(e.ppt) &&
+           (e.sync == 0 || e.sync == 1) && static_cast<long long>(e.nranks) * e.nthreads * e.ppt >= n;
+}
+
+// Picks cluster size, block size and points per thread for n points per cloud: few,
+// fat threads (every warp and every CTA adds a stage to the per-round exchange), and
+// as many CTAs per cloud as keep a CTA's share near 2048-4096 points.
 bool fps_pick_config(int n, FpsConfig* out)
 {
     FpsConfig c;
     c.sync = 1;
-    if (n <= 4096)
-        c.nranks = 1;
-    else if (n <= 8192)
-        c.nranks = 4;
-    else if (n <= 65536)
-        c.nranks = 8;
+    c.nranks = n <= 4096 ? 1 : (n <= 8192 ? 4 : (n <= 32768 ? 8 : 16));
+    const int per_cta = (n + c.nranks - 1) / c.nranks;
+    if (per_cta <= 256)
+        c.nthreads = 32;
+    else if (per_cta <= 1024)
+        c.nthreads = 64;
+    else if (per_cta <= 4096)
+        c.nthreads = 128;
     else
-        c.nranks = 16;
-    c.nthreads = 512;
-    const int per_thread = (n + c.nranks * c.nthreads - 1) / (c.nranks * c.nthreads);
-    c.ppt = round_up_pow2(per_thread < 1 ? 1 : per_thread);
-    if (c.ppt > kFpsMaxPpt) return false;
+        c.nthreads = 512;
+    c.ppt = round_up_pow2((per_cta + c.nthreads - 1) / c.nthreads);
+    if (c.ppt < 1) c.ppt = 1;
+    if (!fps_config_ok(c, n)) return false;
     // override for tuning runs: "nranks,nthreads,ppt,sync"
     if (const char* env = getenv("TPK_FPS_CONFIG"))
     {
         FpsConfig e = c;
-        if (sscanf(env, "%d,%d,%d,%d", &e.nranks, &e.nthreads, &e.ppt, &e.sync) == 4)
-        {
-            const bool ok = (e.nranks == 1 || e.nranks == 2 || e.nranks == 4 || e.nranks == 8 ||
-                             e.nranks == 16) &&
-                            (e.nthreads == 128 || e.nthreads == 256 || e.nthreads == 512) &&
-                            (e.ppt == 1 || e.ppt == 2 || e.ppt == 4 || e.ppt == 8 || e.ppt == 16) &&
-                            (e.sync == 0 || e.sync == 1) &&
-                            static_cast<long long>(e.nranks) * e.nthreads * e.ppt >= n &&
-                            e.nranks * e.nthreads >= 512;
-            if (ok) c = e;
-        }
+        if (sscanf(env, "%d,%d,%d,%d", &e.nranks, &e.nthreads, &e.ppt, &e.sync) == 4 && fps_config_ok(e, n))
+            c = e;
     }
     *out = c;
     return true;
@@ -466,6 +532,7 @@ int fps_launch_s(const FpsConfig& c, int b, int n, int m, int log2bs, const floa
     case 4: return fps_launch_t<4, SYNC>(c, b, n, m, log2bs, xyz, idxs, stream);
     case 8: return fps_launch_t<8, SYNC>(c, b, n, m, log2bs, xyz, idxs, stream);
     case 16: return fps_launch_t<16, SYNC>(c, b, n, m, log2bs, xyz, idxs, stream);
+    case 32: return fps_launch_t<32, SYNC>(c, b, n, m, log2bs, xyz, idxs, stream);
     default: break;
     }
     set_error("fps: unsupported points per thread %d", c.ppt);
