@@ -273,10 +273,10 @@ def run_b200(args, rank, world, local_rank):
 
     # ---- per-kernel durations: serialised pass, CUDA events on the launching stream
     timers = {}
-    for _ in range(max(3, min(args.steps, 10))):
+    for _ in range(max(5, min(args.steps, 11))):
         pipe.step(*split([t.detach() for t in dev_in]), overlap=False, timers=timers)
     torch.cuda.synchronize(dev)
-    kms = {k: sum(a.elapsed_time(b) for a, b in v) / len(v) for k, v in timers.items()}
+    kms = {k: sorted(a.elapsed_time(b) for a, b in v)[len(v) // 2] for k, v in timers.items()}
 
     if rank != 0:
         return

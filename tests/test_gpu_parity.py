@@ -61,11 +61,11 @@ def test_fps_matches_oracle(B, N, m):
     assert _lib.device_status() == 0
 
 
-@pytest.mark.parametrize("cfg", ["1,128,32,0", "1,128,32,1", "1,512,8,1", "1,256,16,0", "2,64,32,1",
-                                 "2,512,4,0", "4,32,32,1", "4,256,4,0", "8,128,4,1", "8,32,16,0",
-                                 "8,512,1,1", "16,32,8,1", "16,512,1,0", "16,64,4,1"])
+@pytest.mark.parametrize("cfg", ["1,128,32", "1,512,8", "1,256,16", "2,64,32", "2,512,4", "4,64,16",
+                                 "4,256,4", "8,128,4", "8,64,8", "8,512,1", "16,64,4", "16,512,1",
+                                 "16,128,2"])
 def test_fps_every_cluster_shape(cfg, fps_env):
-    """Same cloud through every cluster size / block size / exchange mechanism."""
+    """Same cloud through every cluster size / block size (cluster x threads x points per thread)."""
     x = data.unit_ball(3, 4000, seed=77)
     want = orc.fps(x, 300)
     os.environ["TPK_FPS_CONFIG"] = cfg
@@ -86,7 +86,7 @@ def test_fps_tie_break_and_skip_rule(n, fps_env):
     m = min(n, 12)
     want = orc.fps(pts, m)
     # with fewer than bs threads per cluster a thread owns several residues of k mod bs
-    for cfg in (None, "1,32,32,1", "2,64,32,0", "2,256,16,1", "4,128,16,0", "1,64,32,1"):
+    for cfg in (None, "1,64,32", "2,64,32", "2,256,16", "4,128,16", "1,128,8", "2,64,4"):
         if cfg:
             os.environ["TPK_FPS_CONFIG"] = cfg
         np.testing.assert_array_equal(npy(tpk.furthest_point_sample(cu(pts), m)), want)

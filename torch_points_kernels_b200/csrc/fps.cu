@@ -15,6 +15,7 @@
 // encoded as a rank: with bs = largest power of two <= n (at most 512) the reference
 // prefers the smallest bit-reversed (k mod bs), then the smallest (k div bs).
 #include <climits>
+#include <type_traits>
 
 #include <cooperative_groups.h>
 
@@ -61,15 +62,6 @@ __device__ __forceinline__ void cluster_sync_all()
 {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\t"
                  "barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void st_cluster_msg(uint32_t addr_a, uint32_t addr_z, uint32_t hi,
-                                               uint32_t lo, float x, float y, float z)
-{
-    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr_a), "r"(hi),
-                 "r"(lo), "r"(__float_as_uint(x)), "r"(__float_as_uint(y))
-                 : "memory");
-    asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(addr_z), "r"(__float_as_uint(z))
-                 : "memory");
 }
 // Remote store that signals the destination CTA's mbarrier with the bytes written.
 __device__ __forceinline__ void st_async_msg(uint32_t addr_a, uint32_t addr_z, uint32_t mbar,
@@ -172,13 +164,13 @@ __device__ __forceinline__ int warp_argmax(int key, int k, int log2bs)
 // One round = three arg-max stages, each a redux over at most 32 lanes:
 //   1. inside every warp, over its lanes' best points;
 //   2. inside the CTA, over its warps' winners (shared memory + one __syncthreads);
-//   3. inside the cluster, over its CTAs' winners.  The winner of every CTA is delivered
-//      to all CTAs of the cluster through distributed shared memory:
-//      SYNC == 1: st.async stores that complete a transaction count on the receiver's
-//                 mbarrier; receivers poll their own barrier with a time limit;
-//      SYNC == 0: plain st.shared::cluster stores followed by a cluster barrier.
-// Stages 2 and 3 are skipped for a one-warp CTA / one-CTA cluster.
-template <int PPT, int SYNC>
+//   3. (CLUSTERED) inside the cluster, over its CTAs' winners: warp 0 delivers the CTA's
+//      winner to every CTA of the cluster with st.async stores into distributed shared
+//      memory that complete a transaction count on the receiver's mbarrier; every warp
+//      then polls its own CTA's barrier (with a time limit) and reduces the messages.
+// The round loop is unrolled by two so that the double-buffered message slots and
+// barriers have compile-time addresses.  A CTA has at least two warps.
+template <int PPT, bool CLUSTERED>
 __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
     fps_onchip_kernel(int n, int m, int log2bs, const float* __restrict__ xyz_all,
                       int32_t* __restrict__ idxs_all)
@@ -186,8 +178,8 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nthreads = blockDim.x, nwarps = nthreads >> 5;
-    const int nranks = static_cast<int>(cluster_nctarank());
-    const int rank = static_cast<int>(cluster_ctarank());
+    const int nranks = CLUSTERED ? static_cast<int>(cluster_nctarank()) : 1;
+    const int rank = CLUSTERED ? static_cast<int>(cluster_ctarank()) : 0;
     const int cloud = blockIdx.x / nranks;
     const int total = nranks * nthreads;
     const int gtid = rank * nthreads + tid;
@@ -238,7 +230,8 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
         pz[p] = z;
         // a negative running minimum marks "never a candidate": fminf keeps it negative
         md[p] = valid ? 1e10f : -1.0f;
-        sxyz[p * nthreads + tid] = make_float4(x, y, z, 0.f);
+        // w carries the point's index so that the winner's message needs no index arithmetic
+        sxyz[p * nthreads + tid] = make_float4(x, y, z, __int_as_float(k));
     }
 
     float cx = 0.f, cy = 0.f, cz = 0.f;
@@ -250,23 +243,40 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
     }
     if (gtid == 0 && m > 0) idxs[0] = 0;
 
-    if (SYNC == 1 && tid == 0)
+    if (CLUSTERED)
     {
-        mbar_init(smem_u32(mbar + 0), 1);
-        mbar_init(smem_u32(mbar + 1), 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (nranks > 1)
+        if (tid == 0)
+        {
+            mbar_init(smem_u32(mbar + 0), 1);
+            mbar_init(smem_u32(mbar + 1), 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
         cluster_sync_all();
+    }
     else
-        __syncthreads();
-
-    bool failed = false;
-    for (int j = 1; j < m; ++j)
     {
-        const int par = j & 1;
-        if (SYNC == 1 && nranks > 1 && tid == 0)
-            mbar_arrive_expect_tx(smem_u32(mbar + par), static_cast<uint32_t>(nranks * kMsgBytes));
+        __syncthreads();
+    }
+
+    // remote addresses of this CTA's slot in CTA `lane` of the cluster, both parities
+    uint32_t rem_a[2] = {0, 0}, rem_z[2] = {0, 0}, rem_bar[2] = {0, 0};
+    if (CLUSTERED && warp == 0 && lane < nranks)
+    {
+#pragma unroll
+        for (int par = 0; par < 2; ++par)
+        {
+            rem_a[par] = mapa_cluster(smem_u32(cmsg_a + par * 32 + rank), lane);
+            rem_z[par] = mapa_cluster(smem_u32(cmsg_z + par * 32 + rank), lane);
+            rem_bar[par] = mapa_cluster(smem_u32(mbar + par), lane);
+        }
+    }
+    const float4* my_xyz = sxyz + tid;
+    bool failed = false;
+
+    auto round = [&](int j, auto par_tag) {
+        constexpr int PAR = decltype(par_tag)::value;
+        if (CLUSTERED && tid == 0)
+            mbar_arrive_expect_tx(smem_u32(mbar + PAR), static_cast<uint32_t>(nranks * kMsgBytes));
 
         // ---- every point: distance to the newest sample, running minimum, thread maximum
 #pragma unroll
@@ -281,135 +291,109 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
             for (int p = 0; p < w; ++p) red[p] = fmaxf(red[p], red[p + w]);
         const float best = red[0];
 
-        // ---- stage 1: the warp's best point.  Non-negative floats order like their bits.
-        Msg msg;
-        msg.key = __float_as_int(best);
-        msg.k = 0;
-        msg.x = msg.y = msg.z = 0.f;
-        auto own_best = [&]() {  // this thread's best point: lowest p among equal minima
-            uint32_t eq = 0;
+        // ---- stage 1: the warp's best point.  Non-negative floats order like their bits;
+        // a negative key means "no candidate".  While the redux is in flight every lane
+        // looks up its own best point (lowest p among equal minima), so that the winning
+        // lane only has to store.
+        const int key = __float_as_int(best);
+        const int wkey = __reduce_max_sync(kFullMask, key);
+        uint32_t eq = 0;
 #pragma unroll
-            for (int p = 0; p < PPT; ++p) eq |= (md[p] == best) ? (1u << p) : 0u;
-            return __ffs(eq) - 1;
-        };
-        const int wkey = __reduce_max_sync(kFullMask, msg.key);
-        uint32_t ball = __ballot_sync(kFullMask, msg.key == wkey);
-        int bp = -1;
+        for (int p = 0; p < PPT; ++p) eq |= (md[p] == best) ? (1u << p) : 0u;
+        const int bp = __ffs(eq) - 1;
+        const float4 mine = my_xyz[bp * nthreads];
+        uint32_t ball = __ballot_sync(kFullMask, key == wkey);
         if (__popc(ball) > 1 && wkey >= 0)
         {
-            uint32_t r = 0xFFFFFFFFu;
-            if (msg.key == wkey)
-            {
-                bp = own_best();
-                r = fps_rank(point_index(bp), log2bs);
-            }
+            const uint32_t r = key == wkey ? fps_rank(__float_as_int(mine.w), log2bs) : 0xFFFFFFFFu;
             const uint32_t wr = __reduce_min_sync(kFullMask, r);
-            ball = __ballot_sync(kFullMask, msg.key == wkey && r == wr);
+            ball = __ballot_sync(kFullMask, key == wkey && r == wr);
         }
-        int src = __ffs(ball) - 1;
-        if (lane == src)
+        if (lane == __ffs(ball) - 1)
         {
-            if (bp < 0) bp = wkey >= 0 ? own_best() : 0;
-            msg.k = point_index(bp);
-            const float4 c = sxyz[bp * nthreads + tid];
-            msg.x = c.x;
-            msg.y = c.y;
-            msg.z = c.z;
-            if (nwarps > 1)
-            {
-                wmsg_a[par * 32 + warp] = make_uint4(static_cast<uint32_t>(msg.key), static_cast<uint32_t>(msg.k),
-                                                     __float_as_uint(msg.x), __float_as_uint(msg.y));
-                wmsg_z[par * 32 + warp] = msg.z;
-            }
+            wmsg_a[PAR * 32 + warp] = make_uint4(static_cast<uint32_t>(key), __float_as_uint(mine.w),
+                                                 __float_as_uint(mine.x), __float_as_uint(mine.y));
+            wmsg_z[PAR * 32 + warp] = mine.z;
         }
 
         // ---- stage 2: the CTA's best point
-        if (nwarps > 1)
+        __syncthreads();
+        Msg msg;
         {
-            __syncthreads();
             int key2 = INT_MIN, k2 = 0;  // below every real key, including "no candidate"
+            float x2 = 0.f, y2 = 0.f, z2 = 0.f;
             if (lane < nwarps)
             {
-                const uint2 a = *reinterpret_cast<const uint2*>(wmsg_a + par * 32 + lane);
+                const uint4 a = wmsg_a[PAR * 32 + lane];
                 key2 = static_cast<int>(a.x);
                 k2 = static_cast<int>(a.y);
+                x2 = __uint_as_float(a.z);
+                y2 = __uint_as_float(a.w);
+                z2 = wmsg_z[PAR * 32 + lane];
             }
-            src = warp_argmax(key2, k2, log2bs);
-            const uint4 a = wmsg_a[par * 32 + src];  // same address in every lane: a broadcast
-            msg.key = static_cast<int>(a.x);
-            msg.k = static_cast<int>(a.y);
-            msg.x = __uint_as_float(a.z);
-            msg.y = __uint_as_float(a.w);
-            msg.z = wmsg_z[par * 32 + src];
-        }
-        else
-        {
-            msg.key = wkey;
-            msg.k = __shfl_sync(kFullMask, msg.k, src);
-            msg.x = __shfl_sync(kFullMask, msg.x, src);
-            msg.y = __shfl_sync(kFullMask, msg.y, src);
-            msg.z = __shfl_sync(kFullMask, msg.z, src);
+            const int src = warp_argmax(key2, k2, log2bs);
+            msg.key = __shfl_sync(kFullMask, key2, src);
+            msg.k = __shfl_sync(kFullMask, k2, src);
+            msg.x = __shfl_sync(kFullMask, x2, src);
+            msg.y = __shfl_sync(kFullMask, y2, src);
+            msg.z = __shfl_sync(kFullMask, z2, src);
         }
 
         // ---- stage 3: the cluster's best point
-        if (nranks > 1)
+        if (CLUSTERED)
         {
             if (warp == 0 && lane < nranks)
+                st_async_msg(rem_a[PAR], rem_z[PAR], rem_bar[PAR], static_cast<uint32_t>(msg.key),
+                             static_cast<uint32_t>(msg.k), msg.x, msg.y, msg.z);
+            // a warp whose wait ran out records it and stops waiting, but keeps taking part
+            // in every barrier and exchange so that no other warp or CTA is left behind at
+            // one; the results are then meaningless and the status word says so
+            const uint32_t parity = static_cast<uint32_t>((j - 1) >> 1) & 1u;
+            if (!failed && !mbar_wait_bounded(smem_u32(mbar + PAR), parity))
             {
-                const uint32_t a_remote = mapa_cluster(smem_u32(cmsg_a + par * 32 + rank), lane);
-                const uint32_t z_remote = mapa_cluster(smem_u32(cmsg_z + par * 32 + rank), lane);
-                if (SYNC == 1)
-                    st_async_msg(a_remote, z_remote, mapa_cluster(smem_u32(mbar + par), lane),
-                                 static_cast<uint32_t>(msg.key), static_cast<uint32_t>(msg.k), msg.x,
-                                 msg.y, msg.z);
-                else
-                    st_cluster_msg(a_remote, z_remote, static_cast<uint32_t>(msg.key),
-                                   static_cast<uint32_t>(msg.k), msg.x, msg.y, msg.z);
-            }
-            if (SYNC == 1)
-            {
-                // a warp whose wait ran out records it and stops waiting, but keeps taking
-                // part in every barrier and exchange so that no other warp or CTA is left
-                // behind at one; the results are then meaningless and the status word says so
-                const uint32_t parity = static_cast<uint32_t>((j - 1) >> 1) & 1u;
-                if (!failed && !mbar_wait_bounded(smem_u32(mbar + par), parity))
-                {
-                    if (lane == 0) atomicExch(&g_dev_status, 1);
-                    failed = true;
-                }
-            }
-            else
-            {
-                cluster_sync_all();
+                if (lane == 0) atomicExch(&g_dev_status, 1);
+                failed = true;
             }
             int key3 = INT_MIN, k3 = 0;
+            float x3 = 0.f, y3 = 0.f, z3 = 0.f;
             if (lane < nranks)
             {
-                const uint2 a = *reinterpret_cast<const uint2*>(cmsg_a + par * 32 + lane);
+                const uint4 a = cmsg_a[PAR * 32 + lane];
                 key3 = static_cast<int>(a.x);
                 k3 = static_cast<int>(a.y);
+                x3 = __uint_as_float(a.z);
+                y3 = __uint_as_float(a.w);
+                z3 = cmsg_z[PAR * 32 + lane];
             }
-            src = warp_argmax(key3, k3, log2bs);
-            const uint4 a = cmsg_a[par * 32 + src];
-            msg.key = static_cast<int>(a.x);
-            msg.k = static_cast<int>(a.y);
-            msg.x = __uint_as_float(a.z);
-            msg.y = __uint_as_float(a.w);
-            msg.z = cmsg_z[par * 32 + src];
+            const int src = warp_argmax(key3, k3, log2bs);
+            msg.key = __shfl_sync(kFullMask, key3, src);
+            msg.k = __shfl_sync(kFullMask, k3, src);
+            msg.x = __shfl_sync(kFullMask, x3, src);
+            msg.y = __shfl_sync(kFullMask, y3, src);
+            msg.z = __shfl_sync(kFullMask, z3, src);
         }
 
         cx = msg.x;
         cy = msg.y;
         cz = msg.z;
         if (gtid == 0) idxs[j] = msg.key >= 0 ? msg.k : 0;
+    };
+
+    int j = 1;
+    for (; j + 1 < m; j += 2)
+    {
+        round(j, std::integral_constant<int, 1>{});
+        round(j + 1, std::integral_constant<int, 0>{});
     }
+    if (j < m) round(j, std::integral_constant<int, 1>{});
+
     // no CTA may leave while a peer can still write into its shared memory
-    if (nranks > 1) cluster_sync_all();
+    if (CLUSTERED) cluster_sync_all();
 }
 
 struct FpsConfig
 {
-    int nranks, nthreads, ppt, sync;
+    int nranks, nthreads, ppt;
 };
 
 size_t fps_smem_bytes(const FpsConfig& c)
@@ -437,9 +421,9 @@ bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 bool fps_config_ok(const FpsConfig& e, int n)
 {
     return (e.nranks >= 1 && e.nranks <= kFpsMaxRanks && is_pow2(e.nranks)) &&
-           (e.nthreads >= 32 && e.nthreads <= kFpsMaxThreads && is_pow2(e.nthreads)) &&
+           (e.nthreads >= 64 && e.nthreads <= kFpsMaxThreads && is_pow2(e.nthreads)) &&
            (e.ppt >= 1 && e.ppt <= kFpsMaxPpt && is_pow2(e.ppt)) && e.nthreads <= fps_max_threads(e.ppt) &&
-           (e.sync == 0 || e.sync == 1) && static_cast<long long>(e.nranks) * e.nthreads * e.ppt >= n;
+           static_cast<long long>(e.nranks) * e.nthreads * e.ppt >= n;
 }
 
 // Picks cluster size, block size and points per thread for n points per cloud: few,
@@ -448,36 +432,34 @@ bool fps_config_ok(const FpsConfig& e, int n)
 bool fps_pick_config(int n, FpsConfig* out)
 {
     FpsConfig c;
-    c.sync = 1;
     c.nranks = n <= 4096 ? 1 : (n <= 8192 ? 4 : (n <= 32768 ? 8 : 16));
     const int per_cta = (n + c.nranks - 1) / c.nranks;
     if (per_cta <= 256)
-        c.nthreads = 32;
-    else if (per_cta <= 1024)
         c.nthreads = 64;
-    else if (per_cta <= 4096)
+    else if (per_cta <= 2048)
         c.nthreads = 128;
+    else if (per_cta <= 4096)
+        c.nthreads = c.nranks == 1 ? 256 : 128;
     else
         c.nthreads = 512;
     c.ppt = round_up_pow2((per_cta + c.nthreads - 1) / c.nthreads);
     if (c.ppt < 1) c.ppt = 1;
     if (!fps_config_ok(c, n)) return false;
-    // override for tuning runs: "nranks,nthreads,ppt,sync"
+    // override for tuning runs: "nranks,nthreads,ppt"
     if (const char* env = getenv("TPK_FPS_CONFIG"))
     {
         FpsConfig e = c;
-        if (sscanf(env, "%d,%d,%d,%d", &e.nranks, &e.nthreads, &e.ppt, &e.sync) == 4 && fps_config_ok(e, n))
-            c = e;
+        if (sscanf(env, "%d,%d,%d", &e.nranks, &e.nthreads, &e.ppt) == 3 && fps_config_ok(e, n)) c = e;
     }
     *out = c;
     return true;
 }
 
-template <int PPT, int SYNC>
+template <int PPT, bool CLUSTERED>
 int fps_launch_t(const FpsConfig& c, int b, int n, int m, int log2bs, const float* xyz,
                  int32_t* idxs, cudaStream_t stream)
 {
-    auto kernel = fps_onchip_kernel<PPT, SYNC>;
+    auto kernel = fps_onchip_kernel<PPT, CLUSTERED>;
     const size_t smem = fps_smem_bytes(c);
     cudaError_t err;
     if (smem > 48 * 1024)
@@ -521,18 +503,18 @@ int fps_launch_t(const FpsConfig& c, int b, int n, int m, int log2bs, const floa
     return TPK_OK;
 }
 
-template <int SYNC>
+template <bool CLUSTERED>
 int fps_launch_s(const FpsConfig& c, int b, int n, int m, int log2bs, const float* xyz,
                  int32_t* idxs, cudaStream_t stream)
 {
     switch (c.ppt)
     {
-    case 1: return fps_launch_t<1, SYNC>(c, b, n, m, log2bs, xyz, idxs, stream);
-    case 2: return fps_launch_t<2, SYNC>(c, b, n, m, log2bs, xyz, idxs, stream);
-    case 4: return fps_launch_t<4, SYNC>(c, b, n, m, log2bs, xyz, idxs, stream);
-    case 8: return fps_launch_t<8, SYNC>(c, b, n, m, log2bs, xyz, idxs, stream);
-    case 16: return fps_launch_t<16, SYNC>(c, b, n, m, log2bs, xyz, idxs, stream);
-    case 32: return fps_launch_t<32, SYNC>(c, b, n, m, log2bs, xyz, idxs, stream);
+    case 1: return fps_launch_t<1, CLUSTERED>(c, b, n, m, log2bs, xyz, idxs, stream);
+    case 2: return fps_launch_t<2, CLUSTERED>(c, b, n, m, log2bs, xyz, idxs, stream);
+    case 4: return fps_launch_t<4, CLUSTERED>(c, b, n, m, log2bs, xyz, idxs, stream);
+    case 8: return fps_launch_t<8, CLUSTERED>(c, b, n, m, log2bs, xyz, idxs, stream);
+    case 16: return fps_launch_t<16, CLUSTERED>(c, b, n, m, log2bs, xyz, idxs, stream);
+    case 32: return fps_launch_t<32, CLUSTERED>(c, b, n, m, log2bs, xyz, idxs, stream);
     default: break;
     }
     set_error("fps: unsupported points per thread %d", c.ppt);
@@ -572,8 +554,8 @@ extern "C" int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz
     int log2bs = floor_log2(n);
     if (log2bs > 9) log2bs = 9;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    return c.sync ? fps_launch_s<1>(c, b, n, m, log2bs, xyz, idxs, s)
-                  : fps_launch_s<0>(c, b, n, m, log2bs, xyz, idxs, s);
+    return c.nranks > 1 ? fps_launch_s<true>(c, b, n, m, log2bs, xyz, idxs, s)
+                        : fps_launch_s<false>(c, b, n, m, log2bs, xyz, idxs, s);
 }
 
 extern "C" int tpk_device_status(int* status_out, int reset)

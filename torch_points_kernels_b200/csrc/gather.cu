@@ -241,6 +241,108 @@ __global__ void __launch_bounds__(kScatterThreads)
     for (int i = threadIdx.x; i < nrows * row_len; i += kScatterThreads) dst[i] = acc[i];
 }
 
+// ------------------------------------------------------ grouping backward, shared rows
+
+// A warp takes 32 consecutive positions at a time (one 128-byte line of every gradient
+// row; with nsample = 32 exactly one neighbourhood).  Ball-query neighbourhoods repeat
+// their first index in every unused slot, so many lanes of a warp often target the same
+// feature column, and shared-memory float atomics serialise badly on one address.
+// Lanes whose index equals that of the first lane of their neighbourhood segment are
+// therefore summed with a shuffle butterfly and only the segment's first lane issues
+// the atomic for them.  Any other repetition in idx is still correct: those lanes just
+// use their own atomics.  `seg` = lanes per segment (a power of two <= 32; 1 = no
+// pre-reduction, used when nsample is not a power of two).
+template <int ROWS, int UNROLL>
+__global__ void __launch_bounds__(kScatterThreads)
+    grouping_bwd_rows_kernel(int c, int row_len, long long src_len, int seg,
+                             const float* __restrict__ grad_out, const int64_t* __restrict__ idx,
+                             float* __restrict__ grad_small)
+{
+    extern __shared__ __align__(16) float acc[];
+    const int groups_per_batch = (c + ROWS - 1) / ROWS;
+    const int bi = blockIdx.x / groups_per_batch;
+    const int c0 = (blockIdx.x - bi * groups_per_batch) * ROWS;
+    const int nrows = min(ROWS, c - c0);
+    for (int i = threadIdx.x; i < nrows * row_len; i += kScatterThreads) acc[i] = 0.f;
+    __syncthreads();
+
+    const float* g = grad_out + (static_cast<size_t>(bi) * c + c0) * src_len;
+    const int64_t* ib = idx + static_cast<size_t>(bi) * src_len;
+    const int lane = threadIdx.x & 31;
+    const int seg_first = lane & ~(seg - 1);
+    const long long stride = kScatterThreads;
+    for (long long base = threadIdx.x; base - lane < src_len; base += stride * UNROLL)
+    {
+        int id[UNROLL];
+        float v[UNROLL][ROWS];
+        bool ok[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+        {
+            const long long p = base + u * stride;
+            ok[u] = p < src_len;
+            id[u] = ok[u] ? static_cast<int>(__ldg(ib + p)) : -1 - lane;  // distinct dummies
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r)
+                v[u][r] = (ok[u] && r < nrows) ? __ldcs(g + r * src_len + p) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+        {
+            if (base + u * stride - lane >= src_len) break;  // whole warp past the end
+            const int first_id = __shfl_sync(kFullMask, id[u], seg_first);
+            const bool dup = seg > 1 && id[u] == first_id;  // includes the segment's first lane
+            const uint32_t dups = __ballot_sync(kFullMask, dup && lane != seg_first);
+            if (dups != 0u)
+            {
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r)
+                {
+                    float sum = dup ? v[u][r] : 0.f;
+                    for (int o = seg >> 1; o >= 1; o >>= 1) sum += __shfl_xor_sync(kFullMask, sum, o);
+                    if (lane == seg_first) v[u][r] = sum;
+                }
+            }
+            if (ok[u] && (!dup || lane == seg_first))
+            {
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r)
+                    if (r < nrows) atomicAdd(acc + r * row_len + id[u], v[u][r]);
+            }
+        }
+    }
+    __syncthreads();
+    float* dst = grad_small + (static_cast<size_t>(bi) * c + c0) * row_len;
+    for (int i = threadIdx.x; i < nrows * row_len; i += kScatterThreads) dst[i] = acc[i];
+}
+
+template <int ROWS>
+int launch_grouping_bwd_rows(int b, int c, int row_len, long long src_len, int nsample,
+                             const float* grad_out, const int64_t* idx, float* grad_small,
+                             cudaStream_t s)
+{
+    auto kernel = grouping_bwd_rows_kernel<ROWS, 4>;
+    const size_t smem = static_cast<size_t>(ROWS) * row_len * sizeof(float);
+    if (smem > 48 * 1024)
+    {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(smem));
+        if (err != cudaSuccess)
+        {
+            set_error("grouping_grad: shared memory attribute: %s", cudaGetErrorString(err));
+            return TPK_ERR_CUDA;
+        }
+    }
+    const long long grid = static_cast<long long>(b) * ((c + ROWS - 1) / ROWS);
+    TPK_REQUIRE(grid < (1ll << 31), "grouping_grad: too many rows");
+    // neighbourhood segments line up with warps when nsample is a power of two
+    int seg = 1;
+    if (nsample > 1 && (nsample & (nsample - 1)) == 0) seg = nsample < 32 ? nsample : 32;
+    kernel<<<static_cast<unsigned>(grid), kScatterThreads, smem, s>>>(c, row_len, src_len, seg, grad_out,
+                                                                    idx, grad_small);
+    return check_launch("grouping_grad");
+}
+
 // ------------------------------------------------------------------ backward, global atomics
 
 template <bool INTERP>
@@ -377,6 +479,24 @@ extern "C" int tpk_grouping_grad(int b, int c, int n, int npoint, int nsample,
     }
     TPK_REQUIRE(grad_out && idx, "grouping_grad: NULL pointer");
     TPK_REQUIRE(aligned16(grad_out) && aligned16(idx), "grouping_grad: inputs must be 16-byte aligned");
+    const size_t row_bytes = static_cast<size_t>(n) * sizeof(float);
+    if (row_bytes <= kRowSmemBudget && getenv("TPK_SCATTER_GLOBAL") == nullptr)
+    {
+        // rows per CTA: as many as fit a bit over 100 KB (two CTAs per SM), at most 4,
+        // fewer when that would leave SMs without a CTA
+        int rows = static_cast<int>((104 * 1024) / row_bytes);
+        if (rows < 1) rows = 1;
+        if (rows > 4) rows = 4;
+        if (rows > c) rows = c;
+        while (rows > 1 && static_cast<long long>(b) * ((c + rows - 1) / rows) < 2ll * num_sms()) --rows;
+        switch (rows)
+        {
+        case 1: return launch_grouping_bwd_rows<1>(b, c, n, ps, nsample, grad_out, idx, grad_features, s);
+        case 2: return launch_grouping_bwd_rows<2>(b, c, n, ps, nsample, grad_out, idx, grad_features, s);
+        case 3: return launch_grouping_bwd_rows<3>(b, c, n, ps, nsample, grad_out, idx, grad_features, s);
+        default: return launch_grouping_bwd_rows<4>(b, c, n, ps, nsample, grad_out, idx, grad_features, s);
+        }
+    }
     return launch_scatter<false>(b, c, n, ps, grad_out, idx, nullptr, grad_features, s, "grouping_grad");
 }
 
