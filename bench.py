@@ -425,20 +425,76 @@ def run_reference(args, rank, world):
     }), flush=True)
 
 
+def run_only(args):
+    """One op of the stack at its pipeline shape (optionally fewer clouds / samples), for
+    profiler captures of a single kernel:  --only fps_l1|ball_query_l2|grouping_bwd_l1|...
+    Prints the mean time per launch."""
+    import torch_points_kernels_b200 as tpk
+
+    dev = torch.device("cuda", 0)
+    B = args.clouds or B_CLOUDS
+    name, lvl = args.only.rsplit("_l", 1)
+    l = int(lvl) - 1
+    xyz_h, sa_h, fp_h = make_inputs(B, N_POINTS, 2000)
+    pts = [xyz_h.to(dev)]
+    for i in range(l + 1):  # geometry of the levels below (untimed setup)
+        m = LEVELS["npoint"][i] if not (i == l and args.npoint) else args.npoint
+        idx = tpk.furthest_point_sample(pts[i], m)
+        pts.append(torch.gather(pts[i], 1, idx.long().unsqueeze(-1).expand(-1, -1, 3)).contiguous())
+    m = pts[l + 1].shape[1]
+    r, ns, c = LEVELS["radius"][l], LEVELS["nsample"], LEVELS["channels"][l]
+    g = torch.Generator(device=dev).manual_seed(3)
+    feat = sa_h[l].to(dev)
+    ffeat = torch.randn(B, c, m, device=dev, generator=g)
+    nbr, _ = tpk.ball_query(r, ns, pts[l], pts[l + 1], mode="dense")
+    dist, idx3 = tpk.three_nn(pts[l], pts[l + 1])
+    w = 1.0 / (dist + 1e-8)
+    w = (w / w.sum(dim=2, keepdim=True)).contiguous()
+    g_grouped = torch.randn(B, c, m, ns, device=dev, generator=g)
+    g_up = torch.randn(B, c, pts[l].shape[1], device=dev, generator=g)
+    ops = {
+        "fps": lambda: tpk.furthest_point_sample(pts[l], m),
+        "ball_query": lambda: tpk.ball_query(r, ns, pts[l], pts[l + 1], mode="dense"),
+        "three_nn": lambda: tpk.three_nn(pts[l], pts[l + 1]),
+        "grouping_fwd": lambda: tpk.grouping_operation(feat, nbr),
+        "grouping_bwd": lambda: tpk.GroupingOperation.apply(feat.requires_grad_(True), nbr).backward(g_grouped),
+        "interp_fwd": lambda: tpk.three_interpolate(ffeat, idx3, w),
+        "interp_bwd": lambda: tpk.three_interpolate(ffeat.requires_grad_(True), idx3, w).backward(g_up),
+    }
+    fn = ops[name]
+    for _ in range(args.warmup):
+        fn()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    print(json.dumps({"only": args.only, "clouds": B, "npoint": m, "steps": args.steps,
+                      "ms_per_call": round(e0.elapsed_time(e1) / args.steps, 4)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None, help="run one op of the stack, e.g. fps_l1, grouping_bwd_l1")
+    ap.add_argument("--clouds", type=int, default=0, help="with --only: clouds per batch (default 16)")
+    ap.add_argument("--npoint", type=int, default=0, help="with --only: samples of that level's FPS")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    args.warmup = max(args.warmup, 3) if (args.impl == "b200" and not args.only) else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.only:
+        run_only(args)
         return
     if world > 1:
         import torch.distributed as dist
