@@ -1,0 +1,71 @@
+"""Host-side multi-rank logic on CPU: world_size-2 gloo process group (no GPU)."""
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from torch_points_kernels_b200 import sharding
+
+
+def test_shard_range_covers_everything():
+    for n in (0, 1, 7, 16, 33):
+        for world in (1, 2, 3, 8):
+            spans = [sharding.shard_range(n, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            sizes = [hi - lo for lo, hi in spans]
+            assert max(sizes) - min(sizes) <= 1
+
+
+def test_balanced_blocks():
+    costs = [5, 1, 1, 1, 8, 2, 2, 4]
+    b = sharding.balanced_blocks(costs, 3)
+    assert b[0] == 0 and b[-1] == len(costs) and len(b) == 4 and b == sorted(b)
+    loads = [sum(costs[b[i]:b[i + 1]]) for i in range(3)]
+    assert max(loads) <= 1.5 * sum(costs) / 3
+    assert sharding.balanced_blocks([1, 1], 4)[-1] == 2
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(5)
+        d1 = torch.rand(6, 50, generator=g)   # what the 6 pairs' dist1 / dist2 would be
+        d2 = torch.rand(6, 70, generator=g)
+        lo, hi = sharding.shard_range(6, rank, world)
+        loss = sharding.reduce_chamfer_loss(d1[lo:hi].sum(), d1[lo:hi].numel(), d2[lo:hi].sum(), d2[lo:hi].numel())
+        want = d1.mean() + d2.mean()
+        out.put((rank, float(loss), float(want)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_chamfer_loss_reduction_two_ranks():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for _, got, want in results:
+        assert abs(got - want) < 1e-6
+
+
+def test_single_process_reduction_is_a_plain_mean():
+    d1, d2 = torch.rand(3, 10), torch.rand(3, 20)
+    got = sharding.reduce_chamfer_loss(d1.sum(), d1.numel(), d2.sum(), d2.numel())
+    assert abs(float(got) - float(d1.mean() + d2.mean())) < 1e-6

@@ -10,15 +10,14 @@
 //                                             (0 if none), dist padded with -1
 // partial : cuda/src/ball_query_gpu.cu:54-95  d2 <= r^2, idx and dist padded with -1,
 //                                             idx = position in the packed x array
+#include <math_constants.h>
+
 #include "scan.cuh"
 
 namespace tpk
 {
 namespace
 {
-
-constexpr int kBqTile = 1024;
-constexpr int kBqQ = 2;
 
 template <bool PARTIAL, int Q>
 struct BallOp
@@ -31,51 +30,32 @@ struct BallOp
     float* drow[Q];
     float r2;
     int nsample;
-    long long ncand;
     long long idx_base;
 
-    __device__ __forceinline__ bool group(long long k0, const float (&cx)[4], const float (&cy)[4],
-                                          const float (&cz)[4])
+    __device__ __forceinline__ bool open(int q) const { return act[q] && cnt[q] < nsample; }
+    __device__ __forceinline__ float threshold(int q) const { return open(q) ? r2 : -CUDART_INF_F; }
+    __device__ __forceinline__ bool finished() const
     {
-        float d[Q][4];
-        bool any = false;
-#pragma unroll
-        for (int q = 0; q < Q; ++q)
-        {
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-            {
-                // dense: (centre - candidate); partial: (candidate - centre).  The sign does
-                // not change any of the squares.
-                d[q][i] = PARTIAL ? sumsq_loop(cx[i] - qx[q], cy[i] - qy[q], cz[i] - qz[q])
-                                  : sumsq_abc(qx[q] - cx[i], qy[q] - cy[i], qz[q] - cz[i]);
-                any |= PARTIAL ? (d[q][i] <= r2) : (d[q][i] < r2);
-            }
-        }
-        if (any)
-        {
-#pragma unroll
-            for (int q = 0; q < Q; ++q)
-            {
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                {
-                    const bool hit = PARTIAL ? (d[q][i] <= r2) : (d[q][i] < r2);
-                    if (hit && act[q] && cnt[q] < nsample && k0 + i < ncand)
-                    {
-                        const long long k = k0 + i + idx_base;
-                        if (cnt[q] == 0) first[q] = k;
-                        orow[q][cnt[q]] = k;
-                        drow[q][cnt[q]] = d[q][i];
-                        ++cnt[q];
-                    }
-                }
-            }
-        }
         bool done = true;
 #pragma unroll
-        for (int q = 0; q < Q; ++q) done &= (!act[q] || cnt[q] >= nsample);
+        for (int q = 0; q < Q; ++q) done &= !open(q);
         return done;
+    }
+    __device__ __forceinline__ bool exact(int q, long long k, float cx, float cy, float cz)
+    {
+        if (!open(q)) return false;
+        // dense: (centre - candidate), strict; partial: (candidate - centre), inclusive.
+        // The sign changes none of the squares.
+        const float d = PARTIAL ? sumsq_loop(cx - qx[q], cy - qy[q], cz - qz[q])
+                                : sumsq_abc(qx[q] - cx, qy[q] - cy, qz[q] - cz);
+        const bool hit = PARTIAL ? (d <= r2) : (d < r2);
+        if (!hit) return false;
+        const long long kk = k + idx_base;
+        if (cnt[q] == 0) first[q] = kk;
+        orow[q][cnt[q]] = kk;
+        drow[q][cnt[q]] = d;
+        ++cnt[q];
+        return cnt[q] >= nsample;
     }
 };
 
@@ -85,7 +65,7 @@ __global__ void __launch_bounds__(THREADS)
                             const float* __restrict__ new_xyz, const float* __restrict__ xyz,
                             int64_t* __restrict__ idx_out, float* __restrict__ dist_out)
 {
-    __shared__ __align__(16) float smem[2 * 3 * kBqTile];
+    __shared__ __align__(16) float smem[2 * kScanTileFloats];
     const int cloud = blockIdx.x / tiles_per_cloud;
     const int qtile = blockIdx.x - cloud * tiles_per_cloud;
     const float* cand = xyz + static_cast<size_t>(cloud) * n * 3;
@@ -93,9 +73,7 @@ __global__ void __launch_bounds__(THREADS)
     BallOp<false, Q> op;
     op.r2 = __fmul_rn(radius, radius);
     op.nsample = nsample;
-    op.ncand = n;
     op.idx_base = 0;
-    bool done = true;
 #pragma unroll
     for (int q = 0; q < Q; ++q)
     {
@@ -109,11 +87,9 @@ __global__ void __launch_bounds__(THREADS)
         op.qz[q] = op.act[q] ? __ldg(new_xyz + row * 3 + 2) : 0.f;
         op.orow[q] = idx_out + row * nsample;
         op.drow[q] = dist_out + row * nsample;
-        done &= !op.act[q];
     }
-    if (nsample <= 0) done = true;
 
-    scan_candidates<THREADS, kBqTile>(cand, n, smem, op, done);
+    scan_candidates<THREADS, Q>(cand, n, smem, op.qx, op.qy, op.qz, op);
 
 #pragma unroll
     for (int q = 0; q < Q; ++q)
@@ -139,7 +115,7 @@ __global__ void __launch_bounds__(THREADS)
                               const int64_t* __restrict__ batch_y, int64_t* __restrict__ idx_out,
                               float* __restrict__ dist_out)
 {
-    __shared__ __align__(16) float smem[2 * 3 * kBqTile];
+    __shared__ __align__(16) float smem[2 * kScanTileFloats];
     __shared__ long long s_range[2];
     __shared__ unsigned long long s_next;
 
@@ -178,20 +154,16 @@ __global__ void __launch_bounds__(THREADS)
         }
         __syncthreads();
         const long long lo = s_range[0], hi = s_range[1];
-        bool done = true;
 #pragma unroll
         for (int q = 0; q < Q; ++q)
         {
             op.act[q] = valid[q] && seg[q] == cur;
-            done &= !op.act[q];
             // ids are compared as unsigned so that kNone is larger than any real id
             if (valid[q] && seg[q] > cur)
                 atomicMin(&s_next, static_cast<unsigned long long>(seg[q]));
         }
-        if (nsample <= 0) done = true;
-        op.ncand = hi - lo;
         op.idx_base = lo;
-        scan_candidates<THREADS, kBqTile>(x + lo * 3, hi - lo, smem, op, done);
+        scan_candidates<THREADS, Q>(x + lo * 3, hi - lo, smem, op.qx, op.qy, op.qz, op);
         // scan_candidates ends with a CTA barrier: s_next is final here
         const unsigned long long nxt = s_next;
         __syncthreads();
@@ -211,17 +183,29 @@ __global__ void __launch_bounds__(THREADS)
     }
 }
 
-// Smallest CTA (in threads) that still gives every SM several CTAs to balance.
-int pick_threads(long long queries, int q_per_thread)
+// Launch shape for `queries` centres: two centres per thread only when there are
+// enough of them to fill the GPU several times over, smaller CTAs for small problems.
+void pick_shape(long long queries, int* threads, int* q)
 {
-    const long long want = 6ll * num_sms();
-    if (queries / (128ll * q_per_thread) >= want) return 128;
-    if (queries / (64ll * q_per_thread) >= want) return 64;
-    return 32;
+    *q = queries >= 300000 ? 2 : 1;
+    *threads = queries >= 32768 ? 128 : 64;
 }
 
 }  // namespace
 }  // namespace tpk
+
+#define TPK_BQ_DISPATCH(KERNEL, ...)                                                               \
+    do                                                                                             \
+    {                                                                                              \
+        if (threads == 128 && q == 2)                                                              \
+            KERNEL<128, 2><<<g, 128, 0, s>>>(__VA_ARGS__);                                         \
+        else if (threads == 128)                                                                   \
+            KERNEL<128, 1><<<g, 128, 0, s>>>(__VA_ARGS__);                                         \
+        else if (q == 2)                                                                           \
+            KERNEL<64, 2><<<g, 64, 0, s>>>(__VA_ARGS__);                                           \
+        else                                                                                       \
+            KERNEL<64, 1><<<g, 64, 0, s>>>(__VA_ARGS__);                                           \
+    } while (0)
 
 extern "C" int tpk_ball_query_dense(int b, int n, int m, float radius, int nsample,
                                     const float* new_xyz, const float* xyz, int64_t* idx,
@@ -233,17 +217,13 @@ extern "C" int tpk_ball_query_dense(int b, int n, int m, float radius, int nsamp
     if (b == 0 || m == 0 || nsample == 0) return TPK_OK;
     TPK_REQUIRE(new_xyz && idx && dist && (xyz || n == 0), "ball_query_dense: NULL pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int threads = pick_threads(static_cast<long long>(b) * m, kBqQ);
-    const int tiles = (m + threads * kBqQ - 1) / (threads * kBqQ);
+    int threads, q;
+    pick_shape(static_cast<long long>(b) * m, &threads, &q);
+    const int tiles = (m + threads * q - 1) / (threads * q);
     const long long grid = static_cast<long long>(b) * tiles;
     TPK_REQUIRE(grid < (1ll << 31), "ball_query_dense: too many centres");
     const dim3 g(static_cast<unsigned>(grid));
-    if (threads == 128)
-        ball_query_dense_kernel<128, kBqQ><<<g, 128, 0, s>>>(n, m, tiles, radius, nsample, new_xyz, xyz, idx, dist);
-    else if (threads == 64)
-        ball_query_dense_kernel<64, kBqQ><<<g, 64, 0, s>>>(n, m, tiles, radius, nsample, new_xyz, xyz, idx, dist);
-    else
-        ball_query_dense_kernel<32, kBqQ><<<g, 32, 0, s>>>(n, m, tiles, radius, nsample, new_xyz, xyz, idx, dist);
+    TPK_BQ_DISPATCH(ball_query_dense_kernel, n, m, tiles, radius, nsample, new_xyz, xyz, idx, dist);
     return check_launch("ball_query_dense");
 }
 
@@ -259,15 +239,11 @@ extern "C" int tpk_ball_query_partial_dense(int64_t size_x, int64_t size_y, floa
     TPK_REQUIRE(y && batch_y && idx && dist && ((x && batch_x) || size_x == 0),
                 "ball_query_partial_dense: NULL pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int threads = pick_threads(size_y, kBqQ);
-    const long long grid = (size_y + threads * kBqQ - 1) / (threads * kBqQ);
+    int threads, q;
+    pick_shape(size_y, &threads, &q);
+    const long long grid = (size_y + threads * q - 1) / (threads * q);
     TPK_REQUIRE(grid < (1ll << 31), "ball_query_partial_dense: too many centres");
     const dim3 g(static_cast<unsigned>(grid));
-    if (threads == 128)
-        ball_query_partial_kernel<128, kBqQ><<<g, 128, 0, s>>>(size_x, size_y, radius, nsample, x, y, batch_x, batch_y, idx, dist);
-    else if (threads == 64)
-        ball_query_partial_kernel<64, kBqQ><<<g, 64, 0, s>>>(size_x, size_y, radius, nsample, x, y, batch_x, batch_y, idx, dist);
-    else
-        ball_query_partial_kernel<32, kBqQ><<<g, 32, 0, s>>>(size_x, size_y, radius, nsample, x, y, batch_x, batch_y, idx, dist);
+    TPK_BQ_DISPATCH(ball_query_partial_kernel, size_x, size_y, radius, nsample, x, y, batch_x, batch_y, idx, dist);
     return check_launch("ball_query_partial_dense");
 }

@@ -21,43 +21,29 @@ namespace tpk
 namespace
 {
 
-constexpr int kChTile = 1024;
-constexpr int kChQ = 2;
-
 template <int Q>
 struct ArgMinOp
 {
     float qx[Q], qy[Q], qz[Q];
     float best[Q];
     int besti[Q];
-    long long ncand;
+    bool act[Q];
 
-    __device__ __forceinline__ bool group(long long k0, const float (&cx)[4], const float (&cy)[4],
-                                          const float (&cz)[4])
+    __device__ __forceinline__ float threshold(int q) const { return act[q] ? best[q] : -CUDART_INF_F; }
+    __device__ __forceinline__ bool finished() const
     {
-        float d[Q][4];
-        bool any = false;
+        bool done = true;
 #pragma unroll
-        for (int q = 0; q < Q; ++q)
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-            {
-                d[q][i] = sumsq_abc(cx[i] - qx[q], cy[i] - qy[q], cz[i] - qz[q]);
-                any |= d[q][i] < best[q];
-            }
-        if (any)
-        {
-#pragma unroll
-            for (int q = 0; q < Q; ++q)
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    if (d[q][i] < best[q] && k0 + i < ncand)
-                    {
-                        best[q] = d[q][i];
-                        besti[q] = static_cast<int>(k0) + i;
-                    }
-        }
-        return false;
+        for (int q = 0; q < Q; ++q) done &= !act[q];
+        return done;
+    }
+    __device__ __forceinline__ bool exact(int q, long long k, float cx, float cy, float cz)
+    {
+        const float d = sumsq_abc(cx - qx[q], cy - qy[q], cz - qz[q]);
+        if (!act[q] || !(d < best[q])) return false;
+        best[q] = d;
+        besti[q] = static_cast<int>(k);
+        return true;
     }
 };
 
@@ -67,31 +53,27 @@ __global__ void __launch_bounds__(THREADS)
                        const float* __restrict__ xyz2, float* __restrict__ dist,
                        int32_t* __restrict__ indexes)
 {
-    __shared__ __align__(16) float smem[2 * 3 * kChTile];
+    __shared__ __align__(16) float smem[2 * kScanTileFloats];
     const int cloud = blockIdx.x / tiles_per_cloud;
     const int qtile = blockIdx.x - cloud * tiles_per_cloud;
     ArgMinOp<Q> op;
-    op.ncand = m;
-    bool act[Q];
-    bool done = true;
 #pragma unroll
     for (int q = 0; q < Q; ++q)
     {
         const int j = qtile * (THREADS * Q) + q * THREADS + threadIdx.x;
-        act[q] = j < n;
-        const size_t row = static_cast<size_t>(cloud) * n + (act[q] ? j : 0);
-        op.qx[q] = act[q] ? __ldg(xyz1 + row * 3 + 0) : 0.f;
-        op.qy[q] = act[q] ? __ldg(xyz1 + row * 3 + 1) : 0.f;
-        op.qz[q] = act[q] ? __ldg(xyz1 + row * 3 + 2) : 0.f;
+        op.act[q] = j < n;
+        const size_t row = static_cast<size_t>(cloud) * n + (op.act[q] ? j : 0);
+        op.qx[q] = op.act[q] ? __ldg(xyz1 + row * 3 + 0) : 0.f;
+        op.qy[q] = op.act[q] ? __ldg(xyz1 + row * 3 + 1) : 0.f;
+        op.qz[q] = op.act[q] ? __ldg(xyz1 + row * 3 + 2) : 0.f;
         op.best[q] = CUDART_INF_F;
         op.besti[q] = 0;
-        done &= !act[q];
     }
-    scan_candidates<THREADS, kChTile>(xyz2 + static_cast<size_t>(cloud) * m * 3, m, smem, op, done);
+    scan_candidates<THREADS, Q>(xyz2 + static_cast<size_t>(cloud) * m * 3, m, smem, op.qx, op.qy, op.qz, op);
 #pragma unroll
     for (int q = 0; q < Q; ++q)
     {
-        if (!act[q]) continue;
+        if (!op.act[q]) continue;
         const int j = qtile * (THREADS * Q) + q * THREADS + threadIdx.x;
         const size_t o = static_cast<size_t>(cloud) * n + j;
         dist[o] = op.best[q];
@@ -154,14 +136,6 @@ __global__ void __launch_bounds__(256)
     }
 }
 
-int pick_threads_ch(long long queries, int q_per_thread)
-{
-    const long long want = 6ll * num_sms();
-    if (queries / (128ll * q_per_thread) >= want) return 128;
-    if (queries / (64ll * q_per_thread) >= want) return 64;
-    return 32;
-}
-
 int chamfer_dir_f32(int b, int n, const float* xyz1, int m, const float* xyz2, float* dist,
                     int32_t* idx, cudaStream_t s)
 {
@@ -178,17 +152,21 @@ int chamfer_dir_f32(int b, int n, const float* xyz1, int m, const float* xyz2, f
         }
         return TPK_OK;
     }
-    const int threads = pick_threads_ch(static_cast<long long>(b) * n, kChQ);
-    const int tiles = (n + threads * kChQ - 1) / (threads * kChQ);
+    const long long queries = static_cast<long long>(b) * n;
+    const int q = queries >= 300000 ? 2 : 1;
+    const int threads = queries >= 32768 ? 128 : 64;
+    const int tiles = (n + threads * q - 1) / (threads * q);
     const long long grid = static_cast<long long>(b) * tiles;
     TPK_REQUIRE(grid < (1ll << 31), "chamfer_dist: too many points");
     const dim3 g(static_cast<unsigned>(grid));
-    if (threads == 128)
-        chamfer_f32_kernel<128, kChQ><<<g, 128, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
-    else if (threads == 64)
-        chamfer_f32_kernel<64, kChQ><<<g, 64, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
+    if (threads == 128 && q == 2)
+        chamfer_f32_kernel<128, 2><<<g, 128, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
+    else if (threads == 128)
+        chamfer_f32_kernel<128, 1><<<g, 128, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
+    else if (q == 2)
+        chamfer_f32_kernel<64, 2><<<g, 64, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
     else
-        chamfer_f32_kernel<32, kChQ><<<g, 32, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
+        chamfer_f32_kernel<64, 1><<<g, 64, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
     return check_launch("chamfer_dist");
 }
 

@@ -19,60 +19,43 @@ namespace tpk
 namespace
 {
 
-constexpr int kNnTile = 1024;
-constexpr int kNnQ = 2;
-
 template <int Q>
 struct ThreeNnOp
 {
     float qx[Q], qy[Q], qz[Q];
     float b1[Q], b2[Q], b3[Q];
     int i1[Q], i2[Q], i3[Q];
-    long long ncand;
+    bool act[Q];
 
-    __device__ __forceinline__ bool group(long long k0, const float (&cx)[4], const float (&cy)[4],
-                                          const float (&cz)[4])
+    __device__ __forceinline__ float threshold(int q) const { return act[q] ? b3[q] : -CUDART_INF_F; }
+    __device__ __forceinline__ bool finished() const
     {
-        float d[Q][4];
-        bool any = false;
+        bool done = true;
 #pragma unroll
-        for (int q = 0; q < Q; ++q)
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-            {
-                d[q][i] = sumsq_abc(qx[q] - cx[i], qy[q] - cy[i], qz[q] - cz[i]);
-                any |= d[q][i] < b3[q];
-            }
-        if (any)
+        for (int q = 0; q < Q; ++q) done &= !act[q];
+        return done;
+    }
+    __device__ __forceinline__ bool exact(int q, long long k, float cx, float cy, float cz)
+    {
+        const float v = sumsq_abc(qx[q] - cx, qy[q] - cy, qz[q] - cz);
+        if (!act[q] || !(v < b3[q])) return false;
+        const int kk = static_cast<int>(k);
+        if (v < b1[q])
         {
-#pragma unroll
-            for (int q = 0; q < Q; ++q)
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                {
-                    const float v = d[q][i];
-                    const int k = static_cast<int>(k0) + i;
-                    if (v < b3[q] && k0 + i < ncand)
-                    {
-                        if (v < b1[q])
-                        {
-                            b3[q] = b2[q]; i3[q] = i2[q];
-                            b2[q] = b1[q]; i2[q] = i1[q];
-                            b1[q] = v;     i1[q] = k;
-                        }
-                        else if (v < b2[q])
-                        {
-                            b3[q] = b2[q]; i3[q] = i2[q];
-                            b2[q] = v;     i2[q] = k;
-                        }
-                        else
-                        {
-                            b3[q] = v; i3[q] = k;
-                        }
-                    }
-                }
+            b3[q] = b2[q]; i3[q] = i2[q];
+            b2[q] = b1[q]; i2[q] = i1[q];
+            b1[q] = v;     i1[q] = kk;
         }
-        return false;
+        else if (v < b2[q])
+        {
+            b3[q] = b2[q]; i3[q] = i2[q];
+            b2[q] = v;     i2[q] = kk;
+        }
+        else
+        {
+            b3[q] = v; i3[q] = kk;
+        }
+        return true;
     }
 };
 
@@ -82,32 +65,28 @@ __global__ void __launch_bounds__(THREADS)
                     const float* __restrict__ known, float* __restrict__ dist2,
                     int32_t* __restrict__ idx)
 {
-    __shared__ __align__(16) float smem[2 * 3 * kNnTile];
+    __shared__ __align__(16) float smem[2 * kScanTileFloats];
     const int cloud = blockIdx.x / tiles_per_cloud;
     const int qtile = blockIdx.x - cloud * tiles_per_cloud;
 
     ThreeNnOp<Q> op;
-    op.ncand = m;
-    bool act[Q];
-    bool done = true;
 #pragma unroll
     for (int q = 0; q < Q; ++q)
     {
         const int j = qtile * (THREADS * Q) + q * THREADS + threadIdx.x;
-        act[q] = j < n;
-        const size_t row = static_cast<size_t>(cloud) * n + (act[q] ? j : 0);
-        op.qx[q] = act[q] ? __ldg(unknown + row * 3 + 0) : 0.f;
-        op.qy[q] = act[q] ? __ldg(unknown + row * 3 + 1) : 0.f;
-        op.qz[q] = act[q] ? __ldg(unknown + row * 3 + 2) : 0.f;
+        op.act[q] = j < n;
+        const size_t row = static_cast<size_t>(cloud) * n + (op.act[q] ? j : 0);
+        op.qx[q] = op.act[q] ? __ldg(unknown + row * 3 + 0) : 0.f;
+        op.qy[q] = op.act[q] ? __ldg(unknown + row * 3 + 1) : 0.f;
+        op.qz[q] = op.act[q] ? __ldg(unknown + row * 3 + 2) : 0.f;
         op.b1[q] = op.b2[q] = op.b3[q] = CUDART_INF_F;
         op.i1[q] = op.i2[q] = op.i3[q] = 0;
-        done &= !act[q];
     }
-    scan_candidates<THREADS, kNnTile>(known + static_cast<size_t>(cloud) * m * 3, m, smem, op, done);
+    scan_candidates<THREADS, Q>(known + static_cast<size_t>(cloud) * m * 3, m, smem, op.qx, op.qy, op.qz, op);
 #pragma unroll
     for (int q = 0; q < Q; ++q)
     {
-        if (!act[q]) continue;
+        if (!op.act[q]) continue;
         const int j = qtile * (THREADS * Q) + q * THREADS + threadIdx.x;
         const size_t o = (static_cast<size_t>(cloud) * n + j) * 3;
         dist2[o + 0] = op.b1[q];
@@ -128,13 +107,22 @@ struct KnnOp
     float thr[Q];  // current k-th best (the admission threshold), +inf until the list is full
     int cnt[Q];
     bool act[Q];
-    float* ldist;  // + list id of q = 0; q-th list is at + q * (LISTS / Q)
+    float* ldist;  // list of q = 0 of this thread; the q-th list is at + q * (LISTS / Q)
     int* lidx;
     int k;
-    long long ncand;
 
-    __device__ __forceinline__ void insert(int q, float v, int cand)
+    __device__ __forceinline__ float threshold(int q) const { return act[q] ? thr[q] : -CUDART_INF_F; }
+    __device__ __forceinline__ bool finished() const
     {
+        bool done = true;
+#pragma unroll
+        for (int q = 0; q < Q; ++q) done &= !act[q];
+        return done;
+    }
+    __device__ __forceinline__ bool exact(int q, long long cand, float cx, float cy, float cz)
+    {
+        const float v = sumsq_unfused(qx[q] - cx, qy[q] - cy, qz[q] - cz);
+        if (!act[q] || !(v < thr[q])) return false;
         float* dl = ldist + q * (LISTS / Q);
         int* il = lidx + q * (LISTS / Q);
         int i = cnt[q] < k ? cnt[q] : k - 1;
@@ -144,34 +132,10 @@ struct KnnOp
             il[i * LISTS] = il[(i - 1) * LISTS];
         }
         dl[i * LISTS] = v;
-        il[i * LISTS] = cand;
+        il[i * LISTS] = static_cast<int>(cand);
         if (cnt[q] < k) ++cnt[q];
         if (cnt[q] == k) thr[q] = dl[(k - 1) * LISTS];
-    }
-
-    __device__ __forceinline__ bool group(long long k0, const float (&cx)[4], const float (&cy)[4],
-                                          const float (&cz)[4])
-    {
-        float d[Q][4];
-        bool any = false;
-#pragma unroll
-        for (int q = 0; q < Q; ++q)
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-            {
-                d[q][i] = sumsq_unfused(qx[q] - cx[i], qy[q] - cy[i], qz[q] - cz[i]);
-                any |= d[q][i] < thr[q];
-            }
-        if (any)
-        {
-#pragma unroll
-            for (int q = 0; q < Q; ++q)
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    if (act[q] && d[q][i] < thr[q] && k0 + i < ncand)
-                        insert(q, d[q][i], static_cast<int>(k0) + i);
-        }
-        return false;
+        return true;
     }
 };
 
@@ -197,17 +161,15 @@ __global__ void __launch_bounds__(THREADS)
 {
     extern __shared__ __align__(16) float dyn_smem[];
     float* tile = dyn_smem;
-    float* ldist = dyn_smem + 2 * 3 * kNnTile;
+    float* ldist = dyn_smem + 2 * kScanTileFloats;
     int* lidx = reinterpret_cast<int*>(ldist + static_cast<size_t>(k) * THREADS * Q);
     const int cloud = blockIdx.x / tiles_per_cloud;
     const int qtile = blockIdx.x - cloud * tiles_per_cloud;
 
     KnnOp<Q, THREADS * Q> op;
     op.k = k;
-    op.ncand = n;
     op.ldist = ldist + threadIdx.x;
     op.lidx = lidx + threadIdx.x;
-    bool done = true;
 #pragma unroll
     for (int q = 0; q < Q; ++q)
     {
@@ -219,9 +181,8 @@ __global__ void __launch_bounds__(THREADS)
         op.qz[q] = op.act[q] ? __ldg(query + row * 3 + 2) : 0.f;
         op.thr[q] = CUDART_INF_F;
         op.cnt[q] = 0;
-        done &= !op.act[q];
     }
-    scan_candidates<THREADS, kNnTile>(support + static_cast<size_t>(cloud) * n * 3, n, tile, op, done);
+    scan_candidates<THREADS, Q>(support + static_cast<size_t>(cloud) * n * 3, n, tile, op.qx, op.qy, op.qz, op);
 #pragma unroll
     for (int q = 0; q < Q; ++q)
     {
@@ -243,7 +204,7 @@ __global__ void __launch_bounds__(THREADS)
     __shared__ long long s_range[2];
     __shared__ unsigned long long s_next;
     float* tile = dyn_smem;
-    float* ldist = dyn_smem + 2 * 3 * kNnTile;
+    float* ldist = dyn_smem + 2 * kScanTileFloats;
     int* lidx = reinterpret_cast<int*>(ldist + static_cast<size_t>(k) * THREADS * Q);
 
     KnnOp<Q, THREADS * Q> op;
@@ -280,18 +241,15 @@ __global__ void __launch_bounds__(THREADS)
         }
         __syncthreads();
         const long long lo = s_range[0], hi = s_range[1];
-        bool done = true;
 #pragma unroll
         for (int q = 0; q < Q; ++q)
         {
             op.act[q] = valid[q] && seg[q] == cur;
             if (op.act[q]) base[q] = lo;
-            done &= !op.act[q];
             if (valid[q] && seg[q] > cur)
                 atomicMin(&s_next, static_cast<unsigned long long>(seg[q]));
         }
-        op.ncand = hi - lo;
-        scan_candidates<THREADS, kNnTile>(support + lo * 3, hi - lo, tile, op, done);
+        scan_candidates<THREADS, Q>(support + lo * 3, hi - lo, tile, op.qx, op.qy, op.qz, op);
         const unsigned long long nxt = s_next;
         __syncthreads();
         if (nxt == kNone) break;
@@ -306,17 +264,15 @@ __global__ void __launch_bounds__(THREADS)
     }
 }
 
-int pick_threads_nn(long long queries, int q_per_thread)
+void pick_shape_nn(long long queries, int* threads, int* q)
 {
-    const long long want = 6ll * num_sms();
-    if (queries / (128ll * q_per_thread) >= want) return 128;
-    if (queries / (64ll * q_per_thread) >= want) return 64;
-    return 32;
+    *q = queries >= 300000 ? 2 : 1;
+    *threads = queries >= 32768 ? 128 : 64;
 }
 
-size_t knn_smem_bytes(int threads, int k)
+size_t knn_smem_bytes(int threads, int q, int k)
 {
-    return sizeof(float) * 2 * 3 * kNnTile + static_cast<size_t>(k) * threads * kNnQ * 8;
+    return sizeof(float) * 2 * kScanTileFloats + static_cast<size_t>(k) * threads * q * 8;
 }
 
 template <class K>
@@ -346,19 +302,48 @@ extern "C" int tpk_three_nn(int b, int n, int m, const float* unknown, const flo
     if (b == 0 || n == 0) return TPK_OK;
     TPK_REQUIRE(unknown && dist2 && idx && (known || m == 0), "three_nn: NULL pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int threads = pick_threads_nn(static_cast<long long>(b) * n, kNnQ);
-    const int tiles = (n + threads * kNnQ - 1) / (threads * kNnQ);
+    int threads, q;
+    pick_shape_nn(static_cast<long long>(b) * n, &threads, &q);
+    const int tiles = (n + threads * q - 1) / (threads * q);
     const long long grid = static_cast<long long>(b) * tiles;
     TPK_REQUIRE(grid < (1ll << 31), "three_nn: too many queries");
     const dim3 g(static_cast<unsigned>(grid));
-    if (threads == 128)
-        three_nn_kernel<128, kNnQ><<<g, 128, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
-    else if (threads == 64)
-        three_nn_kernel<64, kNnQ><<<g, 64, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
+    if (threads == 128 && q == 2)
+        three_nn_kernel<128, 2><<<g, 128, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
+    else if (threads == 128)
+        three_nn_kernel<128, 1><<<g, 128, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
+    else if (q == 2)
+        three_nn_kernel<64, 2><<<g, 64, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
     else
-        three_nn_kernel<32, kNnQ><<<g, 32, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
+        three_nn_kernel<64, 1><<<g, 64, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
     return check_launch("three_nn");
 }
+
+#define TPK_KNN_DISPATCH(KERNEL, ...)                                                              \
+    do                                                                                             \
+    {                                                                                              \
+        int rc_;                                                                                   \
+        if (threads == 128 && q == 2)                                                              \
+        {                                                                                          \
+            if ((rc_ = set_smem(KERNEL<128, 2>, smem, "knn")) != TPK_OK) return rc_;               \
+            KERNEL<128, 2><<<g, 128, smem, s>>>(__VA_ARGS__);                                      \
+        }                                                                                          \
+        else if (threads == 128)                                                                   \
+        {                                                                                          \
+            if ((rc_ = set_smem(KERNEL<128, 1>, smem, "knn")) != TPK_OK) return rc_;               \
+            KERNEL<128, 1><<<g, 128, smem, s>>>(__VA_ARGS__);                                      \
+        }                                                                                          \
+        else if (q == 2)                                                                           \
+        {                                                                                          \
+            if ((rc_ = set_smem(KERNEL<64, 2>, smem, "knn")) != TPK_OK) return rc_;                \
+            KERNEL<64, 2><<<g, 64, smem, s>>>(__VA_ARGS__);                                        \
+        }                                                                                          \
+        else                                                                                       \
+        {                                                                                          \
+            if ((rc_ = set_smem(KERNEL<64, 1>, smem, "knn")) != TPK_OK) return rc_;                \
+            KERNEL<64, 1><<<g, 64, smem, s>>>(__VA_ARGS__);                                        \
+        }                                                                                          \
+    } while (0)
 
 extern "C" int tpk_knn_dense(int b, int n, int m, int k, const float* support, const float* query,
                              int64_t* idx, float* dist2, void* stream)
@@ -370,29 +355,16 @@ extern "C" int tpk_knn_dense(int b, int n, int m, int k, const float* support, c
     if (b == 0 || m == 0) return TPK_OK;
     TPK_REQUIRE(support && query && idx && dist2, "knn: NULL pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    int threads = pick_threads_nn(static_cast<long long>(b) * m, kNnQ);
+    int threads, q;
+    pick_shape_nn(static_cast<long long>(b) * m, &threads, &q);
+    if (k > 16) q = 1;
     if (k > 32 && threads > 64) threads = 64;
-    const size_t smem = knn_smem_bytes(threads, k);
-    const int tiles = (m + threads * kNnQ - 1) / (threads * kNnQ);
+    const size_t smem = knn_smem_bytes(threads, q, k);
+    const int tiles = (m + threads * q - 1) / (threads * q);
     const long long grid = static_cast<long long>(b) * tiles;
     TPK_REQUIRE(grid < (1ll << 31), "knn: too many queries");
     const dim3 g(static_cast<unsigned>(grid));
-    int rc;
-    if (threads == 128)
-    {
-        if ((rc = set_smem(knn_dense_kernel<128, kNnQ>, smem, "knn")) != TPK_OK) return rc;
-        knn_dense_kernel<128, kNnQ><<<g, 128, smem, s>>>(n, m, k, tiles, support, query, idx, dist2);
-    }
-    else if (threads == 64)
-    {
-        if ((rc = set_smem(knn_dense_kernel<64, kNnQ>, smem, "knn")) != TPK_OK) return rc;
-        knn_dense_kernel<64, kNnQ><<<g, 64, smem, s>>>(n, m, k, tiles, support, query, idx, dist2);
-    }
-    else
-    {
-        if ((rc = set_smem(knn_dense_kernel<32, kNnQ>, smem, "knn")) != TPK_OK) return rc;
-        knn_dense_kernel<32, kNnQ><<<g, 32, smem, s>>>(n, m, k, tiles, support, query, idx, dist2);
-    }
+    TPK_KNN_DISPATCH(knn_dense_kernel, n, m, k, tiles, support, query, idx, dist2);
     return check_launch("knn_dense");
 }
 
@@ -409,27 +381,14 @@ extern "C" int tpk_knn_partial_dense(int64_t size_s, int64_t size_q, int k, cons
                 "knn_partial_dense: NULL pointer");
     TPK_REQUIRE(size_s < (1ll << 31), "knn_partial_dense: support too large");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    int threads = pick_threads_nn(size_q, kNnQ);
+    int threads, q;
+    pick_shape_nn(size_q, &threads, &q);
+    if (k > 16) q = 1;
     if (k > 32 && threads > 64) threads = 64;
-    const size_t smem = knn_smem_bytes(threads, k);
-    const long long grid = (size_q + threads * kNnQ - 1) / (threads * kNnQ);
+    const size_t smem = knn_smem_bytes(threads, q, k);
+    const long long grid = (size_q + threads * q - 1) / (threads * q);
     TPK_REQUIRE(grid < (1ll << 31), "knn_partial_dense: too many queries");
     const dim3 g(static_cast<unsigned>(grid));
-    int rc;
-    if (threads == 128)
-    {
-        if ((rc = set_smem(knn_partial_kernel<128, kNnQ>, smem, "knn")) != TPK_OK) return rc;
-        knn_partial_kernel<128, kNnQ><<<g, 128, smem, s>>>(size_s, size_q, k, support, query, batch_s, batch_q, idx, dist2);
-    }
-    else if (threads == 64)
-    {
-        if ((rc = set_smem(knn_partial_kernel<64, kNnQ>, smem, "knn")) != TPK_OK) return rc;
-        knn_partial_kernel<64, kNnQ><<<g, 64, smem, s>>>(size_s, size_q, k, support, query, batch_s, batch_q, idx, dist2);
-    }
-    else
-    {
-        if ((rc = set_smem(knn_partial_kernel<32, kNnQ>, smem, "knn")) != TPK_OK) return rc;
-        knn_partial_kernel<32, kNnQ><<<g, 32, smem, s>>>(size_s, size_q, k, support, query, batch_s, batch_q, idx, dist2);
-    }
+    TPK_KNN_DISPATCH(knn_partial_kernel, size_s, size_q, k, support, query, batch_s, batch_q, idx, dist2);
     return check_launch("knn_partial_dense");
 }

@@ -1,123 +1,202 @@
 // Tile scan shared by the brute-force search kernels (ball query, three_nn, kNN, chamfer).
 //
-// A CTA owns THREADS*Q query points (Q per thread, held in registers) and streams the
-// candidate cloud through shared memory in tiles.  The candidate stream is the raw
-// (x,y,z) float triples exactly as they lie in global memory, copied with cp.async
-// into a double buffer, so the copy of tile t+1 overlaps the arithmetic on tile t.
-// Four consecutive candidates are three 16-byte shared-memory loads, every lane
-// reading the same address (a broadcast), which leaves the FP32 pipe as the only busy
-// unit: per (query, candidate) pair 3 subtractions, 1 multiply, 2 fused multiply-adds
-// and one compare.
+// A CTA owns THREADS*Q query points (Q per thread, in registers) and streams the
+// candidate cloud through shared memory in tiles of kScanTile points, double buffered:
+// while the CTA works on tile t, every thread already holds the raw coordinates of its
+// share of tile t+1 in registers (plain coalesced loads issued before the arithmetic).
 //
-// The per-op rule (radius test, top-3, top-k, arg-min) is a functor:
-//   bool op.group(long long k0, const float (&cx)[4], const float (&cy)[4], const float (&cz)[4])
-//        consumes candidates k0..k0+3 in index order (slots past the end of the range
-//        hold kFarAway coordinates); returns true when this thread needs no further
-//        candidates.
+// Two-level test per (query, candidate) pair:
+//   1. filter:  |c|^2 - 2 q.c  <=  T          three fused multiply-adds and one compare,
+//      evaluated two candidates at a time with the packed fma.rn.f32x2 of sm_100;
+//      |c|^2 (slightly shrunk) is computed once per candidate when the tile is staged,
+//      T = thr*(1+2^-17) - |q|^2*(1-2^-17) once per query (and again whenever the
+//      query's threshold thr changes).  The slack of 2^-17 = 128 ulp relative to
+//      |q|^2 + |c|^2 covers every rounding error of the expanded form, so a pair the exact
+//      test accepts always passes the filter; the filter only removes work.
+//   2. exact:   for the few pairs that pass, the op's own arithmetic, in the operation
+//      order of the reference (so distances and decisions are bit-identical).
+//
+// Shared-memory tile layout: blocks of four candidates as x[4] y[4] z[4] w[4] (64 B), so
+// a block is four 16-byte loads with the same address in every lane (broadcasts) and
+// register pairs (x0,x1), (x2,x3) ... feed the packed instructions directly.
+//
+// The per-op rule is a functor:
+//   float threshold(int q)            current admission threshold of query q (squared distance)
+//   bool  inclusive()                 true: d2 <= thr admits, false: d2 < thr
+//   bool  exact(int q, long long k, float cx, float cy, float cz)
+//                                     run the exact test on candidate k (k < ncand is
+//                                     guaranteed) and record it; return true if threshold(q) changed
+//   bool  finished()                  true when this thread needs no further candidates
 #pragma once
+
+#include <math_constants.h>
 
 #include "tpk_common.cuh"
 
 namespace tpk
 {
 
-// Padding coordinate for tile slots past the end of the candidate range: its squared
-// distance to any finite query overflows to +inf, which passes no test.
-constexpr float kFarAway = 1e30f;
+constexpr int kScanTile = 1024;
+constexpr int kScanTileFloats = 4 * kScanTile;
+constexpr float kFilterSlack = 7.62939453125e-06f;  // 2^-17
 
-__device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* gmem_src)
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi)
 {
-    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gmem_src) : "memory");
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait()
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi)
 {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
-
-template <int THREADS>
-__device__ __forceinline__ void cta_sync()
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b,
+                                                   unsigned long long c)
 {
-    if (THREADS == 32)
-        __syncwarp();
-    else
-        __syncthreads();
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
 }
 
-template <int THREADS>
-__device__ __forceinline__ bool cta_all(bool pred)
+// Filter threshold of a query with squared norm q2 and exact threshold thr.
+__device__ __forceinline__ float filter_threshold(float thr, float q2)
 {
-    if (THREADS == 32) return __all_sync(kFullMask, pred);
-    return __syncthreads_and(pred) != 0;
+    const float t = __fmaf_rn(thr, 1.0f + kFilterSlack, -__fmul_rn(q2, 1.0f - kFilterSlack));
+    // non-finite input: let everything through, the exact test decides
+    return (t == t && fabsf(q2) < CUDART_INF_F) ? t : CUDART_INF_F;
 }
 
-// smem: 2 * 3 * TILE floats, 16-byte aligned.  cand points at the first candidate of
-// the range (any 4-byte alignment), ncand may be 0.  All threads of the CTA must call.
-template <int THREADS, int TILE, class Op>
+// smem: 2 * kScanTileFloats floats, 16-byte aligned.  cand points at the first candidate
+// of the range (any 4-byte alignment), ncand may be 0.  All threads of the CTA must call.
+template <int THREADS, int Q, class Op>
 __device__ __forceinline__ void scan_candidates(const float* __restrict__ cand, long long ncand,
-                                                float* smem, Op& op, bool thread_done)
+                                                float* smem, const float (&qx)[Q],
+                                                const float (&qy)[Q], const float (&qz)[Q], Op& op)
 {
-    static_assert(TILE % 64 == 0, "tile must hold whole 64-candidate chunks");
-    constexpr int kTileFloats = 3 * TILE;
+    static_assert(kScanTile % THREADS == 0, "every thread stages the same number of candidates");
+    constexpr int PER = kScanTile / THREADS;  // candidates staged per thread per tile
     const int tid = threadIdx.x;
-    const long long ntiles = (ncand + TILE - 1) / TILE;
+    const long long ntiles = (ncand + kScanTile - 1) / kScanTile;
 
-    auto issue = [&](long long t) {
-        float* dst = smem + (t & 1) * kTileFloats;
-        const long long f0 = t * kTileFloats;
-        long long valid = ncand * 3 - f0;
-        if (valid > kTileFloats) valid = kTileFloats;
-        const float* src = cand + f0;
-#pragma unroll 4
-        for (int i = tid; i < kTileFloats; i += THREADS)
+    float raw[PER][3];
+    auto fetch = [&](long long t) {
+#pragma unroll
+        for (int i = 0; i < PER; ++i)
         {
-            if (i < valid)
-                cp_async_f32(dst + i, src + i);
-            else
-                dst[i] = kFarAway;
+            const long long k = t * kScanTile + i * THREADS + tid;
+            const bool ok = k < ncand;
+            raw[i][0] = ok ? __ldg(cand + 3 * k + 0) : 0.f;
+            raw[i][1] = ok ? __ldg(cand + 3 * k + 1) : 0.f;
+            raw[i][2] = ok ? __ldg(cand + 3 * k + 2) : 0.f;
         }
-        cp_async_commit();
+    };
+    auto stage = [&](long long t) {
+        float* dst = smem + (t & 1) * kScanTileFloats;
+#pragma unroll
+        for (int i = 0; i < PER; ++i)
+        {
+            const int j = i * THREADS + tid;  // position in the tile
+            const bool ok = t * kScanTile + j < ncand;
+            const float x = raw[i][0], y = raw[i][1], z = raw[i][2];
+            float w = __fmaf_rn(z, z, __fmaf_rn(y, y, __fmul_rn(x, x)));
+            w = __fmul_rn(w, 1.0f - kFilterSlack);
+            // slots past the end never pass (+inf); non-finite norms always pass (-inf)
+            w = ok ? ((w == w && w < CUDART_INF_F) ? w : -CUDART_INF_F) : CUDART_INF_F;
+            float* b = dst + (j >> 2) * 16 + (j & 3);
+            b[0] = x;
+            b[4] = y;
+            b[8] = z;
+            b[12] = w;
+        }
     };
 
-    if (ntiles > 0) issue(0);
+    // per-query filter constants
+    unsigned long long m2x[Q], m2y[Q], m2z[Q];
+    float q2[Q], T[Q];
+#pragma unroll
+    for (int q = 0; q < Q; ++q)
+    {
+        m2x[q] = pack2(-2.0f * qx[q], -2.0f * qx[q]);
+        m2y[q] = pack2(-2.0f * qy[q], -2.0f * qy[q]);
+        m2z[q] = pack2(-2.0f * qz[q], -2.0f * qz[q]);
+        q2[q] = __fmaf_rn(qz[q], qz[q], __fmaf_rn(qy[q], qy[q], __fmul_rn(qx[q], qx[q])));
+        T[q] = filter_threshold(op.threshold(q), q2[q]);
+    }
+
+    if (ntiles > 0)
+    {
+        fetch(0);
+        stage(0);
+    }
+    __syncthreads();
     for (long long t = 0; t < ntiles; ++t)
     {
-        if (t + 1 < ntiles)
-        {
-            issue(t + 1);
-            cp_async_wait<1>();
-        }
-        else
-        {
-            cp_async_wait<0>();
-        }
-        cta_sync<THREADS>();
+        const bool more = t + 1 < ntiles;
+        if (more) fetch(t + 1);
 
-        const float4* s4 = reinterpret_cast<const float4*>(smem + (t & 1) * kTileFloats);
-        const long long kbase = t * TILE;
-        for (int chunk = 0; chunk < TILE / 64; ++chunk)
+        const float4* s4 = reinterpret_cast<const float4*>(smem + (t & 1) * kScanTileFloats);
+        const long long kbase = t * kScanTile;
+        bool done = op.finished();
+        for (int chunk = 0; chunk < kScanTile / 64; ++chunk)
         {
-            if (__all_sync(kFullMask, thread_done)) break;
-#pragma unroll 4
+            if (__all_sync(kFullMask, done)) break;
+#pragma unroll 2
             for (int g = chunk * 16; g < chunk * 16 + 16; ++g)
             {
-                const float4 a = s4[3 * g + 0];
-                const float4 b = s4[3 * g + 1];
-                const float4 c = s4[3 * g + 2];
-                const float cx[4] = {a.x, a.w, b.z, c.y};
-                const float cy[4] = {a.y, b.x, b.w, c.z};
-                const float cz[4] = {a.z, b.y, c.x, c.w};
-                if (op.group(kbase + 4 * g, cx, cy, cz)) thread_done = true;
+                const float4 X = s4[4 * g + 0];
+                const float4 Y = s4[4 * g + 1];
+                const float4 Z = s4[4 * g + 2];
+                const float4 W = s4[4 * g + 3];
+                const unsigned long long x01 = pack2(X.x, X.y), x23 = pack2(X.z, X.w);
+                const unsigned long long y01 = pack2(Y.x, Y.y), y23 = pack2(Y.z, Y.w);
+                const unsigned long long z01 = pack2(Z.x, Z.y), z23 = pack2(Z.z, Z.w);
+                const unsigned long long w01 = pack2(W.x, W.y), w23 = pack2(W.z, W.w);
+                float a[Q][4];
+                bool any = false;
+#pragma unroll
+                for (int q = 0; q < Q; ++q)
+                {
+                    const unsigned long long a01 = fma2(m2x[q], x01, fma2(m2y[q], y01, fma2(m2z[q], z01, w01)));
+                    const unsigned long long a23 = fma2(m2x[q], x23, fma2(m2y[q], y23, fma2(m2z[q], z23, w23)));
+                    unpack2(a01, a[q][0], a[q][1]);
+                    unpack2(a23, a[q][2], a[q][3]);
+                    any |= (a[q][0] <= T[q]) | (a[q][1] <= T[q]) | (a[q][2] <= T[q]) | (a[q][3] <= T[q]);
+                }
+                // warp-uniform branch: every lane enters, so the votes inside are convergent
+                if (__any_sync(kFullMask, any))
+                {
+                    const float cx[4] = {X.x, X.y, X.z, X.w};
+                    const float cy[4] = {Y.x, Y.y, Y.z, Y.w};
+                    const float cz[4] = {Z.x, Z.y, Z.z, Z.w};
+                    // candidates in index order; a candidate no lane of the warp lets
+                    // through is skipped with one vote
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                    {
+                        bool pass = false;
+#pragma unroll
+                        for (int q = 0; q < Q; ++q) pass |= a[q][i] <= T[q];
+                        if (!__any_sync(kFullMask, pass)) continue;
+                        const long long k = kbase + 4 * g + i;
+#pragma unroll
+                        for (int q = 0; q < Q; ++q)
+                        {
+                            if (a[q][i] <= T[q] && k < ncand)
+                            {
+                                if (op.exact(q, k, cx[i], cy[i], cz[i]))
+                                    T[q] = filter_threshold(op.threshold(q), q2[q]);
+                            }
+                        }
+                    }
+                    done = op.finished();
+                }
             }
         }
-        // also keeps the buffer just read from being overwritten by the copy of tile t+2
-        if (cta_all<THREADS>(thread_done)) break;
+        if (more) stage(t + 1);
+        // one barrier per tile: it publishes tile t+1 and retires tile t, whose buffer is
+        // only written again while staging tile t+2, after the next barrier
+        if (__syncthreads_and(done)) break;
     }
-    // an early exit can leave the copy of the next tile in flight
-    cp_async_wait<0>();
-    cta_sync<THREADS>();
 }
 
 // First position in sorted ids[0..n) whose value is >= v (upper = false) or > v (upper = true).

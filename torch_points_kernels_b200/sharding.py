@@ -1,0 +1,64 @@
+"""Batch sharding of the path across the GPUs of one node.
+
+Every op on the path is independent per cloud (dense layout), per segment (packed
+layout) or per pair (chamfer), so ranks take contiguous blocks of clouds and no kernel
+needs a collective.  The only exchange is the scalar chamfer loss: two partial sums and
+two counts per rank, all-reduced with torch.distributed (NCCL on GPUs, gloo in the CPU
+tests).  The reference has no multi-device code at all.
+"""
+import torch
+import torch.distributed as dist
+
+
+def shard_range(n_items, rank, world_size):
+    """[lo, hi) of the contiguous block of items rank owns; blocks differ by at most one."""
+    base, extra = divmod(int(n_items), int(world_size))
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def balanced_blocks(costs, world_size):
+    """Contiguous partition of segments into world_size blocks with near-equal total cost
+    (cost of a packed segment = support points x query points for the brute-force search).
+    Returns world_size + 1 boundaries.  Greedy on the prefix sum."""
+    costs = [float(c) for c in costs]
+    total = sum(costs)
+    bounds = [0]
+    acc = 0.0
+    for i, c in enumerate(costs):
+        remaining_blocks = world_size - len(bounds)
+        if remaining_blocks == 0:
+            break
+        target = total * len(bounds) / world_size
+        # close the block before item i if that lands nearer the target than after it
+        if acc > 0 and abs(acc - target) <= abs(acc + c - target) and len(costs) - i >= remaining_blocks:
+            bounds.append(i)
+        acc += c
+    while len(bounds) < world_size:
+        bounds.append(len(costs))
+    bounds.append(len(costs))
+    return bounds
+
+
+def reduce_chamfer_loss(sum1, count1, sum2, count2, group=None):
+    """mean(dist1) + mean(dist2) over the clouds of ALL ranks from per-rank partial sums.
+
+    sum1/sum2: 0-dim tensors (sum of this rank's dist1 / dist2 entries), count1/count2:
+    number of entries behind them.  Matches the reference's single-device
+    ``torch.mean(dist1) + torch.mean(dist2)`` (chamfer_dist.py:54) on the concatenated batch.
+    """
+    buf = torch.stack([sum1.double(), sum2.double(),
+                       torch.as_tensor(float(count1), dtype=torch.float64, device=sum1.device),
+                       torch.as_tensor(float(count2), dtype=torch.float64, device=sum1.device)])
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
+    return (buf[0] / buf[2] + buf[1] / buf[3]).to(sum1.dtype)
+
+
+def chamfer_dist_sharded(xyz1, xyz2, group=None):
+    """Chamfer loss of a batch whose pairs are spread over the ranks of `group`: every
+    rank passes its own pairs, all ranks get the loss of the whole batch."""
+    from .chamfer_dist import ChamferFunction
+
+    dist1, dist2 = ChamferFunction.apply(xyz1, xyz2)
+    return reduce_chamfer_loss(dist1.sum(), dist1.numel(), dist2.sum(), dist2.numel(), group)
