@@ -46,9 +46,13 @@ __device__ __forceinline__ unsigned long long pack2(float lo, float hi)
     asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
     return r;
 }
-__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi)
+__device__ __forceinline__ float lo_f32(unsigned long long v)
 {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+    return __uint_as_float(static_cast<uint32_t>(v));
+}
+__device__ __forceinline__ float hi_f32(unsigned long long v)
+{
+    return __uint_as_float(static_cast<uint32_t>(v >> 32));
 }
 __device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b,
                                                    unsigned long long c)
@@ -134,7 +138,8 @@ __device__ __forceinline__ void scan_candidates(const float* __restrict__ cand, 
         const bool more = t + 1 < ntiles;
         if (more) fetch(t + 1);
 
-        const float4* s4 = reinterpret_cast<const float4*>(smem + (t & 1) * kScanTileFloats);
+        // each 16-byte load yields two packed candidate pairs, ready for fma.rn.f32x2
+        const ulonglong2* s2 = reinterpret_cast<const ulonglong2*>(smem + (t & 1) * kScanTileFloats);
         const long long kbase = t * kScanTile;
         bool done = op.finished();
         for (int chunk = 0; chunk < kScanTile / 64; ++chunk)
@@ -143,31 +148,29 @@ __device__ __forceinline__ void scan_candidates(const float* __restrict__ cand, 
 #pragma unroll 2
             for (int g = chunk * 16; g < chunk * 16 + 16; ++g)
             {
-                const float4 X = s4[4 * g + 0];
-                const float4 Y = s4[4 * g + 1];
-                const float4 Z = s4[4 * g + 2];
-                const float4 W = s4[4 * g + 3];
-                const unsigned long long x01 = pack2(X.x, X.y), x23 = pack2(X.z, X.w);
-                const unsigned long long y01 = pack2(Y.x, Y.y), y23 = pack2(Y.z, Y.w);
-                const unsigned long long z01 = pack2(Z.x, Z.y), z23 = pack2(Z.z, Z.w);
-                const unsigned long long w01 = pack2(W.x, W.y), w23 = pack2(W.z, W.w);
+                const ulonglong2 X = s2[4 * g + 0];
+                const ulonglong2 Y = s2[4 * g + 1];
+                const ulonglong2 Z = s2[4 * g + 2];
+                const ulonglong2 W = s2[4 * g + 3];
                 float a[Q][4];
                 bool any = false;
 #pragma unroll
                 for (int q = 0; q < Q; ++q)
                 {
-                    const unsigned long long a01 = fma2(m2x[q], x01, fma2(m2y[q], y01, fma2(m2z[q], z01, w01)));
-                    const unsigned long long a23 = fma2(m2x[q], x23, fma2(m2y[q], y23, fma2(m2z[q], z23, w23)));
-                    unpack2(a01, a[q][0], a[q][1]);
-                    unpack2(a23, a[q][2], a[q][3]);
+                    const unsigned long long a01 = fma2(m2x[q], X.x, fma2(m2y[q], Y.x, fma2(m2z[q], Z.x, W.x)));
+                    const unsigned long long a23 = fma2(m2x[q], X.y, fma2(m2y[q], Y.y, fma2(m2z[q], Z.y, W.y)));
+                    a[q][0] = lo_f32(a01);
+                    a[q][1] = hi_f32(a01);
+                    a[q][2] = lo_f32(a23);
+                    a[q][3] = hi_f32(a23);
                     any |= (a[q][0] <= T[q]) | (a[q][1] <= T[q]) | (a[q][2] <= T[q]) | (a[q][3] <= T[q]);
                 }
                 // warp-uniform branch: every lane enters, so the votes inside are convergent
                 if (__any_sync(kFullMask, any))
                 {
-                    const float cx[4] = {X.x, X.y, X.z, X.w};
-                    const float cy[4] = {Y.x, Y.y, Y.z, Y.w};
-                    const float cz[4] = {Z.x, Z.y, Z.z, Z.w};
+                    const float cx[4] = {lo_f32(X.x), hi_f32(X.x), lo_f32(X.y), hi_f32(X.y)};
+                    const float cy[4] = {lo_f32(Y.x), hi_f32(Y.x), lo_f32(Y.y), hi_f32(Y.y)};
+                    const float cz[4] = {lo_f32(Z.x), hi_f32(Z.x), lo_f32(Z.y), hi_f32(Z.y)};
                     // candidates in index order; a candidate no lane of the warp lets
                     // through is skipped with one vote
 #pragma unroll
