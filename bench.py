@@ -48,10 +48,16 @@ def make_inputs(B, N, seed):
 # ------------------------------------------------------------------ B200 arm: the pipeline
 
 class Pipeline:
-    """SA + FP stack on one GPU.  FPS is a chain of latency-bound launches that occupy at
-    most 128 of the 148 SMs, so it runs on its own stream; everything that only needs a
-    level's centres (ball query, grouping, three_nn, interpolation, the backward passes)
-    is enqueued on a second stream behind an event and overlaps the next level's FPS."""
+    """SA + FP stack on one GPU, three streams:
+      s_fps  : the FPS chain (latency-bound launches on at most 128 of the 148 SMs) and the
+               gathers of the sampled centres;
+      s_geo  : everything else that only needs coordinates (ball query, three_nn, weights),
+               level by level behind the FPS events;
+      s_feat : the feature work (grouping and interpolation, forward and backward) behind
+               the s_geo events.
+    With pipelined=True consecutive steps are not joined: the geometry of step i+1 (which
+    depends on nothing but its input coordinates) runs while the feature work of step i is
+    still in flight, as it would behind a prefetching data loader."""
 
     def __init__(self, dev, B, N, seed):
         import torch_points_kernels_b200 as tpk
@@ -59,8 +65,14 @@ class Pipeline:
         self.tpk = tpk
         self.dev = dev
         self.B, self.N = B, N
-        self.s_fps = torch.cuda.Stream(dev)
-        self.s_main = torch.cuda.Stream(dev)
+        # two FPS streams, used by alternate steps: the chain is latency-bound and leaves the SMs
+        # mostly idle, so the chains of two consecutive steps can run side by side
+        self.s_fps_pair = [torch.cuda.Stream(dev), torch.cuda.Stream(dev)]
+        self.s_fps = self.s_fps_pair[0]
+        self.nstep = 0
+        self.s_geo = torch.cuda.Stream(dev)
+        self.s_feat = torch.cuda.Stream(dev)
+        self.s_copy = torch.cuda.Stream(dev)
         g = torch.Generator(device=dev).manual_seed(seed + 7)
         # upstream gradients: produced on the device by the layers above in a real model
         n_in = [N] + LEVELS["npoint"][:-1]
@@ -69,16 +81,25 @@ class Pipeline:
         self.g_up = [torch.randn(B, c, n, device=dev, generator=g) for c, n in zip(LEVELS["channels"], n_in)]
         self.launches = 0
 
-    def step(self, xyz, sa_feat, fp_feat, overlap=True, timers=None):
+    def step(self, xyz, sa_feat, fp_feat, overlap=True, timers=None, pipelined=False, ready=None):
         """xyz (B,N,3), sa_feat[l] (B,C_l,N_l), fp_feat[l] (B,C_l,M_l) on the device.
-        Returns (fps indices of every level, gradients of all features)."""
+        Returns (fps indices of every level, gradients of the SA features, of the FP
+        features, event recorded when the step's last kernel has been enqueued).
+        `ready`: event after which the inputs may be read (pipelined mode)."""
         tpk = self.tpk
         cur = torch.cuda.current_stream(self.dev)
+        self.s_fps = self.s_fps_pair[self.nstep & 1] if pipelined else self.s_fps_pair[0]
+        self.nstep += 1
         s_fps = self.s_fps if overlap else cur
-        s_main = self.s_main if overlap else cur
+        s_geo = self.s_geo if overlap else cur
+        s_feat = self.s_feat if overlap else cur
         if overlap:
-            s_fps.wait_stream(cur)
-            s_main.wait_stream(cur)
+            for st in (s_fps, s_geo, s_feat):
+                if pipelined:
+                    if ready is not None:
+                        st.wait_event(ready)
+                else:
+                    st.wait_stream(cur)
 
         def timed(name, fn):
             if timers is None:
@@ -90,46 +111,68 @@ class Pipeline:
             timers.setdefault(name, []).append((e0, e1))
             return out
 
+        def hand_over(t, *streams):
+            # the caching allocator must not recycle t while another stream still reads it
+            if overlap:
+                for st in streams:
+                    t.record_stream(st)
+            return t
+
         pts = [xyz]
-        fps_idx, ready = [], []
+        fps_idx, fps_ready = [], []
         with torch.cuda.stream(s_fps):
             for l, m in enumerate(LEVELS["npoint"]):
                 idx = timed("fps_l%d" % (l + 1), lambda: tpk.furthest_point_sample(pts[l], m))
                 centres = torch.gather(pts[l], 1, idx.long().unsqueeze(-1).expand(-1, -1, 3)).contiguous()
-                fps_idx.append(idx)
-                pts.append(centres)
+                fps_idx.append(hand_over(idx, cur))
+                pts.append(hand_over(centres, s_geo))
                 ev = torch.cuda.Event()
                 ev.record(s_fps)
-                ready.append(ev)
+                fps_ready.append(ev)
         self.launches += 4
 
-        grads_sa, grads_fp = [], []
-        with torch.cuda.stream(s_main):
+        geo, geo_ready = [], []
+        with torch.cuda.stream(s_geo):
             for l in range(4):
                 if overlap:
-                    s_main.wait_event(ready[l])
+                    s_geo.wait_event(fps_ready[l])
                 r, ns = LEVELS["radius"][l], LEVELS["nsample"]
                 nbr, _ = timed("ball_query_l%d" % (l + 1),
                                lambda: tpk.ball_query(r, ns, pts[l], pts[l + 1], mode="dense"))
-                f = sa_feat[l].requires_grad_(True)
-                grouped = timed("grouping_fwd_l%d" % (l + 1), lambda: tpk.grouping_operation(f, nbr))
-                timed("grouping_bwd_l%d" % (l + 1), lambda: grouped.backward(self.g_grouped[l]))
-                grads_sa.append(f.grad)
-                f.grad = None
                 # feature propagation of this level: from its centres back to its input points
                 dist, idx3 = timed("three_nn_l%d" % (l + 1), lambda: tpk.three_nn(pts[l], pts[l + 1]))
                 w = 1.0 / (dist + 1e-8)
                 w = (w / w.sum(dim=2, keepdim=True)).contiguous()
+                geo.append((hand_over(nbr, s_feat), hand_over(idx3, s_feat), hand_over(w, s_feat)))
+                ev = torch.cuda.Event()
+                ev.record(s_geo)
+                geo_ready.append(ev)
+                self.launches += 2
+
+        grads_sa, grads_fp = [], []
+        with torch.cuda.stream(s_feat):
+            for l in range(4):
+                if overlap:
+                    s_feat.wait_event(geo_ready[l])
+                nbr, idx3, w = geo[l]
+                f = sa_feat[l].requires_grad_(True)
+                grouped = timed("grouping_fwd_l%d" % (l + 1), lambda: tpk.grouping_operation(f, nbr))
+                timed("grouping_bwd_l%d" % (l + 1), lambda: grouped.backward(self.g_grouped[l]))
+                grads_sa.append(hand_over(f.grad, cur))
+                f.grad = None
                 ff = fp_feat[l].requires_grad_(True)
                 up = timed("interp_fwd_l%d" % (l + 1), lambda: tpk.three_interpolate(ff, idx3, w))
                 timed("interp_bwd_l%d" % (l + 1), lambda: up.backward(self.g_up[l]))
-                grads_fp.append(ff.grad)
+                grads_fp.append(hand_over(ff.grad, cur))
                 ff.grad = None
-                self.launches += 6
-        if overlap:
+                self.launches += 4
+            done = torch.cuda.Event()
+            done.record(s_feat)
+        if overlap and not pipelined:
             cur.wait_stream(s_fps)
-            cur.wait_stream(s_main)
-        return fps_idx, grads_sa, grads_fp
+            cur.wait_stream(s_geo)
+            cur.wait_stream(s_feat)
+        return fps_idx, grads_sa, grads_fp, done
 
 
 def pipeline_work(B, N):
@@ -228,8 +271,29 @@ def run_b200(args, rank, world, local_rank):
         return float(t.item())
 
     # ---- device-resident timing (inputs already in HBM); > 1 GB moves per step, far beyond L2
-    for _ in range(args.warmup):
-        pipe.step(*split([t.detach() for t in dev_in]))
+    cur = torch.cuda.current_stream(dev)
+
+    def run_resident(k, pipelined):
+        """k steps; pipelined: at most three steps in flight (bounds memory held by the
+        allocator for cross-stream tensors), one join at the end."""
+        dones = []
+        host = 0.0
+        for i in range(k):
+            if pipelined and i >= 3:
+                dones[i - 3].synchronize()
+            t0 = time.perf_counter()
+            out = pipe.step(*split([t.detach() for t in dev_in]), pipelined=pipelined)
+            host += time.perf_counter() - t0
+            dones.append(out[3])
+        pipe.host_ms = host * 1e3 / max(k, 1)
+        if pipelined:
+            for st in pipe.s_fps_pair:
+                cur.wait_stream(st)
+            cur.wait_stream(pipe.s_geo)
+            cur.wait_stream(pipe.s_feat)
+
+    run_resident(args.warmup, True)
+    torch.cuda.synchronize(dev)
     stop = threading.Event()
     clock_file = os.path.join(tempfile.gettempdir(), "tpk_clocks_%d.csv" % rank)
     sampler = threading.Thread(target=sample_clocks, args=(stop, clock_file, local_rank), daemon=True)
@@ -240,27 +304,64 @@ def run_b200(args, rank, world, local_rank):
     pipe.launches = 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        pipe.step(*split([t.detach() for t in dev_in]))
+    run_resident(args.steps, True)
     e1.record()
     barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     launches = pipe.launches
+    host_ms = pipe.host_ms
 
-    # ---- end to end: pinned host inputs copied in, result (indices + gradient checksums) read back
-    def e2e_step():
-        ins = [p.to(dev, non_blocking=True) for p in pinned]
-        fps_idx, g_sa, g_fp = pipe.step(*split(ins))
-        chk = torch.stack([g.sum() for g in g_sa + g_fp])
-        out = [i.cpu() for i in fps_idx] + [chk.cpu()]
-        return out
-
-    for _ in range(max(1, args.warmup // 2)):
-        e2e_step()
+    # the same without overlap between consecutive steps (latency of one isolated step)
     barrier()
     e0.record()
-    for _ in range(args.steps):
-        res = e2e_step()
+    run_resident(args.steps, False)
+    e1.record()
+    barrier()
+    ms_isolated = max_over_ranks(e0.elapsed_time(e1))
+
+    # ---- end to end: pinned host inputs copied in on a copy stream, results (sampled indices
+    # and one checksum per gradient tensor) copied out to pinned host buffers, every step
+    out_bufs = [[torch.empty((B, m), dtype=torch.int32).pin_memory() for m in LEVELS["npoint"]] +
+                [torch.empty((8,), dtype=torch.float32).pin_memory()] for _ in range(3)]
+
+    def run_e2e(k):
+        dones = []
+        for i in range(k):
+            if i >= 3:
+                dones[i - 3].synchronize()
+            with torch.cuda.stream(pipe.s_copy):
+                ins = [p.to(dev, non_blocking=True) for p in pinned]
+                ready = torch.cuda.Event()
+                ready.record(pipe.s_copy)
+            for st in pipe.s_fps_pair:
+                ins[0].record_stream(st)
+            ins[0].record_stream(pipe.s_geo)
+            for t in ins[1:]:
+                t.record_stream(pipe.s_feat)
+            fps_idx, g_sa, g_fp, _ = pipe.step(*split(ins), pipelined=True, ready=ready)
+            bufs = out_bufs[i % 3]
+            with torch.cuda.stream(pipe.s_feat):
+                for ev_src, dst in zip(fps_idx, bufs[:4]):
+                    ev_src.record_stream(pipe.s_feat)
+                pipe.s_feat.wait_stream(pipe.s_fps)
+                for src, dst in zip(fps_idx, bufs[:4]):
+                    dst.copy_(src, non_blocking=True)
+                chk = torch.stack([g.sum() for g in g_sa + g_fp])
+                bufs[4].copy_(chk, non_blocking=True)
+                done = torch.cuda.Event()
+                done.record(pipe.s_feat)
+            dones.append(done)
+        cur.wait_stream(pipe.s_copy)
+        for st in pipe.s_fps_pair:
+            cur.wait_stream(st)
+        cur.wait_stream(pipe.s_geo)
+        cur.wait_stream(pipe.s_feat)
+        return out_bufs[(k - 1) % 3]
+
+    run_e2e(max(2, args.warmup // 2))
+    barrier()
+    e0.record()
+    res = run_e2e(args.steps)
     e1.record()
     barrier()
     ms_e2e = max_over_ranks(e0.elapsed_time(e1))
@@ -304,15 +405,20 @@ def run_b200(args, rank, world, local_rank):
     line = {
         "metric": METRIC, "value": round(clouds * args.steps / (ms_total * 1e-3), 2), "unit": "clouds/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms_total / args.steps, 4), "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": round(ms_total / args.steps, 4),
+        "ms_per_step_isolated": round(ms_isolated / args.steps, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "pointnet2_ssg_sa_fp_stack fwd+bwd, B=16 clouds x N=16384 per GPU, "
                                "npoint 4096/1024/256/64, radius 0.1/0.2/0.4/0.8, nsample 32, C 64/128/256/512",
                    "clouds_per_gpu": B, "points_per_cloud": N, "parallelism": "batch-sharded x%d" % world,
-                   "l2": "each step moves > 1 GB (inputs larger than L2), no explicit flush"},
+                   "l2": "each step moves > 1 GB (inputs larger than L2), no explicit flush",
+                   "steps_in_flight": "up to 3: the geometry kernels of a step (FPS, ball query, three_nn; they "
+                                      "depend on its coordinates only) overlap the feature kernels of the step "
+                                      "before; ms_per_step_isolated is the same step with a join after every step"},
         "e2e": {"value": round(clouds * args.steps / (ms_e2e * 1e-3), 2), "unit": "clouds/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(ms_e2e / args.steps, 4)},
         "gpu_launches": launches,
+        "host_enqueue_ms_per_step": round(host_ms, 3),
         "clocks": clocks,
         "roofline": roof,
         "kernels": kernels,
