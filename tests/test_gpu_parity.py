@@ -92,6 +92,33 @@ def test_fps_tie_break_and_skip_rule(n, fps_env):
         np.testing.assert_array_equal(npy(tpk.furthest_point_sample(cu(pts), m)), want)
 
 
+@pytest.mark.parametrize("B,N,m", [(2, 200000, 48), (3, 140000, 33)])
+def test_fps_large_clouds_use_scratch(B, N, m):
+    """Clouds beyond the on-chip capacity: running minimum in global scratch."""
+    assert _lib.lib().tpk_fps_scratch_bytes(B, N, m) == B * N * 4
+    x = data.gaussian_mixture(B, N, seed=5000 + N)
+    got = npy(tpk.furthest_point_sample(cu(x), m))
+    np.testing.assert_array_equal(got, orc.fps(x, m))
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("n", [3, 37, 700, 5000, 20000])
+def test_fps_scratch_kernel_tie_break_and_skip_rule(n, monkeypatch):
+    monkeypatch.setenv("TPK_FPS_FORCE_GLOBAL", "1")
+    rng = np.random.default_rng(n)
+    pts = np.zeros((2, n, 3), np.float32)
+    pts[:, 0] = (1.0, 1.0, 1.0)
+    pts[:, 1:] = (1.0, 1.0, 1.5)
+    far = rng.choice(np.arange(1, n), size=max(1, (n - 1) // 2), replace=False)
+    pts[0, far] = (5.0, 1.0, 1.0)
+    pts[1, 1:] = rng.integers(0, 3, size=(n - 1, 3)).astype(np.float32)
+    m = min(n, 12)
+    np.testing.assert_array_equal(npy(tpk.furthest_point_sample(cu(pts), m)), orc.fps(pts, m))
+    x = data.unit_ball(2, n, seed=n)
+    mm = min(n, 200)
+    np.testing.assert_array_equal(npy(tpk.furthest_point_sample(cu(x), mm)), orc.fps(x, mm))
+
+
 def test_fps_all_points_skipped():
     tiny = np.full((2, 40, 3), 0.001, np.float32)
     assert npy(tpk.furthest_point_sample(cu(tiny), 7)).tolist() == [[0] * 7] * 2

@@ -391,6 +391,211 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
     if (CLUSTERED) cluster_sync_all();
 }
 
+// ---------------------------------------------------------------- large clouds
+//
+// Clouds too large for the register-resident kernel: one 16-CTA cluster of 512-thread
+// CTAs per cloud; the running minimum lives in caller-provided global scratch (n floats
+// per cloud, the reference's `temp`), coordinates are re-read every round (they stay in
+// L2 for the clouds a B200 runs at once).  Thread g of the cluster owns points
+// g, g + 8192, g + 16384, ...: all share (k mod bs), so the first maximum a thread meets
+// is also the one the tie rule prefers.  The per-round exchange is the same three-stage
+// arg-max as in the on-chip kernel.
+constexpr int kFpsBigRanks = 16;
+constexpr int kFpsBigThreads = 512;
+
+__global__ void __launch_bounds__(kFpsBigThreads, 1)
+    fps_global_kernel(int n, int m, int log2bs, const float* __restrict__ xyz_all,
+                      float* __restrict__ temp_all, int32_t* __restrict__ idxs_all)
+{
+    __shared__ __align__(16) uint4 wmsg_a[64];
+    __shared__ __align__(16) uint4 cmsg_a[64];
+    __shared__ float wmsg_z[64];
+    __shared__ float cmsg_z[64];
+    __shared__ __align__(8) uint64_t mbar[2];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nwarps = kFpsBigThreads / 32;
+    const int nranks = static_cast<int>(cluster_nctarank());
+    const int rank = static_cast<int>(cluster_ctarank());
+    const int cloud = blockIdx.x / nranks;
+    const int total = nranks * kFpsBigThreads;
+    const int gtid = rank * kFpsBigThreads + tid;
+
+    const float* xyz = xyz_all + static_cast<size_t>(cloud) * n * 3;
+    float* temp = temp_all + static_cast<size_t>(cloud) * n;
+    int32_t* idxs = idxs_all + static_cast<size_t>(cloud) * m;
+
+    // running minimum: 1e10, or negative for points that are never candidates
+    for (int k = gtid; k < n; k += total)
+    {
+        const float x = __ldg(xyz + 3 * static_cast<size_t>(k) + 0);
+        const float y = __ldg(xyz + 3 * static_cast<size_t>(k) + 1);
+        const float z = __ldg(xyz + 3 * static_cast<size_t>(k) + 2);
+        const float mag = sumsq_abc(x, y, z);
+        temp[k] = (static_cast<double>(mag) <= 1e-3) ? -1.0f : 1e10f;
+    }
+
+    float cx = __ldg(xyz + 0), cy = __ldg(xyz + 1), cz = __ldg(xyz + 2);
+    if (gtid == 0 && m > 0) idxs[0] = 0;
+    if (tid == 0)
+    {
+        mbar_init(smem_u32(mbar + 0), 1);
+        mbar_init(smem_u32(mbar + 1), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    cluster_sync_all();
+
+    uint32_t rem_a[2] = {0, 0}, rem_z[2] = {0, 0}, rem_bar[2] = {0, 0};
+    if (warp == 0 && lane < nranks)
+    {
+#pragma unroll
+        for (int par = 0; par < 2; ++par)
+        {
+            rem_a[par] = mapa_cluster(smem_u32(cmsg_a + par * 32 + rank), lane);
+            rem_z[par] = mapa_cluster(smem_u32(cmsg_z + par * 32 + rank), lane);
+            rem_bar[par] = mapa_cluster(smem_u32(mbar + par), lane);
+        }
+    }
+    bool failed = false;
+
+    for (int j = 1; j < m; ++j)
+    {
+        const int par = j & 1;
+        if (tid == 0)
+            mbar_arrive_expect_tx(smem_u32(mbar + par), static_cast<uint32_t>(nranks * kMsgBytes));
+
+        // ---- this thread's points: update the running minimum, keep the first maximum
+        float best = -1.0f, bx = 0.f, by = 0.f, bz = 0.f;
+        int bk = 0;
+#pragma unroll 4
+        for (int k = gtid; k < n; k += total)
+        {
+            const float x = __ldg(xyz + 3 * static_cast<size_t>(k) + 0);
+            const float y = __ldg(xyz + 3 * static_cast<size_t>(k) + 1);
+            const float z = __ldg(xyz + 3 * static_cast<size_t>(k) + 2);
+            const float d = fminf(sumsq_abc(x - cx, y - cy, z - cz), temp[k]);
+            temp[k] = d;
+            if (d > best)
+            {
+                best = d;
+                bk = k;
+                bx = x;
+                by = y;
+                bz = z;
+            }
+        }
+
+        // ---- stage 1: warp
+        int key = __float_as_int(best);
+        int src = warp_argmax(key, bk, log2bs);
+        if (lane == src)
+        {
+            wmsg_a[par * 32 + warp] = make_uint4(static_cast<uint32_t>(key), static_cast<uint32_t>(bk),
+                                                 __float_as_uint(bx), __float_as_uint(by));
+            wmsg_z[par * 32 + warp] = bz;
+        }
+        __syncthreads();
+
+        // ---- stage 2: CTA
+        Msg msg;
+        {
+            int key2 = INT_MIN, k2 = 0;
+            float x2 = 0.f, y2 = 0.f, z2 = 0.f;
+            if (lane < nwarps)
+            {
+                const uint4 a = wmsg_a[par * 32 + lane];
+                key2 = static_cast<int>(a.x);
+                k2 = static_cast<int>(a.y);
+                x2 = __uint_as_float(a.z);
+                y2 = __uint_as_float(a.w);
+                z2 = wmsg_z[par * 32 + lane];
+            }
+            src = warp_argmax(key2, k2, log2bs);
+            msg.key = __shfl_sync(kFullMask, key2, src);
+            msg.k = __shfl_sync(kFullMask, k2, src);
+            msg.x = __shfl_sync(kFullMask, x2, src);
+            msg.y = __shfl_sync(kFullMask, y2, src);
+            msg.z = __shfl_sync(kFullMask, z2, src);
+        }
+
+        // ---- stage 3: cluster
+        if (nranks > 1)
+        {
+            if (warp == 0 && lane < nranks)
+                st_async_msg(rem_a[par], rem_z[par], rem_bar[par], static_cast<uint32_t>(msg.key),
+                             static_cast<uint32_t>(msg.k), msg.x, msg.y, msg.z);
+            // a warp whose wait ran out records it and stops waiting but keeps taking part
+            // in every barrier and exchange (see the on-chip kernel)
+            const uint32_t parity = static_cast<uint32_t>((j - 1) >> 1) & 1u;
+            if (!failed && !mbar_wait_bounded(smem_u32(mbar + par), parity))
+            {
+                if (lane == 0) atomicExch(&g_dev_status, 1);
+                failed = true;
+            }
+            int key3 = INT_MIN, k3 = 0;
+            float x3 = 0.f, y3 = 0.f, z3 = 0.f;
+            if (lane < nranks)
+            {
+                const uint4 a = cmsg_a[par * 32 + lane];
+                key3 = static_cast<int>(a.x);
+                k3 = static_cast<int>(a.y);
+                x3 = __uint_as_float(a.z);
+                y3 = __uint_as_float(a.w);
+                z3 = cmsg_z[par * 32 + lane];
+            }
+            src = warp_argmax(key3, k3, log2bs);
+            msg.key = __shfl_sync(kFullMask, key3, src);
+            msg.k = __shfl_sync(kFullMask, k3, src);
+            msg.x = __shfl_sync(kFullMask, x3, src);
+            msg.y = __shfl_sync(kFullMask, y3, src);
+            msg.z = __shfl_sync(kFullMask, z3, src);
+        }
+        else if (tid == 0)
+        {
+            // one-CTA cluster: nobody completes the transaction count, do it locally
+            asm volatile("mbarrier.complete_tx.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(mbar + par)),
+                         "r"(static_cast<uint32_t>(nranks * kMsgBytes))
+                         : "memory");
+        }
+        cx = msg.x;
+        cy = msg.y;
+        cz = msg.z;
+        if (gtid == 0) idxs[j] = msg.key >= 0 ? msg.k : 0;
+    }
+    cluster_sync_all();
+}
+
+int fps_launch_global(int b, int n, int m, int log2bs, const float* xyz, float* temp,
+                      int32_t* idxs, cudaStream_t stream)
+{
+    auto kernel = fps_global_kernel;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (err != cudaSuccess)
+    {
+        set_error("fps: cluster size attribute: %s", cudaGetErrorString(err));
+        return TPK_ERR_CUDA;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(b) * kFpsBigRanks, 1, 1);
+    cfg.blockDim = dim3(kFpsBigThreads, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kFpsBigRanks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, xyz, temp, idxs);
+    if (err != cudaSuccess)
+    {
+        set_error("fps launch (large clouds): %s", cudaGetErrorString(err));
+        return TPK_ERR_CUDA;
+    }
+    return TPK_OK;
+}
+
 struct FpsConfig
 {
     int nranks, nthreads, ppt;
@@ -529,31 +734,35 @@ extern "C" int64_t tpk_fps_scratch_bytes(int b, int n, int m)
     (void)b;
     (void)m;
     tpk::FpsConfig c;
-    if (n <= 0 || tpk::fps_pick_config(n, &c)) return 0;
-    return -1;  // larger clouds: not supported by this build
+    if (n <= 0 || b <= 0) return 0;
+    if (getenv("TPK_FPS_FORCE_GLOBAL") == nullptr && tpk::fps_pick_config(n, &c)) return 0;
+    // large clouds: the running minimum, one float per point
+    return static_cast<int64_t>(b) * n * static_cast<int64_t>(sizeof(float));
 }
 
 extern "C" int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz, void* scratch,
                                            int32_t* idxs, void* stream)
 {
     using namespace tpk;
-    (void)scratch;
     TPK_REQUIRE(b >= 0 && n >= 0 && m >= 0, "fps: negative size (b=%d n=%d m=%d)", b, n, m);
     if (b == 0 || m == 0) return TPK_OK;
     TPK_REQUIRE(n > 0, "fps: cannot sample %d points from an empty cloud", m);
     TPK_REQUIRE(xyz != nullptr && idxs != nullptr, "fps: NULL pointer");
-    FpsConfig c;
-    if (!fps_pick_config(n, &c))
-    {
-        set_error("fps: n=%d exceeds the on-chip capacity of %d points per cloud", n,
-                  kFpsMaxRanks * kFpsMaxThreads * kFpsMaxPpt);
-        return TPK_ERR_UNSUPPORTED;
-    }
     // block size of the reference launch (largest power of two <= n, capped at 512,
     // cuda/include/cuda_utils.h:16-21); it fixes the tie order
     int log2bs = floor_log2(n);
     if (log2bs > 9) log2bs = 9;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    FpsConfig c;
+    if (getenv("TPK_FPS_FORCE_GLOBAL") != nullptr || !fps_pick_config(n, &c))
+    {
+        if (scratch == nullptr)
+        {
+            set_error("fps: clouds of %d points need tpk_fps_scratch_bytes() bytes of scratch", n);
+            return TPK_ERR_SCRATCH;
+        }
+        return fps_launch_global(b, n, m, log2bs, xyz, static_cast<float*>(scratch), idxs, s);
+    }
     return c.nranks > 1 ? fps_launch_s<true>(c, b, n, m, log2bs, xyz, idxs, s)
                         : fps_launch_s<false>(c, b, n, m, log2bs, xyz, idxs, s);
 }
