@@ -72,6 +72,31 @@ TPK_API int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz, v
                                 int32_t* idxs, void* stream);
 TPK_API int64_t tpk_fps_scratch_bytes(int b, int n, int m);
 
+/*
+ * Furthest point sampling for callers that may not allocate device memory.  Same
+ * inputs, outputs and results as tpk_furthest_point_sampling, but the scratch (the
+ * running minimum distance of every point) is a fixed array inside the library instead
+ * of a caller buffer, and the call performs no cudaMalloc / cudaFree or any other
+ * allocation.  It is meant for code that runs where allocation is off limits: a plugin's
+ * enqueue hook in an inference runtime that owns all device memory, a real-time loop
+ * that must not hit the allocator's lock, a process whose memory budget was handed out
+ * in full at start-up.
+ * Limits and rules:
+ *   - b * n <= tpk_fps_static_capacity() (2 Mi points = 8 MiB, held by every GPU that
+ *     loads the library until the process exits); larger requests return
+ *     TPK_ERR_UNSUPPORTED and tpk_last_error() names the limit;
+ *   - the first call on each device looks up the array's device address (with that
+ *     device current); make that first call before starting any stream capture;
+ *   - all calls on a device share the one array: two calls that overlap on the GPU
+ *     (different streams, no ordering between them) race and give wrong indices.
+ *     The array keeps the previous call's contents; every call rewrites what it reads.
+ * No counterpart in the reference, whose FPS always allocates its scratch with torch
+ * (cuda/src/sampling.cpp:17).
+ */
+TPK_API int tpk_furthest_point_sampling_static(int b, int n, int m, const float* xyz,
+                                               int32_t* idxs, void* stream);
+TPK_API int64_t tpk_fps_static_capacity(void);
+
 /* --------------------------------------------------------------- ball query ---- */
 
 /*

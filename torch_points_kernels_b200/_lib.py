@@ -21,6 +21,7 @@ _ptr = ctypes.c_void_p
 # name -> argument types, in the order of include/tpk_b200.h
 _SIGNATURES = {
     "tpk_furthest_point_sampling": [_c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr],
+    "tpk_furthest_point_sampling_static": [_c_int, _c_int, _c_int, _ptr, _ptr, _ptr],
     "tpk_ball_query_dense": [_c_int, _c_int, _c_int, _c_f32, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_ball_query_partial_dense": [_c_i64, _c_i64, _c_f32, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_three_nn": [_c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
@@ -36,7 +37,8 @@ _SIGNATURES = {
     "tpk_chamfer_dist_grad_f64": [_c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
 }
 
-EXPORTS = sorted(list(_SIGNATURES) + ["tpk_version", "tpk_last_error", "tpk_device_status", "tpk_fps_scratch_bytes"])
+EXPORTS = sorted(list(_SIGNATURES) + ["tpk_version", "tpk_last_error", "tpk_device_status", "tpk_fps_scratch_bytes",
+                                       "tpk_fps_static_capacity"])
 
 
 def lib():
@@ -60,6 +62,8 @@ def lib():
         handle.tpk_device_status.restype = _c_int
         handle.tpk_fps_scratch_bytes.argtypes = [_c_int, _c_int, _c_int]
         handle.tpk_fps_scratch_bytes.restype = _c_i64
+        handle.tpk_fps_static_capacity.argtypes = []
+        handle.tpk_fps_static_capacity.restype = _c_i64
         _lib = handle
     return _lib
 

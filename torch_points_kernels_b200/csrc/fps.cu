@@ -767,6 +767,65 @@ extern "C" int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz
                         : fps_launch_s<false>(c, b, n, m, log2bs, xyz, idxs, s);
 }
 
+// ------------------------------------------------------------- entry point without scratch
+//
+// Scratch for tpk_furthest_point_sampling_static: lives in the library image, so every
+// GPU that loads the library holds these 8 MiB until the process exits.
+constexpr long long kFpsStaticFloats = 2ll * 1024 * 1024;
+static __device__ __align__(256) float g_fps_static_scratch[kFpsStaticFloats];
+
+namespace
+{
+constexpr int kMaxDevices = 64;
+float* g_fps_static_ptr[kMaxDevices] = {};  // device address of the array, per device
+}  // namespace
+
+extern "C" int64_t tpk_fps_static_capacity(void) { return kFpsStaticFloats; }
+
+extern "C" int tpk_furthest_point_sampling_static(int b, int n, int m, const float* xyz,
+                                                  int32_t* idxs, void* stream)
+{
+    using namespace tpk;
+    TPK_REQUIRE(b >= 0 && n >= 0 && m >= 0, "fps_static: negative size (b=%d n=%d m=%d)", b, n, m);
+    if (b == 0 || m == 0) return TPK_OK;
+    TPK_REQUIRE(n > 0, "fps_static: cannot sample %d points from an empty cloud", m);
+    TPK_REQUIRE(xyz != nullptr && idxs != nullptr, "fps_static: NULL pointer");
+    if (static_cast<long long>(b) * n > kFpsStaticFloats)
+    {
+        set_error("fps_static: b*n = %lld points exceed the built-in scratch of %lld points; "
+                  "use tpk_furthest_point_sampling with caller-provided scratch",
+                  static_cast<long long>(b) * n, kFpsStaticFloats);
+        return TPK_ERR_UNSUPPORTED;
+    }
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    {
+        set_error("fps_static: cannot identify the current device: %s", cudaGetErrorString(err));
+        return TPK_ERR_CUDA;
+    }
+    // In host code the array's name is only a handle; the kernel needs the address the
+    // array has on the device that is current now.  Looked up once per device.
+    float* scratch = g_fps_static_ptr[dev];
+    if (scratch == nullptr)
+    {
+        void* p = nullptr;
+        err = cudaGetSymbolAddress(&p, g_fps_static_scratch);
+        if (err != cudaSuccess || p == nullptr)
+        {
+            set_error("fps_static: cudaGetSymbolAddress: %s", cudaGetErrorString(err));
+            return TPK_ERR_CUDA;
+        }
+        scratch = static_cast<float*>(p);
+        g_fps_static_ptr[dev] = scratch;
+    }
+    int log2bs = floor_log2(n);
+    if (log2bs > 9) log2bs = 9;
+    // the kernel writes every scratch element it later reads (its first pass sets the
+    // running minima), so whatever an earlier call left behind is irrelevant
+    return fps_launch_global(b, n, m, log2bs, xyz, scratch, idxs, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int tpk_device_status(int* status_out, int reset)
 {
     int v = 0;
