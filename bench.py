@@ -531,6 +531,78 @@ def run_reference(args, rank, world):
     }), flush=True)
 
 
+def _time_calls(fn, steps, warmup, dev):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    return e0.elapsed_time(e1) / steps
+
+
+def run_workload(args):
+    """Secondary workloads (one GPU), one JSON line each:
+    chamfer     B=32 pairs x N=M=16384 (and B=64 x 2048), forward + backward
+    partial     64 packed scenes of 20k-200k points: partial_dense ball query and kNN k=16
+    fps_large   B=8 clouds x N=2^20: FPS to --npoint (default 65536) + dense ball query"""
+    import torch_points_kernels_b200 as tpk
+    from torch_points_kernels_b200 import chamfer_dist as cd
+    from tests import data
+
+    dev = torch.device("cuda", 0)
+    sm_mhz = 1965.0
+    lanes = 148 * 128 * sm_mhz * 1e6
+    out = {"workload": args.workload, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "data": "synthetic"}
+    if args.workload == "chamfer":
+        for B, N in ((32, 16384), (64, 2048)):
+            c1, c2 = data.chamfer_pair(B, N, seed=4000)
+            x1, x2 = c1.to(dev).requires_grad_(True), c2.to(dev).requires_grad_(True)
+
+            def fwd_bwd():
+                x1.grad = None
+                x2.grad = None
+                cd.chamfer_dist(x1, x2).backward()
+
+            ms = _time_calls(fwd_bwd, args.steps, args.warmup, dev)
+            ms_f = _time_calls(lambda: cd.ChamferFunction.apply(x1.detach(), x2.detach()), args.steps, args.warmup, dev)
+            out["B%d_N%d" % (B, N)] = {"ms_fwd_bwd": round(ms, 4), "pairs_per_s": round(B / (ms * 1e-3), 1),
+                                      "ms_fwd": round(ms_f, 4),
+                                      "fp32_frac_fwd": round(6.0 * 2 * B * N * N / (ms_f * 1e-3) / lanes, 4)}
+        out["metric"], out["unit"] = "chamfer_pairs_per_s", "pairs/s"
+        out["value"] = out["B32_N16384"]["pairs_per_s"]
+    elif args.workload == "partial":
+        x, y, bx, by = data.packed_planes(seed=3000)
+        xd, yd, bxd, byd = x.to(dev), y.to(dev), bx.to(dev), by.to(dev)
+        ms_bq = _time_calls(lambda: tpk.ball_query(0.05, 64, xd, yd, mode="partial_dense", batch_x=bxd, batch_y=byd),
+                            args.steps, args.warmup, dev)
+        ms_knn = _time_calls(lambda: tpk.knn(xd, yd, 16, batch_support=bxd, batch_pos=byd), args.steps, args.warmup, dev)
+        nx = torch.bincount(bx).double()
+        ny = torch.bincount(by, minlength=nx.numel()).double()
+        pairs = float((nx * ny).sum())
+        out.update({"metric": "partial_dense_ball_query_queries_per_s", "unit": "queries/s",
+                    "value": round(y.shape[0] / (ms_bq * 1e-3), 1), "points": x.shape[0], "queries": y.shape[0],
+                    "ball_query_ms": round(ms_bq, 3), "knn_k16_ms": round(ms_knn, 3),
+                    "knn_queries_per_s": round(y.shape[0] / (ms_knn * 1e-3), 1), "brute_force_pairs": pairs,
+                    "knn_fp32_frac": round(6.0 * pairs / (ms_knn * 1e-3) / lanes, 4)})
+    elif args.workload == "fps_large":
+        B, N = args.clouds or 8, 1 << 20
+        m = args.npoint or 65536
+        xd = data.gaussian_mixture(B, N, seed=5000).to(dev)
+        idx = tpk.furthest_point_sample(xd, m)
+        ms_fps = _time_calls(lambda: tpk.furthest_point_sample(xd, m), args.steps, 0, dev)
+        centres = torch.gather(xd, 1, idx.long().unsqueeze(-1).expand(-1, -1, 3)).contiguous()
+        ms_bq = _time_calls(lambda: tpk.ball_query(0.02, 32, xd, centres, mode="dense"), args.steps, 1, dev)
+        out.update({"metric": "large_cloud_fps_clouds_per_s", "unit": "clouds/s",
+                    "value": round(B / (ms_fps * 1e-3), 4), "clouds": B, "points_per_cloud": N, "npoint": m,
+                    "fps_ms": round(ms_fps, 2), "fps_us_per_round": round(ms_fps * 1e3 / (m - 1), 2),
+                    "ball_query_ms": round(ms_bq, 3), "ball_query_centres_per_s": round(B * m / (ms_bq * 1e-3), 1)})
+    print(json.dumps(out), flush=True)
+
+
 def run_only(args):
     """One op of the stack at its pipeline shape (optionally fewer clouds / samples), for
     profiler captures of a single kernel:  --only fps_l1|ball_query_l2|grouping_bwd_l1|...
@@ -586,13 +658,15 @@ def main():
     ap.add_argument("--only", default=None, help="run one op of the stack, e.g. fps_l1, grouping_bwd_l1")
     ap.add_argument("--clouds", type=int, default=0, help="with --only: clouds per batch (default 16)")
     ap.add_argument("--npoint", type=int, default=0, help="with --only: samples of that level's FPS")
+    ap.add_argument("--workload", default="sa_fp_pipeline", choices=["sa_fp_pipeline", "chamfer", "partial", "fps_large"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if (args.impl == "b200" and not args.only) else args.warmup
+    if args.impl == "b200" and not args.only and args.workload == "sa_fp_pipeline":
+        args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -601,6 +675,9 @@ def main():
         return
     if args.only:
         run_only(args)
+        return
+    if args.workload != "sa_fp_pipeline":
+        run_workload(args)
         return
     if world > 1:
         import torch.distributed as dist
