@@ -603,6 +603,93 @@ def run_workload(args):
     print(json.dumps(out), flush=True)
 
 
+def run_reference_cuda(args):
+    """Informational arm: the reference's own CUDA extension (compiled for sm_100a from its
+    sources into oracle/_ref/points_cuda.so) on the same inputs, one GPU, its own launch
+    shapes and the legacy stream choices it makes.  grouping = torch.gather on the expanded
+    index, as in torchpoints.py:143-146."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle", "_ref"))
+    try:
+        import points_cuda as ref
+    except Exception as e:
+        print(json.dumps({"impl": "reference_cuda", "unavailable": "points_cuda.so does not load: %s" % e}))
+        return
+    from tests import data
+
+    dev = torch.device("cuda", 0)
+    out = {"impl": "reference_cuda", "workload": args.workload, "steps": args.steps, "warmup": args.warmup}
+    if args.workload == "sa_fp_pipeline":
+        B, N = B_CLOUDS, N_POINTS
+        xyz_h, sa_h, fp_h = make_inputs(B, N, 2000)
+        xyz, sa, fp = xyz_h.to(dev), [t.to(dev) for t in sa_h], [t.to(dev) for t in fp_h]
+        g = torch.Generator(device=dev).manual_seed(2007)
+        n_in = [N] + LEVELS["npoint"][:-1]
+        g_grouped = [torch.randn(B, c, m, LEVELS["nsample"], device=dev, generator=g)
+                     for c, m in zip(LEVELS["channels"], LEVELS["npoint"])]
+        g_up = [torch.randn(B, c, n, device=dev, generator=g) for c, n in zip(LEVELS["channels"], n_in)]
+        times = {}
+
+        def t(name, fn):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = fn()
+            e1.record()
+            times.setdefault(name, []).append((e0, e1))
+            return r
+
+        def step():
+            pts = [xyz]
+            for l, m in enumerate(LEVELS["npoint"]):
+                idx = t("fps_l%d" % (l + 1), lambda: ref.furthest_point_sampling(pts[l], m))
+                centres = torch.gather(pts[l], 1, idx.long().unsqueeze(-1).expand(-1, -1, 3)).contiguous()
+                pts.append(centres)
+                nbr, _ = t("ball_query_l%d" % (l + 1),
+                           lambda: ref.ball_query_dense(centres, pts[l], LEVELS["radius"][l], LEVELS["nsample"]))
+                f = sa[l].detach().requires_grad_(True)
+
+                def group():
+                    all_idx = nbr.reshape(B, -1).unsqueeze(1).repeat(1, f.shape[1], 1)
+                    return f.gather(2, all_idx).reshape(B, f.shape[1], nbr.shape[1], nbr.shape[2])
+
+                grouped = t("grouping_fwd_l%d" % (l + 1), group)
+                t("grouping_bwd_l%d" % (l + 1), lambda: grouped.backward(g_grouped[l]))
+                d2, idx3 = t("three_nn_l%d" % (l + 1), lambda: ref.three_nn(pts[l], centres))
+                dist = torch.sqrt(d2)
+                w = 1.0 / (dist + 1e-8)
+                w = (w / w.sum(dim=2, keepdim=True)).contiguous()
+                t("interp_fwd_l%d" % (l + 1), lambda: ref.three_interpolate(fp[l], idx3, w))
+                t("interp_bwd_l%d" % (l + 1), lambda: ref.three_interpolate_grad(g_up[l], idx3, w, fp[l].shape[2]))
+
+        ms = _time_calls(step, args.steps, args.warmup, dev)
+        out.update({"metric": METRIC, "unit": "clouds/s", "value": round(B / (ms * 1e-3), 2), "ms_per_step": round(ms, 3),
+                    "kernels_ms": {k: round(sorted(a.elapsed_time(b) for a, b in v)[len(v) // 2], 4)
+                                   for k, v in sorted(times.items())}})
+    elif args.workload == "chamfer":
+        for B, N in ((32, 16384), (64, 2048)):
+            c1, c2 = data.chamfer_pair(B, N, seed=4000)
+            x1, x2 = c1.to(dev), c2.to(dev)
+            g1, g2 = torch.ones(B, N, device=dev) / (B * N), torch.ones(B, N, device=dev) / (B * N)
+
+            def fwd_bwd():
+                d1, d2, i1, i2 = ref.chamfer_dist(x1, x2)
+                ref.chamfer_dist_grad(x1, x2, i1, i2, g1, g2)
+
+            ms = _time_calls(fwd_bwd, args.steps, args.warmup, dev)
+            out["B%d_N%d" % (B, N)] = {"ms_fwd_bwd": round(ms, 3), "pairs_per_s": round(B / (ms * 1e-3), 1)}
+    elif args.workload == "partial":
+        x, y, bx, by = data.packed_planes(seed=3000)
+        xd, yd, bxd, byd = x.to(dev), y.to(dev), bx.to(dev), by.to(dev)
+        ms = _time_calls(lambda: ref.ball_query_partial_dense(xd, yd, bxd, byd, 0.05, 64), args.steps, args.warmup, dev)
+        out.update({"ball_query_ms": round(ms, 2), "queries_per_s": round(y.shape[0] / (ms * 1e-3), 1)})
+    elif args.workload == "fps_large":
+        B, N = args.clouds or 8, 1 << 20
+        m = args.npoint or 65536
+        xd = data.gaussian_mixture(B, N, seed=5000).to(dev)
+        ms = _time_calls(lambda: ref.furthest_point_sampling(xd, m), args.steps, 0, dev)
+        out.update({"fps_ms": round(ms, 2), "fps_us_per_round": round(ms * 1e3 / (m - 1), 2), "npoint": m})
+    print(json.dumps(out), flush=True)
+
+
 def run_only(args):
     """One op of the stack at its pipeline shape (optionally fewer clouds / samples), for
     profiler captures of a single kernel:  --only fps_l1|ball_query_l2|grouping_bwd_l1|...
@@ -662,7 +749,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "b200" and not args.only and args.workload == "sa_fp_pipeline":
@@ -672,6 +759,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.impl == "reference_cuda":
+        run_reference_cuda(args)
         return
     if args.only:
         run_only(args)
