@@ -160,13 +160,25 @@ int chamfer_dir_f32(int b, int n, const float* xyz1, int m, const float* xyz2, f
     TPK_REQUIRE(grid < (1ll << 31), "chamfer_dist: too many points");
     const dim3 g(static_cast<unsigned>(grid));
     if (threads == 128 && q == 2)
+    {
+        prefer_max_shared(chamfer_f32_kernel<128, 2>);
         chamfer_f32_kernel<128, 2><<<g, 128, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
+    }
     else if (threads == 128)
+    {
+        prefer_max_shared(chamfer_f32_kernel<128, 1>);
         chamfer_f32_kernel<128, 1><<<g, 128, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
+    }
     else if (q == 2)
+    {
+        prefer_max_shared(chamfer_f32_kernel<64, 2>);
         chamfer_f32_kernel<64, 2><<<g, 64, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
+    }
     else
+    {
+        prefer_max_shared(chamfer_f32_kernel<64, 1>);
         chamfer_f32_kernel<64, 1><<<g, 64, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
+    }
     return check_launch("chamfer_dist");
 }
 

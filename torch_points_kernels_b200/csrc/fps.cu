@@ -569,6 +569,7 @@ int fps_launch_global(int b, int n, int m, int log2bs, const float* xyz, float* 
                       int32_t* idxs, cudaStream_t stream)
 {
     auto kernel = fps_global_kernel;
+    prefer_max_shared(kernel);
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (err != cudaSuccess)
     {
@@ -665,6 +666,7 @@ int fps_launch_t(const FpsConfig& c, int b, int n, int m, int log2bs, const floa
                  int32_t* idxs, cudaStream_t stream)
 {
     auto kernel = fps_onchip_kernel<PPT, CLUSTERED>;
+    prefer_max_shared(kernel);
     const size_t smem = fps_smem_bytes(c);
     cudaError_t err;
     if (smem > 48 * 1024)

@@ -90,6 +90,141 @@ __global__ void __launch_bounds__(kGatherThreads)
     }
 }
 
+// ------------------------------------------------- grouping forward, rows in shared memory
+
+// Bounded wait for a TMA bulk copy into this CTA's shared memory (parity 0 of a fresh
+// mbarrier).  Gives up after one second; the caller then skips its work.
+__device__ __forceinline__ bool wait_bulk_copy(uint32_t mbar)
+{
+    unsigned long long t0 = 0;
+    for (unsigned it = 1;; ++it)
+    {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok)
+                     : "r"(mbar)
+                     : "memory");
+        if (ok) return true;
+        if ((it & 255u) == 0u)
+        {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0)
+                t0 = now;
+            else if (now - t0 > 1000000000ull)
+                return false;
+        }
+    }
+}
+
+// A CTA stages ROWS consecutive (batch, channel) feature rows in shared memory - one TMA
+// bulk copy per row when the rows are 16-byte aligned, coalesced loads otherwise - and
+// then walks a chunk of output positions: per thread four consecutive positions, their
+// indices loaded once (two 16-byte loads), ROWS x 4 shared-memory gathers, ROWS 16-byte
+// streaming stores.  Gathering from shared memory instead of L1/L2 removes the
+// sector-per-lane traffic that bounds the direct-gather kernel.
+template <int ROWS>
+__global__ void __launch_bounds__(kScatterThreads)
+    grouping_fwd_rows_kernel(int c, int n, long long ps, long long chunk, int use_tma,
+                             const float* __restrict__ features, const int64_t* __restrict__ idx,
+                             float* __restrict__ out)
+{
+    extern __shared__ __align__(128) float rows[];
+    __shared__ __align__(8) uint64_t mbar;
+    const int groups_per_batch = (c + ROWS - 1) / ROWS;
+    const int bi = blockIdx.y / groups_per_batch;
+    const int c0 = (blockIdx.y - bi * groups_per_batch) * ROWS;
+    const int nrows = min(ROWS, c - c0);
+    const float* src = features + (static_cast<size_t>(bi) * c + c0) * n;
+
+    if (use_tma)
+    {
+        const uint32_t bar = static_cast<uint32_t>(__cvta_generic_to_shared(&mbar));
+        if (threadIdx.x == 0)
+        {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncthreads();
+        if (threadIdx.x == 0)
+        {
+            const uint32_t bytes = static_cast<uint32_t>(nrows) * n * 4u;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+            for (int r = 0; r < nrows; ++r)
+            {
+                const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(rows + static_cast<size_t>(r) * n));
+                asm volatile(
+                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                    "l"(src + static_cast<size_t>(r) * n), "r"(static_cast<uint32_t>(n) * 4u), "r"(bar)
+                    : "memory");
+            }
+        }
+        if (!wait_bulk_copy(bar)) return;
+    }
+    else
+    {
+        for (int i = threadIdx.x; i < nrows * n; i += kScatterThreads) rows[i] = __ldg(src + i);
+        __syncthreads();
+    }
+
+    const long long p0 = static_cast<long long>(blockIdx.x) * chunk;
+    const long long p1 = min(ps, p0 + chunk);
+    const int64_t* ib = idx + static_cast<size_t>(bi) * ps;
+    float* ob = out + (static_cast<size_t>(bi) * c + c0) * ps;
+    for (long long p = p0 + static_cast<long long>(threadIdx.x) * 4; p < p1; p += kScatterThreads * 4)
+    {
+        const longlong2 a = __ldg(reinterpret_cast<const longlong2*>(ib + p));
+        const longlong2 b2 = __ldg(reinterpret_cast<const longlong2*>(ib + p) + 1);
+        const int i0 = static_cast<int>(a.x), i1 = static_cast<int>(a.y);
+        const int i2 = static_cast<int>(b2.x), i3 = static_cast<int>(b2.y);
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)
+        {
+            if (r < nrows)
+            {
+                const float* row = rows + static_cast<size_t>(r) * n;
+                __stcs(reinterpret_cast<float4*>(ob + r * ps + p), make_float4(row[i0], row[i1], row[i2], row[i3]));
+            }
+        }
+    }
+}
+
+template <int ROWS>
+int launch_grouping_fwd_rows(int b, int c, int n, long long ps, const float* features,
+                             const int64_t* idx, float* out, cudaStream_t s)
+{
+    auto kernel = grouping_fwd_rows_kernel<ROWS>;
+    prefer_max_shared(kernel);
+    const size_t smem = static_cast<size_t>(ROWS) * n * sizeof(float);
+    if (smem > 48 * 1024)
+    {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(smem));
+        if (err != cudaSuccess)
+        {
+            set_error("grouping: shared memory attribute: %s", cudaGetErrorString(err));
+            return TPK_ERR_CUDA;
+        }
+    }
+    const long long groups = static_cast<long long>(b) * ((c + ROWS - 1) / ROWS);
+    // split the positions so that every SM gets a few CTAs, in multiples of the 2048
+    // positions one sweep of the CTA covers
+    long long nchunks = (4ll * num_sms() + groups - 1) / groups;
+    const long long max_chunks = (ps + 8191) / 8192;
+    if (nchunks > max_chunks) nchunks = max_chunks;
+    if (nchunks < 1) nchunks = 1;
+    long long chunk = (ps + nchunks - 1) / nchunks;
+    chunk = (chunk + 2047) / 2048 * 2048;
+    nchunks = (ps + chunk - 1) / chunk;
+    TPK_REQUIRE(groups <= 65535 && nchunks < (1ll << 31), "grouping: grid too large");
+    const int use_tma = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(features) & 15u) == 0);
+    const dim3 g(static_cast<unsigned>(nchunks), static_cast<unsigned>(groups));
+    kernel<<<g, kScatterThreads, smem, s>>>(c, n, ps, chunk, use_tma, features, idx, out);
+    return check_launch("grouping");
+}
+
 // ---------------------------------------------------------- three_interpolate forward
 
 template <bool VEC>
@@ -322,6 +457,7 @@ int launch_grouping_bwd_rows(int b, int c, int row_len, long long src_len, int n
                              cudaStream_t s)
 {
     auto kernel = grouping_bwd_rows_kernel<ROWS, 4>;
+    prefer_max_shared(kernel);
     const size_t smem = static_cast<size_t>(ROWS) * row_len * sizeof(float);
     if (smem > 48 * 1024)
     {
@@ -400,6 +536,7 @@ int launch_scatter(int b, int c, int row_len, long long src_len, const float* gr
         while (rows > 1 && static_cast<long long>(b) * ((c + rows - 1) / rows) < 2ll * num_sms()) --rows;
         const size_t smem = static_cast<size_t>(rows) * row_bytes;
         auto kernel = scatter_rows_kernel<INTERP>;
+        prefer_max_shared(kernel);
         if (smem > 48 * 1024)
         {
             cudaError_t err = cudaFuncSetAttribute(
@@ -445,6 +582,22 @@ extern "C" int tpk_grouping(int b, int c, int n, int npoint, int nsample, const 
     if (b == 0 || c == 0 || ps == 0) return TPK_OK;
     TPK_REQUIRE(features && idx && out && n > 0, "grouping: NULL pointer or empty feature row");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t row_bytes = static_cast<size_t>(n) * sizeof(float);
+    if (ps % 4 == 0 && aligned16(idx) && aligned16(out) && row_bytes <= 96 * 1024 && ps >= 4096 &&
+        static_cast<long long>(b) * c <= 65535 && getenv("TPK_GATHER_DIRECT") == nullptr)
+    {
+        // rows per CTA: up to ~100 KB of shared memory (two CTAs per SM), at most 4
+        int rows = static_cast<int>((100 * 1024) / row_bytes);
+        if (rows > 4) rows = 4;
+        if (rows > c) rows = c;
+        switch (rows)
+        {
+        case 1: return launch_grouping_fwd_rows<1>(b, c, n, ps, features, idx, out, s);
+        case 2: return launch_grouping_fwd_rows<2>(b, c, n, ps, features, idx, out, s);
+        case 3: return launch_grouping_fwd_rows<3>(b, c, n, ps, features, idx, out, s);
+        default: return launch_grouping_fwd_rows<4>(b, c, n, ps, features, idx, out, s);
+        }
+    }
     const long long gx = (ps + kGatherThreads * 4 - 1) / (kGatherThreads * 4);
     const int gy = (c + kChanChunk - 1) / kChanChunk;
     TPK_REQUIRE(gx < (1ll << 31) && gy <= 65535 && b <= 65535, "grouping: grid too large");

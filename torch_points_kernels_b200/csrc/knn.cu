@@ -309,13 +309,25 @@ extern "C" int tpk_three_nn(int b, int n, int m, const float* unknown, const flo
     TPK_REQUIRE(grid < (1ll << 31), "three_nn: too many queries");
     const dim3 g(static_cast<unsigned>(grid));
     if (threads == 128 && q == 2)
+    {
+        prefer_max_shared(three_nn_kernel<128, 2>);
         three_nn_kernel<128, 2><<<g, 128, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
+    }
     else if (threads == 128)
+    {
+        prefer_max_shared(three_nn_kernel<128, 1>);
         three_nn_kernel<128, 1><<<g, 128, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
+    }
     else if (q == 2)
+    {
+        prefer_max_shared(three_nn_kernel<64, 2>);
         three_nn_kernel<64, 2><<<g, 64, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
+    }
     else
+    {
+        prefer_max_shared(three_nn_kernel<64, 1>);
         three_nn_kernel<64, 1><<<g, 64, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
+    }
     return check_launch("three_nn");
 }
 

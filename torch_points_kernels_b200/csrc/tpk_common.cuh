@@ -44,6 +44,17 @@ inline int check_launch(const char* what)
     return TPK_OK;
 }
 
+// Every kernel of the library asks for the same (largest) shared-memory carve-out.  An
+// SM changes its L1/shared split only when it is idle, so kernels with different
+// preferences cannot share an SM; with one common setting the long-running FPS clusters,
+// the search kernels and the row-resident gather kernels co-reside freely.
+template <class K>
+inline void prefer_max_shared(K kernel)
+{
+    (void)cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                               cudaSharedmemCarveoutMaxShared);
+}
+
 #define TPK_REQUIRE(cond, ...)                                                                     \
     do                                                                                             \
     {                                                                                              \
