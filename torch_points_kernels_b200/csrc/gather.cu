@@ -583,11 +583,13 @@ extern "C" int tpk_grouping(int b, int c, int n, int npoint, int nsample, const 
     TPK_REQUIRE(features && idx && out && n > 0, "grouping: NULL pointer or empty feature row");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const size_t row_bytes = static_cast<size_t>(n) * sizeof(float);
-    if (ps % 4 == 0 && aligned16(idx) && aligned16(out) && row_bytes <= 96 * 1024 && ps >= 4096 &&
+    if (ps % 4 == 0 && aligned16(idx) && aligned16(out) && row_bytes <= kRowSmemBudget && ps >= 4096 &&
         static_cast<long long>(b) * c <= 65535 && getenv("TPK_GATHER_DIRECT") == nullptr)
     {
-        // rows per CTA: up to ~100 KB of shared memory (two CTAs per SM), at most 4
-        int rows = static_cast<int>((100 * 1024) / row_bytes);
+        // rows per CTA: as many as fit the shared memory of one SM, at most 4 (the indices
+        // of a position are loaded once for all rows of the CTA)
+        int rows = static_cast<int>(kRowSmemBudget / row_bytes);
+        if (rows < 1) rows = 1;
         if (rows > 4) rows = 4;
         if (rows > c) rows = c;
         switch (rows)
@@ -637,6 +639,7 @@ extern "C" int tpk_grouping_grad(int b, int c, int n, int npoint, int nsample,
     {
         // rows per CTA: as many as fit a bit over 100 KB (two CTAs per SM), at most 4,
         // fewer when that would leave SMs without a CTA
+        // (measured: the atomics want many resident warps more than they want shared indices)
         int rows = static_cast<int>((104 * 1024) / row_bytes);
         if (rows < 1) rows = 1;
         if (rows > 4) rows = 4;
