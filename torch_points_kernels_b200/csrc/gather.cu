@@ -387,12 +387,14 @@ __global__ void __launch_bounds__(kScatterThreads)
 // the atomic for them.  Any other repetition in idx is still correct: those lanes just
 // use their own atomics.  `seg` = lanes per segment (a power of two <= 32; 1 = no
 // pre-reduction, used when nsample is not a power of two).
-template <int ROWS, int UNROLL>
+template <int ROWS, int SEG>
 __global__ void __launch_bounds__(kScatterThreads)
-    grouping_bwd_rows_kernel(int c, int row_len, long long src_len, int seg,
+    grouping_bwd_rows_kernel(int c, int row_len, long long src_len,
                              const float* __restrict__ grad_out, const int64_t* __restrict__ idx,
                              float* __restrict__ grad_small)
 {
+    constexpr int UNROLL = 4;
+    constexpr int NWARPS = kScatterThreads / 32;
     extern __shared__ __align__(16) float acc[];
     const int groups_per_batch = (c + ROWS - 1) / ROWS;
     const int bi = blockIdx.x / groups_per_batch;
@@ -401,49 +403,73 @@ __global__ void __launch_bounds__(kScatterThreads)
     for (int i = threadIdx.x; i < nrows * row_len; i += kScatterThreads) acc[i] = 0.f;
     __syncthreads();
 
-    const float* g = grad_out + (static_cast<size_t>(bi) * c + c0) * src_len;
-    const int64_t* ib = idx + static_cast<size_t>(bi) * src_len;
-    const int lane = threadIdx.x & 31;
-    const int seg_first = lane & ~(seg - 1);
-    const long long stride = kScatterThreads;
-    for (long long base = threadIdx.x; base - lane < src_len; base += stride * UNROLL)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int seg_first = lane & ~(SEG - 1);
+    const long long nfull = src_len / 32;  // whole 32-position sets
+    // this lane's element of set `warp`; sets advance by NWARPS per step
+    const int64_t* ip = idx + static_cast<size_t>(bi) * src_len + warp * 32 + lane;
+    const float* gp[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r)
+        gp[r] = grad_out + (static_cast<size_t>(bi) * c + c0 + (r < nrows ? r : 0)) * src_len + warp * 32 + lane;
+
+    for (long long set = warp; set < nfull; set += NWARPS * UNROLL)
     {
         int id[UNROLL];
         float v[UNROLL][ROWS];
-        bool ok[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u)
         {
-            const long long p = base + u * stride;
-            ok[u] = p < src_len;
-            id[u] = ok[u] ? static_cast<int>(__ldg(ib + p)) : -1 - lane;  // distinct dummies
+            if (set + u * NWARPS < nfull)  // warp-uniform
+            {
+                id[u] = static_cast<int>(__ldg(ip + u * (NWARPS * 32)));
 #pragma unroll
-            for (int r = 0; r < ROWS; ++r)
-                v[u][r] = (ok[u] && r < nrows) ? __ldcs(g + r * src_len + p) : 0.f;
+                for (int r = 0; r < ROWS; ++r) v[u][r] = __ldcs(gp[r] + u * (NWARPS * 32));
+            }
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u)
         {
-            if (base + u * stride - lane >= src_len) break;  // whole warp past the end
-            const int first_id = __shfl_sync(kFullMask, id[u], seg_first);
-            const bool dup = seg > 1 && id[u] == first_id;  // includes the segment's first lane
-            const uint32_t dups = __ballot_sync(kFullMask, dup && lane != seg_first);
-            if (dups != 0u)
+            if (set + u * NWARPS >= nfull) break;  // warp-uniform
+            bool mine = true;  // this lane issues its own atomic
+            if (SEG > 1)
             {
-#pragma unroll
-                for (int r = 0; r < ROWS; ++r)
+                const int first_id = __shfl_sync(kFullMask, id[u], seg_first);
+                const bool same = id[u] == first_id;  // true for the segment's first lane too
+                mine = !same || lane == seg_first;
+                if (__ballot_sync(kFullMask, !mine) != 0u)
                 {
-                    float sum = dup ? v[u][r] : 0.f;
-                    for (int o = seg >> 1; o >= 1; o >>= 1) sum += __shfl_xor_sync(kFullMask, sum, o);
-                    if (lane == seg_first) v[u][r] = sum;
+#pragma unroll
+                    for (int r = 0; r < ROWS; ++r)
+                    {
+                        float sum = same ? v[u][r] : 0.f;
+#pragma unroll
+                        for (int o = SEG / 2; o >= 1; o >>= 1) sum += __shfl_xor_sync(kFullMask, sum, o);
+                        if (lane == seg_first) v[u][r] = sum;
+                    }
                 }
             }
-            if (ok[u] && (!dup || lane == seg_first))
+            if (mine)
             {
 #pragma unroll
                 for (int r = 0; r < ROWS; ++r)
                     if (r < nrows) atomicAdd(acc + r * row_len + id[u], v[u][r]);
             }
+        }
+        ip += NWARPS * UNROLL * 32;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) gp[r] += NWARPS * UNROLL * 32;
+    }
+    // the last src_len % 32 positions
+    if (warp == 0)
+    {
+        const long long p = nfull * 32 + lane;
+        if (p < src_len)
+        {
+            const int i0 = static_cast<int>(__ldg(idx + static_cast<size_t>(bi) * src_len + p));
+            for (int r = 0; r < nrows; ++r)
+                atomicAdd(acc + r * row_len + i0,
+                          grad_out[(static_cast<size_t>(bi) * c + c0 + r) * src_len + p]);
         }
     }
     __syncthreads();
@@ -451,12 +477,11 @@ __global__ void __launch_bounds__(kScatterThreads)
     for (int i = threadIdx.x; i < nrows * row_len; i += kScatterThreads) dst[i] = acc[i];
 }
 
-template <int ROWS>
-int launch_grouping_bwd_rows(int b, int c, int row_len, long long src_len, int nsample,
-                             const float* grad_out, const int64_t* idx, float* grad_small,
-                             cudaStream_t s)
+template <int ROWS, int SEG>
+int launch_grouping_bwd_rows_seg(int b, int c, int row_len, long long src_len, const float* grad_out,
+                                 const int64_t* idx, float* grad_small, cudaStream_t s)
 {
-    auto kernel = grouping_bwd_rows_kernel<ROWS, 4>;
+    auto kernel = grouping_bwd_rows_kernel<ROWS, SEG>;
     prefer_max_shared(kernel);
     const size_t smem = static_cast<size_t>(ROWS) * row_len * sizeof(float);
     if (smem > 48 * 1024)
@@ -471,12 +496,26 @@ int launch_grouping_bwd_rows(int b, int c, int row_len, long long src_len, int n
     }
     const long long grid = static_cast<long long>(b) * ((c + ROWS - 1) / ROWS);
     TPK_REQUIRE(grid < (1ll << 31), "grouping_grad: too many rows");
+    kernel<<<static_cast<unsigned>(grid), kScatterThreads, smem, s>>>(c, row_len, src_len, grad_out, idx,
+                                                                    grad_small);
+    return check_launch("grouping_grad");
+}
+
+template <int ROWS>
+int launch_grouping_bwd_rows(int b, int c, int row_len, long long src_len, int nsample,
+                             const float* grad_out, const int64_t* idx, float* grad_small,
+                             cudaStream_t s)
+{
     // neighbourhood segments line up with warps when nsample is a power of two
     int seg = 1;
     if (nsample > 1 && (nsample & (nsample - 1)) == 0) seg = nsample < 32 ? nsample : 32;
-    kernel<<<static_cast<unsigned>(grid), kScatterThreads, smem, s>>>(c, row_len, src_len, seg, grad_out,
-                                                                    idx, grad_small);
-    return check_launch("grouping_grad");
+    switch (seg)
+    {
+    case 32: return launch_grouping_bwd_rows_seg<ROWS, 32>(b, c, row_len, src_len, grad_out, idx, grad_small, s);
+    case 16: return launch_grouping_bwd_rows_seg<ROWS, 16>(b, c, row_len, src_len, grad_out, idx, grad_small, s);
+    case 8: return launch_grouping_bwd_rows_seg<ROWS, 8>(b, c, row_len, src_len, grad_out, idx, grad_small, s);
+    default: return launch_grouping_bwd_rows_seg<ROWS, 1>(b, c, row_len, src_len, grad_out, idx, grad_small, s);
+    }
 }
 
 // ------------------------------------------------------------------ backward, global atomics
