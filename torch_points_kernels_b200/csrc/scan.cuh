@@ -39,6 +39,7 @@ namespace tpk
 constexpr int kScanTile = 1024;
 constexpr int kScanTileFloats = 4 * kScanTile;
 constexpr float kFilterSlack = 7.62939453125e-06f;  // 2^-17
+constexpr int kPendCap = 16;  // parked pairs per thread between two exact-test batches
 
 __device__ __forceinline__ unsigned long long pack2(float lo, float hi)
 {
@@ -127,6 +128,41 @@ __device__ __forceinline__ void scan_candidates(const float* __restrict__ cand, 
         T[q] = filter_threshold(op.threshold(q), q2[q]);
     }
 
+    // pairs that passed the filter and wait for the exact test: entry e of this thread at
+    // [e * THREADS + tid]
+    __shared__ uint32_t s_pend[kPendCap * THREADS];
+    uint32_t* pend = s_pend + tid;
+    int npend = 0;
+    bool done = op.finished();
+    // Exact test of all parked pairs of the warp, every lane in its own (index) order.
+    // Must be called by all lanes of the warp together.
+    auto flush = [&](long long t) {
+        const float* tile = smem + (t & 1) * kScanTileFloats;
+        const int most = __reduce_max_sync(kFullMask, npend);
+        for (int e = 0; e < most; ++e)
+        {
+            if (e < npend)
+            {
+                const uint32_t ent = pend[e * THREADS];
+                const int j = static_cast<int>(ent >> 1);
+                const long long k = t * kScanTile + j;
+                if (k < ncand)
+                {
+                    const float* c = tile + (j >> 2) * 16 + (j & 3);
+                    const float cx = c[0], cy = c[4], cz = c[8];
+#pragma unroll
+                    for (int q = 0; q < Q; ++q)
+                    {
+                        if (static_cast<int>(ent & 1u) == q && op.exact(q, k, cx, cy, cz))
+                            T[q] = filter_threshold(op.threshold(q), q2[q]);
+                    }
+                }
+            }
+        }
+        npend = 0;
+        done = op.finished();
+    };
+
     if (ntiles > 0)
     {
         fetch(0);
@@ -140,8 +176,6 @@ __device__ __forceinline__ void scan_candidates(const float* __restrict__ cand, 
 
         // each 16-byte load yields two packed candidate pairs, ready for fma.rn.f32x2
         const ulonglong2* s2 = reinterpret_cast<const ulonglong2*>(smem + (t & 1) * kScanTileFloats);
-        const long long kbase = t * kScanTile;
-        bool done = op.finished();
         for (int chunk = 0; chunk < kScanTile / 64; ++chunk)
         {
             if (__all_sync(kFullMask, done)) break;
@@ -168,33 +202,27 @@ __device__ __forceinline__ void scan_candidates(const float* __restrict__ cand, 
                 // warp-uniform branch: every lane enters, so the votes inside are convergent
                 if (__any_sync(kFullMask, any))
                 {
-                    const float cx[4] = {lo_f32(X.x), hi_f32(X.x), lo_f32(X.y), hi_f32(X.y)};
-                    const float cy[4] = {lo_f32(Y.x), hi_f32(Y.x), lo_f32(Y.y), hi_f32(Y.y)};
-                    const float cz[4] = {lo_f32(Z.x), hi_f32(Z.x), lo_f32(Z.y), hi_f32(Z.y)};
-                    // candidates in index order; a candidate no lane of the warp lets
-                    // through is skipped with one vote
+                    // park the pairs that passed (tile position and query, in index order);
+                    // they are examined in batches, with most lanes of the warp busy, instead
+                    // of one at a time with one lane busy
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
                     {
-                        bool pass = false;
-#pragma unroll
-                        for (int q = 0; q < Q; ++q) pass |= a[q][i] <= T[q];
-                        if (!__any_sync(kFullMask, pass)) continue;
-                        const long long k = kbase + 4 * g + i;
 #pragma unroll
                         for (int q = 0; q < Q; ++q)
                         {
-                            if (a[q][i] <= T[q] && k < ncand)
+                            if (a[q][i] <= T[q])
                             {
-                                if (op.exact(q, k, cx[i], cy[i], cz[i]))
-                                    T[q] = filter_threshold(op.threshold(q), q2[q]);
+                                pend[npend * THREADS] = static_cast<uint32_t>(((4 * g + i) << 1) | q);
+                                ++npend;
                             }
                         }
                     }
-                    done = op.finished();
+                    if (__any_sync(kFullMask, npend > kPendCap - 4 * Q)) flush(t);
                 }
             }
         }
+        if (__any_sync(kFullMask, npend > 0)) flush(t);
         if (more) stage(t + 1);
         // one barrier per tile: it publishes tile t+1 and retires tile t, whose buffer is
         // only written again while staging tile t+2, after the next barrier
