@@ -273,6 +273,119 @@ __global__ void __launch_bounds__(kGatherThreads)
     }
 }
 
+// --------------------------------------- three_interpolate forward, rows in shared memory
+
+// Same residency scheme as grouping_fwd_rows_kernel: ROWS feature rows (length m) staged
+// with TMA bulk copies, then every thread produces four consecutive outputs per row
+// from 12 shared-memory gathers; the 12 indices and weights of its four points are
+// loaded once (six 16-byte loads) for all rows.
+template <int ROWS>
+__global__ void __launch_bounds__(kGatherThreads)
+    interp_fwd_rows_kernel(int c, int m, int n, int chunk, int use_tma,
+                           const float* __restrict__ points, const int32_t* __restrict__ idx,
+                           const float* __restrict__ weight, float* __restrict__ out)
+{
+    extern __shared__ __align__(128) float rows[];
+    __shared__ __align__(8) uint64_t mbar;
+    const int groups_per_batch = (c + ROWS - 1) / ROWS;
+    const int bi = blockIdx.y / groups_per_batch;
+    const int c0 = (blockIdx.y - bi * groups_per_batch) * ROWS;
+    const int nrows = min(ROWS, c - c0);
+    const float* src = points + (static_cast<size_t>(bi) * c + c0) * m;
+    if (use_tma)
+    {
+        const uint32_t bar = static_cast<uint32_t>(__cvta_generic_to_shared(&mbar));
+        if (threadIdx.x == 0)
+        {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncthreads();
+        if (threadIdx.x == 0)
+        {
+            // consecutive rows are contiguous in memory: one copy for all of them
+            const uint32_t bytes = static_cast<uint32_t>(nrows) * m * 4u;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+            const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(rows));
+            asm volatile(
+                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                "l"(src), "r"(bytes), "r"(bar)
+                : "memory");
+        }
+        if (!wait_bulk_copy(bar)) return;
+    }
+    else
+    {
+        for (int i = threadIdx.x; i < nrows * m; i += kGatherThreads) rows[i] = __ldg(src + i);
+        __syncthreads();
+    }
+
+    const int j_begin = blockIdx.x * chunk;
+    const int j_end = min(n, j_begin + chunk);
+    for (int j0 = j_begin + threadIdx.x * 4; j0 < j_end; j0 += kGatherThreads * 4)
+    {
+        const size_t o = (static_cast<size_t>(bi) * n + j0) * 3;  // multiple of 12: 16-byte aligned
+        int id[12];
+        float w[12];
+#pragma unroll
+        for (int t = 0; t < 3; ++t)
+        {
+            const int4 a = __ldg(reinterpret_cast<const int4*>(idx + o) + t);
+            const float4 b4 = __ldg(reinterpret_cast<const float4*>(weight + o) + t);
+            id[4 * t + 0] = a.x; id[4 * t + 1] = a.y; id[4 * t + 2] = a.z; id[4 * t + 3] = a.w;
+            w[4 * t + 0] = b4.x; w[4 * t + 1] = b4.y; w[4 * t + 2] = b4.z; w[4 * t + 3] = b4.w;
+        }
+        float* op = out + (static_cast<size_t>(bi) * c + c0) * n + j0;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)
+        {
+            if (r < nrows)
+            {
+                const float* row = rows + r * m;
+                float v[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+                    v[t] = interp3(row[id[3 * t + 0]], w[3 * t + 0], row[id[3 * t + 1]], w[3 * t + 1],
+                                   row[id[3 * t + 2]], w[3 * t + 2]);
+                __stcs(reinterpret_cast<float4*>(op + static_cast<size_t>(r) * n), make_float4(v[0], v[1], v[2], v[3]));
+            }
+        }
+    }
+}
+
+template <int ROWS>
+int launch_interp_fwd_rows(int b, int c, int m, int n, const float* points, const int32_t* idx,
+                           const float* weight, float* out, cudaStream_t s)
+{
+    auto kernel = interp_fwd_rows_kernel<ROWS>;
+    prefer_max_shared(kernel);
+    const size_t smem = static_cast<size_t>(ROWS) * m * sizeof(float);
+    if (smem > 48 * 1024)
+    {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(smem));
+        if (err != cudaSuccess)
+        {
+            set_error("three_interpolate: shared memory attribute: %s", cudaGetErrorString(err));
+            return TPK_ERR_CUDA;
+        }
+    }
+    const long long groups = static_cast<long long>(b) * ((c + ROWS - 1) / ROWS);
+    long long nchunks = (4ll * num_sms() + groups - 1) / groups;
+    const long long max_chunks = (n + 4095) / 4096;
+    if (nchunks > max_chunks) nchunks = max_chunks;
+    if (nchunks < 1) nchunks = 1;
+    int chunk = static_cast<int>((n + nchunks - 1) / nchunks);
+    chunk = (chunk + 1023) / 1024 * 1024;
+    nchunks = (n + chunk - 1) / chunk;
+    TPK_REQUIRE(groups <= 65535, "three_interpolate: grid too large");
+    const int use_tma = (m % 4 == 0) && ((reinterpret_cast<uintptr_t>(points) & 15u) == 0) &&
+                        static_cast<size_t>(ROWS) * m * 4 < (1u << 20);
+    const dim3 g(static_cast<unsigned>(nchunks), static_cast<unsigned>(groups));
+    kernel<<<g, kGatherThreads, smem, s>>>(c, m, n, chunk, use_tma, points, idx, weight, out);
+    return check_launch("three_interpolate");
+}
+
 // ------------------------------------------------------------------ backward, shared rows
 
 // Rows of the small gradient (length row_len) for `rows` consecutive (batch, channel)
@@ -705,6 +818,14 @@ extern "C" int tpk_three_interpolate(int b, int c, int m, int n, const float* po
     TPK_REQUIRE(points && idx && weight && out && m > 0,
                 "three_interpolate: NULL pointer or empty feature row");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (n % 4 == 0 && aligned16(out) && aligned16(idx) && aligned16(weight) && n >= 1024 &&
+        static_cast<size_t>(m) * 4 * 4 <= kRowSmemBudget && static_cast<long long>(b) * c <= 65535 &&
+        getenv("TPK_GATHER_DIRECT") == nullptr)
+    {
+        if (c >= 8 && static_cast<size_t>(m) * 4 * 8 <= 128 * 1024)
+            return launch_interp_fwd_rows<8>(b, c, m, n, points, idx, weight, out, s);
+        return launch_interp_fwd_rows<4>(b, c, m, n, points, idx, weight, out, s);
+    }
     const int gx = (n + kGatherThreads * 4 - 1) / (kGatherThreads * 4);
     const int gy = (c + kChanChunk - 1) / kChanChunk;
     TPK_REQUIRE(gy <= 65535 && b <= 65535, "three_interpolate: grid too large");
