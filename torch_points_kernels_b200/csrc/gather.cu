@@ -631,6 +631,74 @@ int launch_grouping_bwd_rows(int b, int c, int row_len, long long src_len, int n
     }
 }
 
+// ------------------------------------------- three_interpolate backward, shared rows
+
+// ROWS rows of the small gradient (length m) in shared memory; every warp streams sets of
+// 32 consecutive points: their three indices and weights are loaded once, then per row
+// one coalesced load of the incoming gradient and three shared-memory atomics.
+template <int ROWS, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+    interp_bwd_rows_kernel(int c, int m, int n, const float* __restrict__ grad_out,
+                           const int32_t* __restrict__ idx, const float* __restrict__ weight,
+                           float* __restrict__ grad_points)
+{
+    constexpr int NWARPS = THREADS / 32;
+    extern __shared__ __align__(16) float acc[];
+    const int groups_per_batch = (c + ROWS - 1) / ROWS;
+    const int bi = blockIdx.x / groups_per_batch;
+    const int c0 = (blockIdx.x - bi * groups_per_batch) * ROWS;
+    const int nrows = min(ROWS, c - c0);
+    for (int i = threadIdx.x; i < nrows * m; i += THREADS) acc[i] = 0.f;
+    __syncthreads();
+
+    const float* g = grad_out + (static_cast<size_t>(bi) * c + c0) * n;
+    for (int j = threadIdx.x; j < n; j += THREADS)
+    {
+        const size_t o = (static_cast<size_t>(bi) * n + j) * 3;
+        const int i0 = __ldg(idx + o), i1 = __ldg(idx + o + 1), i2 = __ldg(idx + o + 2);
+        const float w0 = __ldg(weight + o), w1 = __ldg(weight + o + 1), w2 = __ldg(weight + o + 2);
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)
+        {
+            if (r < nrows)
+            {
+                const float gv = __ldcs(g + static_cast<size_t>(r) * n + j);
+                float* a = acc + r * m;
+                atomicAdd(a + i0, __fmul_rn(gv, w0));
+                atomicAdd(a + i1, __fmul_rn(gv, w1));
+                atomicAdd(a + i2, __fmul_rn(gv, w2));
+            }
+        }
+    }
+    (void)NWARPS;
+    __syncthreads();
+    float* dst = grad_points + (static_cast<size_t>(bi) * c + c0) * m;
+    for (int i = threadIdx.x; i < nrows * m; i += THREADS) dst[i] = acc[i];
+}
+
+template <int ROWS, int THREADS>
+int launch_interp_bwd_rows(int b, int c, int m, int n, const float* grad_out, const int32_t* idx,
+                           const float* weight, float* grad_points, cudaStream_t s)
+{
+    auto kernel = interp_bwd_rows_kernel<ROWS, THREADS>;
+    prefer_max_shared(kernel);
+    const size_t smem = static_cast<size_t>(ROWS) * m * sizeof(float);
+    if (smem > 48 * 1024)
+    {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(smem));
+        if (err != cudaSuccess)
+        {
+            set_error("three_interpolate_grad: shared memory attribute: %s", cudaGetErrorString(err));
+            return TPK_ERR_CUDA;
+        }
+    }
+    const long long grid = static_cast<long long>(b) * ((c + ROWS - 1) / ROWS);
+    TPK_REQUIRE(grid < (1ll << 31), "three_interpolate_grad: too many rows");
+    kernel<<<static_cast<unsigned>(grid), THREADS, smem, s>>>(c, m, n, grad_out, idx, weight, grad_points);
+    return check_launch("three_interpolate_grad");
+}
+
 // ------------------------------------------------------------------ backward, global atomics
 
 template <bool INTERP>
@@ -859,6 +927,17 @@ extern "C" int tpk_three_interpolate_grad(int b, int c, int n, int m, const floa
     TPK_REQUIRE(grad_out && idx && weight, "three_interpolate_grad: NULL pointer");
     TPK_REQUIRE(aligned16(grad_out) && aligned16(idx) && aligned16(weight),
                 "three_interpolate_grad: inputs must be 16-byte aligned");
+    if (static_cast<size_t>(m) * 4 * 4 <= 64 * 1024 && getenv("TPK_SCATTER_GLOBAL") == nullptr)
+    {
+        // 4 rows per CTA (8 when there are plenty of channels); block size follows the
+        // number of points a row has to stream
+        const bool many = static_cast<long long>(b) * c >= 16ll * num_sms() && static_cast<size_t>(m) * 4 * 8 <= 64 * 1024;
+        if (n >= 4096)
+            return many ? launch_interp_bwd_rows<8, 512>(b, c, m, n, grad_out, idx, weight, grad_points, s)
+                        : launch_interp_bwd_rows<4, 512>(b, c, m, n, grad_out, idx, weight, grad_points, s);
+        return many ? launch_interp_bwd_rows<8, 128>(b, c, m, n, grad_out, idx, weight, grad_points, s)
+                    : launch_interp_bwd_rows<4, 128>(b, c, m, n, grad_out, idx, weight, grad_points, s);
+    }
     return launch_scatter<true>(b, c, m, n, grad_out, idx, weight, grad_points, s,
                                 "three_interpolate_grad");
 }
