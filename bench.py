@@ -80,6 +80,7 @@ class Pipeline:
                           for c, m in zip(LEVELS["channels"], LEVELS["npoint"])]
         self.g_up = [torch.randn(B, c, n, device=dev, generator=g) for c, n in zip(LEVELS["channels"], n_in)]
         self.launches = 0
+        self.keep = None
 
     def step(self, xyz, sa_feat, fp_feat, overlap=True, timers=None, pipelined=False, ready=None):
         """xyz (B,N,3), sa_feat[l] (B,C_l,N_l), fp_feat[l] (B,C_l,M_l) on the device.
@@ -112,8 +113,11 @@ class Pipeline:
             return out
 
         def hand_over(t, *streams):
-            # the caching allocator must not recycle t while another stream still reads it
-            if overlap:
+            # the caching allocator must not recycle t while another stream still reads it;
+            # under graph capture every intermediate is simply kept alive for the whole step
+            if self.keep is not None:
+                self.keep.append(t)
+            elif overlap:
                 for st in streams:
                     t.record_stream(st)
             return t
@@ -173,6 +177,33 @@ class Pipeline:
             cur.wait_stream(s_geo)
             cur.wait_stream(s_feat)
         return fps_idx, grads_sa, grads_fp, done
+
+
+class GraphedSteps:
+    """Three CUDA graphs of one whole step each (all three internal streams captured), replayed
+    in turn on three launch streams: no per-kernel host work, and consecutive steps still
+    overlap because they are launched on different streams."""
+
+    def __init__(self, pipe, dev, like, split):
+        self.slots = []
+        for _ in range(3):
+            ins = [torch.empty_like(t, device=dev) for t in like]
+            launch = torch.cuda.Stream(dev)
+            graph = torch.cuda.CUDAGraph()
+            pipe.keep = []
+            try:
+                with torch.cuda.graph(graph, stream=launch, capture_error_mode="thread_local"):
+                    fps_idx, g_sa, g_fp, _ = pipe.step(*split([t.detach() for t in ins]))
+                    chk = torch.stack([g.sum() for g in g_sa + g_fp])
+            finally:
+                keep, pipe.keep = pipe.keep, None
+            self.slots.append({"graph": graph, "ins": ins, "launch": launch, "fps_idx": fps_idx, "chk": chk,
+                               "keep": (keep, g_sa, g_fp)})
+
+    def load(self, tensors):
+        for slot in self.slots:
+            for dst, src in zip(slot["ins"], tensors):
+                dst.copy_(src)
 
 
 def pipeline_work(B, N):
@@ -294,6 +325,30 @@ def run_b200(args, rank, world, local_rank):
 
     run_resident(args.warmup, True)
     torch.cuda.synchronize(dev)
+    graphs, graph_error = None, None
+    if not args.no_graphs:
+        try:
+            graphs = GraphedSteps(pipe, dev, dev_in, split)
+            graphs.load(dev_in)
+            torch.cuda.synchronize(dev)
+        except Exception as e:  # fall back to eager launches, and say so in the JSON line
+            graphs = None
+            graph_error = "%s: %s" % (type(e).__name__, str(e).splitlines()[0][:200])
+            torch.cuda.synchronize(dev)
+
+    def run_graphs(k):
+        t0 = time.perf_counter()
+        for i in range(k):
+            slot = graphs.slots[i % 3]
+            with torch.cuda.stream(slot["launch"]):
+                slot["graph"].replay()
+        pipe.host_ms = (time.perf_counter() - t0) * 1e3 / max(k, 1)
+        for slot in graphs.slots:
+            cur.wait_stream(slot["launch"])
+
+    if graphs is not None:
+        run_graphs(args.warmup)
+        torch.cuda.synchronize(dev)
     stop = threading.Event()
     clock_file = os.path.join(tempfile.gettempdir(), "tpk_clocks_%d.csv" % rank)
     sampler = threading.Thread(target=sample_clocks, args=(stop, clock_file, local_rank), daemon=True)
@@ -304,7 +359,13 @@ def run_b200(args, rank, world, local_rank):
     pipe.launches = 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    run_resident(args.steps, True)
+    if graphs is not None:
+        for slot in graphs.slots:
+            slot["launch"].wait_stream(cur)
+        run_graphs(args.steps)
+        pipe.launches = 28 * args.steps
+    else:
+        run_resident(args.steps, True)
     e1.record()
     barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
@@ -314,7 +375,15 @@ def run_b200(args, rank, world, local_rank):
     # the same without overlap between consecutive steps (latency of one isolated step)
     barrier()
     e0.record()
-    run_resident(args.steps, False)
+    if graphs is not None:
+        slot = graphs.slots[0]
+        slot["launch"].wait_stream(cur)
+        with torch.cuda.stream(slot["launch"]):
+            for _ in range(args.steps):
+                slot["graph"].replay()
+        cur.wait_stream(slot["launch"])
+    else:
+        run_resident(args.steps, False)
     e1.record()
     barrier()
     ms_isolated = max_over_ranks(e0.elapsed_time(e1))
@@ -358,6 +427,25 @@ def run_b200(args, rank, world, local_rank):
         cur.wait_stream(pipe.s_feat)
         return out_bufs[(k - 1) % 3]
 
+    def run_e2e_graphs(k):
+        for slot in graphs.slots:
+            slot["launch"].wait_stream(cur)
+        for i in range(k):
+            slot = graphs.slots[i % 3]
+            bufs = out_bufs[i % 3]
+            with torch.cuda.stream(slot["launch"]):
+                for dst, src in zip(slot["ins"], pinned):
+                    dst.copy_(src, non_blocking=True)
+                slot["graph"].replay()
+                for src, dst in zip(slot["fps_idx"], bufs[:4]):
+                    dst.copy_(src, non_blocking=True)
+                bufs[4].copy_(slot["chk"], non_blocking=True)
+        for slot in graphs.slots:
+            cur.wait_stream(slot["launch"])
+        return out_bufs[(k - 1) % 3]
+
+    if graphs is not None:
+        run_e2e = run_e2e_graphs
     run_e2e(max(2, args.warmup // 2))
     barrier()
     e0.record()
@@ -419,6 +507,8 @@ def run_b200(args, rank, world, local_rank):
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(ms_e2e / args.steps, 4)},
         "gpu_launches": launches,
         "host_enqueue_ms_per_step": round(host_ms, 3),
+        "launch_mode": "cuda graphs (one per step, three in rotation)" if graphs is not None else "eager",
+        "graph_error": graph_error,
         "clocks": clocks,
         "roofline": roof,
         "kernels": kernels,
@@ -493,7 +583,7 @@ def cpu_inputs(sample_clouds):
     return xyz, sa, fp, g_grouped, g_up
 
 
-def cpu_baseline_sample(sample_clouds=1):
+def cpu_baseline_sample(sample_clouds=16):
     ref = load_reference_cpu()
     ins = cpu_inputs(sample_clouds)
     t0 = time.perf_counter()
@@ -501,7 +591,7 @@ def cpu_baseline_sample(sample_clouds=1):
     dt = time.perf_counter() - t0
     return {"value": round(sample_clouds / dt, 4), "unit": "clouds/s", "cores": torch.get_num_threads(),
             "kind": "reference" if ref is not None else "port",
-            "sample": "%d of the 16 clouds of one step (N=16384, all four SA/FP levels, fwd+bwd), one pass, %.1f s"
+            "sample": "%d clouds = one full step (N=16384, all four SA/FP levels, fwd+bwd), one pass, %.1f s"
                       % (sample_clouds, dt)}
 
 
@@ -751,6 +841,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from Python instead of replaying CUDA graphs")
     args = ap.parse_args()
     if args.impl == "b200" and not args.only and args.workload == "sa_fp_pipeline":
         args.warmup = max(args.warmup, 3)
