@@ -9,7 +9,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libtpk_b200.so")
+# TPK_B200_LIB points at another build of the library (e.g. one made with different tuning flags)
+LIB_PATH = os.environ.get("TPK_B200_LIB") or os.path.join(_HERE, "libtpk_b200.so")
 
 _lib = None
 

@@ -39,7 +39,11 @@ namespace tpk
 constexpr int kScanTile = 1024;
 constexpr int kScanTileFloats = 4 * kScanTile;
 constexpr float kFilterSlack = 7.62939453125e-06f;  // 2^-17
-constexpr int kPendCap = 16;  // parked pairs per thread between two exact-test batches
+#ifndef TPK_SCAN_BATCH
+#define TPK_SCAN_BATCH 2
+#endif
+constexpr int kScanBatch = TPK_SCAN_BATCH;  // blocks of four candidates per filter branch
+constexpr int kPendCap = 8 * kScanBatch + 8;  // parked pairs per thread between two exact-test batches
 
 __device__ __forceinline__ unsigned long long pack2(float lo, float hi)
 {
@@ -130,8 +134,8 @@ __device__ __forceinline__ void scan_candidates(const float* __restrict__ cand, 
 
     // pairs that passed the filter and wait for the exact test: entry e of this thread at
     // [e * THREADS + tid]
-    __shared__ uint32_t s_pend[kPendCap * THREADS];
-    uint32_t* pend = s_pend + tid;
+    __shared__ uint16_t s_pend[kPendCap * THREADS];
+    uint16_t* pend = s_pend + tid;
     int npend = 0;
     bool done = op.finished();
     // Exact test of all parked pairs of the warp, every lane in its own (index) order.
@@ -179,25 +183,31 @@ __device__ __forceinline__ void scan_candidates(const float* __restrict__ cand, 
         for (int chunk = 0; chunk < kScanTile / 64; ++chunk)
         {
             if (__all_sync(kFullMask, done)) break;
-#pragma unroll 2
-            for (int g = chunk * 16; g < chunk * 16 + 16; ++g)
+            // kScanBatch blocks of four candidates per branch: independent FMA chains
+            // for the scheduler, one vote for all of them
+            for (int g0 = chunk * 16; g0 < chunk * 16 + 16; g0 += kScanBatch)
             {
-                const ulonglong2 X = s2[4 * g + 0];
-                const ulonglong2 Y = s2[4 * g + 1];
-                const ulonglong2 Z = s2[4 * g + 2];
-                const ulonglong2 W = s2[4 * g + 3];
-                float a[Q][4];
+                float a[Q][4 * kScanBatch];
                 bool any = false;
 #pragma unroll
-                for (int q = 0; q < Q; ++q)
+                for (int u = 0; u < kScanBatch; ++u)
                 {
-                    const unsigned long long a01 = fma2(m2x[q], X.x, fma2(m2y[q], Y.x, fma2(m2z[q], Z.x, W.x)));
-                    const unsigned long long a23 = fma2(m2x[q], X.y, fma2(m2y[q], Y.y, fma2(m2z[q], Z.y, W.y)));
-                    a[q][0] = lo_f32(a01);
-                    a[q][1] = hi_f32(a01);
-                    a[q][2] = lo_f32(a23);
-                    a[q][3] = hi_f32(a23);
-                    any |= (a[q][0] <= T[q]) | (a[q][1] <= T[q]) | (a[q][2] <= T[q]) | (a[q][3] <= T[q]);
+                    const ulonglong2 X = s2[4 * (g0 + u) + 0];
+                    const ulonglong2 Y = s2[4 * (g0 + u) + 1];
+                    const ulonglong2 Z = s2[4 * (g0 + u) + 2];
+                    const ulonglong2 W = s2[4 * (g0 + u) + 3];
+#pragma unroll
+                    for (int q = 0; q < Q; ++q)
+                    {
+                        const unsigned long long a01 = fma2(m2x[q], X.x, fma2(m2y[q], Y.x, fma2(m2z[q], Z.x, W.x)));
+                        const unsigned long long a23 = fma2(m2x[q], X.y, fma2(m2y[q], Y.y, fma2(m2z[q], Z.y, W.y)));
+                        a[q][4 * u + 0] = lo_f32(a01);
+                        a[q][4 * u + 1] = hi_f32(a01);
+                        a[q][4 * u + 2] = lo_f32(a23);
+                        a[q][4 * u + 3] = hi_f32(a23);
+                        any |= (a[q][4 * u + 0] <= T[q]) | (a[q][4 * u + 1] <= T[q]) |
+                               (a[q][4 * u + 2] <= T[q]) | (a[q][4 * u + 3] <= T[q]);
+                    }
                 }
                 // warp-uniform branch: every lane enters, so the votes inside are convergent
                 if (__any_sync(kFullMask, any))
@@ -206,19 +216,19 @@ __device__ __forceinline__ void scan_candidates(const float* __restrict__ cand, 
                     // they are examined in batches, with most lanes of the warp busy, instead
                     // of one at a time with one lane busy
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
+                    for (int i = 0; i < 4 * kScanBatch; ++i)
                     {
 #pragma unroll
                         for (int q = 0; q < Q; ++q)
                         {
                             if (a[q][i] <= T[q])
                             {
-                                pend[npend * THREADS] = static_cast<uint32_t>(((4 * g + i) << 1) | q);
+                                pend[npend * THREADS] = static_cast<uint16_t>(((4 * g0 + i) << 1) | q);
                                 ++npend;
                             }
                         }
                     }
-                    if (__any_sync(kFullMask, npend > kPendCap - 4 * Q)) flush(t);
+                    if (__any_sync(kFullMask, npend > kPendCap - 4 * kScanBatch * Q)) flush(t);
                 }
             }
         }
