@@ -64,13 +64,16 @@ def test_fps_matches_oracle(B, N, m):
 @pytest.mark.parametrize("cfg", ["1,128,32", "1,512,8", "1,256,16", "2,64,32", "2,512,4", "4,64,16",
                                  "4,256,4", "8,128,4", "8,64,8", "8,512,1", "16,64,4", "16,512,1",
                                  "16,128,2"])
-def test_fps_every_cluster_shape(cfg, fps_env):
-    """Same cloud through every cluster size / block size (cluster x threads x points per thread)."""
+def test_fps_every_cluster_shape(cfg, fps_env, monkeypatch):
+    """Same cloud through every cluster size / block size (cluster x threads x points per thread),
+    with the flat and with the three-stage exchange."""
     x = data.unit_ball(3, 4000, seed=77)
     want = orc.fps(x, 300)
     os.environ["TPK_FPS_CONFIG"] = cfg
-    got = npy(tpk.furthest_point_sample(cu(x), 300))
-    np.testing.assert_array_equal(got, want)
+    for flat in ("1", "0"):
+        monkeypatch.setenv("TPK_FPS_FLAT", flat)
+        got = npy(tpk.furthest_point_sample(cu(x), 300))
+        np.testing.assert_array_equal(got, want)
     assert _lib.device_status() == 0
 
 
