@@ -406,3 +406,37 @@ def test_config1_plumbing_end_to_end():
     w = w / w.sum(2, keepdim=True)
     out = tpk.three_interpolate(cu(feat), i3, w.contiguous())
     np.testing.assert_allclose(npy(out), orc.three_interpolate(feat, oi3, npy(w)), rtol=1e-5, atol=1e-6)
+
+
+# ------------------------------------------------------------------ empty and degenerate inputs
+
+def test_empty_and_degenerate_inputs():
+    z3 = torch.zeros((0, 16, 3), device=DEV)
+    assert tuple(tpk.furthest_point_sample(z3, 4).shape) == (0, 4)
+    x = cu(data.unit_ball(2, 64, seed=1))
+    # npoint == N: every valid point is selected exactly once before repeats start
+    idx = npy(tpk.furthest_point_sample(x, 64))
+    np.testing.assert_array_equal(idx, orc.fps(x.cpu(), 64))
+    # no centres / no candidates / nsample 0
+    i, d = tpk.ball_query(0.5, 8, x, torch.zeros((2, 0, 3), device=DEV))
+    assert tuple(i.shape) == (2, 0, 8) and tuple(d.shape) == (2, 0, 8)
+    i, d = tpk.ball_query(0.5, 8, torch.zeros((2, 0, 3), device=DEV), x[:, :5].contiguous())
+    assert (npy(i) == 0).all() and (npy(d) == -1).all()
+    i, d = tpk.ball_query(0.5, 4, torch.zeros((0, 3), device=DEV), x[0, :5].contiguous(), mode="partial_dense",
+                          batch_x=torch.zeros((0,), dtype=torch.long, device=DEV),
+                          batch_y=torch.zeros((5,), dtype=torch.long, device=DEV))
+    assert (npy(i) == -1).all() and (npy(d) == -1).all()
+    # three_nn with no known points: +inf distances, index 0
+    dist, i3 = tpk.three_nn(x, torch.zeros((2, 0, 3), device=DEV))
+    assert np.isinf(npy(dist)).all() and (npy(i3) == 0).all()
+    # grouping / interpolation with empty outputs, gradient of an empty grouping is zero
+    f = cu(torch.randn(2, 3, 64)).requires_grad_(True)
+    g = tpk.grouping_operation(f, torch.zeros((2, 0, 4), dtype=torch.long, device=DEV))
+    assert tuple(g.shape) == (2, 3, 0, 4)
+    g.sum().backward()
+    assert (npy(f.grad) == 0).all()
+    # chamfer against an empty cloud: the reference leaves zeros
+    d1, d2 = cd.ChamferFunction.apply(x, torch.zeros((2, 0, 3), device=DEV))
+    assert (npy(d1) == 0).all() and tuple(d2.shape) == (2, 0)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
