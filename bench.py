@@ -224,6 +224,17 @@ def pipeline_work(B, N):
     return w
 
 
+# DRAM bytes (read + write) per launch of the HBM-bound kernels at the bench's shapes, from the
+# ncu captures summarised under profiles/ (taken with 4 clouds, scaled x4 to the bench's 16:
+# traffic grows in proportion to the number of clouds).
+NCU_TRAFFIC_BYTES = {
+    "grouping_bwd_l1": 4 * (138470400 + 3958272),
+    "grouping_fwd_l1": 4 * (20982784 + 76009472),
+    "interp_fwd_l1": 4 * (5781248 + 0),
+    "interp_bwd_l1": 4 * (18360064 + 0),
+}
+
+
 def sample_clocks(stop, path, dev_index):
     q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -487,7 +498,8 @@ def run_b200(args, rank, world, local_rank):
         kernels[name] = entry
     dom = max((k for k in kernels if kernels[k]["bound"] == "hbm"), key=lambda k: kms[k])
     roof = {"kernel": dom, "bound": "hbm", "achieved": kernels[dom]["achieved_gbs"], "peak": hbm_peak,
-            "peak_source": peak_kind, "unit": "GB/s", "frac": kernels[dom]["frac"], "traffic": None,
+            "peak_source": peak_kind, "unit": "GB/s", "frac": kernels[dom]["frac"], "traffic": NCU_TRAFFIC_BYTES.get(dom),
+            "algorithmic_bytes": work[dom][1],
             "time_dominant_kernel": max(kms, key=kms.get)}
     clouds = B * world
     line = {
