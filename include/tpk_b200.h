@@ -111,6 +111,20 @@ TPK_API int tpk_ball_query_dense(int b, int n, int m, float radius, int nsample,
                          const float* xyz, int64_t* idx, float* dist, void* stream);
 
 /*
+ * The same search with caller scratch: clouds are binned into a uniform grid (cells at
+ * least one radius wide) and a centre only examines the 27 cells around it; centres in
+ * very dense neighbourhoods, for which the early-exit scan is cheaper, fall through to
+ * the scan.  Results are identical to tpk_ball_query_dense bit for bit.
+ * scratch: tpk_ball_query_dense_scratch_bytes(b,n,m,nsample) bytes, 256-byte aligned;
+ * when that returns 0 (small clouds, nsample > 128) or scratch is NULL the call is
+ * tpk_ball_query_dense.  No counterpart in the reference.
+ */
+TPK_API int tpk_ball_query_dense_ws(int b, int n, int m, float radius, int nsample,
+                                    const float* new_xyz, const float* xyz, int64_t* idx, float* dist,
+                                    void* scratch, int64_t scratch_bytes, void* stream);
+TPK_API int64_t tpk_ball_query_dense_scratch_bytes(int b, int n, int m, int nsample);
+
+/*
  * Radius search on packed segments.  x (size_x,3) candidates, y (size_y,3) centres,
  * batch_x (size_x) / batch_y (size_y) sorted int64 segment ids ->
  * idx (size_y,nsample) int64 positions in x, dist (size_y,nsample) f32; test is

@@ -156,6 +156,40 @@ def test_ball_query_dense_matches_oracle(B, N, M, r, ns):
     same_bits(npy(dist), od)
 
 
+@pytest.mark.parametrize("case", ["uniform", "blobs", "offset", "flat", "far_queries", "ns1", "ns100"])
+def test_ball_query_dense_grid_path_matches_oracle(case, monkeypatch):
+    """Clouds large enough for the uniform-grid search: same bits as the oracle (and as the scan),
+    including centres handed back to the scan (dense blobs) and degenerate grids."""
+    g = data.gen(hash(case) % 1000)
+    B, N, M, r, ns = 3, 9000, 700, 0.07, 32
+    if case == "blobs":
+        x = data.gaussian_mixture(B, N, seed=11, comps=6)
+        r = 0.05
+    else:
+        x = data.unit_ball(B, N, seed=12)
+    if case == "offset":
+        x = (x + torch.tensor([1000.0, -500.0, 250.0])).contiguous()
+    if case == "flat":
+        x[..., 2] = 0.25
+    y = x[:, torch.randperm(N, generator=g)[:M]].contiguous()
+    if case == "far_queries":
+        y = (y + 3.0).contiguous()
+        y[:, :50] = x[:, :50]
+    if case == "ns1":
+        ns = 1
+    if case == "ns100":
+        ns, r = 100, 0.2
+    assert _lib.lib().tpk_ball_query_dense_scratch_bytes(B, N, M, ns) > 0
+    idx, dist = tpk.ball_query(r, ns, cu(x), cu(y), mode="dense")
+    oi, od = orc.ball_query_dense(r, ns, x, y)
+    np.testing.assert_array_equal(npy(idx), oi)
+    same_bits(npy(dist), od)
+    monkeypatch.setenv("TPK_BALL_QUERY_SCAN", "1")
+    idx2, dist2 = tpk.ball_query(r, ns, cu(x), cu(y), mode="dense")
+    np.testing.assert_array_equal(npy(idx2), oi)
+    same_bits(npy(dist2), od)
+
+
 def test_ball_query_dense_boundary_is_strict_partial_is_inclusive():
     x = np.array([[[0, 0, 0], [0.5, 0, 0], [0.25, 0, 0]]], np.float32)
     y = np.array([[[0, 0, 0]]], np.float32)

@@ -16,6 +16,12 @@
 
 namespace tpk
 {
+// grid_query.cu
+size_t grid_scratch_bytes(int b, int n, int m);
+int grid_ball_query_dense(int b, int n, int m, float radius, int nsample, const float* new_xyz,
+                          const float* xyz, int64_t* idx, float* dist, void* scratch,
+                          const unsigned char** need_scan_out, cudaStream_t s);
+
 namespace
 {
 
@@ -63,7 +69,8 @@ template <int THREADS, int Q>
 __global__ void __launch_bounds__(THREADS)
     ball_query_dense_kernel(int n, int m, int tiles_per_cloud, float radius, int nsample,
                             const float* __restrict__ new_xyz, const float* __restrict__ xyz,
-                            int64_t* __restrict__ idx_out, float* __restrict__ dist_out)
+                            int64_t* __restrict__ idx_out, float* __restrict__ dist_out,
+                            const unsigned char* __restrict__ need)
 {
     __shared__ __align__(16) float smem[2 * kScanTileFloats];
     const int cloud = blockIdx.x / tiles_per_cloud;
@@ -78,7 +85,8 @@ __global__ void __launch_bounds__(THREADS)
     for (int q = 0; q < Q; ++q)
     {
         const int j = qtile * (THREADS * Q) + q * THREADS + threadIdx.x;
-        op.act[q] = j < m;
+        // `need` (optional): one byte per centre, 0 = already answered by the grid path
+        op.act[q] = j < m && (need == nullptr || need[static_cast<size_t>(cloud) * m + j] != 0);
         op.cnt[q] = 0;
         op.first[q] = 0;
         const size_t row = static_cast<size_t>(cloud) * m + (op.act[q] ? j : 0);
@@ -235,7 +243,47 @@ extern "C" int tpk_ball_query_dense(int b, int n, int m, float radius, int nsamp
     const long long grid = static_cast<long long>(b) * tiles;
     TPK_REQUIRE(grid < (1ll << 31), "ball_query_dense: too many centres");
     const dim3 g(static_cast<unsigned>(grid));
-    TPK_BQ_DISPATCH(ball_query_dense_kernel, n, m, tiles, radius, nsample, new_xyz, xyz, idx, dist);
+    const unsigned char* need = nullptr;
+    TPK_BQ_DISPATCH(ball_query_dense_kernel, n, m, tiles, radius, nsample, new_xyz, xyz, idx, dist, need);
+    return check_launch("ball_query_dense");
+}
+
+extern "C" int64_t tpk_ball_query_dense_scratch_bytes(int b, int n, int m, int nsample)
+{
+    // the grid path needs clouds worth binning and a hit list that fits shared memory
+    if (b <= 0 || m <= 0 || n < 8192 || nsample <= 0 || nsample > 128) return 0;
+    return static_cast<int64_t>(tpk::grid_scratch_bytes(b, n, m));
+}
+
+extern "C" int tpk_ball_query_dense_ws(int b, int n, int m, float radius, int nsample,
+                                       const float* new_xyz, const float* xyz, int64_t* idx,
+                                       float* dist, void* scratch, int64_t scratch_bytes,
+                                       void* stream)
+{
+    using namespace tpk;
+    const int64_t want = tpk_ball_query_dense_scratch_bytes(b, n, m, nsample);
+    if (want == 0 || scratch == nullptr)
+        return tpk_ball_query_dense(b, n, m, radius, nsample, new_xyz, xyz, idx, dist, stream);
+    if (scratch_bytes < want)
+    {
+        set_error("ball_query_dense: scratch of %lld bytes given, %lld needed",
+                  static_cast<long long>(scratch_bytes), static_cast<long long>(want));
+        return TPK_ERR_SCRATCH;
+    }
+    TPK_REQUIRE(new_xyz && xyz && idx && dist, "ball_query_dense: NULL pointer");
+    TPK_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "ball_query_dense: scratch must be 256-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned char* need = nullptr;
+    int rc = grid_ball_query_dense(b, n, m, radius, nsample, new_xyz, xyz, idx, dist, scratch, &need, s);
+    if (rc != TPK_OK) return rc;
+    // centres the grid left over (dense neighbourhoods, degenerate clouds): index-order scan
+    int threads, q;
+    pick_shape(static_cast<long long>(b) * m, &threads, &q);
+    const int tiles = (m + threads * q - 1) / (threads * q);
+    const long long grid = static_cast<long long>(b) * tiles;
+    TPK_REQUIRE(grid < (1ll << 31), "ball_query_dense: too many centres");
+    const dim3 g(static_cast<unsigned>(grid));
+    TPK_BQ_DISPATCH(ball_query_dense_kernel, n, m, tiles, radius, nsample, new_xyz, xyz, idx, dist, need);
     return check_launch("ball_query_dense");
 }
 

@@ -5,6 +5,7 @@ torch_points_kernels/torchpoints.py of the reference; every op runs a hand-writt
 sm_100a kernel through the C ABI in include/tpk_b200.h.  Tensors must live on a CUDA
 device: there is no CPU path.
 """
+import os
 from typing import Optional
 
 import torch
@@ -207,8 +208,16 @@ def ball_query_dense(radius, nsample, xyz, new_xyz, batch_xyz=None, batch_new_xy
     idx = torch.empty((b, m, nsample), dtype=torch.int64, device=new_xyz.device)
     dist = torch.empty((b, m, nsample), dtype=torch.float32, device=new_xyz.device)
     with torch.cuda.device(new_xyz.device):
-        _lib.call("tpk_ball_query_dense", b, n, m, float(radius), int(nsample), _lib.ptr(new_xyz),
-                  _lib.ptr(xyz), _lib.ptr(idx), _lib.ptr(dist), _lib.stream_of(new_xyz))
+        need = _lib.lib().tpk_ball_query_dense_scratch_bytes(b, n, m, int(nsample))
+        if need > 0 and not os.environ.get("TPK_BALL_QUERY_SCAN"):
+            # large clouds: uniform-grid search with scratch (same results as the scan)
+            scratch = torch.empty((need,), dtype=torch.uint8, device=new_xyz.device)
+            _lib.call("tpk_ball_query_dense_ws", b, n, m, float(radius), int(nsample), _lib.ptr(new_xyz),
+                      _lib.ptr(xyz), _lib.ptr(idx), _lib.ptr(dist), _lib.ptr(scratch), need,
+                      _lib.stream_of(new_xyz))
+        else:
+            _lib.call("tpk_ball_query_dense", b, n, m, float(radius), int(nsample), _lib.ptr(new_xyz),
+                      _lib.ptr(xyz), _lib.ptr(idx), _lib.ptr(dist), _lib.stream_of(new_xyz))
     return idx, dist
 
 
