@@ -151,6 +151,18 @@ TPK_API int tpk_three_nn(int b, int n, int m, const float* unknown, const float*
                  int32_t* idx, void* stream);
 
 /*
+ * The same search with caller scratch: the known points of every cloud are binned into a
+ * uniform grid and a query grows a block of cells around itself until its third-best
+ * distance is provably final.  Results are identical to tpk_three_nn bit for bit.
+ * scratch: tpk_three_nn_scratch_bytes(b,n,m) bytes, 256-byte aligned; when that returns
+ * 0 (fewer than 4096 known points per cloud) or scratch is NULL the call is tpk_three_nn.
+ * No counterpart in the reference.
+ */
+TPK_API int tpk_three_nn_ws(int b, int n, int m, const float* unknown, const float* known, float* dist2,
+                            int32_t* idx, void* scratch, int64_t scratch_bytes, void* stream);
+TPK_API int64_t tpk_three_nn_scratch_bytes(int b, int n, int m);
+
+/*
  * k nearest support points per query.  support (b,n,3), query (b,m,3) ->
  * idx (b,m,k) int64, dist2 (b,m,k) f32, ascending squared distance evaluated
  * unfused as ((dx*dx)+dy*dy)+dz*dz; equal distances keep index order.

@@ -261,6 +261,56 @@ def test_three_nn_duplicates_keep_lowest_index_first():
     np.testing.assert_array_equal(npy(idx), oi)
 
 
+def _three_nn_grid_cases():
+    rng = np.random.default_rng(77)
+    cases = {}
+    cases["uniform"] = (data.unit_ball(3, 6000, seed=11), data.unit_ball(3, 8192, seed=12))
+    # queries far outside the bounding box of the known points, and on its faces
+    u = data.unit_ball(2, 3000, seed=13) * 4.0
+    u[:, :50] = 1.0
+    cases["outside"] = (u, data.unit_ball(2, 4096, seed=14))
+    # clustered known points: most cells empty, a few crowded; many exact duplicates
+    k = (rng.standard_normal((2, 5000, 3)) * 0.01 + rng.integers(0, 3, (2, 5000, 1))).astype(np.float32)
+    k[:, 1000:1600] = k[:, :600]
+    cases["clustered_duplicates"] = (rng.uniform(-1, 4, (2, 2500, 3)).astype(np.float32), k)
+    # known points on a plane (one grid dimension collapses) and on a coarse lattice (ties)
+    k = rng.uniform(0, 1, (2, 4500, 3)).astype(np.float32)
+    k[..., 2] = 0.25
+    cases["planar"] = (rng.uniform(0, 1, (2, 2000, 3)).astype(np.float32), k)
+    k = rng.integers(0, 12, (1, 6000, 3)).astype(np.float32) / 4
+    cases["lattice_ties"] = (rng.integers(0, 24, (1, 3000, 3)).astype(np.float32) / 8, k)
+    # the PointNet++ shape: upsampling 4096 -> 16384
+    x = data.unit_ball(2, 16384, seed=15)
+    cases["upsample"] = (x, np.ascontiguousarray(x[:, ::4]))
+    return cases
+
+
+@pytest.mark.parametrize("name", ["uniform", "outside", "clustered_duplicates", "planar", "lattice_ties", "upsample"])
+def test_three_nn_grid_path_matches_oracle(name):
+    unknown, known = _three_nn_grid_cases()[name]
+    b, n, m = unknown.shape[0], unknown.shape[1], known.shape[1]
+    assert _lib.lib().tpk_three_nn_scratch_bytes(b, n, m) > 0  # the grid path is the one tested
+    dist, idx = tpk.three_nn(cu(unknown), cu(known))
+    od2, oi = orc.three_nn(unknown, known)
+    np.testing.assert_array_equal(npy(idx), oi)
+    same_bits(npy(dist), np.sqrt(od2))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+
+
+def test_three_nn_grid_path_nonfinite_falls_back_to_scan():
+    unknown = data.unit_ball(2, 1500, seed=21)
+    known = data.unit_ball(2, 4096, seed=22)
+    unknown[0, 7, 1] = np.inf
+    unknown[1, 9, 0] = np.nan
+    known[1, 100, 2] = np.inf  # cloud 1: no grid at all
+    dist, idx = tpk.three_nn(cu(unknown), cu(known))
+    od2, oi = orc.three_nn(unknown, known)
+    np.testing.assert_array_equal(npy(idx), oi)
+    with np.errstate(invalid="ignore"):
+        same_bits(npy(dist), np.sqrt(od2))
+
+
 def test_knn_known_answer(known_answers):
     ka = known_answers["knn"]
     s, q = cu(np.asarray(ka["support"], np.float32)), cu(np.asarray(ka["query"], np.float32))

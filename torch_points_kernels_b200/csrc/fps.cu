@@ -170,6 +170,36 @@ __device__ __forceinline__ int warp_argmax(int key, int k, int log2bs)
 //      then polls its own CTA's barrier (with a time limit) and reduces the messages.
 // The round loop is unrolled by two so that the double-buffered message slots and
 // barriers have compile-time addresses.  A CTA has at least two warps.
+// packed pairs of floats for the two-wide FP32 instructions of sm_100
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi)
+{
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b)
+{
+    unsigned long long r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b)
+{
+    unsigned long long r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c)
+{
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
 template <int PPT, bool CLUSTERED>
 __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
     fps_onchip_kernel(int n, int m, int log2bs, int flat, const float* __restrict__ xyz_all,
@@ -283,9 +313,30 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
             mbar_arrive_expect_tx(smem_u32(mbar + PAR), static_cast<uint32_t>(nslots * kMsgBytes));
 
         // ---- every point: distance to the newest sample, running minimum, thread maximum
+        if constexpr (PPT >= 2)
+        {
+            // two points per packed instruction; x + (-c) rounds like x - c, and
+            // mul, fma, fma is the operation order of sumsq_abc
+            const unsigned long long ncx = pack2(-cx, -cx), ncy = pack2(-cy, -cy), ncz = pack2(-cz, -cz);
 #pragma unroll
-        for (int p = 0; p < PPT; ++p)
-            md[p] = fminf(sumsq_abc(px[p] - cx, py[p] - cy, pz[p] - cz), md[p]);
+            for (int p = 0; p < PPT; p += 2)
+            {
+                const unsigned long long dx = add2(pack2(px[p], px[p + 1]), ncx);
+                const unsigned long long dy = add2(pack2(py[p], py[p + 1]), ncy);
+                const unsigned long long dz = add2(pack2(pz[p], pz[p + 1]), ncz);
+                const unsigned long long d = fma2(dz, dz, fma2(dx, dx, mul2(dy, dy)));
+                float d0, d1;
+                unpack2(d, d0, d1);
+                md[p] = fminf(d0, md[p]);
+                md[p + 1] = fminf(d1, md[p + 1]);
+            }
+        }
+        else
+        {
+#pragma unroll
+            for (int p = 0; p < PPT; ++p)
+                md[p] = fminf(sumsq_abc(px[p] - cx, py[p] - cy, pz[p] - cz), md[p]);
+        }
         float red[PPT];
 #pragma unroll
         for (int p = 0; p < PPT; ++p) red[p] = md[p];
@@ -369,22 +420,22 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
                 failed = true;
             }
             int key3 = INT_MIN, k3 = 0;
-            float x3 = 0.f, y3 = 0.f, z3 = 0.f;
             if (lane < nslots)
             {
-                const uint4 a = cmsg_a[PAR * 32 + lane];
+                const uint2 a = *reinterpret_cast<const uint2*>(cmsg_a + PAR * 32 + lane);
                 key3 = static_cast<int>(a.x);
                 k3 = static_cast<int>(a.y);
-                x3 = __uint_as_float(a.z);
-                y3 = __uint_as_float(a.w);
-                z3 = cmsg_z[PAR * 32 + lane];
             }
+            // every lane reads the winning slot itself (two broadcast loads instead of five
+            // shuffles); the slot is not rewritten before all warps of the cluster have
+            // sent their messages of the next round, i.e. after this read
             const int src = warp_argmax(key3, k3, log2bs);
-            msg.key = __shfl_sync(kFullMask, key3, src);
-            msg.k = __shfl_sync(kFullMask, k3, src);
-            msg.x = __shfl_sync(kFullMask, x3, src);
-            msg.y = __shfl_sync(kFullMask, y3, src);
-            msg.z = __shfl_sync(kFullMask, z3, src);
+            const uint4 win = cmsg_a[PAR * 32 + src];
+            msg.key = static_cast<int>(win.x);
+            msg.k = static_cast<int>(win.y);
+            msg.x = __uint_as_float(win.z);
+            msg.y = __uint_as_float(win.w);
+            msg.z = cmsg_z[PAR * 32 + src];
         }
 
         cx = msg.x;

@@ -316,6 +316,122 @@ __global__ void __launch_bounds__(kGridQueryThreads)
     }
 }
 
+// Three nearest known points per unknown point on the grid of the known cloud: search
+// the 3x3x3 cell block around the query, then grow the block ring by ring until the third
+// best squared distance is smaller than the squared distance to the nearest face of the
+// block that still has cells behind it (or the block covers the grid).  Candidates are
+// compared as (distance, index) pairs, which is the order the reference's index-ordered
+// strict-'<' cascade produces.
+__global__ void __launch_bounds__(kGridQueryThreads)
+    grid_three_nn_kernel(int b, int n, int m, size_t cells_cap, const float* __restrict__ unknown,
+                         const GridInfo* __restrict__ info, const int* __restrict__ cells_all,
+                         const float4* __restrict__ sorted_all, float* __restrict__ dist2,
+                         int32_t* __restrict__ idx, unsigned char* __restrict__ need_scan)
+{
+    const long long t = static_cast<long long>(blockIdx.x) * kGridQueryThreads + threadIdx.x;
+    if (t >= static_cast<long long>(b) * n) return;
+    const int bi = static_cast<int>(t / n);
+    const GridInfo g = info[bi];
+    const float qx = __ldg(unknown + 3 * t + 0), qy = __ldg(unknown + 3 * t + 1), qz = __ldg(unknown + 3 * t + 2);
+    if (!g.use || !(fabsf(qx) < 1.0e18f && fabsf(qy) < 1.0e18f && fabsf(qz) < 1.0e18f))
+    {
+        need_scan[t] = 1;
+        return;
+    }
+    const int* cells = cells_all + static_cast<size_t>(bi) * (cells_cap + 1);
+    const float4* pts = sorted_all + static_cast<size_t>(bi) * m;
+    const float h = 1.0f / g.inv_h;
+    const int cx = cell_coord(qx, g.minx, g.inv_h, g.dx);
+    const int cy = cell_coord(qy, g.miny, g.inv_h, g.dy);
+    const int cz = cell_coord(qz, g.minz, g.inv_h, g.dz);
+
+    float b1 = CUDART_INF_F, b2 = CUDART_INF_F, b3 = CUDART_INF_F;
+    int i1 = 0x7fffffff, i2 = 0x7fffffff, i3 = 0x7fffffff;
+    int px0 = 0, px1 = -1, py0 = 0, py1 = -1, pz0 = 0, pz1 = -1;  // block already searched (empty)
+    const int max_ring = max(g.dx, max(g.dy, g.dz));
+    for (int ring = 1; ring <= max_ring; ++ring)
+    {
+        const int x0 = max(cx - ring, 0), x1 = min(cx + ring, g.dx - 1);
+        const int y0 = max(cy - ring, 0), y1 = min(cy + ring, g.dy - 1);
+        const int z0 = max(cz - ring, 0), z1 = min(cz + ring, g.dz - 1);
+        for (int z = z0; z <= z1; ++z)
+            for (int y = y0; y <= y1; ++y)
+            {
+                const bool inner_row = z >= pz0 && z <= pz1 && y >= py0 && y <= py1;
+                const int row = (z * g.dy + y) * g.dx;
+                // cells of this row not searched before: all of [x0,x1], or the two ends
+                for (int part = 0; part < 2; ++part)
+                {
+                    int xa, xb;
+                    if (!inner_row)
+                    {
+                        if (part == 1) break;
+                        xa = x0;
+                        xb = x1;
+                    }
+                    else if (part == 0)
+                    {
+                        xa = x0;
+                        xb = px0 - 1;
+                    }
+                    else
+                    {
+                        xa = px1 + 1;
+                        xb = x1;
+                    }
+                    if (xa > xb) continue;
+                    const int beg = __ldg(cells + row + xa), end = __ldg(cells + row + xb + 1);
+                    for (int p = beg; p < end; ++p)
+                    {
+                        const float4 c = __ldg(pts + p);
+                        const float d = sumsq_abc(qx - c.x, qy - c.y, qz - c.z);
+                        const int k = __float_as_int(c.w);
+                        if (d < b3 || (d == b3 && k < i3))
+                        {
+                            if (d < b1 || (d == b1 && k < i1))
+                            {
+                                b3 = b2; i3 = i2;
+                                b2 = b1; i2 = i1;
+                                b1 = d;  i1 = k;
+                            }
+                            else if (d < b2 || (d == b2 && k < i2))
+                            {
+                                b3 = b2; i3 = i2;
+                                b2 = d;  i2 = k;
+                            }
+                            else
+                            {
+                                b3 = d; i3 = k;
+                            }
+                        }
+                    }
+                }
+            }
+        px0 = x0; px1 = x1; py0 = y0; py1 = y1; pz0 = z0; pz1 = z1;
+        const bool whole = x0 == 0 && y0 == 0 && z0 == 0 && x1 == g.dx - 1 && y1 == g.dy - 1 && z1 == g.dz - 1;
+        if (whole) break;
+        // distance to the nearest face of the block with unsearched cells behind it
+        float rho = CUDART_INF_F;
+        if (x0 > 0) rho = fminf(rho, qx - (g.minx + x0 * h));
+        if (x1 < g.dx - 1) rho = fminf(rho, (g.minx + (x1 + 1) * h) - qx);
+        if (y0 > 0) rho = fminf(rho, qy - (g.miny + y0 * h));
+        if (y1 < g.dy - 1) rho = fminf(rho, (g.miny + (y1 + 1) * h) - qy);
+        if (z0 > 0) rho = fminf(rho, qz - (g.minz + z0 * h));
+        if (z1 < g.dz - 1) rho = fminf(rho, (g.minz + (z1 + 1) * h) - qz);
+        // faces are computed in floating point and points near a face may be binned on either
+        // side of it: take a margin of a thousandth of a cell plus the coordinate rounding
+        rho -= 1.0e-3f * h + 4.0e-7f * (fabsf(qx) + fabsf(qy) + fabsf(qz) + fabsf(g.minx) + fabsf(g.miny) + fabsf(g.minz));
+        if (rho > 0.f && b3 < rho * rho * 0.9999f) break;
+    }
+    need_scan[t] = 0;
+    dist2[3 * t + 0] = b1;
+    dist2[3 * t + 1] = b2;
+    dist2[3 * t + 2] = b3;
+    idx[3 * t + 0] = i1 == 0x7fffffff ? 0 : i1;
+    idx[3 * t + 1] = i2 == 0x7fffffff ? 0 : i2;
+    idx[3 * t + 2] = i3 == 0x7fffffff ? 0 : i3;
+}
+
 }  // namespace
 
 size_t grid_scratch_bytes(int b, int n, int m)
@@ -372,5 +488,42 @@ int grid_ball_query_dense(int b, int n, int m, float radius, int nsample, const 
     *need_scan_out = need;
     return check_launch("ball_query grid");
 }
+
+}  // namespace tpk
+
+namespace tpk
+{
+
+// Grid of the `m` known points of every cloud; answers the unknown points the grid is good for.
+int grid_three_nn(int b, int n, int m, const float* unknown, const float* known, float* dist2,
+                  int32_t* idx, void* scratch, const unsigned char** need_scan_out, cudaStream_t s)
+{
+    const size_t cap = grid_cells_capacity(m);
+    unsigned char* p = static_cast<unsigned char*>(scratch);
+    GridInfo* info = reinterpret_cast<GridInfo*>(p);
+    p += (static_cast<size_t>(b) * sizeof(GridInfo) + 255) / 256 * 256;
+    int* cells = reinterpret_cast<int*>(p);
+    p += (static_cast<size_t>(b) * (cap + 1) * sizeof(int) + 255) / 256 * 256;
+    float4* sorted = reinterpret_cast<float4*>(p);
+    p += (static_cast<size_t>(b) * m * sizeof(float4) + 255) / 256 * 256;
+    unsigned char* need = p;
+
+    const long long npts = static_cast<long long>(b) * m;
+    const unsigned gp = static_cast<unsigned>((npts + kGridThreads - 1) / kGridThreads);
+    // no radius here: cells as small as the capacity allows (radius argument just above zero)
+    grid_setup_kernel<<<b, kGridThreads, 0, s>>>(m, 1.0e-30f, grid_max_dim(m), cap, known, info, cells);
+    grid_bin_kernel<false><<<gp, kGridThreads, 0, s>>>(b, m, cap, known, info, cells, sorted);
+    grid_scan_kernel<<<b, 1024, 0, s>>>(cap, info, cells);
+    grid_bin_kernel<true><<<gp, kGridThreads, 0, s>>>(b, m, cap, known, info, cells, sorted);
+    const long long nq = static_cast<long long>(b) * n;
+    const unsigned gq = static_cast<unsigned>((nq + kGridQueryThreads - 1) / kGridQueryThreads);
+    prefer_max_shared(grid_three_nn_kernel);
+    grid_three_nn_kernel<<<gq, kGridQueryThreads, 0, s>>>(b, n, m, cap, unknown, info, cells, sorted, dist2, idx, need);
+    *need_scan_out = need;
+    return check_launch("three_nn grid");
+}
+
+// scratch for grid_three_nn: grid of m known points, one flag per unknown point
+size_t grid_three_nn_scratch_bytes(int b, int n, int m) { return grid_scratch_bytes(b, m, n); }
 
 }  // namespace tpk

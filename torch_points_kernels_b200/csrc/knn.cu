@@ -63,7 +63,7 @@ template <int THREADS, int Q>
 __global__ void __launch_bounds__(THREADS)
     three_nn_kernel(int n, int m, int tiles_per_cloud, const float* __restrict__ unknown,
                     const float* __restrict__ known, float* __restrict__ dist2,
-                    int32_t* __restrict__ idx)
+                    int32_t* __restrict__ idx, const unsigned char* __restrict__ need)
 {
     __shared__ __align__(16) float smem[2 * kScanTileFloats];
     const int cloud = blockIdx.x / tiles_per_cloud;
@@ -74,7 +74,8 @@ __global__ void __launch_bounds__(THREADS)
     for (int q = 0; q < Q; ++q)
     {
         const int j = qtile * (THREADS * Q) + q * THREADS + threadIdx.x;
-        op.act[q] = j < n;
+        // `need` (optional): one byte per query, 0 = already answered by the grid path
+        op.act[q] = j < n && (need == nullptr || need[static_cast<size_t>(cloud) * n + j] != 0);
         const size_t row = static_cast<size_t>(cloud) * n + (op.act[q] ? j : 0);
         op.qx[q] = op.act[q] ? __ldg(unknown + row * 3 + 0) : 0.f;
         op.qy[q] = op.act[q] ? __ldg(unknown + row * 3 + 1) : 0.f;
@@ -294,14 +295,16 @@ int set_smem(K kernel, size_t bytes, const char* what)
 }  // namespace
 }  // namespace tpk
 
-extern "C" int tpk_three_nn(int b, int n, int m, const float* unknown, const float* known,
-                            float* dist2, int32_t* idx, void* stream)
+namespace tpk
 {
-    using namespace tpk;
-    TPK_REQUIRE(b >= 0 && n >= 0 && m >= 0, "three_nn: negative size (b=%d n=%d m=%d)", b, n, m);
-    if (b == 0 || n == 0) return TPK_OK;
-    TPK_REQUIRE(unknown && dist2 && idx && (known || m == 0), "three_nn: NULL pointer");
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
+// grid_query.cu
+size_t grid_three_nn_scratch_bytes(int b, int n, int m);
+int grid_three_nn(int b, int n, int m, const float* unknown, const float* known, float* dist2,
+                  int32_t* idx, void* scratch, const unsigned char** need_scan_out, cudaStream_t s);
+
+static int launch_three_nn_scan(int b, int n, int m, const float* unknown, const float* known,
+                                float* dist2, int32_t* idx, const unsigned char* need, cudaStream_t s)
+{
     int threads, q;
     pick_shape_nn(static_cast<long long>(b) * n, &threads, &q);
     const int tiles = (n + threads * q - 1) / (threads * q);
@@ -311,24 +314,63 @@ extern "C" int tpk_three_nn(int b, int n, int m, const float* unknown, const flo
     if (threads == 128 && q == 2)
     {
         prefer_max_shared(three_nn_kernel<128, 2>);
-        three_nn_kernel<128, 2><<<g, 128, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
+        three_nn_kernel<128, 2><<<g, 128, 0, s>>>(n, m, tiles, unknown, known, dist2, idx, need);
     }
     else if (threads == 128)
     {
         prefer_max_shared(three_nn_kernel<128, 1>);
-        three_nn_kernel<128, 1><<<g, 128, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
+        three_nn_kernel<128, 1><<<g, 128, 0, s>>>(n, m, tiles, unknown, known, dist2, idx, need);
     }
     else if (q == 2)
     {
         prefer_max_shared(three_nn_kernel<64, 2>);
-        three_nn_kernel<64, 2><<<g, 64, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
+        three_nn_kernel<64, 2><<<g, 64, 0, s>>>(n, m, tiles, unknown, known, dist2, idx, need);
     }
     else
     {
         prefer_max_shared(three_nn_kernel<64, 1>);
-        three_nn_kernel<64, 1><<<g, 64, 0, s>>>(n, m, tiles, unknown, known, dist2, idx);
+        three_nn_kernel<64, 1><<<g, 64, 0, s>>>(n, m, tiles, unknown, known, dist2, idx, need);
     }
     return check_launch("three_nn");
+}
+}  // namespace tpk
+
+extern "C" int tpk_three_nn(int b, int n, int m, const float* unknown, const float* known,
+                            float* dist2, int32_t* idx, void* stream)
+{
+    using namespace tpk;
+    TPK_REQUIRE(b >= 0 && n >= 0 && m >= 0, "three_nn: negative size (b=%d n=%d m=%d)", b, n, m);
+    if (b == 0 || n == 0) return TPK_OK;
+    TPK_REQUIRE(unknown && dist2 && idx && (known || m == 0), "three_nn: NULL pointer");
+    return launch_three_nn_scan(b, n, m, unknown, known, dist2, idx, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int64_t tpk_three_nn_scratch_bytes(int b, int n, int m)
+{
+    if (b <= 0 || n <= 0 || m < 4096) return 0;
+    return static_cast<int64_t>(tpk::grid_three_nn_scratch_bytes(b, n, m));
+}
+
+extern "C" int tpk_three_nn_ws(int b, int n, int m, const float* unknown, const float* known,
+                               float* dist2, int32_t* idx, void* scratch, int64_t scratch_bytes,
+                               void* stream)
+{
+    using namespace tpk;
+    const int64_t want = tpk_three_nn_scratch_bytes(b, n, m);
+    if (want == 0 || scratch == nullptr) return tpk_three_nn(b, n, m, unknown, known, dist2, idx, stream);
+    if (scratch_bytes < want)
+    {
+        set_error("three_nn: scratch of %lld bytes given, %lld needed", static_cast<long long>(scratch_bytes),
+                  static_cast<long long>(want));
+        return TPK_ERR_SCRATCH;
+    }
+    TPK_REQUIRE(unknown && known && dist2 && idx, "three_nn: NULL pointer");
+    TPK_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "three_nn: scratch must be 256-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned char* need = nullptr;
+    int rc = grid_three_nn(b, n, m, unknown, known, dist2, idx, scratch, &need, s);
+    if (rc != TPK_OK) return rc;
+    return launch_three_nn_scan(b, n, m, unknown, known, dist2, idx, need, s);
 }
 
 #define TPK_KNN_DISPATCH(KERNEL, ...)                                                              \

@@ -86,8 +86,15 @@ def three_nn(unknown, known):
     dist2 = torch.empty((b, n, 3), dtype=torch.float32, device=unknown.device)
     idx = torch.empty((b, n, 3), dtype=torch.int32, device=unknown.device)
     with torch.cuda.device(unknown.device):
-        _lib.call("tpk_three_nn", b, n, m, _lib.ptr(unknown), _lib.ptr(known), _lib.ptr(dist2),
-                  _lib.ptr(idx), _lib.stream_of(unknown))
+        need = _lib.lib().tpk_three_nn_scratch_bytes(b, n, m)
+        if need > 0 and not os.environ.get("TPK_THREE_NN_SCAN"):
+            # many known points: uniform-grid search with scratch (same results as the scan)
+            scratch = torch.empty((need,), dtype=torch.uint8, device=unknown.device)
+            _lib.call("tpk_three_nn_ws", b, n, m, _lib.ptr(unknown), _lib.ptr(known), _lib.ptr(dist2),
+                      _lib.ptr(idx), _lib.ptr(scratch), need, _lib.stream_of(unknown))
+        else:
+            _lib.call("tpk_three_nn", b, n, m, _lib.ptr(unknown), _lib.ptr(known), _lib.ptr(dist2),
+                      _lib.ptr(idx), _lib.stream_of(unknown))
     return torch.sqrt(dist2), idx
 
 
