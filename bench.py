@@ -184,9 +184,9 @@ class GraphedSteps:
     in turn on three launch streams: no per-kernel host work, and consecutive steps still
     overlap because they are launched on different streams."""
 
-    def __init__(self, pipe, dev, like, split):
+    def __init__(self, pipe, dev, like, split, nslots=3):
         self.slots = []
-        for _ in range(3):
+        for _ in range(nslots):
             ins = [torch.empty_like(t, device=dev) for t in like]
             launch = torch.cuda.Stream(dev)
             graph = torch.cuda.CUDAGraph()
@@ -339,7 +339,7 @@ def run_b200(args, rank, world, local_rank):
     graphs, graph_error = None, None
     if not args.no_graphs:
         try:
-            graphs = GraphedSteps(pipe, dev, dev_in, split)
+            graphs = GraphedSteps(pipe, dev, dev_in, split, args.in_flight)
             graphs.load(dev_in)
             torch.cuda.synchronize(dev)
         except Exception as e:  # fall back to eager launches, and say so in the JSON line
@@ -350,7 +350,7 @@ def run_b200(args, rank, world, local_rank):
     def run_graphs(k):
         t0 = time.perf_counter()
         for i in range(k):
-            slot = graphs.slots[i % 3]
+            slot = graphs.slots[i % len(graphs.slots)]
             with torch.cuda.stream(slot["launch"]):
                 slot["graph"].replay()
         pipe.host_ms = (time.perf_counter() - t0) * 1e3 / max(k, 1)
@@ -402,7 +402,7 @@ def run_b200(args, rank, world, local_rank):
     # ---- end to end: pinned host inputs copied in on a copy stream, results (sampled indices
     # and one checksum per gradient tensor) copied out to pinned host buffers, every step
     out_bufs = [[torch.empty((B, m), dtype=torch.int32).pin_memory() for m in LEVELS["npoint"]] +
-                [torch.empty((8,), dtype=torch.float32).pin_memory()] for _ in range(3)]
+                [torch.empty((8,), dtype=torch.float32).pin_memory()] for _ in range(max(3, args.in_flight))]
 
     def run_e2e(k):
         dones = []
@@ -442,8 +442,8 @@ def run_b200(args, rank, world, local_rank):
         for slot in graphs.slots:
             slot["launch"].wait_stream(cur)
         for i in range(k):
-            slot = graphs.slots[i % 3]
-            bufs = out_bufs[i % 3]
+            slot = graphs.slots[i % len(graphs.slots)]
+            bufs = out_bufs[i % len(graphs.slots)]
             with torch.cuda.stream(slot["launch"]):
                 for dst, src in zip(slot["ins"], pinned):
                     dst.copy_(src, non_blocking=True)
@@ -453,7 +453,7 @@ def run_b200(args, rank, world, local_rank):
                 bufs[4].copy_(slot["chk"], non_blocking=True)
         for slot in graphs.slots:
             cur.wait_stream(slot["launch"])
-        return out_bufs[(k - 1) % 3]
+        return out_bufs[(k - 1) % len(graphs.slots)]
 
     if graphs is not None:
         run_e2e = run_e2e_graphs
@@ -519,7 +519,7 @@ def run_b200(args, rank, world, local_rank):
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(ms_e2e / args.steps, 4)},
         "gpu_launches": launches,
         "host_enqueue_ms_per_step": round(host_ms, 3),
-        "launch_mode": "cuda graphs (one per step, three in rotation)" if graphs is not None else "eager",
+        "launch_mode": "cuda graphs (one per step, %d in rotation)" % args.in_flight if graphs is not None else "eager",
         "graph_error": graph_error,
         "clocks": clocks,
         "roofline": roof,
@@ -853,6 +853,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--in-flight", type=int, default=6, help="CUDA graphs (steps) replayed in rotation, each on its own stream")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from Python instead of replaying CUDA graphs")
     args = ap.parse_args()
     if args.impl == "b200" and not args.only and args.workload == "sa_fp_pipeline":

@@ -54,7 +54,9 @@ def test_fps_known_answer(known_answers):
 
 @pytest.mark.parametrize("B,N,m", [(3, 1000, 200), (2, 4096, 512), (2, 16384, 700), (1, 40000, 150),
                                    (1, 100000, 40), (4, 257, 257), (2, 31, 9), (5, 1, 1), (2, 2, 2)])
-def test_fps_matches_oracle(B, N, m):
+@pytest.mark.parametrize("sorted_copy", ["0", "1"])
+def test_fps_matches_oracle(B, N, m, sorted_copy, monkeypatch):
+    monkeypatch.setenv("TPK_FPS_SORTED", sorted_copy)  # without / with the spatially sorted copy and warp skipping
     x = data.unit_ball(B, N, seed=2000 + N)
     got = npy(tpk.furthest_point_sample(cu(x), m))
     np.testing.assert_array_equal(got, orc.fps(x, m))
@@ -71,14 +73,16 @@ def test_fps_every_cluster_shape(cfg, fps_env, monkeypatch):
     want = orc.fps(x, 300)
     os.environ["TPK_FPS_CONFIG"] = cfg
     for flat in ("1", "0"):
-        monkeypatch.setenv("TPK_FPS_FLAT", flat)
-        got = npy(tpk.furthest_point_sample(cu(x), 300))
-        np.testing.assert_array_equal(got, want)
+        for sorted_copy in ("0", "1"):
+            monkeypatch.setenv("TPK_FPS_FLAT", flat)
+            monkeypatch.setenv("TPK_FPS_SORTED", sorted_copy)
+            got = npy(tpk.furthest_point_sample(cu(x), 300))
+            np.testing.assert_array_equal(got, want)
     assert _lib.device_status() == 0
 
 
 @pytest.mark.parametrize("n", [3, 8, 37, 64, 300, 700, 1000, 1500, 2048, 5000])
-def test_fps_tie_break_and_skip_rule(n, fps_env):
+def test_fps_tie_break_and_skip_rule(n, fps_env, monkeypatch):
     rng = np.random.default_rng(n)
     pts = np.zeros((2, n, 3), np.float32)
     pts[:, 0] = (1.0, 1.0, 1.0)
@@ -92,7 +96,42 @@ def test_fps_tie_break_and_skip_rule(n, fps_env):
     for cfg in (None, "1,64,32", "2,64,32", "2,256,16", "4,128,16", "1,128,8", "2,64,4"):
         if cfg:
             os.environ["TPK_FPS_CONFIG"] = cfg
-        np.testing.assert_array_equal(npy(tpk.furthest_point_sample(cu(pts), m)), want)
+        for sorted_copy in ("0", "1"):
+            monkeypatch.setenv("TPK_FPS_SORTED", sorted_copy)
+            np.testing.assert_array_equal(npy(tpk.furthest_point_sample(cu(pts), m)), want)
+
+
+def test_fps_sorted_copy_is_the_default_for_big_on_chip_clouds():
+    assert _lib.lib().tpk_fps_scratch_bytes(4, 16384, 4096) == 4 * 16384 * 16
+    assert _lib.lib().tpk_fps_scratch_bytes(4, 1024, 256) == 0
+
+
+@pytest.mark.parametrize("kind", ["clustered", "lattice", "planar", "nonfinite", "many_skipped"])
+def test_fps_sorted_copy_hard_clouds(kind, monkeypatch):
+    """Warp skipping must never change a result: crowded cells, exact ties everywhere, a
+    collapsed axis, coordinates that are not finite, and points the skip rule excludes."""
+    monkeypatch.setenv("TPK_FPS_SORTED", "1")
+    rng = np.random.default_rng(len(kind))
+    B, n, m = 2, 6000, 400
+    if kind == "clustered":
+        x = (rng.standard_normal((B, n, 3)) * 0.02 + rng.integers(0, 4, (B, n, 1)) * 2.0).astype(np.float32)
+    elif kind == "lattice":
+        x = rng.integers(0, 9, (B, n, 3)).astype(np.float32) / 4
+    elif kind == "planar":
+        x = rng.uniform(-1, 1, (B, n, 3)).astype(np.float32)
+        x[..., 1] = 0.5
+    elif kind == "nonfinite":
+        x = np.array(data.unit_ball(B, n, seed=5))
+        x[0, 17, 0] = np.inf
+        x[0, 400, 2] = np.nan
+        x[1, 3000] = (-np.inf, 0.0, np.nan)
+        m = 60
+    else:
+        x = np.array(data.unit_ball(B, n, seed=6))
+        x[:, 1::2] *= 0.01  # |p|^2 <= 1e-3: never candidates
+    got = npy(tpk.furthest_point_sample(cu(x), m))
+    np.testing.assert_array_equal(got, orc.fps(x, m))
+    assert _lib.device_status() == 0
 
 
 @pytest.mark.parametrize("B,N,m", [(2, 200000, 48), (3, 140000, 33)])

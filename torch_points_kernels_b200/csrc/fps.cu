@@ -15,6 +15,7 @@
 // encoded as a rank: with bs = largest power of two <= n (at most 512) the reference
 // prefers the smallest bit-reversed (k mod bs), then the smallest (k div bs).
 #include <climits>
+#include <math_constants.h>
 #include <type_traits>
 
 #include <cooperative_groups.h>
@@ -200,10 +201,18 @@ __device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigne
     return r;
 }
 
-template <int PPT, bool CLUSTERED>
+//
+// SORTED: the points come from a spatially sorted copy (x, y, z, original index) and a
+// warp owns a contiguous run of it, i.e. a compact region of space.  A warp whose
+// bounding box is farther from the newest sample than its largest running minimum
+// cannot change any of its minima, so it skips the update and sends last round's winner
+// again.  In the late rounds, which are most of them, a sample only reaches a few warps.
+// The result does not depend on the order of the copy: ties are decided by the rank of
+// the original index at every level.
+template <int PPT, bool CLUSTERED, bool SORTED>
 __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
     fps_onchip_kernel(int n, int m, int log2bs, int flat, const float* __restrict__ xyz_all,
-                      int32_t* __restrict__ idxs_all)
+                      const float4* __restrict__ sorted_all, int32_t* __restrict__ idxs_all)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -241,13 +250,39 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
     };
 
     float px[PPT], py[PPT], pz[PPT], md[PPT];
+    // bounding box of the warp's points (SORTED only)
+    float bminx = CUDART_INF_F, bminy = CUDART_INF_F, bminz = CUDART_INF_F;
+    float bmaxx = -CUDART_INF_F, bmaxy = -CUDART_INF_F, bmaxz = -CUDART_INF_F;
 #pragma unroll
     for (int p = 0; p < PPT; ++p)
     {
-        const int k = point_index(p);
+        int k = point_index(p);
         float x = 0.f, y = 0.f, z = 0.f;
         bool valid = false;
-        if (k < n)
+        if (SORTED)
+        {
+            // slot of the sorted copy: warp-contiguous, lanes interleaved
+            const int slot = ((rank * nwarps + warp) * PPT + p) * 32 + lane;
+            k = n;
+            if (slot < n)
+            {
+                const float4 v = __ldg(sorted_all + static_cast<size_t>(cloud) * n + slot);
+                x = v.x;
+                y = v.y;
+                z = v.z;
+                k = __float_as_int(v.w);
+                const float mag = sumsq_abc(x, y, z);
+                valid = !(static_cast<double>(mag) <= 1e-3);
+                // fminf/fmaxf drop NaN: such a point never changes its minimum anyway
+                bminx = fminf(bminx, x);
+                bminy = fminf(bminy, y);
+                bminz = fminf(bminz, z);
+                bmaxx = fmaxf(bmaxx, x);
+                bmaxy = fmaxf(bmaxy, y);
+                bmaxz = fmaxf(bmaxz, z);
+            }
+        }
+        else if (k < n)
         {
             x = __ldg(xyz + 3 * static_cast<size_t>(k) + 0);
             y = __ldg(xyz + 3 * static_cast<size_t>(k) + 1);
@@ -263,6 +298,24 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
         // w carries the point's index so that the winner's message needs no index arithmetic
         sxyz[p * nthreads + tid] = make_float4(x, y, z, __int_as_float(k));
     }
+
+    if (SORTED)
+    {
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1)
+        {
+            bminx = fminf(bminx, __shfl_xor_sync(kFullMask, bminx, o));
+            bminy = fminf(bminy, __shfl_xor_sync(kFullMask, bminy, o));
+            bminz = fminf(bminz, __shfl_xor_sync(kFullMask, bminz, o));
+            bmaxx = fmaxf(bmaxx, __shfl_xor_sync(kFullMask, bmaxx, o));
+            bmaxy = fmaxf(bmaxy, __shfl_xor_sync(kFullMask, bmaxy, o));
+            bmaxz = fmaxf(bmaxz, __shfl_xor_sync(kFullMask, bmaxz, o));
+        }
+    }
+    // SORTED: the warp's winner of the last round it updated in, and the bound a sample's
+    // squared distance to the box must exceed for the warp to skip (infinite: never skip)
+    Msg wm = {INT_MIN, 0, 0.f, 0.f, 0.f};
+    float skip_above = CUDART_INF_F;
 
     float cx = 0.f, cy = 0.f, cz = 0.f;
     if (n > 0)
@@ -312,6 +365,22 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
         if (CLUSTERED && tid == 0)
             mbar_arrive_expect_tx(smem_u32(mbar + PAR), static_cast<uint32_t>(nslots * kMsgBytes));
 
+        bool active = true;
+        if (SORTED)
+        {
+            // squared distance from the sample to the warp's box; a computed distance is at
+            // least this bound less a few ulp, far inside the margin taken here
+            const float ex = fmaxf(fmaxf(bminx - cx, cx - bmaxx), 0.f);
+            const float ey = fmaxf(fmaxf(bminy - cy, cy - bmaxy), 0.f);
+            const float ez = fmaxf(fmaxf(bminz - cz, cz - bmaxz), 0.f);
+            const float lb = __fmaf_rn(ez, ez, __fmaf_rn(ex, ex, __fmul_rn(ey, ey)));
+            // the operands are the same in every lane; the vote makes the branch provably
+            // uniform for the warp-wide instructions inside it
+            active = __any_sync(kFullMask, !(__fmul_rn(lb, 0.9999f) > skip_above)) != 0;
+        }
+        Msg msg;
+        if (active)
+        {
         // ---- every point: distance to the newest sample, running minimum, thread maximum
         if constexpr (PPT >= 2)
         {
@@ -355,7 +424,23 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
         uint32_t eq = 0;
 #pragma unroll
         for (int p = 0; p < PPT; ++p) eq |= (md[p] == best) ? (1u << p) : 0u;
-        const int bp = __ffs(eq) - 1;
+        int bp = __ffs(eq) - 1;
+        if (SORTED && key == wkey && wkey >= 0 && (eq & (eq - 1u)) != 0u)
+        {
+            // several of this lane's points tie: the original index decides (no layout rule
+            // in a sorted copy).  Plain per-lane code, no warp-wide instruction.
+            uint32_t best_rank = 0xFFFFFFFFu;
+            for (uint32_t e = eq; e != 0u; e &= e - 1u)
+            {
+                const int p = __ffs(e) - 1;
+                const uint32_t r = fps_rank(__float_as_int(my_xyz[p * nthreads].w), log2bs);
+                if (r < best_rank)
+                {
+                    best_rank = r;
+                    bp = p;
+                }
+            }
+        }
         const float4 mine = my_xyz[bp * nthreads];
         uint32_t ball = __ballot_sync(kFullMask, key == wkey);
         if (__popc(ball) > 1 && wkey >= 0)
@@ -364,21 +449,37 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
             const uint32_t wr = __reduce_min_sync(kFullMask, r);
             ball = __ballot_sync(kFullMask, key == wkey && r == wr);
         }
-        Msg msg;
         const int src1 = __ffs(ball) - 1;
-        if (CLUSTERED && flat)
+        if (SORTED || (CLUSTERED && flat))
         {
             msg.key = wkey;
             msg.k = __shfl_sync(kFullMask, __float_as_int(mine.w), src1);
             msg.x = __shfl_sync(kFullMask, mine.x, src1);
             msg.y = __shfl_sync(kFullMask, mine.y, src1);
             msg.z = __shfl_sync(kFullMask, mine.z, src1);
+            if (SORTED)
+            {
+                wm = msg;
+                // no skipping on tiny bounds, where a computed distance may have lost precision
+                skip_above = fmaxf(__int_as_float(wkey), 1.0e-30f);
+            }
         }
         else if (lane == src1)
         {
             wmsg_a[PAR * 32 + warp] = make_uint4(static_cast<uint32_t>(key), __float_as_uint(mine.w),
                                                  __float_as_uint(mine.x), __float_as_uint(mine.y));
             wmsg_z[PAR * 32 + warp] = mine.z;
+        }
+        }  // active
+        else
+        {
+            msg = wm;
+        }
+        if (SORTED && !(CLUSTERED && flat) && lane == 0)
+        {
+            wmsg_a[PAR * 32 + warp] = make_uint4(static_cast<uint32_t>(msg.key), static_cast<uint32_t>(msg.k),
+                                                 __float_as_uint(msg.x), __float_as_uint(msg.y));
+            wmsg_z[PAR * 32 + warp] = msg.z;
         }
 
         // ---- stage 2: the CTA's best point
@@ -454,6 +555,172 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
 
     // no CTA may leave while a peer can still write into its shared memory
     if (CLUSTERED) cluster_sync_all();
+}
+
+// ---------------------------------------------------------------- spatial sort
+//
+// Copy of every cloud in Morton order of a 2^bits-per-axis grid over its bounding box,
+// as (x, y, z, original index): one CTA per cloud, counting sort with the cell counters
+// in shared memory.  The order inside a cell is whatever the atomics give; the sampling
+// kernel's result does not depend on it.
+constexpr int kSortThreads = 1024;
+
+__device__ __forceinline__ uint32_t spread3(uint32_t v)
+{
+    v = (v | (v << 16)) & 0x030000FFu;
+    v = (v | (v << 8)) & 0x0300F00Fu;
+    v = (v | (v << 4)) & 0x030C30C3u;
+    v = (v | (v << 2)) & 0x09249249u;
+    return v;
+}
+
+__global__ void __launch_bounds__(kSortThreads)
+    fps_sort_kernel(int n, int bits, const float* __restrict__ xyz_all, float4* __restrict__ sorted_all)
+{
+    extern __shared__ int cnt[];  // 8^bits counters
+    __shared__ float s_min[3][kSortThreads / 32], s_max[3][kSortThreads / 32];
+    __shared__ int s_warp[kSortThreads / 32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* xyz = xyz_all + static_cast<size_t>(blockIdx.x) * n * 3;
+    float4* sorted = sorted_all + static_cast<size_t>(blockIdx.x) * n;
+    const int ncell = 1 << (3 * bits);
+
+    float mn[3] = {CUDART_INF_F, CUDART_INF_F, CUDART_INF_F};
+    float mx[3] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+    for (int k = tid; k < n; k += kSortThreads)
+    {
+#pragma unroll
+        for (int a = 0; a < 3; ++a)
+        {
+            const float v = __ldg(xyz + 3 * static_cast<size_t>(k) + a);
+            if (fabsf(v) < 1.0e18f)  // the box of the finite coordinates
+            {
+                mn[a] = fminf(mn[a], v);
+                mx[a] = fmaxf(mx[a], v);
+            }
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < 3; ++a)
+    {
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1)
+        {
+            mn[a] = fminf(mn[a], __shfl_xor_sync(kFullMask, mn[a], o));
+            mx[a] = fmaxf(mx[a], __shfl_xor_sync(kFullMask, mx[a], o));
+        }
+        if (lane == 0)
+        {
+            s_min[a][warp] = mn[a];
+            s_max[a][warp] = mx[a];
+        }
+    }
+    for (int c = tid; c < ncell; c += kSortThreads) cnt[c] = 0;
+    __syncthreads();
+    float ext = 0.f;
+#pragma unroll
+    for (int a = 0; a < 3; ++a)
+    {
+        float lo = s_min[a][0], hi = s_max[a][0];
+        for (int w = 1; w < kSortThreads / 32; ++w)
+        {
+            lo = fminf(lo, s_min[a][w]);
+            hi = fmaxf(hi, s_max[a][w]);
+        }
+        mn[a] = lo;
+        ext = fmaxf(ext, hi - lo);
+    }
+    const float qmax = static_cast<float>((1 << bits) - 1);
+    const float inv_h = (ext > 0.f && ext < CUDART_INF_F) ? static_cast<float>(1 << bits) * 0.999999f / ext : 0.f;
+    auto cell_of_point = [&](float x, float y, float z) -> int {
+        // fmaxf drops NaN, the clamp takes care of infinities: any cell is a correct cell
+        const uint32_t qx = static_cast<uint32_t>(fminf(fmaxf((x - mn[0]) * inv_h, 0.f), qmax));
+        const uint32_t qy = static_cast<uint32_t>(fminf(fmaxf((y - mn[1]) * inv_h, 0.f), qmax));
+        const uint32_t qz = static_cast<uint32_t>(fminf(fmaxf((z - mn[2]) * inv_h, 0.f), qmax));
+        return static_cast<int>(spread3(qx) | (spread3(qy) << 1) | (spread3(qz) << 2));
+    };
+
+    for (int k = tid; k < n; k += kSortThreads)
+    {
+        const float x = __ldg(xyz + 3 * static_cast<size_t>(k) + 0);
+        const float y = __ldg(xyz + 3 * static_cast<size_t>(k) + 1);
+        const float z = __ldg(xyz + 3 * static_cast<size_t>(k) + 2);
+        atomicAdd(&cnt[cell_of_point(x, y, z)], 1);
+    }
+    __syncthreads();
+
+    // exclusive prefix sum of the counters: a run of cells per thread, then the runs' totals
+    const int per = ncell >= kSortThreads ? ncell / kSortThreads : 1;
+    const int c0 = tid * per;
+    int sum = 0;
+    if (c0 < ncell)
+        for (int c = c0; c < c0 + per; ++c) sum += cnt[c];
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1)
+    {
+        const int t = __shfl_up_sync(kFullMask, incl, o);
+        if (lane >= o) incl += t;
+    }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    if (warp == 0)
+    {
+        int w = s_warp[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1)
+        {
+            const int t = __shfl_up_sync(kFullMask, w, o);
+            if (lane >= o) w += t;
+        }
+        s_warp[lane] = w;
+    }
+    __syncthreads();
+    int run = (warp ? s_warp[warp - 1] : 0) + incl - sum;
+    if (c0 < ncell)
+        for (int c = c0; c < c0 + per; ++c)
+        {
+            const int v = cnt[c];
+            cnt[c] = run;
+            run += v;
+        }
+    __syncthreads();
+
+    for (int k = tid; k < n; k += kSortThreads)
+    {
+        const float x = __ldg(xyz + 3 * static_cast<size_t>(k) + 0);
+        const float y = __ldg(xyz + 3 * static_cast<size_t>(k) + 1);
+        const float z = __ldg(xyz + 3 * static_cast<size_t>(k) + 2);
+        const int pos = atomicAdd(&cnt[cell_of_point(x, y, z)], 1);
+        sorted[pos] = make_float4(x, y, z, __int_as_float(k));
+    }
+}
+
+// about four points per cell, at most 32^3 cells (128 KB of counters)
+int fps_sort_bits(int n)
+{
+    int bits = 1;
+    while (bits < 5 && (1ll << (3 * bits)) * 4 < n) ++bits;
+    return bits;
+}
+
+int fps_launch_sort(int b, int n, const float* xyz, float4* sorted, cudaStream_t stream)
+{
+    const int bits = fps_sort_bits(n);
+    const size_t smem = sizeof(int) << (3 * bits);
+    prefer_max_shared(fps_sort_kernel);
+    if (smem > 48 * 1024)
+    {
+        cudaError_t err = cudaFuncSetAttribute(fps_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(smem));
+        if (err != cudaSuccess)
+        {
+            set_error("fps sort: shared memory attribute: %s", cudaGetErrorString(err));
+            return TPK_ERR_CUDA;
+        }
+    }
+    fps_sort_kernel<<<b, kSortThreads, smem, stream>>>(n, bits, xyz, sorted);
+    return check_launch("fps sort");
 }
 
 // ---------------------------------------------------------------- large clouds
@@ -715,9 +982,12 @@ bool fps_config_ok(const FpsConfig& e, int n)
 // Picks cluster size, block size and points per thread for n points per cloud: few,
 // fat threads (every warp and every CTA adds a stage to the per-round exchange), and
 // as many CTAs per cloud as keep a CTA's share near 2048-4096 points.
-bool fps_pick_config(int n, FpsConfig* out)
+bool fps_wants_sorted(int n, int m);
+
+bool fps_pick_config(int n, int m, FpsConfig* out)
 {
     FpsConfig c;
+    (void)m;
     c.nranks = n <= 4096 ? 1 : (n <= 8192 ? 4 : (n <= 32768 ? 8 : 16));
     const int per_cta = (n + c.nranks - 1) / c.nranks;
     if (per_cta <= 256)
@@ -741,11 +1011,11 @@ bool fps_pick_config(int n, FpsConfig* out)
     return true;
 }
 
-template <int PPT, bool CLUSTERED>
+template <int PPT, bool CLUSTERED, bool SORTED>
 int fps_launch_t(const FpsConfig& c, int b, int n, int m, int log2bs, const float* xyz,
-                 int32_t* idxs, cudaStream_t stream)
+                 const float4* sorted, int32_t* idxs, cudaStream_t stream)
 {
-    auto kernel = fps_onchip_kernel<PPT, CLUSTERED>;
+    auto kernel = fps_onchip_kernel<PPT, CLUSTERED, SORTED>;
     prefer_max_shared(kernel);
     const size_t smem = fps_smem_bytes(c);
     cudaError_t err;
@@ -784,7 +1054,7 @@ int fps_launch_t(const FpsConfig& c, int b, int n, int m, int log2bs, const floa
     // TPK_FPS_FLAT=0 selects the three-stage exchange for comparison runs
     const char* flat_env = getenv("TPK_FPS_FLAT");
     const int flat = (c.nranks > 1 && c.nranks * (c.nthreads / 32) <= 32 && !(flat_env && flat_env[0] == '0')) ? 1 : 0;
-    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, flat, xyz, idxs);
+    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, flat, xyz, sorted, idxs);
     if (err != cudaSuccess)
     {
         set_error("fps launch (cluster %d x %d threads x %d points): %s", c.nranks, c.nthreads,
@@ -794,22 +1064,30 @@ int fps_launch_t(const FpsConfig& c, int b, int n, int m, int log2bs, const floa
     return TPK_OK;
 }
 
-template <bool CLUSTERED>
+template <bool CLUSTERED, bool SORTED>
 int fps_launch_s(const FpsConfig& c, int b, int n, int m, int log2bs, const float* xyz,
-                 int32_t* idxs, cudaStream_t stream)
+                 const float4* sorted, int32_t* idxs, cudaStream_t stream)
 {
     switch (c.ppt)
     {
-    case 1: return fps_launch_t<1, CLUSTERED>(c, b, n, m, log2bs, xyz, idxs, stream);
-    case 2: return fps_launch_t<2, CLUSTERED>(c, b, n, m, log2bs, xyz, idxs, stream);
-    case 4: return fps_launch_t<4, CLUSTERED>(c, b, n, m, log2bs, xyz, idxs, stream);
-    case 8: return fps_launch_t<8, CLUSTERED>(c, b, n, m, log2bs, xyz, idxs, stream);
-    case 16: return fps_launch_t<16, CLUSTERED>(c, b, n, m, log2bs, xyz, idxs, stream);
-    case 32: return fps_launch_t<32, CLUSTERED>(c, b, n, m, log2bs, xyz, idxs, stream);
+    case 1: return fps_launch_t<1, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
+    case 2: return fps_launch_t<2, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
+    case 4: return fps_launch_t<4, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
+    case 8: return fps_launch_t<8, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
+    case 16: return fps_launch_t<16, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
+    case 32: return fps_launch_t<32, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
     default: break;
     }
     set_error("fps: unsupported points per thread %d", c.ppt);
     return TPK_ERR_UNSUPPORTED;
+}
+
+// The sorted copy pays when a cloud has enough warps for most of them to be skipped and
+// enough rounds to earn back the sort.  TPK_FPS_SORTED=0/1 overrides for comparison runs.
+bool fps_wants_sorted(int n, int m)
+{
+    if (const char* env = getenv("TPK_FPS_SORTED")) return env[0] != '0';
+    return n >= 4096 && m >= 128;
 }
 
 }  // namespace
@@ -817,11 +1095,11 @@ int fps_launch_s(const FpsConfig& c, int b, int n, int m, int log2bs, const floa
 
 extern "C" int64_t tpk_fps_scratch_bytes(int b, int n, int m)
 {
-    (void)b;
-    (void)m;
     tpk::FpsConfig c;
-    if (n <= 0 || b <= 0) return 0;
-    if (getenv("TPK_FPS_FORCE_GLOBAL") == nullptr && tpk::fps_pick_config(n, &c)) return 0;
+    if (n <= 0 || b <= 0 || m <= 0) return 0;
+    if (getenv("TPK_FPS_FORCE_GLOBAL") == nullptr && tpk::fps_pick_config(n, m, &c))
+        // optional: the spatially sorted copy, (x, y, z, index) per point
+        return tpk::fps_wants_sorted(n, m) ? static_cast<int64_t>(b) * n * 16 : 0;
     // large clouds: the running minimum, one float per point
     return static_cast<int64_t>(b) * n * static_cast<int64_t>(sizeof(float));
 }
@@ -840,7 +1118,7 @@ extern "C" int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz
     if (log2bs > 9) log2bs = 9;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     FpsConfig c;
-    if (getenv("TPK_FPS_FORCE_GLOBAL") != nullptr || !fps_pick_config(n, &c))
+    if (getenv("TPK_FPS_FORCE_GLOBAL") != nullptr || !fps_pick_config(n, m, &c))
     {
         if (scratch == nullptr)
         {
@@ -849,8 +1127,16 @@ extern "C" int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz
         }
         return fps_launch_global(b, n, m, log2bs, xyz, static_cast<float*>(scratch), idxs, s);
     }
-    return c.nranks > 1 ? fps_launch_s<true>(c, b, n, m, log2bs, xyz, idxs, s)
-                        : fps_launch_s<false>(c, b, n, m, log2bs, xyz, idxs, s);
+    if (scratch != nullptr && fps_wants_sorted(n, m) && (reinterpret_cast<uintptr_t>(scratch) & 15u) == 0)
+    {
+        float4* sorted = static_cast<float4*>(scratch);
+        const int rc = fps_launch_sort(b, n, xyz, sorted, s);
+        if (rc != TPK_OK) return rc;
+        return c.nranks > 1 ? fps_launch_s<true, true>(c, b, n, m, log2bs, xyz, sorted, idxs, s)
+                            : fps_launch_s<false, true>(c, b, n, m, log2bs, xyz, sorted, idxs, s);
+    }
+    return c.nranks > 1 ? fps_launch_s<true, false>(c, b, n, m, log2bs, xyz, nullptr, idxs, s)
+                        : fps_launch_s<false, false>(c, b, n, m, log2bs, xyz, nullptr, idxs, s);
 }
 
 // ------------------------------------------------------------- entry point without scratch

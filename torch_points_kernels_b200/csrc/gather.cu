@@ -808,7 +808,9 @@ extern "C" int tpk_grouping(int b, int c, int n, int npoint, int nsample, const 
     {
         // rows per CTA: as many as fit the shared memory of one SM, at most 4 (the indices
         // of a position are loaded once for all rows of the CTA)
-        int rows = static_cast<int>(kRowSmemBudget / row_bytes);
+        size_t budget = kRowSmemBudget;
+        if (const char* env = getenv("TPK_GROUP_FWD_KB")) budget = static_cast<size_t>(atoi(env)) * 1024;
+        int rows = static_cast<int>(budget / row_bytes);
         if (rows < 1) rows = 1;
         if (rows > 4) rows = 4;
         if (rows > c) rows = c;
@@ -860,7 +862,9 @@ extern "C" int tpk_grouping_grad(int b, int c, int n, int npoint, int nsample,
         // rows per CTA: as many as fit a bit over 100 KB (two CTAs per SM), at most 4,
         // fewer when that would leave SMs without a CTA
         // (measured: the atomics want many resident warps more than they want shared indices)
-        int rows = static_cast<int>((104 * 1024) / row_bytes);
+        size_t budget = 104 * 1024;
+        if (const char* env = getenv("TPK_GROUP_BWD_KB")) budget = static_cast<size_t>(atoi(env)) * 1024;
+        int rows = static_cast<int>(budget / row_bytes);
         if (rows < 1) rows = 1;
         if (rows > 4) rows = 4;
         if (rows > c) rows = c;
