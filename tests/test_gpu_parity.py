@@ -219,14 +219,42 @@ def test_ball_query_dense_grid_path_matches_oracle(case, monkeypatch):
     if case == "ns100":
         ns, r = 100, 0.2
     assert _lib.lib().tpk_ball_query_dense_scratch_bytes(B, N, M, ns) > 0
+    oi, od = orc.ball_query_dense(r, ns, x, y)
+    # the grid in shared memory (where it fits), the grid in global memory, the plain scan
+    for env in (None, "TPK_BALL_QUERY_GLOBAL_GRID", "TPK_BALL_QUERY_SCAN"):
+        if env:
+            monkeypatch.setenv(env, "1")
+        idx, dist = tpk.ball_query(r, ns, cu(x), cu(y), mode="dense")
+        np.testing.assert_array_equal(npy(idx), oi)
+        same_bits(npy(dist), od)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("case", ["crowded_layer", "nonfinite_centres", "nonfinite_points", "thin_cells", "many_centres"])
+def test_ball_query_dense_shared_memory_grid_edge_cases(case):
+    """The shared-memory grid hands back what it cannot answer: a layer with more points than
+    fit, centres without a cell, clouds without a grid; cells exactly one radius wide; more
+    centres than one list pass takes."""
+    B, N, M, r, ns = 2, 6000, 500, 0.08, 16
+    x = np.array(data.unit_ball(B, N, seed=31))
+    if case == "crowded_layer":
+        x[0, :5000, 2] = 0.123  # one z layer holds most of cloud 0
+    if case == "thin_cells":
+        r = 0.3  # the radius, not the cell budget, sets the cell size
+    if case == "many_centres":
+        M = 5000
+    y = np.array(x[:, :M])
+    if case == "nonfinite_centres":
+        y[0, 3, 1] = np.nan
+        y[1, 7, 2] = np.inf
+    if case == "nonfinite_points":
+        x[1, 10, 0] = np.inf
+    assert _lib.lib().tpk_ball_query_dense_scratch_bytes(B, N, M, ns) == (B * M + 255) // 256 * 256
     idx, dist = tpk.ball_query(r, ns, cu(x), cu(y), mode="dense")
     oi, od = orc.ball_query_dense(r, ns, x, y)
     np.testing.assert_array_equal(npy(idx), oi)
     same_bits(npy(dist), od)
-    monkeypatch.setenv("TPK_BALL_QUERY_SCAN", "1")
-    idx2, dist2 = tpk.ball_query(r, ns, cu(x), cu(y), mode="dense")
-    np.testing.assert_array_equal(npy(idx2), oi)
-    same_bits(npy(dist2), od)
 
 
 def test_ball_query_dense_boundary_is_strict_partial_is_inclusive():
@@ -278,7 +306,8 @@ def test_ball_query_partial_scene_scale():
 
 # ------------------------------------------------------------------ three_nn and kNN
 
-@pytest.mark.parametrize("B,n,m", [(4, 4096, 1024), (2, 1000, 2000), (3, 77, 3), (2, 10, 2), (2, 5, 1), (16, 256, 64)])
+@pytest.mark.parametrize("B,n,m", [(4, 4096, 1024), (2, 1000, 2000), (3, 77, 3), (2, 10, 2), (2, 5, 1), (16, 256, 64),
+                                   (2, 3000, 10000), (3, 700, 256), (1, 100000, 300)])
 def test_three_nn_matches_oracle(B, n, m):
     unknown = data.unit_ball(B, n, seed=n)
     known = data.unit_ball(B, m, seed=m + 1)
@@ -325,21 +354,28 @@ def _three_nn_grid_cases():
 
 
 @pytest.mark.parametrize("name", ["uniform", "outside", "clustered_duplicates", "planar", "lattice_ties", "upsample"])
-def test_three_nn_grid_path_matches_oracle(name):
+def test_three_nn_grid_path_matches_oracle(name, monkeypatch):
     unknown, known = _three_nn_grid_cases()[name]
     b, n, m = unknown.shape[0], unknown.shape[1], known.shape[1]
     assert _lib.lib().tpk_three_nn_scratch_bytes(b, n, m) > 0  # the grid path is the one tested
-    dist, idx = tpk.three_nn(cu(unknown), cu(known))
     od2, oi = orc.three_nn(unknown, known)
-    np.testing.assert_array_equal(npy(idx), oi)
-    same_bits(npy(dist), np.sqrt(od2))
+    # the grid in shared memory (up to 8192 known points), then the grid in global memory
+    for env in (None, "TPK_THREE_NN_GLOBAL_GRID"):
+        if env:
+            monkeypatch.setenv(env, "1")
+        dist, idx = tpk.three_nn(cu(unknown), cu(known))
+        np.testing.assert_array_equal(npy(idx), oi)
+        same_bits(npy(dist), np.sqrt(od2))
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
 
 
-def test_three_nn_grid_path_nonfinite_falls_back_to_scan():
-    unknown = data.unit_ball(2, 1500, seed=21)
-    known = data.unit_ball(2, 4096, seed=22)
+@pytest.mark.parametrize("env", [None, "TPK_THREE_NN_GLOBAL_GRID"])
+def test_three_nn_grid_path_nonfinite_falls_back_to_scan(env, monkeypatch):
+    if env:
+        monkeypatch.setenv(env, "1")
+    unknown = np.array(data.unit_ball(2, 1500, seed=21))
+    known = np.array(data.unit_ball(2, 4096, seed=22))
     unknown[0, 7, 1] = np.inf
     unknown[1, 9, 0] = np.nan
     known[1, 100, 2] = np.inf  # cloud 1: no grid at all

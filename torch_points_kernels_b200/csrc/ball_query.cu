@@ -21,6 +21,10 @@ size_t grid_scratch_bytes(int b, int n, int m);
 int grid_ball_query_dense(int b, int n, int m, float radius, int nsample, const float* new_xyz,
                           const float* xyz, int64_t* idx, float* dist, void* scratch,
                           const unsigned char** need_scan_out, cudaStream_t s);
+// smem_grid.cu
+bool sg_ball_query_fits(int b, int n, int nsample);
+int sg_ball_query(int b, int n, int m, float radius, int nsample, const float* new_xyz, const float* xyz,
+                  int64_t* idx, float* dist, unsigned char* need, cudaStream_t s);
 
 namespace
 {
@@ -248,10 +252,20 @@ extern "C" int tpk_ball_query_dense(int b, int n, int m, float radius, int nsamp
     return check_launch("ball_query_dense");
 }
 
+// TPK_BALL_QUERY_GLOBAL_GRID selects the grid in global memory where the shared-memory grid
+// would be used (comparison runs and tests of that path)
+static bool use_smem_grid(int b, int n, int nsample)
+{
+    return tpk::sg_ball_query_fits(b, n, nsample) && getenv("TPK_BALL_QUERY_GLOBAL_GRID") == nullptr;
+}
+
 extern "C" int64_t tpk_ball_query_dense_scratch_bytes(int b, int n, int m, int nsample)
 {
-    // the grid path needs clouds worth binning and a hit list that fits shared memory
-    if (b <= 0 || m <= 0 || n < 8192 || nsample <= 0 || nsample > 128) return 0;
+    if (b <= 0 || m <= 0 || nsample <= 0) return 0;
+    // shared-memory grid: one flag per centre
+    if (use_smem_grid(b, n, nsample)) return (static_cast<int64_t>(b) * m + 255) / 256 * 256;
+    // the grid in global memory needs clouds worth binning and a hit list that fits shared memory
+    if (n < 8192 || nsample > 128) return 0;
     return static_cast<int64_t>(tpk::grid_scratch_bytes(b, n, m));
 }
 
@@ -274,7 +288,16 @@ extern "C" int tpk_ball_query_dense_ws(int b, int n, int m, float radius, int ns
     TPK_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "ball_query_dense: scratch must be 256-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const unsigned char* need = nullptr;
-    int rc = grid_ball_query_dense(b, n, m, radius, nsample, new_xyz, xyz, idx, dist, scratch, &need, s);
+    int rc;
+    if (use_smem_grid(b, n, nsample))
+    {
+        need = static_cast<const unsigned char*>(scratch);
+        rc = sg_ball_query(b, n, m, radius, nsample, new_xyz, xyz, idx, dist, static_cast<unsigned char*>(scratch), s);
+    }
+    else
+    {
+        rc = grid_ball_query_dense(b, n, m, radius, nsample, new_xyz, xyz, idx, dist, scratch, &need, s);
+    }
     if (rc != TPK_OK) return rc;
     // centres the grid left over (dense neighbourhoods, degenerate clouds): index-order scan
     int threads, q;

@@ -302,6 +302,11 @@ size_t grid_three_nn_scratch_bytes(int b, int n, int m);
 int grid_three_nn(int b, int n, int m, const float* unknown, const float* known, float* dist2,
                   int32_t* idx, void* scratch, const unsigned char** need_scan_out, cudaStream_t s);
 
+// smem_grid.cu
+bool sg_three_nn_fits(int m);
+int sg_three_nn(int b, int n, int m, const float* unknown, const float* known, float* dist2, int32_t* idx,
+                unsigned char* need, cudaStream_t s);
+
 static int launch_three_nn_scan(int b, int n, int m, const float* unknown, const float* known,
                                 float* dist2, int32_t* idx, const unsigned char* need, cudaStream_t s)
 {
@@ -345,9 +350,19 @@ extern "C" int tpk_three_nn(int b, int n, int m, const float* unknown, const flo
     return launch_three_nn_scan(b, n, m, unknown, known, dist2, idx, nullptr, static_cast<cudaStream_t>(stream));
 }
 
+// TPK_THREE_NN_GLOBAL_GRID selects the grid in global memory where the shared-memory grid
+// would be used (comparison runs and tests of that path)
+static bool three_nn_smem_grid(int m)
+{
+    return tpk::sg_three_nn_fits(m) && getenv("TPK_THREE_NN_GLOBAL_GRID") == nullptr;
+}
+
 extern "C" int64_t tpk_three_nn_scratch_bytes(int b, int n, int m)
 {
-    if (b <= 0 || n <= 0 || m < 4096) return 0;
+    if (b <= 0 || n <= 0) return 0;
+    // shared-memory grid: one flag per unknown point
+    if (three_nn_smem_grid(m)) return (static_cast<int64_t>(b) * n + 255) / 256 * 256;
+    if (m < 4096) return 0;
     return static_cast<int64_t>(tpk::grid_three_nn_scratch_bytes(b, n, m));
 }
 
@@ -368,7 +383,16 @@ extern "C" int tpk_three_nn_ws(int b, int n, int m, const float* unknown, const 
     TPK_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "three_nn: scratch must be 256-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const unsigned char* need = nullptr;
-    int rc = grid_three_nn(b, n, m, unknown, known, dist2, idx, scratch, &need, s);
+    int rc;
+    if (three_nn_smem_grid(m))
+    {
+        need = static_cast<const unsigned char*>(scratch);
+        rc = sg_three_nn(b, n, m, unknown, known, dist2, idx, static_cast<unsigned char*>(scratch), s);
+    }
+    else
+    {
+        rc = grid_three_nn(b, n, m, unknown, known, dist2, idx, scratch, &need, s);
+    }
     if (rc != TPK_OK) return rc;
     return launch_three_nn_scan(b, n, m, unknown, known, dist2, idx, need, s);
 }
