@@ -832,13 +832,23 @@ def run_only(args):
     for _ in range(args.warmup):
         fn()
     torch.cuda.synchronize(dev)
+    run = fn
+    if args.graph:
+        # device time of the op alone: its launches replayed from a CUDA graph, no host work between them
+        side = torch.cuda.Stream(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+            fn()
+        run = graph.replay
+        run()
+        torch.cuda.synchronize(dev)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        fn()
+        run()
     e1.record()
     torch.cuda.synchronize(dev)
-    print(json.dumps({"only": args.only, "clouds": B, "npoint": m, "steps": args.steps,
+    print(json.dumps({"only": args.only, "clouds": B, "npoint": m, "steps": args.steps, "graph": bool(args.graph),
                       "ms_per_call": round(e0.elapsed_time(e1) / args.steps, 4)}), flush=True)
 
 
@@ -847,6 +857,7 @@ def main():
     ap.add_argument("--only", default=None, help="run one op of the stack, e.g. fps_l1, grouping_bwd_l1")
     ap.add_argument("--clouds", type=int, default=0, help="with --only: clouds per batch (default 16)")
     ap.add_argument("--npoint", type=int, default=0, help="with --only: samples of that level's FPS")
+    ap.add_argument("--graph", action="store_true", help="with --only: time the op replayed from a CUDA graph")
     ap.add_argument("--workload", default="sa_fp_pipeline", choices=["sa_fp_pipeline", "chamfer", "partial", "fps_large"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)

@@ -101,6 +101,15 @@ __global__ void __launch_bounds__(THREADS)
         op.drow[q] = dist_out + row * nsample;
     }
 
+    if (need != nullptr)
+    {
+        // nothing left over for this CTA (the usual case behind the grid kernels): leave
+        // before staging a single tile
+        bool any = false;
+#pragma unroll
+        for (int q = 0; q < Q; ++q) any |= op.act[q];
+        if (!__syncthreads_or(any ? 1 : 0)) return;
+    }
     scan_candidates<THREADS, Q>(cand, n, smem, op.qx, op.qy, op.qz, op);
 
 #pragma unroll

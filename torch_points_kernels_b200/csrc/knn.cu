@@ -83,6 +83,15 @@ __global__ void __launch_bounds__(THREADS)
         op.b1[q] = op.b2[q] = op.b3[q] = CUDART_INF_F;
         op.i1[q] = op.i2[q] = op.i3[q] = 0;
     }
+    if (need != nullptr)
+    {
+        // nothing left over for this CTA (the usual case behind the grid kernels): leave
+        // before staging a single tile
+        bool any = false;
+#pragma unroll
+        for (int q = 0; q < Q; ++q) any |= op.act[q];
+        if (!__syncthreads_or(any ? 1 : 0)) return;
+    }
     scan_candidates<THREADS, Q>(known + static_cast<size_t>(cloud) * m * 3, m, smem, op.qx, op.qy, op.qz, op);
 #pragma unroll
     for (int q = 0; q < Q; ++q)

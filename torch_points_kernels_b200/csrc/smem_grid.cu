@@ -28,6 +28,27 @@ namespace tpk
 size_t grid_cells_capacity(int n);  // grid_query.cu
 int grid_max_dim(int n);
 
+#ifdef TPK_SG_TIMING
+// Debug builds: slot i holds the longest time (ns) any CTA spent between stamp i - 1 and stamp i.
+__device__ unsigned long long g_sg_stamps[16];
+#define SG_STAMP(i)                                                                        \
+    do                                                                                     \
+    {                                                                                      \
+        __syncthreads();                                                                   \
+        if (threadIdx.x == 0)                                                              \
+        {                                                                                  \
+            unsigned long long t_;                                                         \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                       \
+            if (sg_t_last_ != 0) atomicMax(&g_sg_stamps[i], t_ - sg_t_last_);              \
+            sg_t_last_ = t_;                                                               \
+        }                                                                                  \
+    } while (0)
+#define SG_TIMING_BEGIN() unsigned long long sg_t_last_ = 0
+#else
+#define SG_STAMP(i)
+#define SG_TIMING_BEGIN()
+#endif
+
 namespace
 {
 
@@ -35,7 +56,7 @@ constexpr int kSgThreads = 512;
 constexpr int kSgMaxPoints = 8192;       // three_nn: known points per cloud
 constexpr size_t kSgSmemBudget = 200 * 1024;
 constexpr int kSgSlotBits = 14;          // ball query: staged points per CTA < 2^14
-constexpr int kSgQueryChunk = 2048;      // ball query: centres examined per list pass
+constexpr int kSgQueryChunk = 1024;      // ball query: centres examined per list pass
 
 struct SgGrid
 {
@@ -219,42 +240,92 @@ __device__ __forceinline__ int sg_bin(const float* __restrict__ xyz, int n, cons
 
 // ------------------------------------------------------------------------------ three_nn
 //
-// Grid: blockIdx.x = cloud * parts + part; the CTA answers unknown points
-// [part * chunk, (part + 1) * chunk) of its cloud.
+// Grid: blockIdx.x = cloud * parts + part.  Every CTA of a cloud bins all known points.
+// The cells in x-fastest order cut the known points into `parts` runs of equal length;
+// the CTA owns the unknown points that fall into the cells of run `part` (as many
+// unknown points per CTA as the known density predicts).  It collects them from one pass
+// over the cloud's unknown points and sorts them by cell, so that the lanes of a warp
+// search the same or adjacent cells: same loop counts, same shared-memory rows.
+constexpr int kSgQueryCapMin = 1024;
+
 __global__ void __launch_bounds__(kSgThreads, 2)
-    sg_three_nn_kernel(int n, int m, int parts, int chunk, int max_dim, int cells_cap,
+    sg_three_nn_kernel(int n, int m, int parts, int qcap, int max_dim, int cells_cap,
                        const float* __restrict__ unknown_all, const float* __restrict__ known_all,
                        float* __restrict__ dist2_all, int32_t* __restrict__ idx_all,
                        unsigned char* __restrict__ need_all)
 {
     extern __shared__ __align__(16) unsigned char sg_raw[];
+    __shared__ int s_nq;
     float4* spts = reinterpret_cast<float4*>(sg_raw);
     int* cells = reinterpret_cast<int*>(spts + m);
+    int* qj = cells + cells_cap + 1;   // collected unknown points, in arrival order
+    int* qsorted = qj + qcap;          // the same, sorted by key
+    int* counts = qsorted + qcap;      // per key: run length + 1 entries
+    unsigned short* qkey = reinterpret_cast<unsigned short*>(counts + (m / parts + 3));
 
+    const int tid = threadIdx.x;
     const int cloud = blockIdx.x / parts, part = blockIdx.x - cloud * parts;
     const float* known = known_all + static_cast<size_t>(cloud) * m * 3;
-    const int q0 = part * chunk, q1 = min(n, q0 + chunk);
+    const float* unknown = unknown_all + static_cast<size_t>(cloud) * n * 3;
     const size_t qbase = static_cast<size_t>(cloud) * n;
 
+    SG_TIMING_BEGIN();
+    SG_STAMP(8);
     const SgGrid g = sg_make_grid(known, m, 1.0e-30f, max_dim, static_cast<size_t>(cells_cap));
+    SG_STAMP(9);
     int staged = -1;
     if (g.ok) staged = sg_bin(known, m, g, 0, g.dz - 1, cells, spts, m);
+    SG_STAMP(10);
     if (staged < 0)
     {
-        for (int j = q0 + threadIdx.x; j < q1; j += kSgThreads) need_all[qbase + j] = 1;
+        if (part == 0)
+            for (int j = tid; j < n; j += kSgThreads) need_all[qbase + j] = 1;
         return;
     }
-
-    for (int j = q0 + threadIdx.x; j < q1; j += kSgThreads)
-    {
-        const size_t t = qbase + j;
-        const float qx = __ldg(unknown_all + 3 * t + 0), qy = __ldg(unknown_all + 3 * t + 1),
-                    qz = __ldg(unknown_all + 3 * t + 2);
+    // run of known points this CTA owns: a cell belongs to the run its first slot lies in
+    // (the last run also takes the empty cells behind the last point)
+    const int lo = static_cast<int>(static_cast<long long>(part) * m / parts);
+    const int hi = part == parts - 1 ? m + 1 : static_cast<int>(static_cast<long long>(part + 1) * m / parts);
+    const int nkeys = hi - lo;  // at most m / parts + 2
+    if (tid == 0) s_nq = 0;
+    for (int k = tid; k <= nkeys; k += kSgThreads) counts[k] = 0;
+    __syncthreads();
+    sg_for_points(unknown, n, [&](int j, float qx, float qy, float qz) {
         if (!(fabsf(qx) < 1.0e18f && fabsf(qy) < 1.0e18f && fabsf(qz) < 1.0e18f))
         {
-            need_all[t] = 1;
-            continue;
+            if (part == 0) need_all[qbase + j] = 1;  // no cell: the first CTA hands it to the scan
+            return;
         }
+        const int cx = sg_cell_coord(qx, g.minx, g.inv_h, g.dx);
+        const int cy = sg_cell_coord(qy, g.miny, g.inv_h, g.dy);
+        const int cz = sg_cell_coord(qz, g.minz, g.inv_h, g.dz);
+        const int first_slot = cells[(cz * g.dy + cy) * g.dx + cx];
+        if (first_slot < lo || first_slot >= hi) return;
+        const int pos = atomicAdd(&s_nq, 1);
+        if (pos < qcap)
+        {
+            qj[pos] = j;
+            qkey[pos] = static_cast<unsigned short>(first_slot - lo);
+            atomicAdd(&counts[first_slot - lo + 1], 1);
+        }
+        else
+        {
+            need_all[qbase + j] = 1;  // far more unknown points here than known ones: left to the scan
+        }
+    });
+    __syncthreads();
+    SG_STAMP(11);
+    const int nq = min(s_nq, qcap);
+    sg_block_scan(counts + 1, nkeys);
+    for (int i = tid; i < nq; i += kSgThreads) qsorted[atomicAdd(&counts[qkey[i] + 1], 1)] = qj[i];
+    __syncthreads();
+    SG_STAMP(12);
+
+    for (int i = tid; i < nq; i += kSgThreads)
+    {
+        const int j = qsorted[i];
+        const size_t t = qbase + j;
+        const float qx = __ldg(unknown + 3 * j + 0), qy = __ldg(unknown + 3 * j + 1), qz = __ldg(unknown + 3 * j + 2);
         const int cx = sg_cell_coord(qx, g.minx, g.inv_h, g.dx);
         const int cy = sg_cell_coord(qy, g.miny, g.inv_h, g.dy);
         const int cz = sg_cell_coord(qz, g.minz, g.inv_h, g.dz);
@@ -294,33 +365,51 @@ __global__ void __launch_bounds__(kSgThreads, 2)
                         }
                         if (xa > xb) continue;
                         const int beg = cells[row + xa], end = cells[row + xb + 1];
-                        for (int p = beg; p < end; ++p)
+#ifdef TPK_SG_TIMING
+                        atomicAdd(&g_sg_stamps[14], static_cast<unsigned long long>(end - beg));
+#endif
+                        // four candidates per step: the loads and distances are independent,
+                        // only the updates of the three best run in order
+                        for (int p = beg; p < end; p += 4)
                         {
-                            const float4 c = spts[p];
-                            const float d = sumsq_abc(qx - c.x, qy - c.y, qz - c.z);
-                            const int k = __float_as_int(c.w);
-                            if (d < b3 || (d == b3 && k < i3))
+                            float d[4];
+                            int k[4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u)
                             {
-                                if (d < b1 || (d == b1 && k < i1))
+                                const float4 c = spts[min(p + u, end - 1)];
+                                d[u] = p + u < end ? sumsq_abc(qx - c.x, qy - c.y, qz - c.z) : CUDART_INF_F;
+                                k[u] = p + u < end ? __float_as_int(c.w) : 0x7fffffff;
+                            }
+#pragma unroll
+                            for (int u = 0; u < 4; ++u)
+                            {
+                                if (d[u] < b3 || (d[u] == b3 && k[u] < i3))
                                 {
-                                    b3 = b2; i3 = i2;
-                                    b2 = b1; i2 = i1;
-                                    b1 = d;  i1 = k;
-                                }
-                                else if (d < b2 || (d == b2 && k < i2))
-                                {
-                                    b3 = b2; i3 = i2;
-                                    b2 = d;  i2 = k;
-                                }
-                                else
-                                {
-                                    b3 = d; i3 = k;
+                                    if (d[u] < b1 || (d[u] == b1 && k[u] < i1))
+                                    {
+                                        b3 = b2; i3 = i2;
+                                        b2 = b1; i2 = i1;
+                                        b1 = d[u]; i1 = k[u];
+                                    }
+                                    else if (d[u] < b2 || (d[u] == b2 && k[u] < i2))
+                                    {
+                                        b3 = b2; i3 = i2;
+                                        b2 = d[u]; i2 = k[u];
+                                    }
+                                    else
+                                    {
+                                        b3 = d[u]; i3 = k[u];
+                                    }
                                 }
                             }
                         }
                     }
                 }
             px0 = x0; px1 = x1; py0 = y0; py1 = y1; pz0 = z0; pz1 = z1;
+#ifdef TPK_SG_TIMING
+            atomicAdd(&g_sg_stamps[15], 1ull);
+#endif
             if (x0 == 0 && y0 == 0 && z0 == 0 && x1 == g.dx - 1 && y1 == g.dy - 1 && z1 == g.dz - 1) break;
             // distance to the nearest face of the block with unsearched cells behind it
             float rho = CUDART_INF_F;
@@ -343,6 +432,7 @@ __global__ void __launch_bounds__(kSgThreads, 2)
         idx_all[3 * t + 1] = i2 == 0x7fffffff ? 0 : i2;
         idx_all[3 * t + 2] = i3 == 0x7fffffff ? 0 : i3;
     }
+    SG_STAMP(13);
 }
 
 // ---------------------------------------------------------------------------- ball query
@@ -389,7 +479,10 @@ __global__ void __launch_bounds__(kSgThreads, 2)
 
     const float r1 = radius * 1.00001f + 1.0e-30f;
     const float r2 = __fmul_rn(radius, radius);
+    SG_TIMING_BEGIN();
+    SG_STAMP(0);
     const SgGrid g = sg_make_grid(xyz, n, r1, max_dim, static_cast<size_t>(cells_cap));
+    SG_STAMP(1);
     // too few cells: the scan is as good; a radius that is not a positive finite number: the scan decides
     const bool use = g.ok && radius > 0.f && radius < 1.0e18f && g.dx * g.dy * g.dz >= 64;
     if (!use)
@@ -402,6 +495,7 @@ __global__ void __launch_bounds__(kSgThreads, 2)
     if (own_lo > own_hi) return;
     const int za = max(own_lo - 1, 0), zb = min(own_hi + 1, g.dz - 1);
     const int staged = sg_bin(xyz, n, g, za, zb, cells, spts, pcap);
+    SG_STAMP(2);
 
     SgWarpScratch& ws = wscr[warp];
     for (int base = 0; base < m; base += kSgQueryChunk)
@@ -409,29 +503,40 @@ __global__ void __launch_bounds__(kSgThreads, 2)
         if (tid == 0) s_count = 0;
         __syncthreads();
         const int jend = min(m, base + kSgQueryChunk);
-        for (int j = base + tid; j < jend; j += kSgThreads)
-        {
-            const float qx = __ldg(new_xyz + 3 * j + 0), qy = __ldg(new_xyz + 3 * j + 1), qz = __ldg(new_xyz + 3 * j + 2);
+        // (a chunk starts at a multiple of four centres, so the 16-byte path stays aligned)
+        sg_for_points(new_xyz + 3 * static_cast<size_t>(base), jend - base, [&](int jj, float qx, float qy, float qz) {
+            const int j = base + jj;
             if (!(fabsf(qx) < 1.0e18f && fabsf(qy) < 1.0e18f && fabsf(qz) < 1.0e18f))
             {
                 if (part == 0) need_all[qbase + j] = 1;  // no cell: the first CTA hands it to the scan
-                continue;
+                return;
             }
             const int qcz = sg_cell_coord(qz, g.minz, g.inv_h, g.dz);
-            if (qcz < own_lo || qcz > own_hi) continue;
+            if (qcz < own_lo || qcz > own_hi) return;
             if (staged < 0)
                 need_all[qbase + j] = 1;  // more points around these layers than fit
             else
                 qlist[atomicAdd(&s_count, 1)] = j;
-        }
+        });
         __syncthreads();
         const int nq = s_count;
+        SG_STAMP(3);
+        // the next centre's coordinates are requested one centre ahead (they come from L2)
+        int j_next = warp < nq ? qlist[warp] : 0;
+        float nx = __ldg(new_xyz + 3 * j_next + 0), ny_ = __ldg(new_xyz + 3 * j_next + 1), nz = __ldg(new_xyz + 3 * j_next + 2);
         for (int i = warp; i < nq; i += kSgWarps)
         {
             // everything up to the candidate loop is the same in all lanes of the warp
-            const int j = qlist[i];
+            const int j = j_next;
             const size_t t = qbase + j;
-            const float qx = __ldg(new_xyz + 3 * j + 0), qy = __ldg(new_xyz + 3 * j + 1), qz = __ldg(new_xyz + 3 * j + 2);
+            const float qx = nx, qy = ny_, qz = nz;
+            if (i + kSgWarps < nq)
+            {
+                j_next = qlist[i + kSgWarps];
+                nx = __ldg(new_xyz + 3 * j_next + 0);
+                ny_ = __ldg(new_xyz + 3 * j_next + 1);
+                nz = __ldg(new_xyz + 3 * j_next + 2);
+            }
             // cell range of the ball, enlarged by the rounding of the exact test (1e-5 relative)
             // and of q +- r itself (2e-7 |q|); the cell function is monotone, so every point the
             // exact test can accept lies in a cell of the range
@@ -530,6 +635,7 @@ __global__ void __launch_bounds__(kSgThreads, 2)
             if (lane == 0) need_all[t] = 0;
         }
         __syncthreads();
+        SG_STAMP(4);
     }
 }
 
@@ -545,13 +651,23 @@ int sg_three_nn(int b, int n, int m, const float* unknown, const float* known, f
 {
     const int max_dim = grid_max_dim(m);
     const int cap = static_cast<int>(grid_cells_capacity(m));
-    const size_t smem = static_cast<size_t>(m) * sizeof(float4) + (static_cast<size_t>(cap) + 1) * sizeof(int);
-    int parts = (2 * num_sms() + b - 1) / b;
-    const int max_parts = (n + kSgThreads - 1) / kSgThreads;
-    if (parts > max_parts) parts = max_parts;
+    // CTAs per cloud: at most two per SM over the batch (one wave), at least 256 unknown points each, and runs of
+    // known points short enough for a 16-bit sort key
+    int parts = 2 * num_sms() / b;
+    if (parts > n / 256) parts = n / 256;
+    if (parts > m / 8) parts = m / 8;
     if (parts < 1) parts = 1;
-    const int chunk = (n + parts - 1) / parts;
-    parts = (n + chunk - 1) / chunk;
+    const size_t base = static_cast<size_t>(m) * sizeof(float4) + (static_cast<size_t>(cap) + 1) * sizeof(int) +
+                        (static_cast<size_t>(m / parts) + 3) * sizeof(int);
+    // unknown points a CTA takes: 2.5 times its share, whatever still fits
+    long long qcap = 5ll * n / (2 * parts) + 64;
+    if (qcap < kSgQueryCapMin) qcap = kSgQueryCapMin;
+    if (qcap > n) qcap = n;
+    const long long room = (static_cast<long long>(kSgSmemBudget) - static_cast<long long>(base)) / 10;
+    if (qcap > room) qcap = room;
+    qcap = (qcap + 1) / 2 * 2;
+    TPK_REQUIRE(qcap >= 2, "three_nn grid: no room for the query list");
+    const size_t smem = base + static_cast<size_t>(qcap) * 10;
     auto kernel = sg_three_nn_kernel;
     prefer_max_shared(kernel);
     if (smem > 48 * 1024)
@@ -565,8 +681,8 @@ int sg_three_nn(int b, int n, int m, const float* unknown, const float* known, f
     }
     const long long grid = static_cast<long long>(b) * parts;
     TPK_REQUIRE(grid < (1ll << 31), "three_nn: too many queries");
-    kernel<<<static_cast<unsigned>(grid), kSgThreads, smem, s>>>(n, m, parts, chunk, max_dim, cap, unknown, known, dist2,
-                                                                 idx, need);
+    kernel<<<static_cast<unsigned>(grid), kSgThreads, smem, s>>>(n, m, parts, static_cast<int>(qcap), max_dim, cap, unknown,
+                                                                 known, dist2, idx, need);
     return check_launch("three_nn grid");
 }
 
@@ -579,26 +695,26 @@ struct SgBallPlan
     bool ok;
 };
 
-// Layers per CTA: as many as still give every SM a CTA (each CTA passes over the whole
-// cloud to bin its layers, so fewer, larger parts do less redundant work), and few
-// enough that twice the expected number of staged points fits.
-SgBallPlan sg_ball_plan(int b, int n, int nsample)
+// Layers per CTA.  Every CTA passes over the whole cloud three times to bin its layers
+// (a fixed cost) and then answers the centres of the layers it owns.  The plan minimises
+// the larger of the heaviest CTA and the total work divided by the CTAs the SMs hold at once.
+SgBallPlan sg_ball_plan(int b, int n, int m, int nsample)
 {
-    SgBallPlan p = {};
-    p.ok = false;
-    if (b < 1 || n < 1024 || n >= (1 << (32 - kSgSlotBits)) || nsample < 1 || nsample > kSgHitCap) return p;
-    p.max_dim = grid_max_dim(n);
-    p.cells_cap = static_cast<int>(grid_cells_capacity(n));
-    for (int lpp = p.max_dim; lpp >= 1; --lpp)
+    SgBallPlan best = {};
+    best.ok = false;
+    if (b < 1 || n < 1024 || n >= (1 << (32 - kSgSlotBits)) || nsample < 1 || nsample > kSgHitCap) return best;
+    const int max_dim = grid_max_dim(n);
+    double best_cost = 0.0;
+    for (int lpp = 1; lpp <= max_dim; ++lpp)
     {
-        const int parts = (p.max_dim + lpp - 1) / lpp;
-        if (lpp > 1 && static_cast<long long>(b) * parts < num_sms()) continue;
-        const int layers = lpp + 2 < p.max_dim ? lpp + 2 : p.max_dim;
-        const size_t slab_cells = static_cast<size_t>(layers) * p.max_dim * p.max_dim;
+        const int parts = (max_dim + lpp - 1) / lpp;
+        if (lpp > 1 && parts == (max_dim + lpp - 2) / (lpp - 1)) continue;  // same parts with fewer layers each
+        const int layers = lpp + 2 < max_dim ? lpp + 2 : max_dim;
+        const size_t slab_cells = static_cast<size_t>(layers) * max_dim * max_dim;
         const size_t fixed = (slab_cells + 1) * sizeof(int) + static_cast<size_t>(kSgQueryChunk) * sizeof(int) +
                              kSgWarps * sizeof(SgWarpScratch) + 64;
         if (fixed + 1024 * sizeof(float4) > kSgSmemBudget) continue;
-        size_t want = static_cast<size_t>(2.0 * n * layers / p.max_dim) + 256;
+        size_t want = static_cast<size_t>(2.0 * n * layers / max_dim) + 256;
         if (want > static_cast<size_t>(n)) want = n;
         size_t room = (kSgSmemBudget - fixed) / sizeof(float4);
         if (room > (1u << kSgSlotBits)) room = 1u << kSgSlotBits;
@@ -607,24 +723,40 @@ SgBallPlan sg_ball_plan(int b, int n, int nsample)
             if (lpp > 1) continue;
             want = room;  // single layers: take what fits, crowded layers go to the scan
         }
+        SgBallPlan p = {};
+        p.max_dim = max_dim;
+        p.cells_cap = static_cast<int>(grid_cells_capacity(n));
         p.lpp = lpp;
         p.parts = parts;
         p.slab_cells_cap = static_cast<int>(slab_cells);
         p.pcap = static_cast<int>((want + 3) / 4 * 4);
         p.smem = static_cast<size_t>(p.pcap) * sizeof(float4) + fixed;
         p.ok = true;
-        return p;
+        // 228 KB of shared memory per SM, 1 KB reserved per CTA; registers allow two CTAs
+        const int per_sm = (p.smem + 1024) * 2 <= 228 * 1024 ? 2 : 1;
+        const double slots = static_cast<double>(num_sms()) * per_sm;
+        // measured: about 1 ns per point for the three passes, 75 ns per centre (one warp each,
+        // sixteen at a time); the middle layers of a round cloud hold 1.5 times the average
+        const double passes = 1.0 * n, per_layer = 75.0 * m / max_dim;
+        const double total = static_cast<double>(b) * (parts * passes + max_dim * per_layer);
+        const double heaviest = passes + 1.5 * lpp * per_layer;
+        const double cost = total / slots > heaviest ? total / slots : heaviest;
+        if (!best.ok || cost < best_cost)
+        {
+            best = p;
+            best_cost = cost;
+        }
     }
-    return p;
+    return best;
 }
 }  // namespace
 
-bool sg_ball_query_fits(int b, int n, int nsample) { return sg_ball_plan(b, n, nsample).ok; }
+bool sg_ball_query_fits(int b, int n, int nsample) { return sg_ball_plan(b, n, n, nsample).ok; }
 
 int sg_ball_query(int b, int n, int m, float radius, int nsample, const float* new_xyz, const float* xyz,
                   int64_t* idx, float* dist, unsigned char* need, cudaStream_t s)
 {
-    const SgBallPlan p = sg_ball_plan(b, n, nsample);
+    const SgBallPlan p = sg_ball_plan(b, n, m, nsample);
     if (!p.ok)
     {
         set_error("ball_query grid: sizes do not fit shared memory (n=%d nsample=%d)", n, nsample);
@@ -651,3 +783,13 @@ int sg_ball_query(int b, int n, int m, float radius, int nsample, const float* n
 }
 
 }  // namespace tpk
+
+#ifdef TPK_SG_TIMING
+// Debug builds only: phase time stamps (ns) of the middle CTA of the last launches.
+extern "C" __attribute__((visibility("default"))) int tpk_debug_sg_stamps(unsigned long long* out16)
+{
+    static const unsigned long long zeros[16] = {};
+    if (cudaMemcpyFromSymbol(out16, tpk::g_sg_stamps, sizeof(zeros)) != cudaSuccess) return 2;
+    return cudaMemcpyToSymbol(tpk::g_sg_stamps, zeros, sizeof(zeros)) == cudaSuccess ? 0 : 2;
+}
+#endif
