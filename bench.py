@@ -79,7 +79,6 @@ class Pipeline:
         self.g_grouped = [torch.randn(B, c, m, LEVELS["nsample"], device=dev, generator=g)
                           for c, m in zip(LEVELS["channels"], LEVELS["npoint"])]
         self.g_up = [torch.randn(B, c, n, device=dev, generator=g) for c, n in zip(LEVELS["channels"], n_in)]
-        self.launches = 0
         self.keep = None
 
     def step(self, xyz, sa_feat, fp_feat, overlap=True, timers=None, pipelined=False, ready=None):
@@ -133,7 +132,6 @@ class Pipeline:
                 ev = torch.cuda.Event()
                 ev.record(s_fps)
                 fps_ready.append(ev)
-        self.launches += 4
 
         geo, geo_ready = [], []
         with torch.cuda.stream(s_geo):
@@ -151,7 +149,6 @@ class Pipeline:
                 ev = torch.cuda.Event()
                 ev.record(s_geo)
                 geo_ready.append(ev)
-                self.launches += 2
 
         grads_sa, grads_fp = [], []
         with torch.cuda.stream(s_feat):
@@ -169,7 +166,6 @@ class Pipeline:
                 timed("interp_bwd_l%d" % (l + 1), lambda: up.backward(self.g_up[l]))
                 grads_fp.append(hand_over(ff.grad, cur))
                 ff.grad = None
-                self.launches += 4
             done = torch.cuda.Event()
             done.record(s_feat)
         if overlap and not pipelined:
@@ -177,6 +173,12 @@ class Pipeline:
             cur.wait_stream(s_geo)
             cur.wait_stream(s_feat)
         return fps_idx, grads_sa, grads_fp, done
+
+
+def _lib_launches():
+    from torch_points_kernels_b200 import _lib
+
+    return _lib.kernel_launches()
 
 
 class GraphedSteps:
@@ -191,12 +193,15 @@ class GraphedSteps:
             launch = torch.cuda.Stream(dev)
             graph = torch.cuda.CUDAGraph()
             pipe.keep = []
+            before = _lib_launches()
             try:
                 with torch.cuda.graph(graph, stream=launch, capture_error_mode="thread_local"):
                     fps_idx, g_sa, g_fp, _ = pipe.step(*split([t.detach() for t in ins]))
                     chk = torch.stack([g.sum() for g in g_sa + g_fp])
             finally:
                 keep, pipe.keep = pipe.keep, None
+            # kernels of the library in one step: counted by the library while the step was captured
+            self.launches_per_step = _lib_launches() - before
             self.slots.append({"graph": graph, "ins": ins, "launch": launch, "fps_idx": fps_idx, "chk": chk,
                                "keep": (keep, g_sa, g_fp)})
 
@@ -367,20 +372,20 @@ def run_b200(args, rank, world, local_rank):
         sampler.start()
         time.sleep(0.3)
     barrier()
-    pipe.launches = 0
+    launches_before = _lib.kernel_launches()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     if graphs is not None:
         for slot in graphs.slots:
             slot["launch"].wait_stream(cur)
         run_graphs(args.steps)
-        pipe.launches = 28 * args.steps
+        launches = graphs.launches_per_step * args.steps  # replays are not seen by the library's counter
     else:
         run_resident(args.steps, True)
+        launches = _lib.kernel_launches() - launches_before
     e1.record()
     barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
-    launches = pipe.launches
     host_ms = pipe.host_ms
 
     # the same without overlap between consecutive steps (latency of one isolated step)

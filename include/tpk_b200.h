@@ -54,6 +54,13 @@ TPK_API const char* tpk_last_error(void);
  */
 TPK_API int tpk_device_status(int* status_out, int reset);
 
+/*
+ * Number of kernels the library has launched in this process so far, on any device and
+ * stream.  A launch recorded by a stream capture counts once, when it is captured, not when
+ * the graph is replayed.  For launch accounting in benchmarks; no counterpart in the reference.
+ */
+TPK_API int64_t tpk_kernel_launches(void);
+
 /* ---------------------------------------------------------------- sampling ---- */
 
 /*

@@ -40,7 +40,7 @@ _SIGNATURES = {
     "tpk_chamfer_dist_grad_f64": [_c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
 }
 
-EXPORTS = sorted(list(_SIGNATURES) + ["tpk_version", "tpk_last_error", "tpk_device_status", "tpk_fps_scratch_bytes",
+EXPORTS = sorted(list(_SIGNATURES) + ["tpk_version", "tpk_last_error", "tpk_device_status", "tpk_kernel_launches", "tpk_fps_scratch_bytes",
                                        "tpk_fps_static_capacity", "tpk_ball_query_dense_scratch_bytes",
                                        "tpk_three_nn_scratch_bytes"])
 
@@ -62,6 +62,8 @@ def lib():
             fn.restype = _c_int
         handle.tpk_version.restype = _c_int
         handle.tpk_last_error.restype = ctypes.c_char_p
+        handle.tpk_kernel_launches.argtypes = []
+        handle.tpk_kernel_launches.restype = _c_i64
         handle.tpk_device_status.argtypes = [ctypes.POINTER(_c_int), _c_int]
         handle.tpk_device_status.restype = _c_int
         handle.tpk_fps_scratch_bytes.argtypes = [_c_int, _c_int, _c_int]
@@ -120,3 +122,8 @@ def device_status(reset=True):
     if status != 0:
         raise RuntimeError(lib().tpk_last_error().decode("utf-8", "replace"))
     return out.value
+
+
+def kernel_launches():
+    """Kernels the library has launched (or recorded into a stream capture) in this process."""
+    return int(lib().tpk_kernel_launches())

@@ -221,22 +221,22 @@ void pick_shape(long long queries, int* threads, int* q)
         if (threads == 128 && q == 2)                                                              \
         {                                                                                          \
             prefer_max_shared(KERNEL<128, 2>);                                                     \
-            KERNEL<128, 2><<<g, 128, 0, s>>>(__VA_ARGS__);                                         \
+            count_launches(1), KERNEL<128, 2><<<g, 128, 0, s>>>(__VA_ARGS__);                                         \
         }                                                                                          \
         else if (threads == 128)                                                                   \
         {                                                                                          \
             prefer_max_shared(KERNEL<128, 1>);                                                     \
-            KERNEL<128, 1><<<g, 128, 0, s>>>(__VA_ARGS__);                                         \
+            count_launches(1), KERNEL<128, 1><<<g, 128, 0, s>>>(__VA_ARGS__);                                         \
         }                                                                                          \
         else if (q == 2)                                                                           \
         {                                                                                          \
             prefer_max_shared(KERNEL<64, 2>);                                                      \
-            KERNEL<64, 2><<<g, 64, 0, s>>>(__VA_ARGS__);                                           \
+            count_launches(1), KERNEL<64, 2><<<g, 64, 0, s>>>(__VA_ARGS__);                                           \
         }                                                                                          \
         else                                                                                       \
         {                                                                                          \
             prefer_max_shared(KERNEL<64, 1>);                                                      \
-            KERNEL<64, 1><<<g, 64, 0, s>>>(__VA_ARGS__);                                           \
+            count_launches(1), KERNEL<64, 1><<<g, 64, 0, s>>>(__VA_ARGS__);                                           \
         }                                                                                          \
     } while (0)
 

@@ -1,5 +1,7 @@
-// Error text and version of the C ABI.
+// Error text, version and launch counter of the C ABI.
 #include <stdarg.h>
+
+#include <atomic>
 
 #include "tpk_common.cuh"
 
@@ -14,8 +16,14 @@ void set_error(const char* fmt, ...)
     vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
     va_end(ap);
 }
+
+static std::atomic<long long> g_kernel_launches{0};
+
+void count_launches(int k) { g_kernel_launches.fetch_add(k, std::memory_order_relaxed); }
 }  // namespace tpk
 
 extern "C" int tpk_version(void) { return 100; }
+
+extern "C" int64_t tpk_kernel_launches(void) { return tpk::g_kernel_launches.load(std::memory_order_relaxed); }
 
 extern "C" const char* tpk_last_error(void) { return tpk::g_last_error; }

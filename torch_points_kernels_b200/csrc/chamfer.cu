@@ -162,22 +162,22 @@ int chamfer_dir_f32(int b, int n, const float* xyz1, int m, const float* xyz2, f
     if (threads == 128 && q == 2)
     {
         prefer_max_shared(chamfer_f32_kernel<128, 2>);
-        chamfer_f32_kernel<128, 2><<<g, 128, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
+        count_launches(1), chamfer_f32_kernel<128, 2><<<g, 128, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
     }
     else if (threads == 128)
     {
         prefer_max_shared(chamfer_f32_kernel<128, 1>);
-        chamfer_f32_kernel<128, 1><<<g, 128, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
+        count_launches(1), chamfer_f32_kernel<128, 1><<<g, 128, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
     }
     else if (q == 2)
     {
         prefer_max_shared(chamfer_f32_kernel<64, 2>);
-        chamfer_f32_kernel<64, 2><<<g, 64, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
+        count_launches(1), chamfer_f32_kernel<64, 2><<<g, 64, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
     }
     else
     {
         prefer_max_shared(chamfer_f32_kernel<64, 1>);
-        chamfer_f32_kernel<64, 1><<<g, 64, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
+        count_launches(1), chamfer_f32_kernel<64, 1><<<g, 64, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
     }
     return check_launch("chamfer_dist");
 }
@@ -200,7 +200,7 @@ int chamfer_dir_f64(int b, int n, const double* xyz1, int m, const double* xyz2,
     const long long total = static_cast<long long>(b) * n;
     const long long grid = (total + 127) / 128;
     TPK_REQUIRE(grid < (1ll << 31), "chamfer_dist: too many points");
-    chamfer_f64_kernel<<<static_cast<unsigned>(grid), 128, 0, s>>>(b, n, m, xyz1, xyz2, dist, idx);
+    count_launches(1), chamfer_f64_kernel<<<static_cast<unsigned>(grid), 128, 0, s>>>(b, n, m, xyz1, xyz2, dist, idx);
     return check_launch("chamfer_dist_f64");
 }
 
@@ -224,7 +224,7 @@ int chamfer_grad_t(int b, int n, const T* xyz1, int m, const T* xyz2, const int3
     const long long total = (static_cast<long long>(n) + m) * b;
     const long long grid = (total + 255) / 256;
     TPK_REQUIRE(grid < (1ll << 31), "chamfer_dist_grad: too many points");
-    chamfer_grad_kernel<T><<<static_cast<unsigned>(grid), 256, 0, s>>>(b, n, m, xyz1, xyz2, idx1, idx2,
+    count_launches(1), chamfer_grad_kernel<T><<<static_cast<unsigned>(grid), 256, 0, s>>>(b, n, m, xyz1, xyz2, idx1, idx2,
                                                                       gd1, gd2, g1, g2);
     return check_launch("chamfer_dist_grad");
 }

@@ -719,7 +719,7 @@ int fps_launch_sort(int b, int n, const float* xyz, float4* sorted, cudaStream_t
             return TPK_ERR_CUDA;
         }
     }
-    fps_sort_kernel<<<b, kSortThreads, smem, stream>>>(n, bits, xyz, sorted);
+    count_launches(1), fps_sort_kernel<<<b, kSortThreads, smem, stream>>>(n, bits, xyz, sorted);
     return check_launch("fps sort");
 }
 
@@ -935,6 +935,7 @@ int fps_launch_global(int b, int n, int m, int log2bs, const float* xyz, float* 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    count_launches(1);
     err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, xyz, temp, idxs);
     if (err != cudaSuccess)
     {
@@ -1054,6 +1055,7 @@ int fps_launch_t(const FpsConfig& c, int b, int n, int m, int log2bs, const floa
     // TPK_FPS_FLAT=0 selects the three-stage exchange for comparison runs
     const char* flat_env = getenv("TPK_FPS_FLAT");
     const int flat = (c.nranks > 1 && c.nranks * (c.nthreads / 32) <= 32 && !(flat_env && flat_env[0] == '0')) ? 1 : 0;
+    count_launches(1);
     err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, flat, xyz, sorted, idxs);
     if (err != cudaSuccess)
     {

@@ -18,6 +18,10 @@
 // three_interpolate : cuda/src/interpolate_gpu.cu:78-107, :122-152
 #include "tpk_common.cuh"
 
+#ifndef TPK_GBWD_UNROLL
+#define TPK_GBWD_UNROLL 4
+#endif
+
 namespace tpk
 {
 namespace
@@ -221,7 +225,7 @@ int launch_grouping_fwd_rows(int b, int c, int n, long long ps, const float* fea
     TPK_REQUIRE(groups <= 65535 && nchunks < (1ll << 31), "grouping: grid too large");
     const int use_tma = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(features) & 15u) == 0);
     const dim3 g(static_cast<unsigned>(nchunks), static_cast<unsigned>(groups));
-    kernel<<<g, kScatterThreads, smem, s>>>(c, n, ps, chunk, use_tma, features, idx, out);
+    count_launches(1), kernel<<<g, kScatterThreads, smem, s>>>(c, n, ps, chunk, use_tma, features, idx, out);
     return check_launch("grouping");
 }
 
@@ -382,7 +386,7 @@ int launch_interp_fwd_rows(int b, int c, int m, int n, const float* points, cons
     const int use_tma = (m % 4 == 0) && ((reinterpret_cast<uintptr_t>(points) & 15u) == 0) &&
                         static_cast<size_t>(ROWS) * m * 4 < (1u << 20);
     const dim3 g(static_cast<unsigned>(nchunks), static_cast<unsigned>(groups));
-    kernel<<<g, kGatherThreads, smem, s>>>(c, m, n, chunk, use_tma, points, idx, weight, out);
+    count_launches(1), kernel<<<g, kGatherThreads, smem, s>>>(c, m, n, chunk, use_tma, points, idx, weight, out);
     return check_launch("three_interpolate");
 }
 
@@ -506,7 +510,7 @@ __global__ void __launch_bounds__(kScatterThreads)
                              const float* __restrict__ grad_out, const int64_t* __restrict__ idx,
                              float* __restrict__ grad_small)
 {
-    constexpr int UNROLL = 4;
+    constexpr int UNROLL = TPK_GBWD_UNROLL;
     constexpr int NWARPS = kScatterThreads / 32;
     extern __shared__ __align__(16) float acc[];
     const int groups_per_batch = (c + ROWS - 1) / ROWS;
@@ -609,7 +613,7 @@ int launch_grouping_bwd_rows_seg(int b, int c, int row_len, long long src_len, c
     }
     const long long grid = static_cast<long long>(b) * ((c + ROWS - 1) / ROWS);
     TPK_REQUIRE(grid < (1ll << 31), "grouping_grad: too many rows");
-    kernel<<<static_cast<unsigned>(grid), kScatterThreads, smem, s>>>(c, row_len, src_len, grad_out, idx,
+    count_launches(1), kernel<<<static_cast<unsigned>(grid), kScatterThreads, smem, s>>>(c, row_len, src_len, grad_out, idx,
                                                                     grad_small);
     return check_launch("grouping_grad");
 }
@@ -695,7 +699,7 @@ int launch_interp_bwd_rows(int b, int c, int m, int n, const float* grad_out, co
     }
     const long long grid = static_cast<long long>(b) * ((c + ROWS - 1) / ROWS);
     TPK_REQUIRE(grid < (1ll << 31), "three_interpolate_grad: too many rows");
-    kernel<<<static_cast<unsigned>(grid), THREADS, smem, s>>>(c, m, n, grad_out, idx, weight, grad_points);
+    count_launches(1), kernel<<<static_cast<unsigned>(grid), THREADS, smem, s>>>(c, m, n, grad_out, idx, weight, grad_points);
     return check_launch("three_interpolate_grad");
 }
 
@@ -769,7 +773,7 @@ int launch_scatter(int b, int c, int row_len, long long src_len, const float* gr
         }
         const long long grid = static_cast<long long>(b) * ((c + rows - 1) / rows);
         TPK_REQUIRE(grid < (1ll << 31), "%s: too many rows", what);
-        kernel<<<static_cast<unsigned>(grid), kScatterThreads, smem, s>>>(
+        count_launches(1), kernel<<<static_cast<unsigned>(grid), kScatterThreads, smem, s>>>(
             c, row_len, src_len, rows, grad_out, idx, weight, grad_small);
         return check_launch(what);
     }
@@ -783,7 +787,7 @@ int launch_scatter(int b, int c, int row_len, long long src_len, const float* gr
     TPK_REQUIRE(gx < (1ll << 31) && b <= 65535 && (c + kChanChunk - 1) / kChanChunk <= 65535,
                 "%s: grid too large", what);
     const dim3 g(static_cast<unsigned>(gx), (c + kChanChunk - 1) / kChanChunk, b);
-    scatter_global_kernel<INTERP><<<g, kGatherThreads, 0, s>>>(c, row_len, src_len, grad_out, idx,
+    count_launches(1), scatter_global_kernel<INTERP><<<g, kGatherThreads, 0, s>>>(c, row_len, src_len, grad_out, idx,
                                                               weight, grad_small);
     return check_launch(what);
 }
@@ -827,9 +831,9 @@ extern "C" int tpk_grouping(int b, int c, int n, int npoint, int nsample, const 
     TPK_REQUIRE(gx < (1ll << 31) && gy <= 65535 && b <= 65535, "grouping: grid too large");
     const dim3 g(static_cast<unsigned>(gx), gy, b);
     if (ps % 4 == 0 && aligned16(idx) && aligned16(out))
-        grouping_fwd_kernel<true><<<g, kGatherThreads, 0, s>>>(c, n, ps, features, idx, out);
+        count_launches(1), grouping_fwd_kernel<true><<<g, kGatherThreads, 0, s>>>(c, n, ps, features, idx, out);
     else
-        grouping_fwd_kernel<false><<<g, kGatherThreads, 0, s>>>(c, n, ps, features, idx, out);
+        count_launches(1), grouping_fwd_kernel<false><<<g, kGatherThreads, 0, s>>>(c, n, ps, features, idx, out);
     return check_launch("grouping");
 }
 
@@ -903,9 +907,9 @@ extern "C" int tpk_three_interpolate(int b, int c, int m, int n, const float* po
     TPK_REQUIRE(gy <= 65535 && b <= 65535, "three_interpolate: grid too large");
     const dim3 g(gx, gy, b);
     if (n % 4 == 0 && aligned16(out))
-        interp_fwd_kernel<true><<<g, kGatherThreads, 0, s>>>(c, m, n, points, idx, weight, out);
+        count_launches(1), interp_fwd_kernel<true><<<g, kGatherThreads, 0, s>>>(c, m, n, points, idx, weight, out);
     else
-        interp_fwd_kernel<false><<<g, kGatherThreads, 0, s>>>(c, m, n, points, idx, weight, out);
+        count_launches(1), interp_fwd_kernel<false><<<g, kGatherThreads, 0, s>>>(c, m, n, points, idx, weight, out);
     return check_launch("three_interpolate");
 }
 

@@ -463,10 +463,10 @@ int grid_ball_query_dense(int b, int n, int m, float radius, int nsample, const 
 
     const long long npts = static_cast<long long>(b) * n;
     const unsigned gp = static_cast<unsigned>((npts + kGridThreads - 1) / kGridThreads);
-    grid_setup_kernel<<<b, kGridThreads, 0, s>>>(n, radius, grid_max_dim(n), cap, xyz, info, cells);
-    grid_bin_kernel<false><<<gp, kGridThreads, 0, s>>>(b, n, cap, xyz, info, cells, sorted);
-    grid_scan_kernel<<<b, 1024, 0, s>>>(cap, info, cells);
-    grid_bin_kernel<true><<<gp, kGridThreads, 0, s>>>(b, n, cap, xyz, info, cells, sorted);
+    count_launches(1), grid_setup_kernel<<<b, kGridThreads, 0, s>>>(n, radius, grid_max_dim(n), cap, xyz, info, cells);
+    count_launches(1), grid_bin_kernel<false><<<gp, kGridThreads, 0, s>>>(b, n, cap, xyz, info, cells, sorted);
+    count_launches(1), grid_scan_kernel<<<b, 1024, 0, s>>>(cap, info, cells);
+    count_launches(1), grid_bin_kernel<true><<<gp, kGridThreads, 0, s>>>(b, n, cap, xyz, info, cells, sorted);
     const size_t smem = static_cast<size_t>(nsample) * kGridQueryThreads * 8;
     auto qk = grid_query_kernel;
     prefer_max_shared(qk);
@@ -483,7 +483,7 @@ int grid_ball_query_dense(int b, int n, int m, float radius, int nsample, const 
     const float max_cand = 2.0f * sqrtf(6.45f * static_cast<float>(n) * static_cast<float>(nsample));
     const long long nq = static_cast<long long>(b) * m;
     const unsigned gq = static_cast<unsigned>((nq + kGridQueryThreads - 1) / kGridQueryThreads);
-    qk<<<gq, kGridQueryThreads, smem, s>>>(b, n, m, radius, nsample, max_cand, cap, new_xyz, info, cells, sorted, idx,
+    count_launches(1), qk<<<gq, kGridQueryThreads, smem, s>>>(b, n, m, radius, nsample, max_cand, cap, new_xyz, info, cells, sorted, idx,
                                            dist, need);
     *need_scan_out = need;
     return check_launch("ball_query grid");
@@ -511,14 +511,14 @@ int grid_three_nn(int b, int n, int m, const float* unknown, const float* known,
     const long long npts = static_cast<long long>(b) * m;
     const unsigned gp = static_cast<unsigned>((npts + kGridThreads - 1) / kGridThreads);
     // no radius here: cells as small as the capacity allows (radius argument just above zero)
-    grid_setup_kernel<<<b, kGridThreads, 0, s>>>(m, 1.0e-30f, grid_max_dim(m), cap, known, info, cells);
-    grid_bin_kernel<false><<<gp, kGridThreads, 0, s>>>(b, m, cap, known, info, cells, sorted);
-    grid_scan_kernel<<<b, 1024, 0, s>>>(cap, info, cells);
-    grid_bin_kernel<true><<<gp, kGridThreads, 0, s>>>(b, m, cap, known, info, cells, sorted);
+    count_launches(1), grid_setup_kernel<<<b, kGridThreads, 0, s>>>(m, 1.0e-30f, grid_max_dim(m), cap, known, info, cells);
+    count_launches(1), grid_bin_kernel<false><<<gp, kGridThreads, 0, s>>>(b, m, cap, known, info, cells, sorted);
+    count_launches(1), grid_scan_kernel<<<b, 1024, 0, s>>>(cap, info, cells);
+    count_launches(1), grid_bin_kernel<true><<<gp, kGridThreads, 0, s>>>(b, m, cap, known, info, cells, sorted);
     const long long nq = static_cast<long long>(b) * n;
     const unsigned gq = static_cast<unsigned>((nq + kGridQueryThreads - 1) / kGridQueryThreads);
     prefer_max_shared(grid_three_nn_kernel);
-    grid_three_nn_kernel<<<gq, kGridQueryThreads, 0, s>>>(b, n, m, cap, unknown, info, cells, sorted, dist2, idx, need);
+    count_launches(1), grid_three_nn_kernel<<<gq, kGridQueryThreads, 0, s>>>(b, n, m, cap, unknown, info, cells, sorted, dist2, idx, need);
     *need_scan_out = need;
     return check_launch("three_nn grid");
 }

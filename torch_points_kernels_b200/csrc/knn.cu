@@ -328,22 +328,22 @@ static int launch_three_nn_scan(int b, int n, int m, const float* unknown, const
     if (threads == 128 && q == 2)
     {
         prefer_max_shared(three_nn_kernel<128, 2>);
-        three_nn_kernel<128, 2><<<g, 128, 0, s>>>(n, m, tiles, unknown, known, dist2, idx, need);
+        count_launches(1), three_nn_kernel<128, 2><<<g, 128, 0, s>>>(n, m, tiles, unknown, known, dist2, idx, need);
     }
     else if (threads == 128)
     {
         prefer_max_shared(three_nn_kernel<128, 1>);
-        three_nn_kernel<128, 1><<<g, 128, 0, s>>>(n, m, tiles, unknown, known, dist2, idx, need);
+        count_launches(1), three_nn_kernel<128, 1><<<g, 128, 0, s>>>(n, m, tiles, unknown, known, dist2, idx, need);
     }
     else if (q == 2)
     {
         prefer_max_shared(three_nn_kernel<64, 2>);
-        three_nn_kernel<64, 2><<<g, 64, 0, s>>>(n, m, tiles, unknown, known, dist2, idx, need);
+        count_launches(1), three_nn_kernel<64, 2><<<g, 64, 0, s>>>(n, m, tiles, unknown, known, dist2, idx, need);
     }
     else
     {
         prefer_max_shared(three_nn_kernel<64, 1>);
-        three_nn_kernel<64, 1><<<g, 64, 0, s>>>(n, m, tiles, unknown, known, dist2, idx, need);
+        count_launches(1), three_nn_kernel<64, 1><<<g, 64, 0, s>>>(n, m, tiles, unknown, known, dist2, idx, need);
     }
     return check_launch("three_nn");
 }
@@ -413,22 +413,22 @@ extern "C" int tpk_three_nn_ws(int b, int n, int m, const float* unknown, const 
         if (threads == 128 && q == 2)                                                              \
         {                                                                                          \
             if ((rc_ = set_smem(KERNEL<128, 2>, smem, "knn")) != TPK_OK) return rc_;               \
-            KERNEL<128, 2><<<g, 128, smem, s>>>(__VA_ARGS__);                                      \
+            count_launches(1), KERNEL<128, 2><<<g, 128, smem, s>>>(__VA_ARGS__);                                      \
         }                                                                                          \
         else if (threads == 128)                                                                   \
         {                                                                                          \
             if ((rc_ = set_smem(KERNEL<128, 1>, smem, "knn")) != TPK_OK) return rc_;               \
-            KERNEL<128, 1><<<g, 128, smem, s>>>(__VA_ARGS__);                                      \
+            count_launches(1), KERNEL<128, 1><<<g, 128, smem, s>>>(__VA_ARGS__);                                      \
         }                                                                                          \
         else if (q == 2)                                                                           \
         {                                                                                          \
             if ((rc_ = set_smem(KERNEL<64, 2>, smem, "knn")) != TPK_OK) return rc_;                \
-            KERNEL<64, 2><<<g, 64, smem, s>>>(__VA_ARGS__);                                        \
+            count_launches(1), KERNEL<64, 2><<<g, 64, smem, s>>>(__VA_ARGS__);                                        \
         }                                                                                          \
         else                                                                                       \
         {                                                                                          \
             if ((rc_ = set_smem(KERNEL<64, 1>, smem, "knn")) != TPK_OK) return rc_;                \
-            KERNEL<64, 1><<<g, 64, smem, s>>>(__VA_ARGS__);                                        \
+            count_launches(1), KERNEL<64, 1><<<g, 64, smem, s>>>(__VA_ARGS__);                                        \
         }                                                                                          \
     } while (0)
 

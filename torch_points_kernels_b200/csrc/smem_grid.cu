@@ -681,7 +681,7 @@ int sg_three_nn(int b, int n, int m, const float* unknown, const float* known, f
     }
     const long long grid = static_cast<long long>(b) * parts;
     TPK_REQUIRE(grid < (1ll << 31), "three_nn: too many queries");
-    kernel<<<static_cast<unsigned>(grid), kSgThreads, smem, s>>>(n, m, parts, static_cast<int>(qcap), max_dim, cap, unknown,
+    count_launches(1), kernel<<<static_cast<unsigned>(grid), kSgThreads, smem, s>>>(n, m, parts, static_cast<int>(qcap), max_dim, cap, unknown,
                                                                  known, dist2, idx, need);
     return check_launch("three_nn grid");
 }
@@ -776,7 +776,7 @@ int sg_ball_query(int b, int n, int m, float radius, int nsample, const float* n
     const float max_cand = 2.0f * sqrtf(6.45f * static_cast<float>(n) * static_cast<float>(nsample));
     const long long grid = static_cast<long long>(b) * p.parts;
     TPK_REQUIRE(grid < (1ll << 31), "ball_query_dense: too many clouds");
-    kernel<<<static_cast<unsigned>(grid), kSgThreads, p.smem, s>>>(n, m, p.parts, p.lpp, radius, nsample, max_cand,
+    count_launches(1), kernel<<<static_cast<unsigned>(grid), kSgThreads, p.smem, s>>>(n, m, p.parts, p.lpp, radius, nsample, max_cand,
                                                                    p.max_dim, p.cells_cap, p.slab_cells_cap, p.pcap,
                                                                    new_xyz, xyz, idx, dist, need);
     return check_launch("ball_query grid");

@@ -13,6 +13,10 @@ namespace tpk
 // Records the text returned by tpk_last_error() for the calling thread.
 void set_error(const char* fmt, ...);
 
+// Adds to the process-wide count of kernels this library has launched (or recorded into a
+// stream capture); every launch site calls it.
+void count_launches(int k);
+
 constexpr unsigned kFullMask = 0xffffffffu;
 constexpr int kNumSmsB200 = 148;
 
