@@ -107,10 +107,14 @@ def test_fps_sorted_copy_is_the_default_for_big_on_chip_clouds():
 
 
 @pytest.mark.parametrize("kind", ["clustered", "lattice", "planar", "nonfinite", "many_skipped"])
-def test_fps_sorted_copy_hard_clouds(kind, monkeypatch):
-    """Warp skipping must never change a result: crowded cells, exact ties everywhere, a
-    collapsed axis, coordinates that are not finite, and points the skip rule excludes."""
+@pytest.mark.parametrize("large_cloud_kernel", [False, True])
+def test_fps_sorted_copy_hard_clouds(kind, large_cloud_kernel, monkeypatch):
+    """Warp and chunk skipping must never change a result: crowded cells, exact ties everywhere,
+    a collapsed axis, coordinates that are not finite, and points the skip rule excludes.
+    Both kernels that skip: the register-resident one and the one for large clouds."""
     monkeypatch.setenv("TPK_FPS_SORTED", "1")
+    if large_cloud_kernel:
+        monkeypatch.setenv("TPK_FPS_FORCE_GLOBAL", "1")
     rng = np.random.default_rng(len(kind))
     B, n, m = 2, 6000, 400
     if kind == "clustered":
@@ -121,23 +125,26 @@ def test_fps_sorted_copy_hard_clouds(kind, monkeypatch):
         x = rng.uniform(-1, 1, (B, n, 3)).astype(np.float32)
         x[..., 1] = 0.5
     elif kind == "nonfinite":
-        x = np.array(data.unit_ball(B, n, seed=5))
+        x = data.unit_ball(B, n, seed=5).numpy().copy()
         x[0, 17, 0] = np.inf
         x[0, 400, 2] = np.nan
         x[1, 3000] = (-np.inf, 0.0, np.nan)
         m = 60
     else:
-        x = np.array(data.unit_ball(B, n, seed=6))
+        x = data.unit_ball(B, n, seed=6).numpy().copy()
         x[:, 1::2] *= 0.01  # |p|^2 <= 1e-3: never candidates
     got = npy(tpk.furthest_point_sample(cu(x), m))
     np.testing.assert_array_equal(got, orc.fps(x, m))
     assert _lib.device_status() == 0
 
 
-@pytest.mark.parametrize("B,N,m", [(2, 200000, 48), (3, 140000, 33)])
-def test_fps_large_clouds_use_scratch(B, N, m):
-    """Clouds beyond the on-chip capacity: running minimum in global scratch."""
-    assert _lib.lib().tpk_fps_scratch_bytes(B, N, m) == B * N * 4
+@pytest.mark.parametrize("B,N,m", [(2, 200000, 48), (3, 140000, 33), (1, 1200000, 20)])
+@pytest.mark.parametrize("sorted_copy", ["1", "0"])
+def test_fps_large_clouds_use_scratch(B, N, m, sorted_copy, monkeypatch):
+    """Clouds beyond the on-chip capacity: running minimum in global scratch, with the sorted
+    copy and chunk skipping (20 bytes per point) or without (4 bytes per point)."""
+    monkeypatch.setenv("TPK_FPS_SORTED", sorted_copy)
+    assert _lib.lib().tpk_fps_scratch_bytes(B, N, m) == B * N * (20 if sorted_copy == "1" else 4)
     x = data.gaussian_mixture(B, N, seed=5000 + N)
     got = npy(tpk.furthest_point_sample(cu(x), m))
     np.testing.assert_array_equal(got, orc.fps(x, m))
@@ -145,8 +152,10 @@ def test_fps_large_clouds_use_scratch(B, N, m):
 
 
 @pytest.mark.parametrize("n", [3, 37, 700, 5000, 20000])
-def test_fps_scratch_kernel_tie_break_and_skip_rule(n, monkeypatch):
+@pytest.mark.parametrize("sorted_copy", ["1", "0"])
+def test_fps_scratch_kernel_tie_break_and_skip_rule(n, sorted_copy, monkeypatch):
     monkeypatch.setenv("TPK_FPS_FORCE_GLOBAL", "1")
+    monkeypatch.setenv("TPK_FPS_SORTED", sorted_copy)
     rng = np.random.default_rng(n)
     pts = np.zeros((2, n, 3), np.float32)
     pts[:, 0] = (1.0, 1.0, 1.0)
@@ -237,7 +246,7 @@ def test_ball_query_dense_shared_memory_grid_edge_cases(case):
     fit, centres without a cell, clouds without a grid; cells exactly one radius wide; more
     centres than one list pass takes."""
     B, N, M, r, ns = 2, 6000, 500, 0.08, 16
-    x = np.array(data.unit_ball(B, N, seed=31))
+    x = data.unit_ball(B, N, seed=31).numpy().copy()
     if case == "crowded_layer":
         x[0, :5000, 2] = 0.123  # one z layer holds most of cloud 0
     if case == "thin_cells":
@@ -374,8 +383,8 @@ def test_three_nn_grid_path_matches_oracle(name, monkeypatch):
 def test_three_nn_grid_path_nonfinite_falls_back_to_scan(env, monkeypatch):
     if env:
         monkeypatch.setenv(env, "1")
-    unknown = np.array(data.unit_ball(2, 1500, seed=21))
-    known = np.array(data.unit_ball(2, 4096, seed=22))
+    unknown = data.unit_ball(2, 1500, seed=21).numpy().copy()
+    known = data.unit_ball(2, 4096, seed=22).numpy().copy()
     unknown[0, 7, 1] = np.inf
     unknown[1, 9, 0] = np.nan
     known[1, 100, 2] = np.inf  # cloud 1: no grid at all

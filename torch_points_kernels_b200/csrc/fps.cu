@@ -912,6 +912,317 @@ __global__ void __launch_bounds__(kFpsBigThreads, 1)
     cluster_sync_all();
 }
 
+// ---------------------------------------------------------------- large clouds, sorted
+//
+// The same clouds on a spatially sorted copy.  The copy is cut into chunks of 128
+// consecutive points (a compact region each); lane c of a warp keeps, in registers, the
+// bounding box of the warp's chunk c, the chunk's largest running minimum and the point
+// that holds it.  A round tests every chunk's box against the new sample: a chunk farther
+// away than its largest minimum cannot change and is skipped.  The few chunks in reach are
+// updated by their whole warp (four points per lane: coordinates from the sorted copy,
+// minima from scratch, written back only where they changed).  Late rounds touch a few
+// kilobytes per cloud instead of the whole cloud.
+constexpr int kFpsChunk = 128;  // points per chunk: 32 lanes x 4
+
+template <int CPL>  // chunks per lane: a warp owns 32 * CPL chunks
+__global__ void __launch_bounds__(kFpsBigThreads, 1)
+    fps_pruned_kernel(int n, int m, int log2bs, const float* __restrict__ xyz_all,
+                      const float4* __restrict__ sorted_all, float* __restrict__ temp_all,
+                      int32_t* __restrict__ idxs_all)
+{
+    __shared__ __align__(16) uint4 wmsg_a[64];
+    __shared__ __align__(16) uint4 cmsg_a[64];
+    __shared__ float wmsg_z[64];
+    __shared__ float cmsg_z[64];
+    __shared__ __align__(8) uint64_t mbar[2];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nwarps = kFpsBigThreads / 32;
+    const int nranks = static_cast<int>(cluster_nctarank());
+    const int rank = static_cast<int>(cluster_ctarank());
+    const int cloud = blockIdx.x / nranks;
+    const int gtid = rank * kFpsBigThreads + tid;
+
+    const float* xyz = xyz_all + static_cast<size_t>(cloud) * n * 3;
+    const float4* sorted = sorted_all + static_cast<size_t>(cloud) * n;
+    float* temp = temp_all + static_cast<size_t>(cloud) * n;
+    int32_t* idxs = idxs_all + static_cast<size_t>(cloud) * m;
+
+    // Chunk (slot s, lane c) of warp w is chunk (s * 32 + c) * total_warps + w of the cloud:
+    // neighbouring chunks belong to different warps, so the handful of chunks a sample
+    // reaches are updated side by side instead of one after the other.
+    const long long gwarp = static_cast<long long>(rank) * nwarps + warp;
+    const long long total_warps = static_cast<long long>(nranks) * nwarps;
+    float bmin[CPL][3], bmax[CPL][3], cmax[CPL], bx[CPL], by[CPL], bz[CPL];
+    int bk[CPL];
+#pragma unroll
+    for (int s = 0; s < CPL; ++s)
+    {
+        float kmin[3] = {CUDART_INF_F, CUDART_INF_F, CUDART_INF_F};
+        float kmax[3] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+        cmax[s] = -1.0f;
+        bk[s] = 0;
+        bx[s] = by[s] = bz[s] = 0.f;
+        for (int c = 0; c < 32; ++c)
+        {
+            const long long base = (static_cast<long long>(s * 32 + c) * total_warps + gwarp) * kFpsChunk;
+            if (base >= n) break;  // warp-uniform
+            float lo[3] = {CUDART_INF_F, CUDART_INF_F, CUDART_INF_F};
+            float hi[3] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+            bool any_valid = false;
+#pragma unroll
+            for (int u = 0; u < kFpsChunk / 32; ++u)
+            {
+                const long long p = base + u * 32 + lane;
+                if (p < n)
+                {
+                    const float4 v = __ldg(sorted + p);
+                    const float mag = sumsq_abc(v.x, v.y, v.z);
+                    const bool valid = !(static_cast<double>(mag) <= 1e-3);
+                    temp[p] = valid ? 1e10f : -1.0f;
+                    any_valid |= valid;
+                    // fminf/fmaxf drop NaN: such a point never changes its minimum anyway
+                    lo[0] = fminf(lo[0], v.x);
+                    lo[1] = fminf(lo[1], v.y);
+                    lo[2] = fminf(lo[2], v.z);
+                    hi[0] = fmaxf(hi[0], v.x);
+                    hi[1] = fmaxf(hi[1], v.y);
+                    hi[2] = fmaxf(hi[2], v.z);
+                }
+            }
+#pragma unroll
+            for (int a = 0; a < 3; ++a)
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1)
+                {
+                    lo[a] = fminf(lo[a], __shfl_xor_sync(kFullMask, lo[a], o));
+                    hi[a] = fmaxf(hi[a], __shfl_xor_sync(kFullMask, hi[a], o));
+                }
+            const bool chunk_valid = __any_sync(kFullMask, any_valid) != 0;
+            if (lane == c)
+            {
+#pragma unroll
+                for (int a = 0; a < 3; ++a)
+                {
+                    kmin[a] = lo[a];
+                    kmax[a] = hi[a];
+                }
+                cmax[s] = chunk_valid ? 1e10f : -1.0f;  // every chunk with a candidate is updated in round 1
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < 3; ++a)
+        {
+            bmin[s][a] = kmin[a];
+            bmax[s][a] = kmax[a];
+        }
+    }
+
+    float cx = __ldg(xyz + 0), cy = __ldg(xyz + 1), cz = __ldg(xyz + 2);
+    if (gtid == 0 && m > 0) idxs[0] = 0;
+    if (tid == 0)
+    {
+        mbar_init(smem_u32(mbar + 0), 1);
+        mbar_init(smem_u32(mbar + 1), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    cluster_sync_all();
+
+    uint32_t rem_a[2] = {0, 0}, rem_z[2] = {0, 0}, rem_bar[2] = {0, 0};
+    if (warp == 0 && lane < nranks)
+    {
+#pragma unroll
+        for (int par = 0; par < 2; ++par)
+        {
+            rem_a[par] = mapa_cluster(smem_u32(cmsg_a + par * 32 + rank), lane);
+            rem_z[par] = mapa_cluster(smem_u32(cmsg_z + par * 32 + rank), lane);
+            rem_bar[par] = mapa_cluster(smem_u32(mbar + par), lane);
+        }
+    }
+    bool failed = false;
+    Msg wm = {INT_MIN, 0, 0.f, 0.f, 0.f};  // the warp's winner, recomputed when a chunk of it changed
+
+    for (int j = 1; j < m; ++j)
+    {
+        const int par = j & 1;
+        if (tid == 0)
+            mbar_arrive_expect_tx(smem_u32(mbar + par), static_cast<uint32_t>(nranks * kMsgBytes));
+
+        // ---- chunks in reach of the new sample
+        bool touched = false;
+#pragma unroll
+        for (int s = 0; s < CPL; ++s)
+        {
+            const float ex = fmaxf(fmaxf(bmin[s][0] - cx, cx - bmax[s][0]), 0.f);
+            const float ey = fmaxf(fmaxf(bmin[s][1] - cy, cy - bmax[s][1]), 0.f);
+            const float ez = fmaxf(fmaxf(bmin[s][2] - cz, cz - bmax[s][2]), 0.f);
+            const float lb = __fmaf_rn(ez, ez, __fmaf_rn(ex, ex, __fmul_rn(ey, ey)));
+            // a computed distance is at least this bound less a few ulp; no skipping on tiny
+            // bounds, where it may have lost precision.  A chunk without candidates
+            // (largest minimum -1) is skipped whenever the bound is positive or its box is empty.
+            const bool in_reach = !(__fmul_rn(lb, 0.9999f) > fmaxf(cmax[s], 1.0e-30f));
+            uint32_t todo = __ballot_sync(kFullMask, in_reach);
+            touched |= todo != 0u;
+            while (todo != 0u)  // warp-uniform
+            {
+                const int c = __ffs(todo) - 1;
+                todo &= todo - 1u;
+                const long long base = (static_cast<long long>(s * 32 + c) * total_warps + gwarp) * kFpsChunk;
+                float4 v[kFpsChunk / 32];
+                float t[kFpsChunk / 32];
+#pragma unroll
+                for (int u = 0; u < kFpsChunk / 32; ++u)
+                {
+                    const long long p = base + u * 32 + lane;
+                    const bool ok = p < n;
+                    v[u] = ok ? __ldg(sorted + p) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    t[u] = ok ? temp[p] : -1.0f;
+                }
+                float best = -1.0f, mx = 0.f, my = 0.f, mz = 0.f;
+                int mk = 0;
+                uint32_t mrank = 0xFFFFFFFFu;
+#pragma unroll
+                for (int u = 0; u < kFpsChunk / 32; ++u)
+                {
+                    const float d = fminf(sumsq_abc(v[u].x - cx, v[u].y - cy, v[u].z - cz), t[u]);
+                    if (d < t[u]) temp[base + u * 32 + lane] = d;
+                    // among equal minima the original index decides (tie rank)
+                    const int k = __float_as_int(v[u].w);
+                    bool better = d > best;
+                    if (d == best && d >= 0.f)
+                    {
+                        if (mrank == 0xFFFFFFFFu) mrank = fps_rank(mk, log2bs);
+                        better = fps_rank(k, log2bs) < mrank;
+                    }
+                    if (better)
+                    {
+                        best = d;
+                        mk = k;
+                        mx = v[u].x;
+                        my = v[u].y;
+                        mz = v[u].z;
+                        mrank = 0xFFFFFFFFu;
+                    }
+                }
+                const int key = __float_as_int(best);
+                const int src = warp_argmax(key, mk, log2bs);
+                const int wkey = __shfl_sync(kFullMask, key, src);
+                const int wk = __shfl_sync(kFullMask, mk, src);
+                const float wx = __shfl_sync(kFullMask, mx, src);
+                const float wy = __shfl_sync(kFullMask, my, src);
+                const float wz = __shfl_sync(kFullMask, mz, src);
+                if (lane == c)
+                {
+                    cmax[s] = __int_as_float(wkey);
+                    bk[s] = wk;
+                    bx[s] = wx;
+                    by[s] = wy;
+                    bz[s] = wz;
+                }
+            }
+        }
+
+        // ---- stage 1: the warp's winner over its chunks (unchanged if no chunk was touched)
+        if (touched)  // warp-uniform
+        {
+            float best = cmax[0], x1 = bx[0], y1 = by[0], z1 = bz[0];
+            int k1 = bk[0];
+#pragma unroll
+            for (int s = 1; s < CPL; ++s)
+            {
+                bool better = cmax[s] > best;
+                if (cmax[s] == best && best >= 0.f) better = fps_rank(bk[s], log2bs) < fps_rank(k1, log2bs);
+                if (better)
+                {
+                    best = cmax[s];
+                    k1 = bk[s];
+                    x1 = bx[s];
+                    y1 = by[s];
+                    z1 = bz[s];
+                }
+            }
+            const int key = __float_as_int(best);
+            const int src = warp_argmax(key, k1, log2bs);
+            wm.key = __shfl_sync(kFullMask, key, src);
+            wm.k = __shfl_sync(kFullMask, k1, src);
+            wm.x = __shfl_sync(kFullMask, x1, src);
+            wm.y = __shfl_sync(kFullMask, y1, src);
+            wm.z = __shfl_sync(kFullMask, z1, src);
+        }
+        if (lane == 0)
+        {
+            wmsg_a[par * 32 + warp] = make_uint4(static_cast<uint32_t>(wm.key), static_cast<uint32_t>(wm.k),
+                                                 __float_as_uint(wm.x), __float_as_uint(wm.y));
+            wmsg_z[par * 32 + warp] = wm.z;
+        }
+        __syncthreads();
+
+        // ---- stage 2: CTA
+        Msg msg;
+        {
+            int key2 = INT_MIN, k2 = 0;
+            float x2 = 0.f, y2 = 0.f, z2 = 0.f;
+            if (lane < nwarps)
+            {
+                const uint4 a = wmsg_a[par * 32 + lane];
+                key2 = static_cast<int>(a.x);
+                k2 = static_cast<int>(a.y);
+                x2 = __uint_as_float(a.z);
+                y2 = __uint_as_float(a.w);
+                z2 = wmsg_z[par * 32 + lane];
+            }
+            const int src = warp_argmax(key2, k2, log2bs);
+            msg.key = __shfl_sync(kFullMask, key2, src);
+            msg.k = __shfl_sync(kFullMask, k2, src);
+            msg.x = __shfl_sync(kFullMask, x2, src);
+            msg.y = __shfl_sync(kFullMask, y2, src);
+            msg.z = __shfl_sync(kFullMask, z2, src);
+        }
+
+        // ---- stage 3: cluster
+        if (nranks > 1)
+        {
+            if (warp == 0 && lane < nranks)
+                st_async_msg(rem_a[par], rem_z[par], rem_bar[par], static_cast<uint32_t>(msg.key),
+                             static_cast<uint32_t>(msg.k), msg.x, msg.y, msg.z);
+            // a warp whose wait ran out records it and stops waiting but keeps taking part
+            // in every barrier and exchange (see the on-chip kernel)
+            const uint32_t parity = static_cast<uint32_t>((j - 1) >> 1) & 1u;
+            if (!failed && !mbar_wait_bounded(smem_u32(mbar + par), parity))
+            {
+                if (lane == 0) atomicExch(&g_dev_status, 1);
+                failed = true;
+            }
+            int key3 = INT_MIN, k3 = 0;
+            if (lane < nranks)
+            {
+                const uint2 a = *reinterpret_cast<const uint2*>(cmsg_a + par * 32 + lane);
+                key3 = static_cast<int>(a.x);
+                k3 = static_cast<int>(a.y);
+            }
+            const int src = warp_argmax(key3, k3, log2bs);
+            const uint4 win = cmsg_a[par * 32 + src];
+            msg.key = static_cast<int>(win.x);
+            msg.k = static_cast<int>(win.y);
+            msg.x = __uint_as_float(win.z);
+            msg.y = __uint_as_float(win.w);
+            msg.z = cmsg_z[par * 32 + src];
+        }
+        else if (tid == 0)
+        {
+            // one-CTA cluster: nobody completes the transaction count, do it locally
+            asm volatile("mbarrier.complete_tx.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(mbar + par)),
+                         "r"(static_cast<uint32_t>(nranks * kMsgBytes))
+                         : "memory");
+        }
+        cx = msg.x;
+        cy = msg.y;
+        cz = msg.z;
+        if (gtid == 0) idxs[j] = msg.key >= 0 ? msg.k : 0;
+    }
+    cluster_sync_all();
+}
+
 int fps_launch_global(int b, int n, int m, int log2bs, const float* xyz, float* temp,
                       int32_t* idxs, cudaStream_t stream)
 {
@@ -943,6 +1254,57 @@ int fps_launch_global(int b, int n, int m, int log2bs, const float* xyz, float* 
         return TPK_ERR_CUDA;
     }
     return TPK_OK;
+}
+
+// Largest cloud the sorted large-cloud kernel takes: 256 warps x 32 lanes x 4 chunks x 128 points.
+constexpr long long kFpsPrunedMaxPoints = 256ll * 32 * 4 * kFpsChunk;
+
+template <int CPL>
+int fps_launch_pruned_t(int b, int n, int m, int log2bs, const float* xyz, const float4* sorted, float* temp,
+                        int32_t* idxs, cudaStream_t stream)
+{
+    auto kernel = fps_pruned_kernel<CPL>;
+    prefer_max_shared(kernel);
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (err != cudaSuccess)
+    {
+        set_error("fps: cluster size attribute: %s", cudaGetErrorString(err));
+        return TPK_ERR_CUDA;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(b) * kFpsBigRanks, 1, 1);
+    cfg.blockDim = dim3(kFpsBigThreads, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kFpsBigRanks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    count_launches(1);
+    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, xyz, sorted, temp, idxs);
+    if (err != cudaSuccess)
+    {
+        set_error("fps launch (large clouds, sorted): %s", cudaGetErrorString(err));
+        return TPK_ERR_CUDA;
+    }
+    return TPK_OK;
+}
+
+// scratch: the sorted copy (16 bytes per point), then the running minima (4 bytes per point)
+int fps_launch_pruned(int b, int n, int m, int log2bs, const float* xyz, void* scratch, int32_t* idxs,
+                      cudaStream_t stream)
+{
+    float4* sorted = static_cast<float4*>(scratch);
+    float* temp = reinterpret_cast<float*>(sorted + static_cast<size_t>(b) * n);
+    const int rc = fps_launch_sort(b, n, xyz, sorted, stream);
+    if (rc != TPK_OK) return rc;
+    const long long per_lane = (static_cast<long long>(n) + 256ll * 32 * kFpsChunk - 1) / (256ll * 32 * kFpsChunk);
+    if (per_lane <= 1) return fps_launch_pruned_t<1>(b, n, m, log2bs, xyz, sorted, temp, idxs, stream);
+    if (per_lane <= 2) return fps_launch_pruned_t<2>(b, n, m, log2bs, xyz, sorted, temp, idxs, stream);
+    return fps_launch_pruned_t<4>(b, n, m, log2bs, xyz, sorted, temp, idxs, stream);
 }
 
 struct FpsConfig
@@ -1095,6 +1457,13 @@ bool fps_wants_sorted(int n, int m)
 }  // namespace
 }  // namespace tpk
 
+// TPK_FPS_SORTED=0 keeps large clouds on the unsorted kernel too (comparison runs, tests)
+static bool fps_large_sorted(int n)
+{
+    const char* env = getenv("TPK_FPS_SORTED");
+    return static_cast<long long>(n) <= tpk::kFpsPrunedMaxPoints && !(env && env[0] == '0');
+}
+
 extern "C" int64_t tpk_fps_scratch_bytes(int b, int n, int m)
 {
     tpk::FpsConfig c;
@@ -1102,8 +1471,8 @@ extern "C" int64_t tpk_fps_scratch_bytes(int b, int n, int m)
     if (getenv("TPK_FPS_FORCE_GLOBAL") == nullptr && tpk::fps_pick_config(n, m, &c))
         // optional: the spatially sorted copy, (x, y, z, index) per point
         return tpk::fps_wants_sorted(n, m) ? static_cast<int64_t>(b) * n * 16 : 0;
-    // large clouds: the running minimum, one float per point
-    return static_cast<int64_t>(b) * n * static_cast<int64_t>(sizeof(float));
+    // large clouds: the running minimum, one float per point, behind the sorted copy if one is used
+    return static_cast<int64_t>(b) * n * (fps_large_sorted(n) ? 20 : 4);
 }
 
 extern "C" int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz, void* scratch,
@@ -1126,6 +1495,11 @@ extern "C" int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz
         {
             set_error("fps: clouds of %d points need tpk_fps_scratch_bytes() bytes of scratch", n);
             return TPK_ERR_SCRATCH;
+        }
+        if (fps_large_sorted(n))
+        {
+            TPK_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 15u) == 0, "fps: scratch must be 16-byte aligned");
+            return fps_launch_pruned(b, n, m, log2bs, xyz, scratch, idxs, s);
         }
         return fps_launch_global(b, n, m, log2bs, xyz, static_cast<float*>(scratch), idxs, s);
     }
