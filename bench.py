@@ -223,8 +223,11 @@ def pipeline_work(B, N):
         w["grouping_bwd_l%d" % (l + 1)] = ("hbm", 4 * B * c * m * ns + 8 * B * m * ns + 4 * B * c * n)
         w["interp_fwd_l%d" % (l + 1)] = ("hbm", 4 * B * c * n + 4 * B * c * m + B * n * 3 * 8)
         w["interp_bwd_l%d" % (l + 1)] = ("hbm", 4 * B * c * n + 4 * B * c * m + B * n * 3 * 8)
-        w["three_nn_l%d" % (l + 1)] = ("fp32", 6 * B * n * m)
-        w["ball_query_l%d" % (l + 1)] = ("fp32", None)  # pairs depend on the data: filled from the oracle
+        # grid searches (three_nn with 256..8192 known points, ball query on 1024+ points) look at a
+        # few dozen candidates per query: no brute-force pair count describes them, so no fraction
+        w["three_nn_l%d" % (l + 1)] = ("fp32", 6 * B * n * m) if m < 256 else ("grid", None)
+        w["ball_query_l%d" % (l + 1)] = ("fp32", None) if n < 1024 else ("grid", None)
+        # brute-force-equivalent work: the sorted kernels skip most of it in late rounds
         w["fps_l%d" % (l + 1)] = ("fp32", 6 * B * (m - 1) * n)
     return w
 
@@ -517,9 +520,10 @@ def run_b200(args, rank, world, local_rank):
                                "npoint 4096/1024/256/64, radius 0.1/0.2/0.4/0.8, nsample 32, C 64/128/256/512",
                    "clouds_per_gpu": B, "points_per_cloud": N, "parallelism": "batch-sharded x%d" % world,
                    "l2": "each step moves > 1 GB (inputs larger than L2), no explicit flush",
-                   "steps_in_flight": "up to 3: the geometry kernels of a step (FPS, ball query, three_nn; they "
-                                      "depend on its coordinates only) overlap the feature kernels of the step "
-                                      "before; ms_per_step_isolated is the same step with a join after every step"},
+                   "steps_in_flight": "up to %d (one CUDA graph each): the geometry kernels of a step (FPS, ball "
+                                      "query, three_nn; they depend on its coordinates only) overlap the feature "
+                                      "kernels of the steps before; ms_per_step_isolated is the same step with a "
+                                      "join after every step" % (args.in_flight if graphs is not None else 3)},
         "e2e": {"value": round(clouds * args.steps / (ms_e2e * 1e-3), 2), "unit": "clouds/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(ms_e2e / args.steps, 4)},
         "gpu_launches": launches,
