@@ -47,6 +47,33 @@ def test_invalid_arguments_return_status_without_gpu():
     assert l.tpk_grouping(0, 4, 4, 4, 4, None, None, None, None) == 0
 
 
+def test_scratch_sizes_are_host_arithmetic(monkeypatch):
+    """What the callers must allocate: pure host functions, usable without a GPU."""
+    for env in ("TPK_FPS_SORTED", "TPK_FPS_FORCE_GLOBAL", "TPK_BALL_QUERY_GLOBAL_GRID", "TPK_THREE_NN_GLOBAL_GRID"):
+        monkeypatch.delenv(env, raising=False)
+    l = _lib.lib()
+    # FPS: nothing for small clouds or few samples, the sorted copy (16 B/point) for clouds that stay
+    # on chip, the sorted copy plus the running minima (20 B/point) above 131072 points
+    assert l.tpk_fps_scratch_bytes(4, 1024, 256) == 0
+    assert l.tpk_fps_scratch_bytes(4, 16384, 64) == 0
+    assert l.tpk_fps_scratch_bytes(16, 16384, 4096) == 16 * 16384 * 16
+    assert l.tpk_fps_scratch_bytes(2, 200000, 48) == 2 * 200000 * 20
+    monkeypatch.setenv("TPK_FPS_SORTED", "0")
+    assert l.tpk_fps_scratch_bytes(16, 16384, 4096) == 0
+    assert l.tpk_fps_scratch_bytes(2, 200000, 48) == 2 * 200000 * 4
+    monkeypatch.delenv("TPK_FPS_SORTED")
+    # ball query: one flag per centre with the grid in shared memory, the whole grid for huge clouds
+    assert l.tpk_ball_query_dense_scratch_bytes(2, 256, 64, 32) == 0
+    assert l.tpk_ball_query_dense_scratch_bytes(16, 16384, 4096, 32) == 16 * 4096
+    assert l.tpk_ball_query_dense_scratch_bytes(2, 300000, 100, 32) > 2 * 300000 * 16
+    # three_nn: one flag per unknown point up to 8192 known points
+    assert l.tpk_three_nn_scratch_bytes(2, 256, 64) == 0
+    assert l.tpk_three_nn_scratch_bytes(16, 16384, 4096) == 16 * 16384
+    assert l.tpk_three_nn_scratch_bytes(2, 3000, 10000) > 2 * 10000 * 16
+    assert l.tpk_three_nn_scratch_bytes(0, 10, 10) == 0
+    assert _lib.kernel_launches() >= 0
+
+
 def test_python_surface_matches_reference_names():
     for name in ("ball_query", "furthest_point_sample", "grouping_operation", "three_interpolate",
                  "three_nn", "knn"):

@@ -18,10 +18,6 @@
 // three_interpolate : cuda/src/interpolate_gpu.cu:78-107, :122-152
 #include "tpk_common.cuh"
 
-#ifndef TPK_GBWD_UNROLL
-#define TPK_GBWD_UNROLL 4
-#endif
-
 namespace tpk
 {
 namespace
@@ -510,7 +506,7 @@ __global__ void __launch_bounds__(kScatterThreads)
                              const float* __restrict__ grad_out, const int64_t* __restrict__ idx,
                              float* __restrict__ grad_small)
 {
-    constexpr int UNROLL = TPK_GBWD_UNROLL;
+    constexpr int UNROLL = 4;
     constexpr int NWARPS = kScatterThreads / 32;
     extern __shared__ __align__(16) float acc[];
     const int groups_per_batch = (c + ROWS - 1) / ROWS;
