@@ -182,8 +182,8 @@ def _lib_launches():
 
 
 class GraphedSteps:
-    """Three CUDA graphs of one whole step each (all three internal streams captured), replayed
-    in turn on three launch streams: no per-kernel host work, and consecutive steps still
+    """`nslots` CUDA graphs of one whole step each (all three internal streams captured), replayed
+    in turn, each on its own launch stream: no per-kernel host work, and consecutive steps still
     overlap because they are launched on different streams."""
 
     def __init__(self, pipe, dev, like, split, nslots=3):
