@@ -250,6 +250,19 @@ TPK_API int tpk_chamfer_dist_f64(int b, int n, const double* xyz1, int m, const 
                          double* dist1, double* dist2, int32_t* idx1, int32_t* idx2, void* stream);
 
 /*
+ * The float32 forward pass with caller scratch: each direction searches the uniform grid of
+ * the other cloud (nearest point by (distance, index), i.e. the lowest index among equal
+ * distances, as the reference's strict-'<' scan keeps it); results are identical to
+ * tpk_chamfer_dist_f32 bit for bit.  scratch: tpk_chamfer_dist_scratch_bytes(b,n,m) bytes,
+ * 256-byte aligned; when that returns 0 (both clouds below 4096 points) or scratch is NULL
+ * the call is tpk_chamfer_dist_f32.  No counterpart in the reference.
+ */
+TPK_API int tpk_chamfer_dist_f32_ws(int b, int n, const float* xyz1, int m, const float* xyz2, float* dist1,
+                                    float* dist2, int32_t* idx1, int32_t* idx2, void* scratch,
+                                    int64_t scratch_bytes, void* stream);
+TPK_API int64_t tpk_chamfer_dist_scratch_bytes(int b, int n, int m);
+
+/*
  * Gradient of both directions w.r.t. both clouds; grad_xyz1 (b,n,3) and grad_xyz2
  * (b,m,3) are fully written.
  * Replaces chamfer_dist_grad_kernel_wrapper, cuda/include/chamfer_dist.h:12-15

@@ -543,6 +543,82 @@ def test_chamfer_indices_bit_exact_with_duplicates():
     assert npy(i1).tolist() == [[0, 0, 0, 0]]
 
 
+@pytest.mark.parametrize("case", ["sphere_pair", "one_side_small", "duplicates", "lattice_ties", "nonfinite", "planar"])
+def test_chamfer_grid_path_matches_oracle_and_scan(case, monkeypatch):
+    """Clouds of 4096+ points search the other cloud's uniform grid: same distances (bits) and
+    same indices as the all-pairs scan and the oracle, also where many candidates tie."""
+    rng = np.random.default_rng(len(case))
+    B = 2
+    if case == "sphere_pair":
+        c1, c2 = data.chamfer_pair(B, 6000, seed=4100)
+        c1, c2 = c1.numpy().copy(), c2.numpy().copy()
+    elif case == "one_side_small":
+        c1, c2 = data.chamfer_pair(B, 5000, seed=4101)
+        c1, c2 = c1.numpy().copy(), c2[:, :700].numpy().copy()   # only one direction has a grid
+    elif case == "duplicates":
+        c2 = rng.uniform(-1, 1, (B, 4500, 3)).astype(np.float32)
+        c2[:, 2000:3000] = c2[:, :1000]                          # every nearest neighbour twice
+        c1 = (c2[:, ::2] + rng.normal(0, 1e-3, (B, 2250, 3))).astype(np.float32)
+        c1 = np.concatenate([c1, c2[:, :2000]], axis=1)          # and queries that sit on candidates
+    elif case == "lattice_ties":
+        c1 = (rng.integers(0, 20, (B, 4096, 3)) / 8).astype(np.float32)
+        c2 = (rng.integers(0, 10, (B, 5000, 3)) / 4).astype(np.float32)
+    elif case == "nonfinite":
+        c1, c2 = data.chamfer_pair(B, 4096, seed=4102)
+        c1, c2 = c1.numpy().copy(), c2.numpy().copy()
+        c1[0, 5, 1] = np.inf       # a query without a cell
+        c2[1, 77, 0] = np.inf      # a cloud without a grid
+    else:
+        c1 = rng.uniform(0, 1, (B, 4200, 3)).astype(np.float32)
+        c2 = rng.uniform(0, 1, (B, 4300, 3)).astype(np.float32)
+        c1[..., 2] = 0.5
+        c2[..., 2] = 0.5
+    n, m = c1.shape[1], c2.shape[1]
+    assert _lib.lib().tpk_chamfer_dist_scratch_bytes(B, n, m) > 0
+    results = []
+    for env in (None, "TPK_CHAMFER_SCAN"):
+        if env:
+            monkeypatch.setenv(env, "1")
+        x1, x2 = cu(c1).requires_grad_(True), cu(c2).requires_grad_(True)
+        d1, d2 = cd.ChamferFunction.apply(x1, x2)
+        torch.autograd.backward([d1, d2], [torch.ones_like(d1), torch.ones_like(d2)])
+        results.append((npy(d1), npy(d2), npy(x1.grad), npy(x2.grad)))
+    if case != "nonfinite":  # the oracle and the kernels agree on finite data; non-finite: grid == scan
+        o1, o2, _, _ = orc.chamfer(c1, c2)
+        same_bits(results[0][0], o1)
+        same_bits(results[0][1], o2)
+    with np.errstate(invalid="ignore"):
+        same_bits(results[0][0], results[1][0])
+        same_bits(results[0][1], results[1][1])
+        # gradients are summed with atomics (order varies): equal up to rounding
+        np.testing.assert_allclose(results[0][2], results[1][2], rtol=1e-4, atol=1e-4)
+        np.testing.assert_allclose(results[0][3], results[1][3], rtol=1e-4, atol=1e-4)
+    # the indices themselves, through the C ABI: grid + scratch against the plain scan
+    monkeypatch.delenv("TPK_CHAMFER_SCAN")
+    x1, x2 = cu(c1), cu(c2)
+    out = []
+    for use_ws in (True, False):
+        d1 = torch.empty(B, n, device=DEV); d2 = torch.empty(B, m, device=DEV)
+        i1 = torch.empty(B, n, dtype=torch.int32, device=DEV); i2 = torch.empty(B, m, dtype=torch.int32, device=DEV)
+        if use_ws:
+            need = _lib.lib().tpk_chamfer_dist_scratch_bytes(B, n, m)
+            scratch = torch.empty(need, dtype=torch.uint8, device=DEV)
+            _lib.call("tpk_chamfer_dist_f32_ws", B, n, _lib.ptr(x1), m, _lib.ptr(x2), _lib.ptr(d1), _lib.ptr(d2),
+                      _lib.ptr(i1), _lib.ptr(i2), _lib.ptr(scratch), need, _lib.stream_of(x1))
+        else:
+            _lib.call("tpk_chamfer_dist_f32", B, n, _lib.ptr(x1), m, _lib.ptr(x2), _lib.ptr(d1), _lib.ptr(d2),
+                      _lib.ptr(i1), _lib.ptr(i2), _lib.stream_of(x1))
+        out.append((npy(i1), npy(i2)))
+    np.testing.assert_array_equal(out[0][0], out[1][0])
+    np.testing.assert_array_equal(out[0][1], out[1][1])
+    if case != "nonfinite":
+        _, _, oi1, oi2 = orc.chamfer(c1, c2)
+        np.testing.assert_array_equal(out[0][0], oi1)
+        np.testing.assert_array_equal(out[0][1], oi2)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+
+
 def test_chamfer_float64_gradcheck():
     g = data.gen(11)
     x = torch.rand(4, 64, 3, generator=g).double().to(DEV).requires_grad_(True)

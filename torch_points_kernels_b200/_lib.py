@@ -27,6 +27,7 @@ _SIGNATURES = {
     "tpk_ball_query_dense_ws": [_c_int, _c_int, _c_int, _c_f32, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr],
     "tpk_ball_query_partial_dense": [_c_i64, _c_i64, _c_f32, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_three_nn": [_c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
+    "tpk_chamfer_dist_f32_ws": [_c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr],
     "tpk_three_nn_ws": [_c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr],
     "tpk_knn_dense": [_c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_knn_partial_dense": [_c_i64, _c_i64, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
@@ -42,7 +43,7 @@ _SIGNATURES = {
 
 EXPORTS = sorted(list(_SIGNATURES) + ["tpk_version", "tpk_last_error", "tpk_device_status", "tpk_kernel_launches", "tpk_fps_scratch_bytes",
                                        "tpk_fps_static_capacity", "tpk_ball_query_dense_scratch_bytes",
-                                       "tpk_three_nn_scratch_bytes"])
+                                       "tpk_three_nn_scratch_bytes", "tpk_chamfer_dist_scratch_bytes"])
 
 
 def lib():
@@ -70,6 +71,8 @@ def lib():
         handle.tpk_fps_scratch_bytes.restype = _c_i64
         handle.tpk_ball_query_dense_scratch_bytes.argtypes = [_c_int, _c_int, _c_int, _c_int]
         handle.tpk_ball_query_dense_scratch_bytes.restype = _c_i64
+        handle.tpk_chamfer_dist_scratch_bytes.argtypes = [_c_int, _c_int, _c_int]
+        handle.tpk_chamfer_dist_scratch_bytes.restype = _c_i64
         handle.tpk_three_nn_scratch_bytes.argtypes = [_c_int, _c_int, _c_int]
         handle.tpk_three_nn_scratch_bytes.restype = _c_i64
         handle.tpk_fps_static_capacity.argtypes = []

@@ -23,8 +23,16 @@ class ChamferFunction(torch.autograd.Function):
         idx2 = torch.empty((b, m), dtype=torch.int32, device=xyz1.device)
         name = "tpk_chamfer_dist_f32" if xyz1.dtype == torch.float32 else "tpk_chamfer_dist_f64"
         with torch.cuda.device(xyz1.device):
-            _lib.call(name, b, n, _lib.ptr(xyz1), m, _lib.ptr(xyz2), _lib.ptr(dist1), _lib.ptr(dist2),
-                      _lib.ptr(idx1), _lib.ptr(idx2), _lib.stream_of(xyz1))
+            need = _lib.lib().tpk_chamfer_dist_scratch_bytes(b, n, m) if xyz1.dtype == torch.float32 else 0
+            if need > 0:
+                # large clouds: nearest neighbours on a uniform grid (same results as the all-pairs scan)
+                scratch = torch.empty((need,), dtype=torch.uint8, device=xyz1.device)
+                _lib.call("tpk_chamfer_dist_f32_ws", b, n, _lib.ptr(xyz1), m, _lib.ptr(xyz2), _lib.ptr(dist1),
+                          _lib.ptr(dist2), _lib.ptr(idx1), _lib.ptr(idx2), _lib.ptr(scratch), need,
+                          _lib.stream_of(xyz1))
+            else:
+                _lib.call(name, b, n, _lib.ptr(xyz1), m, _lib.ptr(xyz2), _lib.ptr(dist1), _lib.ptr(dist2),
+                          _lib.ptr(idx1), _lib.ptr(idx2), _lib.stream_of(xyz1))
         ctx.save_for_backward(xyz1, xyz2, idx1, idx2)
         return dist1, dist2
 

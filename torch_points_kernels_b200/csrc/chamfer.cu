@@ -18,6 +18,11 @@
 
 namespace tpk
 {
+// grid_query.cu
+size_t grid_three_nn_scratch_bytes(int b, int n, int m);
+int grid_nn(int k, int b, int n, int m, const float* unknown, const float* known, float* dist2,
+            int32_t* idx, void* scratch, const unsigned char** need_scan_out, cudaStream_t s);
+
 namespace
 {
 
@@ -51,7 +56,7 @@ template <int THREADS, int Q>
 __global__ void __launch_bounds__(THREADS)
     chamfer_f32_kernel(int n, int m, int tiles_per_cloud, const float* __restrict__ xyz1,
                        const float* __restrict__ xyz2, float* __restrict__ dist,
-                       int32_t* __restrict__ indexes)
+                       int32_t* __restrict__ indexes, const unsigned char* __restrict__ need)
 {
     __shared__ __align__(16) float smem[2 * kScanTileFloats];
     const int cloud = blockIdx.x / tiles_per_cloud;
@@ -61,13 +66,23 @@ __global__ void __launch_bounds__(THREADS)
     for (int q = 0; q < Q; ++q)
     {
         const int j = qtile * (THREADS * Q) + q * THREADS + threadIdx.x;
-        op.act[q] = j < n;
+        // `need` (optional): one byte per point, 0 = already answered by the grid path
+        op.act[q] = j < n && (need == nullptr || need[static_cast<size_t>(cloud) * n + j] != 0);
         const size_t row = static_cast<size_t>(cloud) * n + (op.act[q] ? j : 0);
         op.qx[q] = op.act[q] ? __ldg(xyz1 + row * 3 + 0) : 0.f;
         op.qy[q] = op.act[q] ? __ldg(xyz1 + row * 3 + 1) : 0.f;
         op.qz[q] = op.act[q] ? __ldg(xyz1 + row * 3 + 2) : 0.f;
         op.best[q] = CUDART_INF_F;
         op.besti[q] = 0;
+    }
+    if (need != nullptr)
+    {
+        // nothing left over for this CTA (the usual case behind the grid kernel): leave
+        // before staging a single tile
+        bool any = false;
+#pragma unroll
+        for (int q = 0; q < Q; ++q) any |= op.act[q];
+        if (!__syncthreads_or(any ? 1 : 0)) return;
     }
     scan_candidates<THREADS, Q>(xyz2 + static_cast<size_t>(cloud) * m * 3, m, smem, op.qx, op.qy, op.qz, op);
 #pragma unroll
@@ -137,7 +152,7 @@ __global__ void __launch_bounds__(256)
 }
 
 int chamfer_dir_f32(int b, int n, const float* xyz1, int m, const float* xyz2, float* dist,
-                    int32_t* idx, cudaStream_t s)
+                    int32_t* idx, const unsigned char* need, cudaStream_t s)
 {
     if (b == 0 || n == 0) return TPK_OK;
     if (m == 0)
@@ -162,22 +177,22 @@ int chamfer_dir_f32(int b, int n, const float* xyz1, int m, const float* xyz2, f
     if (threads == 128 && q == 2)
     {
         prefer_max_shared(chamfer_f32_kernel<128, 2>);
-        count_launches(1), chamfer_f32_kernel<128, 2><<<g, 128, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
+        count_launches(1), chamfer_f32_kernel<128, 2><<<g, 128, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx, need);
     }
     else if (threads == 128)
     {
         prefer_max_shared(chamfer_f32_kernel<128, 1>);
-        count_launches(1), chamfer_f32_kernel<128, 1><<<g, 128, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
+        count_launches(1), chamfer_f32_kernel<128, 1><<<g, 128, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx, need);
     }
     else if (q == 2)
     {
         prefer_max_shared(chamfer_f32_kernel<64, 2>);
-        count_launches(1), chamfer_f32_kernel<64, 2><<<g, 64, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
+        count_launches(1), chamfer_f32_kernel<64, 2><<<g, 64, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx, need);
     }
     else
     {
         prefer_max_shared(chamfer_f32_kernel<64, 1>);
-        count_launches(1), chamfer_f32_kernel<64, 1><<<g, 64, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx);
+        count_launches(1), chamfer_f32_kernel<64, 1><<<g, 64, 0, s>>>(n, m, tiles, xyz1, xyz2, dist, idx, need);
     }
     return check_launch("chamfer_dist");
 }
@@ -241,9 +256,57 @@ extern "C" int tpk_chamfer_dist_f32(int b, int n, const float* xyz1, int m, cons
     TPK_REQUIRE(b == 0 || ((n == 0 || (xyz1 && dist1 && idx1)) && (m == 0 || (xyz2 && dist2 && idx2))),
                 "chamfer_dist: NULL pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    int rc = chamfer_dir_f32(b, n, xyz1, m, xyz2, dist1, idx1, s);
+    int rc = chamfer_dir_f32(b, n, xyz1, m, xyz2, dist1, idx1, nullptr, s);
     if (rc != TPK_OK) return rc;
-    return chamfer_dir_f32(b, m, xyz2, n, xyz1, dist2, idx2, s);
+    return chamfer_dir_f32(b, m, xyz2, n, xyz1, dist2, idx2, nullptr, s);
+}
+
+// The grid pays from a few thousand candidates per cloud on (TPK_CHAMFER_SCAN forces the scan).
+static bool chamfer_wants_grid(int known) { return known >= 4096 && getenv("TPK_CHAMFER_SCAN") == nullptr; }
+
+extern "C" int64_t tpk_chamfer_dist_scratch_bytes(int b, int n, int m)
+{
+    if (b <= 0 || n <= 0 || m <= 0) return 0;
+    // the two directions run one after the other on the same scratch
+    size_t bytes = 0;
+    if (chamfer_wants_grid(m)) bytes = tpk::grid_three_nn_scratch_bytes(b, n, m);
+    if (chamfer_wants_grid(n))
+    {
+        const size_t other = tpk::grid_three_nn_scratch_bytes(b, m, n);
+        if (other > bytes) bytes = other;
+    }
+    return static_cast<int64_t>(bytes);
+}
+
+extern "C" int tpk_chamfer_dist_f32_ws(int b, int n, const float* xyz1, int m, const float* xyz2,
+                                       float* dist1, float* dist2, int32_t* idx1, int32_t* idx2,
+                                       void* scratch, int64_t scratch_bytes, void* stream)
+{
+    using namespace tpk;
+    const int64_t want = tpk_chamfer_dist_scratch_bytes(b, n, m);
+    if (want == 0 || scratch == nullptr)
+        return tpk_chamfer_dist_f32(b, n, xyz1, m, xyz2, dist1, dist2, idx1, idx2, stream);
+    if (scratch_bytes < want)
+    {
+        set_error("chamfer_dist: scratch of %lld bytes given, %lld needed", static_cast<long long>(scratch_bytes),
+                  static_cast<long long>(want));
+        return TPK_ERR_SCRATCH;
+    }
+    TPK_REQUIRE(xyz1 && xyz2 && dist1 && dist2 && idx1 && idx2, "chamfer_dist: NULL pointer");
+    TPK_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "chamfer_dist: scratch must be 256-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // per direction: nearest neighbour on the uniform grid of the other cloud, then the
+    // all-pairs scan for the points the grid handed back (non-finite coordinates, degenerate clouds)
+    const unsigned char* need = nullptr;
+    int rc = TPK_OK;
+    if (chamfer_wants_grid(m)) rc = grid_nn(1, b, n, m, xyz1, xyz2, dist1, idx1, scratch, &need, s);
+    if (rc != TPK_OK) return rc;
+    rc = chamfer_dir_f32(b, n, xyz1, m, xyz2, dist1, idx1, need, s);
+    if (rc != TPK_OK) return rc;
+    need = nullptr;
+    if (chamfer_wants_grid(n)) rc = grid_nn(1, b, m, n, xyz2, xyz1, dist2, idx2, scratch, &need, s);
+    if (rc != TPK_OK) return rc;
+    return chamfer_dir_f32(b, m, xyz2, n, xyz1, dist2, idx2, need, s);
 }
 
 extern "C" int tpk_chamfer_dist_f64(int b, int n, const double* xyz1, int m, const double* xyz2,

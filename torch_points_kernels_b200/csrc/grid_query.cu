@@ -316,17 +316,19 @@ __global__ void __launch_bounds__(kGridQueryThreads)
     }
 }
 
-// Three nearest known points per unknown point on the grid of the known cloud: search
-// the 3x3x3 cell block around the query, then grow the block ring by ring until the third
+// K (1 or 3) nearest known points per unknown point on the grid of the known cloud: search
+// the 3x3x3 cell block around the query, then grow the block ring by ring until the K-th
 // best squared distance is smaller than the squared distance to the nearest face of the
 // block that still has cells behind it (or the block covers the grid).  Candidates are
 // compared as (distance, index) pairs, which is the order the reference's index-ordered
-// strict-'<' cascade produces.
+// strict-'<' scans produce (three_nn: interpolate_gpu.cu:30-49; chamfer: chamfer_dist_gpu.cu:25-60).
+// Output: K distances and K indices per unknown point.
+template <int K>
 __global__ void __launch_bounds__(kGridQueryThreads)
-    grid_three_nn_kernel(int b, int n, int m, size_t cells_cap, const float* __restrict__ unknown,
-                         const GridInfo* __restrict__ info, const int* __restrict__ cells_all,
-                         const float4* __restrict__ sorted_all, float* __restrict__ dist2,
-                         int32_t* __restrict__ idx, unsigned char* __restrict__ need_scan)
+    grid_nn_kernel(int b, int n, int m, size_t cells_cap, const float* __restrict__ unknown,
+                   const GridInfo* __restrict__ info, const int* __restrict__ cells_all,
+                   const float4* __restrict__ sorted_all, float* __restrict__ dist2,
+                   int32_t* __restrict__ idx, unsigned char* __restrict__ need_scan)
 {
     const long long t = static_cast<long long>(blockIdx.x) * kGridQueryThreads + threadIdx.x;
     if (t >= static_cast<long long>(b) * n) return;
@@ -381,27 +383,47 @@ __global__ void __launch_bounds__(kGridQueryThreads)
                     }
                     if (xa > xb) continue;
                     const int beg = __ldg(cells + row + xa), end = __ldg(cells + row + xb + 1);
-                    for (int p = beg; p < end; ++p)
+                    // four candidates per step: the loads (L2) and distances are independent,
+                    // only the updates of the best list run in order
+                    for (int p = beg; p < end; p += 4)
                     {
-                        const float4 c = __ldg(pts + p);
-                        const float d = sumsq_abc(qx - c.x, qy - c.y, qz - c.z);
-                        const int k = __float_as_int(c.w);
-                        if (d < b3 || (d == b3 && k < i3))
+                        float d[4];
+                        int k[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
                         {
-                            if (d < b1 || (d == b1 && k < i1))
+                            const float4 c = __ldg(pts + min(p + u, end - 1));
+                            d[u] = p + u < end ? sumsq_abc(qx - c.x, qy - c.y, qz - c.z) : CUDART_INF_F;
+                            k[u] = p + u < end ? __float_as_int(c.w) : 0x7fffffff;
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                        {
+                            if (K == 1)
                             {
-                                b3 = b2; i3 = i2;
-                                b2 = b1; i2 = i1;
-                                b1 = d;  i1 = k;
+                                if (d[u] < b1 || (d[u] == b1 && k[u] < i1))
+                                {
+                                    b1 = d[u];
+                                    i1 = k[u];
+                                }
                             }
-                            else if (d < b2 || (d == b2 && k < i2))
+                            else if (d[u] < b3 || (d[u] == b3 && k[u] < i3))
                             {
-                                b3 = b2; i3 = i2;
-                                b2 = d;  i2 = k;
-                            }
-                            else
-                            {
-                                b3 = d; i3 = k;
+                                if (d[u] < b1 || (d[u] == b1 && k[u] < i1))
+                                {
+                                    b3 = b2; i3 = i2;
+                                    b2 = b1; i2 = i1;
+                                    b1 = d[u]; i1 = k[u];
+                                }
+                                else if (d[u] < b2 || (d[u] == b2 && k[u] < i2))
+                                {
+                                    b3 = b2; i3 = i2;
+                                    b2 = d[u]; i2 = k[u];
+                                }
+                                else
+                                {
+                                    b3 = d[u]; i3 = k[u];
+                                }
                             }
                         }
                     }
@@ -421,15 +443,19 @@ __global__ void __launch_bounds__(kGridQueryThreads)
         // faces are computed in floating point and points near a face may be binned on either
         // side of it: take a margin of a thousandth of a cell plus the coordinate rounding
         rho -= 1.0e-3f * h + 4.0e-7f * (fabsf(qx) + fabsf(qy) + fabsf(qz) + fabsf(g.minx) + fabsf(g.miny) + fabsf(g.minz));
-        if (rho > 0.f && b3 < rho * rho * 0.9999f) break;
+        const float kth = K == 1 ? b1 : b3;
+        if (rho > 0.f && kth < rho * rho * 0.9999f) break;
     }
     need_scan[t] = 0;
-    dist2[3 * t + 0] = b1;
-    dist2[3 * t + 1] = b2;
-    dist2[3 * t + 2] = b3;
-    idx[3 * t + 0] = i1 == 0x7fffffff ? 0 : i1;
-    idx[3 * t + 1] = i2 == 0x7fffffff ? 0 : i2;
-    idx[3 * t + 2] = i3 == 0x7fffffff ? 0 : i3;
+    dist2[K * t + 0] = b1;
+    idx[K * t + 0] = i1 == 0x7fffffff ? 0 : i1;
+    if (K == 3)
+    {
+        dist2[3 * t + 1] = b2;
+        dist2[3 * t + 2] = b3;
+        idx[3 * t + 1] = i2 == 0x7fffffff ? 0 : i2;
+        idx[3 * t + 2] = i3 == 0x7fffffff ? 0 : i3;
+    }
 }
 
 }  // namespace
@@ -494,9 +520,10 @@ int grid_ball_query_dense(int b, int n, int m, float radius, int nsample, const 
 namespace tpk
 {
 
-// Grid of the `m` known points of every cloud; answers the unknown points the grid is good for.
-int grid_three_nn(int b, int n, int m, const float* unknown, const float* known, float* dist2,
-                  int32_t* idx, void* scratch, const unsigned char** need_scan_out, cudaStream_t s)
+// Grid of the `m` known points of every cloud; answers, with the k (1 or 3) nearest known
+// points, the unknown points the grid is good for.
+int grid_nn(int k, int b, int n, int m, const float* unknown, const float* known, float* dist2,
+            int32_t* idx, void* scratch, const unsigned char** need_scan_out, cudaStream_t s)
 {
     const size_t cap = grid_cells_capacity(m);
     unsigned char* p = static_cast<unsigned char*>(scratch);
@@ -517,13 +544,27 @@ int grid_three_nn(int b, int n, int m, const float* unknown, const float* known,
     count_launches(1), grid_bin_kernel<true><<<gp, kGridThreads, 0, s>>>(b, m, cap, known, info, cells, sorted);
     const long long nq = static_cast<long long>(b) * n;
     const unsigned gq = static_cast<unsigned>((nq + kGridQueryThreads - 1) / kGridQueryThreads);
-    prefer_max_shared(grid_three_nn_kernel);
-    count_launches(1), grid_three_nn_kernel<<<gq, kGridQueryThreads, 0, s>>>(b, n, m, cap, unknown, info, cells, sorted, dist2, idx, need);
+    if (k == 1)
+    {
+        prefer_max_shared(grid_nn_kernel<1>);
+        count_launches(1), grid_nn_kernel<1><<<gq, kGridQueryThreads, 0, s>>>(b, n, m, cap, unknown, info, cells, sorted, dist2, idx, need);
+    }
+    else
+    {
+        prefer_max_shared(grid_nn_kernel<3>);
+        count_launches(1), grid_nn_kernel<3><<<gq, kGridQueryThreads, 0, s>>>(b, n, m, cap, unknown, info, cells, sorted, dist2, idx, need);
+    }
     *need_scan_out = need;
-    return check_launch("three_nn grid");
+    return check_launch("nearest neighbours on the grid");
 }
 
-// scratch for grid_three_nn: grid of m known points, one flag per unknown point
+int grid_three_nn(int b, int n, int m, const float* unknown, const float* known, float* dist2,
+                  int32_t* idx, void* scratch, const unsigned char** need_scan_out, cudaStream_t s)
+{
+    return grid_nn(3, b, n, m, unknown, known, dist2, idx, scratch, need_scan_out, s);
+}
+
+// scratch for grid_nn: grid of m known points, one flag per unknown point
 size_t grid_three_nn_scratch_bytes(int b, int n, int m) { return grid_scratch_bytes(b, m, n); }
 
 }  // namespace tpk
