@@ -254,7 +254,7 @@ TPK_API int tpk_chamfer_dist_f64(int b, int n, const double* xyz1, int m, const 
  * the other cloud (nearest point by (distance, index), i.e. the lowest index among equal
  * distances, as the reference's strict-'<' scan keeps it); results are identical to
  * tpk_chamfer_dist_f32 bit for bit.  scratch: tpk_chamfer_dist_scratch_bytes(b,n,m) bytes,
- * 256-byte aligned; when that returns 0 (both clouds below 4096 points) or scratch is NULL
+ * 256-byte aligned; when that returns 0 (both clouds below 1024 points) or scratch is NULL
  * the call is tpk_chamfer_dist_f32.  No counterpart in the reference.
  */
 TPK_API int tpk_chamfer_dist_f32_ws(int b, int n, const float* xyz1, int m, const float* xyz2, float* dist1,

@@ -543,15 +543,20 @@ def test_chamfer_indices_bit_exact_with_duplicates():
     assert npy(i1).tolist() == [[0, 0, 0, 0]]
 
 
-@pytest.mark.parametrize("case", ["sphere_pair", "one_side_small", "duplicates", "lattice_ties", "nonfinite", "planar"])
+@pytest.mark.parametrize("case", ["sphere_pair", "sphere_pair_large", "one_side_small", "duplicates", "lattice_ties",
+                                  "nonfinite", "planar"])
 def test_chamfer_grid_path_matches_oracle_and_scan(case, monkeypatch):
-    """Clouds of 4096+ points search the other cloud's uniform grid: same distances (bits) and
-    same indices as the all-pairs scan and the oracle, also where many candidates tie."""
+    """Clouds of 1024+ points search the other cloud's uniform grid (in shared memory up to 8192
+    points, in global scratch above): same distances (bits) and same indices as the all-pairs
+    scan and the oracle, also where many candidates tie."""
     rng = np.random.default_rng(len(case))
     B = 2
     if case == "sphere_pair":
         c1, c2 = data.chamfer_pair(B, 6000, seed=4100)
         c1, c2 = c1.numpy().copy(), c2.numpy().copy()
+    elif case == "sphere_pair_large":
+        c1, c2 = data.chamfer_pair(B, 11000, seed=4103)
+        c1, c2 = c1.numpy().copy(), c2[:, :9000].numpy().copy()
     elif case == "one_side_small":
         c1, c2 = data.chamfer_pair(B, 5000, seed=4101)
         c1, c2 = c1.numpy().copy(), c2[:, :700].numpy().copy()   # only one direction has a grid

@@ -22,6 +22,10 @@ namespace tpk
 size_t grid_three_nn_scratch_bytes(int b, int n, int m);
 int grid_nn(int k, int b, int n, int m, const float* unknown, const float* known, float* dist2,
             int32_t* idx, void* scratch, const unsigned char** need_scan_out, cudaStream_t s);
+// smem_grid.cu
+bool sg_three_nn_fits(int m);
+int sg_nn(int k, int b, int n, int m, const float* unknown, const float* known, float* dist2, int32_t* idx,
+          unsigned char* need, cudaStream_t s);
 
 namespace
 {
@@ -261,21 +265,38 @@ extern "C" int tpk_chamfer_dist_f32(int b, int n, const float* xyz1, int m, cons
     return chamfer_dir_f32(b, m, xyz2, n, xyz1, dist2, idx2, nullptr, s);
 }
 
-// The grid pays from a few thousand candidates per cloud on (TPK_CHAMFER_SCAN forces the scan).
-static bool chamfer_wants_grid(int known) { return known >= 4096 && getenv("TPK_CHAMFER_SCAN") == nullptr; }
+// The grid pays from about a thousand candidates per cloud on (TPK_CHAMFER_SCAN forces the scan).
+static bool chamfer_wants_grid(int known) { return known >= 1024 && getenv("TPK_CHAMFER_SCAN") == nullptr; }
+
+// scratch of one direction: one flag per query with the grid in shared memory (up to 8192
+// candidates), the whole grid in global memory above
+static size_t chamfer_dir_scratch(int b, int queries, int known)
+{
+    if (!chamfer_wants_grid(known)) return 0;
+    if (tpk::sg_three_nn_fits(known)) return (static_cast<size_t>(b) * queries + 255) / 256 * 256;
+    return tpk::grid_three_nn_scratch_bytes(b, queries, known);
+}
 
 extern "C" int64_t tpk_chamfer_dist_scratch_bytes(int b, int n, int m)
 {
     if (b <= 0 || n <= 0 || m <= 0) return 0;
     // the two directions run one after the other on the same scratch
-    size_t bytes = 0;
-    if (chamfer_wants_grid(m)) bytes = tpk::grid_three_nn_scratch_bytes(b, n, m);
-    if (chamfer_wants_grid(n))
+    const size_t d1 = chamfer_dir_scratch(b, n, m), d2 = chamfer_dir_scratch(b, m, n);
+    return static_cast<int64_t>(d1 > d2 ? d1 : d2);
+}
+
+// One direction on the grid of the `known` cloud; *need = flags of the points left to the scan.
+static int chamfer_dir_grid(int b, int queries, const float* q, int known, const float* c, float* dist,
+                            int32_t* idx, void* scratch, const unsigned char** need, cudaStream_t s)
+{
+    *need = nullptr;
+    if (!chamfer_wants_grid(known)) return TPK_OK;
+    if (tpk::sg_three_nn_fits(known))
     {
-        const size_t other = tpk::grid_three_nn_scratch_bytes(b, m, n);
-        if (other > bytes) bytes = other;
+        *need = static_cast<const unsigned char*>(scratch);
+        return tpk::sg_nn(1, b, queries, known, q, c, dist, idx, static_cast<unsigned char*>(scratch), s);
     }
-    return static_cast<int64_t>(bytes);
+    return tpk::grid_nn(1, b, queries, known, q, c, dist, idx, scratch, need, s);
 }
 
 extern "C" int tpk_chamfer_dist_f32_ws(int b, int n, const float* xyz1, int m, const float* xyz2,
@@ -298,13 +319,11 @@ extern "C" int tpk_chamfer_dist_f32_ws(int b, int n, const float* xyz1, int m, c
     // per direction: nearest neighbour on the uniform grid of the other cloud, then the
     // all-pairs scan for the points the grid handed back (non-finite coordinates, degenerate clouds)
     const unsigned char* need = nullptr;
-    int rc = TPK_OK;
-    if (chamfer_wants_grid(m)) rc = grid_nn(1, b, n, m, xyz1, xyz2, dist1, idx1, scratch, &need, s);
+    int rc = chamfer_dir_grid(b, n, xyz1, m, xyz2, dist1, idx1, scratch, &need, s);
     if (rc != TPK_OK) return rc;
     rc = chamfer_dir_f32(b, n, xyz1, m, xyz2, dist1, idx1, need, s);
     if (rc != TPK_OK) return rc;
-    need = nullptr;
-    if (chamfer_wants_grid(n)) rc = grid_nn(1, b, m, n, xyz2, xyz1, dist2, idx2, scratch, &need, s);
+    rc = chamfer_dir_grid(b, m, xyz2, n, xyz1, dist2, idx2, scratch, &need, s);
     if (rc != TPK_OK) return rc;
     return chamfer_dir_f32(b, m, xyz2, n, xyz1, dist2, idx2, need, s);
 }

@@ -248,6 +248,7 @@ __device__ __forceinline__ int sg_bin(const float* __restrict__ xyz, int n, cons
 // search the same or adjacent cells: same loop counts, same shared-memory rows.
 constexpr int kSgQueryCapMin = 1024;
 
+template <int K>  // K = 3: three_nn, K = 1: nearest neighbour (chamfer); K outputs per unknown point
 __global__ void __launch_bounds__(kSgThreads, 2)
     sg_three_nn_kernel(int n, int m, int parts, int qcap, int max_dim, int cells_cap,
                        const float* __restrict__ unknown_all, const float* __restrict__ known_all,
@@ -384,7 +385,15 @@ __global__ void __launch_bounds__(kSgThreads, 2)
 #pragma unroll
                             for (int u = 0; u < 4; ++u)
                             {
-                                if (d[u] < b3 || (d[u] == b3 && k[u] < i3))
+                                if (K == 1)
+                                {
+                                    if (d[u] < b1 || (d[u] == b1 && k[u] < i1))
+                                    {
+                                        b1 = d[u];
+                                        i1 = k[u];
+                                    }
+                                }
+                                else if (d[u] < b3 || (d[u] == b3 && k[u] < i3))
                                 {
                                     if (d[u] < b1 || (d[u] == b1 && k[u] < i1))
                                     {
@@ -422,15 +431,19 @@ __global__ void __launch_bounds__(kSgThreads, 2)
             // faces are computed in floating point and a point next to a face may be binned on
             // either side: a thousandth of a cell plus the coordinate rounding as margin
             rho -= 1.0e-3f * g.h + 4.0e-7f * (fabsf(qx) + fabsf(qy) + fabsf(qz) + fabsf(g.minx) + fabsf(g.miny) + fabsf(g.minz));
-            if (rho > 0.f && b3 < rho * rho * 0.9999f) break;
+            const float kth = K == 1 ? b1 : b3;
+            if (rho > 0.f && kth < rho * rho * 0.9999f) break;
         }
         need_all[t] = 0;
-        dist2_all[3 * t + 0] = b1;
-        dist2_all[3 * t + 1] = b2;
-        dist2_all[3 * t + 2] = b3;
-        idx_all[3 * t + 0] = i1 == 0x7fffffff ? 0 : i1;
-        idx_all[3 * t + 1] = i2 == 0x7fffffff ? 0 : i2;
-        idx_all[3 * t + 2] = i3 == 0x7fffffff ? 0 : i3;
+        dist2_all[K * t + 0] = b1;
+        idx_all[K * t + 0] = i1 == 0x7fffffff ? 0 : i1;
+        if (K == 3)
+        {
+            dist2_all[3 * t + 1] = b2;
+            dist2_all[3 * t + 2] = b3;
+            idx_all[3 * t + 1] = i2 == 0x7fffffff ? 0 : i2;
+            idx_all[3 * t + 2] = i3 == 0x7fffffff ? 0 : i3;
+        }
     }
     SG_STAMP(13);
 }
@@ -646,8 +659,9 @@ __global__ void __launch_bounds__(kSgThreads, 2)
 // Whether the shared-memory grid serves a three_nn call with m known points per cloud.
 bool sg_three_nn_fits(int m) { return m >= 256 && m <= kSgMaxPoints; }
 
-int sg_three_nn(int b, int n, int m, const float* unknown, const float* known, float* dist2, int32_t* idx,
-                unsigned char* need, cudaStream_t s)
+// k = 3: three_nn; k = 1: the nearest neighbour only (one distance and one index per unknown point)
+int sg_nn(int k, int b, int n, int m, const float* unknown, const float* known, float* dist2, int32_t* idx,
+          unsigned char* need, cudaStream_t s)
 {
     const int max_dim = grid_max_dim(m);
     const int cap = static_cast<int>(grid_cells_capacity(m));
@@ -668,7 +682,7 @@ int sg_three_nn(int b, int n, int m, const float* unknown, const float* known, f
     qcap = (qcap + 1) / 2 * 2;
     TPK_REQUIRE(qcap >= 2, "three_nn grid: no room for the query list");
     const size_t smem = base + static_cast<size_t>(qcap) * 10;
-    auto kernel = sg_three_nn_kernel;
+    auto kernel = k == 1 ? sg_three_nn_kernel<1> : sg_three_nn_kernel<3>;
     prefer_max_shared(kernel);
     if (smem > 48 * 1024)
     {
@@ -684,6 +698,12 @@ int sg_three_nn(int b, int n, int m, const float* unknown, const float* known, f
     count_launches(1), kernel<<<static_cast<unsigned>(grid), kSgThreads, smem, s>>>(n, m, parts, static_cast<int>(qcap), max_dim, cap, unknown,
                                                                  known, dist2, idx, need);
     return check_launch("three_nn grid");
+}
+
+int sg_three_nn(int b, int n, int m, const float* unknown, const float* known, float* dist2, int32_t* idx,
+                unsigned char* need, cudaStream_t s)
+{
+    return sg_nn(3, b, n, m, unknown, known, dist2, idx, need, s);
 }
 
 namespace
