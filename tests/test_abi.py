@@ -49,7 +49,8 @@ def test_invalid_arguments_return_status_without_gpu():
 
 def test_scratch_sizes_are_host_arithmetic(monkeypatch):
     """What the callers must allocate: pure host functions, usable without a GPU."""
-    for env in ("TPK_FPS_SORTED", "TPK_FPS_FORCE_GLOBAL", "TPK_BALL_QUERY_GLOBAL_GRID", "TPK_THREE_NN_GLOBAL_GRID"):
+    for env in ("TPK_FPS_SORTED", "TPK_FPS_FORCE_GLOBAL", "TPK_BALL_QUERY_GLOBAL_GRID", "TPK_THREE_NN_GLOBAL_GRID",
+                "TPK_NN_GLOBAL_GRID", "TPK_CHAMFER_SCAN"):
         monkeypatch.delenv(env, raising=False)
     l = _lib.lib()
     # FPS: nothing for small clouds or few samples, the sorted copy (16 B/point) for clouds that stay
@@ -66,10 +67,14 @@ def test_scratch_sizes_are_host_arithmetic(monkeypatch):
     assert l.tpk_ball_query_dense_scratch_bytes(2, 256, 64, 32) == 0
     assert l.tpk_ball_query_dense_scratch_bytes(16, 16384, 4096, 32) == 16 * 4096
     assert l.tpk_ball_query_dense_scratch_bytes(2, 300000, 100, 32) > 2 * 300000 * 16
-    # three_nn: one flag per unknown point up to 8192 known points
+    # three_nn: one flag per unknown point (grid in shared memory), the whole grid for huge known clouds
     assert l.tpk_three_nn_scratch_bytes(2, 256, 64) == 0
     assert l.tpk_three_nn_scratch_bytes(16, 16384, 4096) == 16 * 16384
-    assert l.tpk_three_nn_scratch_bytes(2, 3000, 10000) > 2 * 10000 * 16
+    assert l.tpk_three_nn_scratch_bytes(2, 3000, 10000) == (2 * 3000 + 255) // 256 * 256
+    assert l.tpk_three_nn_scratch_bytes(1, 1000, 3000000) > 3000000 * 16
+    # chamfer: flags for the larger direction
+    assert l.tpk_chamfer_dist_scratch_bytes(4, 512, 700) == 0
+    assert l.tpk_chamfer_dist_scratch_bytes(32, 16384, 16384) == 32 * 16384
     assert l.tpk_three_nn_scratch_bytes(0, 10, 10) == 0
     assert _lib.kernel_launches() >= 0
 

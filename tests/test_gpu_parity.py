@@ -359,10 +359,16 @@ def _three_nn_grid_cases():
     # the PointNet++ shape: upsampling 4096 -> 16384
     x = data.unit_ball(2, 16384, seed=15)
     cases["upsample"] = (x, np.ascontiguousarray(x[:, ::4]))
+    # more than 8192 known points: the grid is staged by layers; sparse regions and far
+    # queries need rings beyond the staged layers and go to the scan
+    cases["many_known"] = (data.unit_ball(2, 5000, seed=16) * 1.2, data.unit_ball(2, 12000, seed=17))
+    k = (rng.standard_normal((2, 11000, 3)) * 0.05 + rng.integers(0, 3, (2, 11000, 1))).astype(np.float32)
+    cases["many_known_clustered"] = (rng.uniform(-1, 3, (2, 3000, 3)).astype(np.float32), k)
     return cases
 
 
-@pytest.mark.parametrize("name", ["uniform", "outside", "clustered_duplicates", "planar", "lattice_ties", "upsample"])
+@pytest.mark.parametrize("name", ["uniform", "outside", "clustered_duplicates", "planar", "lattice_ties", "upsample",
+                                  "many_known", "many_known_clustered"])
 def test_three_nn_grid_path_matches_oracle(name, monkeypatch):
     unknown, known = _three_nn_grid_cases()[name]
     b, n, m = unknown.shape[0], unknown.shape[1], known.shape[1]
@@ -581,7 +587,8 @@ def test_chamfer_grid_path_matches_oracle_and_scan(case, monkeypatch):
     n, m = c1.shape[1], c2.shape[1]
     assert _lib.lib().tpk_chamfer_dist_scratch_bytes(B, n, m) > 0
     results = []
-    for env in (None, "TPK_CHAMFER_SCAN"):
+    # default (grid in shared memory, by layers above 8192 points), grid in global memory, scan
+    for env in (None, "TPK_NN_GLOBAL_GRID", "TPK_CHAMFER_SCAN"):
         if env:
             monkeypatch.setenv(env, "1")
         x1, x2 = cu(c1).requires_grad_(True), cu(c2).requires_grad_(True)
@@ -593,13 +600,15 @@ def test_chamfer_grid_path_matches_oracle_and_scan(case, monkeypatch):
         same_bits(results[0][0], o1)
         same_bits(results[0][1], o2)
     with np.errstate(invalid="ignore"):
-        same_bits(results[0][0], results[1][0])
-        same_bits(results[0][1], results[1][1])
-        # gradients are summed with atomics (order varies): equal up to rounding
-        np.testing.assert_allclose(results[0][2], results[1][2], rtol=1e-4, atol=1e-4)
-        np.testing.assert_allclose(results[0][3], results[1][3], rtol=1e-4, atol=1e-4)
+        for other in results[1:]:
+            same_bits(results[0][0], other[0])
+            same_bits(results[0][1], other[1])
+            # gradients are summed with atomics (order varies): equal up to rounding
+            np.testing.assert_allclose(results[0][2], other[2], rtol=1e-4, atol=1e-4)
+            np.testing.assert_allclose(results[0][3], other[3], rtol=1e-4, atol=1e-4)
     # the indices themselves, through the C ABI: grid + scratch against the plain scan
     monkeypatch.delenv("TPK_CHAMFER_SCAN")
+    monkeypatch.delenv("TPK_NN_GLOBAL_GRID")
     x1, x2 = cu(c1), cu(c2)
     out = []
     for use_ws in (True, False):

@@ -26,6 +26,9 @@ int grid_nn(int k, int b, int n, int m, const float* unknown, const float* known
 bool sg_three_nn_fits(int m);
 int sg_nn(int k, int b, int n, int m, const float* unknown, const float* known, float* dist2, int32_t* idx,
           unsigned char* need, cudaStream_t s);
+bool sg_nn_slab_fits(int b, int n, int m);
+int sg_nn_slab(int k, int b, int n, int m, const float* unknown, const float* known, float* dist2, int32_t* idx,
+               unsigned char* need, cudaStream_t s);
 
 namespace
 {
@@ -268,12 +271,20 @@ extern "C" int tpk_chamfer_dist_f32(int b, int n, const float* xyz1, int m, cons
 // The grid pays from about a thousand candidates per cloud on (TPK_CHAMFER_SCAN forces the scan).
 static bool chamfer_wants_grid(int known) { return known >= 1024 && getenv("TPK_CHAMFER_SCAN") == nullptr; }
 
-// scratch of one direction: one flag per query with the grid in shared memory (up to 8192
-// candidates), the whole grid in global memory above
+// TPK_NN_GLOBAL_GRID keeps clouds above 8192 points on the grid in global memory
+// (comparison runs and tests of that path)
+static bool chamfer_by_layers(int b, int queries, int known)
+{
+    return tpk::sg_nn_slab_fits(b, queries, known) && getenv("TPK_NN_GLOBAL_GRID") == nullptr;
+}
+
+// scratch of one direction: one flag per query with the grid in shared memory (whole cloud
+// up to 8192 candidates, by layers above), the whole grid where it has to live in global memory
 static size_t chamfer_dir_scratch(int b, int queries, int known)
 {
     if (!chamfer_wants_grid(known)) return 0;
-    if (tpk::sg_three_nn_fits(known)) return (static_cast<size_t>(b) * queries + 255) / 256 * 256;
+    if (tpk::sg_three_nn_fits(known) || chamfer_by_layers(b, queries, known))
+        return (static_cast<size_t>(b) * queries + 255) / 256 * 256;
     return tpk::grid_three_nn_scratch_bytes(b, queries, known);
 }
 
@@ -295,6 +306,11 @@ static int chamfer_dir_grid(int b, int queries, const float* q, int known, const
     {
         *need = static_cast<const unsigned char*>(scratch);
         return tpk::sg_nn(1, b, queries, known, q, c, dist, idx, static_cast<unsigned char*>(scratch), s);
+    }
+    if (chamfer_by_layers(b, queries, known))
+    {
+        *need = static_cast<const unsigned char*>(scratch);
+        return tpk::sg_nn_slab(1, b, queries, known, q, c, dist, idx, static_cast<unsigned char*>(scratch), s);
     }
     return tpk::grid_nn(1, b, queries, known, q, c, dist, idx, scratch, need, s);
 }

@@ -315,6 +315,9 @@ int grid_three_nn(int b, int n, int m, const float* unknown, const float* known,
 bool sg_three_nn_fits(int m);
 int sg_three_nn(int b, int n, int m, const float* unknown, const float* known, float* dist2, int32_t* idx,
                 unsigned char* need, cudaStream_t s);
+bool sg_nn_slab_fits(int b, int n, int m);
+int sg_nn_slab(int k, int b, int n, int m, const float* unknown, const float* known, float* dist2, int32_t* idx,
+               unsigned char* need, cudaStream_t s);
 
 static int launch_three_nn_scan(int b, int n, int m, const float* unknown, const float* known,
                                 float* dist2, int32_t* idx, const unsigned char* need, cudaStream_t s)
@@ -366,11 +369,17 @@ static bool three_nn_smem_grid(int m)
     return tpk::sg_three_nn_fits(m) && getenv("TPK_THREE_NN_GLOBAL_GRID") == nullptr;
 }
 
+// above 8192 known points: the shared-memory grid by layers
+static bool three_nn_by_layers(int b, int n, int m)
+{
+    return tpk::sg_nn_slab_fits(b, n, m) && getenv("TPK_THREE_NN_GLOBAL_GRID") == nullptr;
+}
+
 extern "C" int64_t tpk_three_nn_scratch_bytes(int b, int n, int m)
 {
     if (b <= 0 || n <= 0) return 0;
     // shared-memory grid: one flag per unknown point
-    if (three_nn_smem_grid(m)) return (static_cast<int64_t>(b) * n + 255) / 256 * 256;
+    if (three_nn_smem_grid(m) || three_nn_by_layers(b, n, m)) return (static_cast<int64_t>(b) * n + 255) / 256 * 256;
     if (m < 4096) return 0;
     return static_cast<int64_t>(tpk::grid_three_nn_scratch_bytes(b, n, m));
 }
@@ -397,6 +406,11 @@ extern "C" int tpk_three_nn_ws(int b, int n, int m, const float* unknown, const 
     {
         need = static_cast<const unsigned char*>(scratch);
         rc = sg_three_nn(b, n, m, unknown, known, dist2, idx, static_cast<unsigned char*>(scratch), s);
+    }
+    else if (three_nn_by_layers(b, n, m))
+    {
+        need = static_cast<const unsigned char*>(scratch);
+        rc = sg_nn_slab(3, b, n, m, unknown, known, dist2, idx, static_cast<unsigned char*>(scratch), s);
     }
     else
     {

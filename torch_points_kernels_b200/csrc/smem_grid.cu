@@ -238,6 +238,128 @@ __device__ __forceinline__ int sg_bin(const float* __restrict__ xyz, int n, cons
     return total;
 }
 
+// The K (1 or 3) nearest staged points of (qx, qy, qz) by (distance, index): the 3x3x3 cells
+// around the query, then ring by ring until the K-th best squared distance is below the
+// squared distance to the nearest face of the searched block that has unsearched cells behind
+// it.  `cells` / `spts` hold the z layers [za, zb] of the grid.  Returns false if a ring
+// would need layers outside [za, zb] before the search could stop (the best list is then
+// incomplete).
+template <int K>
+__device__ __forceinline__ bool sg_nn_search(const SgGrid& g, const int* cells, const float4* spts, int za, int zb,
+                                             float qx, float qy, float qz, float& b1, float& b2, float& b3,
+                                             int& i1, int& i2, int& i3)
+{
+    const int cx = sg_cell_coord(qx, g.minx, g.inv_h, g.dx);
+    const int cy = sg_cell_coord(qy, g.miny, g.inv_h, g.dy);
+    const int cz = sg_cell_coord(qz, g.minz, g.inv_h, g.dz);
+    b1 = b2 = b3 = CUDART_INF_F;
+    i1 = i2 = i3 = 0x7fffffff;
+    int px0 = 0, px1 = -1, py0 = 0, py1 = -1, pz0 = 0, pz1 = -1;  // block searched so far
+    const int max_ring = max(g.dx, max(g.dy, g.dz));
+    for (int ring = 1; ring <= max_ring; ++ring)
+    {
+        const int x0 = max(cx - ring, 0), x1 = min(cx + ring, g.dx - 1);
+        const int y0 = max(cy - ring, 0), y1 = min(cy + ring, g.dy - 1);
+        const int z0 = max(cz - ring, 0), z1 = min(cz + ring, g.dz - 1);
+        if (z0 < za || z1 > zb) return false;  // this ring leaves the staged layers
+        for (int z = z0; z <= z1; ++z)
+            for (int y = y0; y <= y1; ++y)
+            {
+                const bool inner_row = z >= pz0 && z <= pz1 && y >= py0 && y <= py1;
+                const int row = ((z - za) * g.dy + y) * g.dx;
+                // cells of the row not searched before: all of [x0, x1], or its two ends
+                for (int side = 0; side < 2; ++side)
+                {
+                    int xa, xb;
+                    if (!inner_row)
+                    {
+                        if (side == 1) break;
+                        xa = x0;
+                        xb = x1;
+                    }
+                    else if (side == 0)
+                    {
+                        xa = x0;
+                        xb = px0 - 1;
+                    }
+                    else
+                    {
+                        xa = px1 + 1;
+                        xb = x1;
+                    }
+                    if (xa > xb) continue;
+                    const int beg = cells[row + xa], end = cells[row + xb + 1];
+#ifdef TPK_SG_TIMING
+                    atomicAdd(&g_sg_stamps[14], static_cast<unsigned long long>(end - beg));
+#endif
+                    // four candidates per step: the loads and distances are independent,
+                    // only the updates of the three best run in order
+                    for (int p = beg; p < end; p += 4)
+                    {
+                        float d[4];
+                        int k[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                        {
+                            const float4 c = spts[min(p + u, end - 1)];
+                            d[u] = p + u < end ? sumsq_abc(qx - c.x, qy - c.y, qz - c.z) : CUDART_INF_F;
+                            k[u] = p + u < end ? __float_as_int(c.w) : 0x7fffffff;
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                        {
+                            if (K == 1)
+                            {
+                                if (d[u] < b1 || (d[u] == b1 && k[u] < i1))
+                                {
+                                    b1 = d[u];
+                                    i1 = k[u];
+                                }
+                            }
+                            else if (d[u] < b3 || (d[u] == b3 && k[u] < i3))
+                            {
+                                if (d[u] < b1 || (d[u] == b1 && k[u] < i1))
+                                {
+                                    b3 = b2; i3 = i2;
+                                    b2 = b1; i2 = i1;
+                                    b1 = d[u]; i1 = k[u];
+                                }
+                                else if (d[u] < b2 || (d[u] == b2 && k[u] < i2))
+                                {
+                                    b3 = b2; i3 = i2;
+                                    b2 = d[u]; i2 = k[u];
+                                }
+                                else
+                                {
+                                    b3 = d[u]; i3 = k[u];
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        px0 = x0; px1 = x1; py0 = y0; py1 = y1; pz0 = z0; pz1 = z1;
+#ifdef TPK_SG_TIMING
+        atomicAdd(&g_sg_stamps[15], 1ull);
+#endif
+        if (x0 == 0 && y0 == 0 && z0 == 0 && x1 == g.dx - 1 && y1 == g.dy - 1 && z1 == g.dz - 1) return true;
+        // distance to the nearest face of the block with unsearched cells behind it
+        float rho = CUDART_INF_F;
+        if (x0 > 0) rho = fminf(rho, qx - (g.minx + x0 * g.h));
+        if (x1 < g.dx - 1) rho = fminf(rho, (g.minx + (x1 + 1) * g.h) - qx);
+        if (y0 > 0) rho = fminf(rho, qy - (g.miny + y0 * g.h));
+        if (y1 < g.dy - 1) rho = fminf(rho, (g.miny + (y1 + 1) * g.h) - qy);
+        if (z0 > 0) rho = fminf(rho, qz - (g.minz + z0 * g.h));
+        if (z1 < g.dz - 1) rho = fminf(rho, (g.minz + (z1 + 1) * g.h) - qz);
+        // faces are computed in floating point and a point next to a face may be binned on
+        // either side: a thousandth of a cell plus the coordinate rounding as margin
+        rho -= 1.0e-3f * g.h + 4.0e-7f * (fabsf(qx) + fabsf(qy) + fabsf(qz) + fabsf(g.minx) + fabsf(g.miny) + fabsf(g.minz));
+        const float kth = K == 1 ? b1 : b3;
+        if (rho > 0.f && kth < rho * rho * 0.9999f) return true;
+    }
+    return true;
+}
+
 // ------------------------------------------------------------------------------ three_nn
 //
 // Grid: blockIdx.x = cloud * parts + part.  Every CTA of a cloud bins all known points.
@@ -327,113 +449,9 @@ __global__ void __launch_bounds__(kSgThreads, 2)
         const int j = qsorted[i];
         const size_t t = qbase + j;
         const float qx = __ldg(unknown + 3 * j + 0), qy = __ldg(unknown + 3 * j + 1), qz = __ldg(unknown + 3 * j + 2);
-        const int cx = sg_cell_coord(qx, g.minx, g.inv_h, g.dx);
-        const int cy = sg_cell_coord(qy, g.miny, g.inv_h, g.dy);
-        const int cz = sg_cell_coord(qz, g.minz, g.inv_h, g.dz);
-        float b1 = CUDART_INF_F, b2 = CUDART_INF_F, b3 = CUDART_INF_F;
-        int i1 = 0x7fffffff, i2 = 0x7fffffff, i3 = 0x7fffffff;
-        int px0 = 0, px1 = -1, py0 = 0, py1 = -1, pz0 = 0, pz1 = -1;  // block searched so far
-        const int max_ring = max(g.dx, max(g.dy, g.dz));
-        for (int ring = 1; ring <= max_ring; ++ring)
-        {
-            const int x0 = max(cx - ring, 0), x1 = min(cx + ring, g.dx - 1);
-            const int y0 = max(cy - ring, 0), y1 = min(cy + ring, g.dy - 1);
-            const int z0 = max(cz - ring, 0), z1 = min(cz + ring, g.dz - 1);
-            for (int z = z0; z <= z1; ++z)
-                for (int y = y0; y <= y1; ++y)
-                {
-                    const bool inner_row = z >= pz0 && z <= pz1 && y >= py0 && y <= py1;
-                    const int row = (z * g.dy + y) * g.dx;
-                    // cells of the row not searched before: all of [x0, x1], or its two ends
-                    for (int side = 0; side < 2; ++side)
-                    {
-                        int xa, xb;
-                        if (!inner_row)
-                        {
-                            if (side == 1) break;
-                            xa = x0;
-                            xb = x1;
-                        }
-                        else if (side == 0)
-                        {
-                            xa = x0;
-                            xb = px0 - 1;
-                        }
-                        else
-                        {
-                            xa = px1 + 1;
-                            xb = x1;
-                        }
-                        if (xa > xb) continue;
-                        const int beg = cells[row + xa], end = cells[row + xb + 1];
-#ifdef TPK_SG_TIMING
-                        atomicAdd(&g_sg_stamps[14], static_cast<unsigned long long>(end - beg));
-#endif
-                        // four candidates per step: the loads and distances are independent,
-                        // only the updates of the three best run in order
-                        for (int p = beg; p < end; p += 4)
-                        {
-                            float d[4];
-                            int k[4];
-#pragma unroll
-                            for (int u = 0; u < 4; ++u)
-                            {
-                                const float4 c = spts[min(p + u, end - 1)];
-                                d[u] = p + u < end ? sumsq_abc(qx - c.x, qy - c.y, qz - c.z) : CUDART_INF_F;
-                                k[u] = p + u < end ? __float_as_int(c.w) : 0x7fffffff;
-                            }
-#pragma unroll
-                            for (int u = 0; u < 4; ++u)
-                            {
-                                if (K == 1)
-                                {
-                                    if (d[u] < b1 || (d[u] == b1 && k[u] < i1))
-                                    {
-                                        b1 = d[u];
-                                        i1 = k[u];
-                                    }
-                                }
-                                else if (d[u] < b3 || (d[u] == b3 && k[u] < i3))
-                                {
-                                    if (d[u] < b1 || (d[u] == b1 && k[u] < i1))
-                                    {
-                                        b3 = b2; i3 = i2;
-                                        b2 = b1; i2 = i1;
-                                        b1 = d[u]; i1 = k[u];
-                                    }
-                                    else if (d[u] < b2 || (d[u] == b2 && k[u] < i2))
-                                    {
-                                        b3 = b2; i3 = i2;
-                                        b2 = d[u]; i2 = k[u];
-                                    }
-                                    else
-                                    {
-                                        b3 = d[u]; i3 = k[u];
-                                    }
-                                }
-                            }
-                        }
-                    }
-                }
-            px0 = x0; px1 = x1; py0 = y0; py1 = y1; pz0 = z0; pz1 = z1;
-#ifdef TPK_SG_TIMING
-            atomicAdd(&g_sg_stamps[15], 1ull);
-#endif
-            if (x0 == 0 && y0 == 0 && z0 == 0 && x1 == g.dx - 1 && y1 == g.dy - 1 && z1 == g.dz - 1) break;
-            // distance to the nearest face of the block with unsearched cells behind it
-            float rho = CUDART_INF_F;
-            if (x0 > 0) rho = fminf(rho, qx - (g.minx + x0 * g.h));
-            if (x1 < g.dx - 1) rho = fminf(rho, (g.minx + (x1 + 1) * g.h) - qx);
-            if (y0 > 0) rho = fminf(rho, qy - (g.miny + y0 * g.h));
-            if (y1 < g.dy - 1) rho = fminf(rho, (g.miny + (y1 + 1) * g.h) - qy);
-            if (z0 > 0) rho = fminf(rho, qz - (g.minz + z0 * g.h));
-            if (z1 < g.dz - 1) rho = fminf(rho, (g.minz + (z1 + 1) * g.h) - qz);
-            // faces are computed in floating point and a point next to a face may be binned on
-            // either side: a thousandth of a cell plus the coordinate rounding as margin
-            rho -= 1.0e-3f * g.h + 4.0e-7f * (fabsf(qx) + fabsf(qy) + fabsf(qz) + fabsf(g.minx) + fabsf(g.miny) + fabsf(g.minz));
-            const float kth = K == 1 ? b1 : b3;
-            if (rho > 0.f && kth < rho * rho * 0.9999f) break;
-        }
+        float b1, b2, b3;
+        int i1, i2, i3;
+        sg_nn_search<K>(g, cells, spts, 0, g.dz - 1, qx, qy, qz, b1, b2, b3, i1, i2, i3);
         need_all[t] = 0;
         dist2_all[K * t + 0] = b1;
         idx_all[K * t + 0] = i1 == 0x7fffffff ? 0 : i1;
@@ -446,6 +464,105 @@ __global__ void __launch_bounds__(kSgThreads, 2)
         }
     }
     SG_STAMP(13);
+}
+
+// ----------------------------------------------------------- nearest neighbours, by layers
+//
+// The same search for known clouds too large for one CTA's shared memory.  Grid:
+// blockIdx.x = cloud * parts + part; the CTA owns the unknown points whose z cell lies in
+// layers [part * lpp, (part + 1) * lpp) of the grid of the known points and stages those
+// layers plus `pad` layers on either side.  It collects its unknown points from one pass
+// over the cloud, sorts them by cell and answers one per thread.  A search that would have
+// to leave the staged layers (its ring-1 block never does) is flagged for the scan.
+template <int K>
+__global__ void __launch_bounds__(kSgThreads, 2)
+    sg_nn_slab_kernel(int n, int m, int parts, int lpp, int pad, int qcap, int max_dim, int cells_cap,
+                      int slab_cells_cap, int own_cells_cap, int pcap, const float* __restrict__ unknown_all,
+                      const float* __restrict__ known_all, float* __restrict__ dist2_all,
+                      int32_t* __restrict__ idx_all, unsigned char* __restrict__ need_all)
+{
+    extern __shared__ __align__(16) unsigned char sg_raw[];
+    __shared__ int s_nq;
+    float4* spts = reinterpret_cast<float4*>(sg_raw);
+    int* cells = reinterpret_cast<int*>(spts + pcap);
+    int* counts = cells + slab_cells_cap + 1;   // per owned cell: run of collected unknown points
+    int* qj = counts + own_cells_cap + 2;       // collected unknown points, in arrival order
+    int* qsorted = qj + qcap;                   // the same, sorted by cell
+    unsigned short* qkey = reinterpret_cast<unsigned short*>(qsorted + qcap);
+
+    const int tid = threadIdx.x;
+    const int cloud = blockIdx.x / parts, part = blockIdx.x - cloud * parts;
+    const float* known = known_all + static_cast<size_t>(cloud) * m * 3;
+    const float* unknown = unknown_all + static_cast<size_t>(cloud) * n * 3;
+    const size_t qbase = static_cast<size_t>(cloud) * n;
+
+    const SgGrid g = sg_make_grid(known, m, 1.0e-30f, max_dim, static_cast<size_t>(cells_cap));
+    if (!g.ok)
+    {
+        if (part == 0)
+            for (int j = tid; j < n; j += kSgThreads) need_all[qbase + j] = 1;
+        return;
+    }
+    const int own_lo = part * lpp, own_hi = min(g.dz, own_lo + lpp) - 1;
+    if (own_lo > own_hi) return;
+    const int za = max(own_lo - pad, 0), zb = min(own_hi + pad, g.dz - 1);
+    const int staged = sg_bin(known, m, g, za, zb, cells, spts, pcap);
+    const int nkeys = (own_hi - own_lo + 1) * g.dy * g.dx;  // at most own_cells_cap, below 65536
+    if (tid == 0) s_nq = 0;
+    for (int k = tid; k <= nkeys; k += kSgThreads) counts[k] = 0;
+    __syncthreads();
+    sg_for_points(unknown, n, [&](int j, float qx, float qy, float qz) {
+        if (!(fabsf(qx) < 1.0e18f && fabsf(qy) < 1.0e18f && fabsf(qz) < 1.0e18f))
+        {
+            if (part == 0) need_all[qbase + j] = 1;  // no cell: the first CTA hands it to the scan
+            return;
+        }
+        const int cz = sg_cell_coord(qz, g.minz, g.inv_h, g.dz);
+        if (cz < own_lo || cz > own_hi) return;
+        const int cy = sg_cell_coord(qy, g.miny, g.inv_h, g.dy);
+        const int cx = sg_cell_coord(qx, g.minx, g.inv_h, g.dx);
+        const int key = ((cz - own_lo) * g.dy + cy) * g.dx + cx;
+        const int pos = staged < 0 ? qcap : atomicAdd(&s_nq, 1);
+        if (pos < qcap)
+        {
+            qj[pos] = j;
+            qkey[pos] = static_cast<unsigned short>(key);
+            atomicAdd(&counts[key + 1], 1);
+        }
+        else
+        {
+            need_all[qbase + j] = 1;  // more known or unknown points around these layers than fit
+        }
+    });
+    __syncthreads();
+    const int nq = min(s_nq, qcap);
+    sg_block_scan(counts + 1, nkeys);
+    for (int i = tid; i < nq; i += kSgThreads) qsorted[atomicAdd(&counts[qkey[i] + 1], 1)] = qj[i];
+    __syncthreads();
+
+    for (int i = tid; i < nq; i += kSgThreads)
+    {
+        const int j = qsorted[i];
+        const size_t t = qbase + j;
+        const float qx = __ldg(unknown + 3 * j + 0), qy = __ldg(unknown + 3 * j + 1), qz = __ldg(unknown + 3 * j + 2);
+        float b1, b2, b3;
+        int i1, i2, i3;
+        if (!sg_nn_search<K>(g, cells, spts, za, zb, qx, qy, qz, b1, b2, b3, i1, i2, i3))
+        {
+            need_all[t] = 1;
+            continue;
+        }
+        need_all[t] = 0;
+        dist2_all[K * t + 0] = b1;
+        idx_all[K * t + 0] = i1 == 0x7fffffff ? 0 : i1;
+        if (K == 3)
+        {
+            dist2_all[3 * t + 1] = b2;
+            dist2_all[3 * t + 2] = b3;
+            idx_all[3 * t + 1] = i2 == 0x7fffffff ? 0 : i2;
+            idx_all[3 * t + 2] = i3 == 0x7fffffff ? 0 : i3;
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------- ball query
@@ -708,6 +825,109 @@ int sg_three_nn(int b, int n, int m, const float* unknown, const float* known, f
 
 namespace
 {
+struct SgSlabPlan
+{
+    int max_dim, cells_cap, slab_cells_cap, own_cells_cap, pcap, qcap, lpp, pad, parts;
+    size_t smem;
+    bool ok;
+};
+
+// Layers per CTA for the nearest-neighbour search by layers: the same trade as for the ball
+// query (every CTA passes over both clouds; CTAs beyond what the SMs hold wait), one layer
+// of padding on either side.
+SgSlabPlan sg_slab_plan(int b, int n, int m)
+{
+    SgSlabPlan best = {};
+    best.ok = false;
+    if (b < 1 || n < 1 || m < 1024) return best;
+    const int max_dim = grid_max_dim(m);
+    const int pad = 1;
+    double best_cost = 0.0;
+    for (int lpp = 1; lpp <= max_dim; ++lpp)
+    {
+        const int parts = (max_dim + lpp - 1) / lpp;
+        if (lpp > 1 && parts == (max_dim + lpp - 2) / (lpp - 1)) continue;  // same parts with fewer layers each
+        const int layers = lpp + 2 * pad < max_dim ? lpp + 2 * pad : max_dim;
+        const size_t slab_cells = static_cast<size_t>(layers) * max_dim * max_dim;
+        const size_t own_cells = static_cast<size_t>(lpp) * max_dim * max_dim;
+        if (own_cells >= 65536) continue;  // 16-bit sort keys
+        size_t qcap = static_cast<size_t>(2.5 * n * lpp / max_dim) + 256;
+        if (qcap > static_cast<size_t>(n)) qcap = n;
+        qcap = (qcap + 1) / 2 * 2;
+        const size_t fixed = (slab_cells + 1 + own_cells + 2) * sizeof(int) + qcap * 10 + 64;
+        if (fixed + 1024 * sizeof(float4) > kSgSmemBudget) continue;
+        size_t want = static_cast<size_t>(2.0 * m * layers / max_dim) + 256;
+        if (want > static_cast<size_t>(m)) want = m;
+        const size_t room = (kSgSmemBudget - fixed) / sizeof(float4);
+        if (want > room)
+        {
+            // single layers: take what fits (crowded layers go to the scan), unless even an
+            // average layer would not fit
+            if (lpp > 1 || static_cast<double>(m) * layers / max_dim > static_cast<double>(room)) continue;
+            want = room;
+        }
+        SgSlabPlan p = {};
+        p.max_dim = max_dim;
+        p.cells_cap = static_cast<int>(grid_cells_capacity(m));
+        p.lpp = lpp;
+        p.pad = pad;
+        p.parts = parts;
+        p.slab_cells_cap = static_cast<int>(slab_cells);
+        p.own_cells_cap = static_cast<int>(own_cells);
+        p.qcap = static_cast<int>(qcap);
+        p.pcap = static_cast<int>((want + 3) / 4 * 4);
+        p.smem = static_cast<size_t>(p.pcap) * sizeof(float4) + fixed;
+        p.ok = true;
+        const int per_sm = (p.smem + 1024) * 2 <= 228 * 1024 ? 2 : 1;
+        const double slots = static_cast<double>(num_sms()) * per_sm;
+        // about 1 ns per point for the passes over both clouds, 25 ns per unknown point answered
+        const double passes = 1.0 * m + 0.4 * n, per_layer = 25.0 * n / max_dim;
+        const double total = static_cast<double>(b) * (parts * passes + max_dim * per_layer);
+        const double heaviest = passes + 1.5 * lpp * per_layer;
+        const double cost = total / slots > heaviest ? total / slots : heaviest;
+        if (!best.ok || cost < best_cost)
+        {
+            best = p;
+            best_cost = cost;
+        }
+    }
+    return best;
+}
+}  // namespace
+
+// Whether the search by layers serves m known points per cloud (above the whole-cloud limit).
+bool sg_nn_slab_fits(int b, int n, int m) { return m > kSgMaxPoints && sg_slab_plan(b, n, m).ok; }
+
+int sg_nn_slab(int k, int b, int n, int m, const float* unknown, const float* known, float* dist2, int32_t* idx,
+               unsigned char* need, cudaStream_t s)
+{
+    const SgSlabPlan p = sg_slab_plan(b, n, m);
+    if (!p.ok)
+    {
+        set_error("nearest neighbours by layers: sizes do not fit shared memory (n=%d m=%d)", n, m);
+        return TPK_ERR_UNSUPPORTED;
+    }
+    auto kernel = k == 1 ? sg_nn_slab_kernel<1> : sg_nn_slab_kernel<3>;
+    prefer_max_shared(kernel);
+    if (p.smem > 48 * 1024)
+    {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(p.smem));
+        if (err != cudaSuccess)
+        {
+            set_error("nearest neighbours by layers: shared memory attribute: %s", cudaGetErrorString(err));
+            return TPK_ERR_CUDA;
+        }
+    }
+    const long long grid = static_cast<long long>(b) * p.parts;
+    TPK_REQUIRE(grid < (1ll << 31), "nearest neighbours: too many clouds");
+    count_launches(1), kernel<<<static_cast<unsigned>(grid), kSgThreads, p.smem, s>>>(n, m, p.parts, p.lpp, p.pad, p.qcap, p.max_dim,
+                                                                   p.cells_cap, p.slab_cells_cap, p.own_cells_cap, p.pcap,
+                                                                   unknown, known, dist2, idx, need);
+    return check_launch("nearest neighbours by layers");
+}
+
+namespace
+{
 struct SgBallPlan
 {
     int max_dim, cells_cap, slab_cells_cap, pcap, lpp, parts;
@@ -740,8 +960,10 @@ SgBallPlan sg_ball_plan(int b, int n, int m, int nsample)
         if (room > (1u << kSgSlotBits)) room = 1u << kSgSlotBits;
         if (want > room)
         {
-            if (lpp > 1) continue;
-            want = room;  // single layers: take what fits, crowded layers go to the scan
+            // single layers: take what fits (crowded layers go to the scan), unless even an
+            // average layer would not fit
+            if (lpp > 1 || static_cast<double>(n) * layers / max_dim > static_cast<double>(room)) continue;
+            want = room;
         }
         SgBallPlan p = {};
         p.max_dim = max_dim;
