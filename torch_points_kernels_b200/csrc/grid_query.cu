@@ -383,49 +383,55 @@ __global__ void __launch_bounds__(kGridQueryThreads)
                     }
                     if (xa > xb) continue;
                     const int beg = __ldg(cells + row + xa), end = __ldg(cells + row + xb + 1);
-                    // four candidates per step: the loads (L2) and distances are independent,
-                    // only the updates of the best list run in order
-                    for (int p = beg; p < end; p += 4)
+                    // Four candidates per step: the loads (L2) and distances are independent; a
+                    // candidate that cannot beat the K-th best (one compare) costs nothing more,
+                    // the others update the best list in order.
+                    auto consider = [&](float d, int k) {
+                        if (K == 1)
+                        {
+                            if (d < b1 || k < i1)  // reached only with d <= b1
+                            {
+                                b1 = d;
+                                i1 = k;
+                            }
+                        }
+                        else if (d < b3 || k < i3)  // reached only with d <= b3
+                        {
+                            if (d < b1 || (d == b1 && k < i1))
+                            {
+                                b3 = b2; i3 = i2;
+                                b2 = b1; i2 = i1;
+                                b1 = d;  i1 = k;
+                            }
+                            else if (d < b2 || (d == b2 && k < i2))
+                            {
+                                b3 = b2; i3 = i2;
+                                b2 = d;  i2 = k;
+                            }
+                            else
+                            {
+                                b3 = d; i3 = k;
+                            }
+                        }
+                    };
+                    int p = beg;
+                    for (; p + 4 <= end; p += 4)
                     {
+                        float4 c[4];
                         float d[4];
-                        int k[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) c[u] = __ldg(pts + p + u);
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) d[u] = sumsq_abc(qx - c[u].x, qy - c[u].y, qz - c[u].z);
 #pragma unroll
                         for (int u = 0; u < 4; ++u)
-                        {
-                            const float4 c = __ldg(pts + min(p + u, end - 1));
-                            d[u] = p + u < end ? sumsq_abc(qx - c.x, qy - c.y, qz - c.z) : CUDART_INF_F;
-                            k[u] = p + u < end ? __float_as_int(c.w) : 0x7fffffff;
-                        }
-#pragma unroll
-                        for (int u = 0; u < 4; ++u)
-                        {
-                            if (K == 1)
-                            {
-                                if (d[u] < b1 || (d[u] == b1 && k[u] < i1))
-                                {
-                                    b1 = d[u];
-                                    i1 = k[u];
-                                }
-                            }
-                            else if (d[u] < b3 || (d[u] == b3 && k[u] < i3))
-                            {
-                                if (d[u] < b1 || (d[u] == b1 && k[u] < i1))
-                                {
-                                    b3 = b2; i3 = i2;
-                                    b2 = b1; i2 = i1;
-                                    b1 = d[u]; i1 = k[u];
-                                }
-                                else if (d[u] < b2 || (d[u] == b2 && k[u] < i2))
-                                {
-                                    b3 = b2; i3 = i2;
-                                    b2 = d[u]; i2 = k[u];
-                                }
-                                else
-                                {
-                                    b3 = d[u]; i3 = k[u];
-                                }
-                            }
-                        }
+                            if (d[u] <= (K == 1 ? b1 : b3)) consider(d[u], __float_as_int(c[u].w));
+                    }
+                    for (; p < end; ++p)
+                    {
+                        const float4 c = __ldg(pts + p);
+                        const float d = sumsq_abc(qx - c.x, qy - c.y, qz - c.z);
+                        if (d <= (K == 1 ? b1 : b3)) consider(d, __float_as_int(c.w));
                     }
                 }
             }
