@@ -125,8 +125,8 @@ class Pipeline:
         fps_idx, fps_ready = [], []
         with torch.cuda.stream(s_fps):
             for l, m in enumerate(LEVELS["npoint"]):
-                idx = timed("fps_l%d" % (l + 1), lambda: tpk.furthest_point_sample(pts[l], m))
-                centres = torch.gather(pts[l], 1, idx.long().unsqueeze(-1).expand(-1, -1, 3)).contiguous()
+                # indices and the sampled coordinates from the same kernel (no gather pass)
+                idx, centres = timed("fps_l%d" % (l + 1), lambda: tpk.furthest_point_sample(pts[l], m, return_xyz=True))
                 fps_idx.append(hand_over(idx, cur))
                 pts.append(hand_over(centres, s_geo))
                 ev = torch.cuda.Event()
@@ -175,6 +175,12 @@ class Pipeline:
         return fps_idx, grads_sa, grads_fp, done
 
 
+def checksums(tensors):
+    """One number per gradient tensor for the device-to-host result of a step: the L2 norms,
+    computed for all tensors by one multi-tensor kernel."""
+    return torch.stack(torch._foreach_norm(list(tensors)))
+
+
 def _lib_launches():
     from torch_points_kernels_b200 import _lib
 
@@ -197,7 +203,7 @@ class GraphedSteps:
             try:
                 with torch.cuda.graph(graph, stream=launch, capture_error_mode="thread_local"):
                     fps_idx, g_sa, g_fp, _ = pipe.step(*split([t.detach() for t in ins]))
-                    chk = torch.stack([g.sum() for g in g_sa + g_fp])
+                    chk = checksums(g_sa + g_fp)
             finally:
                 keep, pipe.keep = pipe.keep, None
             # kernels of the library in one step: counted by the library while the step was captured
@@ -434,7 +440,7 @@ def run_b200(args, rank, world, local_rank):
                 pipe.s_feat.wait_stream(pipe.s_fps)
                 for src, dst in zip(fps_idx, bufs[:4]):
                     dst.copy_(src, non_blocking=True)
-                chk = torch.stack([g.sum() for g in g_sa + g_fp])
+                chk = checksums(g_sa + g_fp)
                 bufs[4].copy_(chk, non_blocking=True)
                 done = torch.cuda.Event()
                 done.record(pipe.s_feat)

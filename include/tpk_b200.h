@@ -71,12 +71,21 @@ TPK_API int64_t tpk_kernel_launches(void);
  * (kernel cuda/src/sampling_gpu.cu:16-144), including the zero/1e10 fills of
  * cuda/src/sampling.cpp:14-18.
  *
- * scratch: tpk_fps_scratch_bytes(b,n,m) bytes of device memory, or NULL when that
- * function returns 0 (clouds small enough to keep the running min-distance array
- * on chip).  Content on entry is irrelevant.
+ * scratch: tpk_fps_scratch_bytes(b,n,m) bytes of device memory (16-byte aligned).  Required
+ * for clouds of more than 131072 points (sorted copy + running minima); optional below, where
+ * it holds a spatially sorted copy that lets most warps skip most rounds (NULL: the kernel
+ * without it, same result).  Content on entry is irrelevant.
  */
 TPK_API int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz, void* scratch,
                                 int32_t* idxs, void* stream);
+
+/*
+ * The same, also writing the coordinates of the samples: new_xyz (b,m,3) f32, i.e.
+ * xyz[b, idxs[b, j], :] (what callers otherwise gather from idxs in a second pass); NULL
+ * skips it.  No counterpart in the reference.
+ */
+TPK_API int tpk_furthest_point_sampling_xyz(int b, int n, int m, const float* xyz, void* scratch,
+                                    int32_t* idxs, float* new_xyz, void* stream);
 TPK_API int64_t tpk_fps_scratch_bytes(int b, int n, int m);
 
 /*

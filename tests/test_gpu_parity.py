@@ -170,6 +170,23 @@ def test_fps_scratch_kernel_tie_break_and_skip_rule(n, sorted_copy, monkeypatch)
     np.testing.assert_array_equal(npy(tpk.furthest_point_sample(cu(x), mm)), orc.fps(x, mm))
 
 
+@pytest.mark.parametrize("B,N,m,env", [(3, 1000, 200, None), (2, 16384, 700, None), (2, 16384, 700, "TPK_FPS_SORTED"),
+                                       (1, 150000, 40, None), (1, 150000, 40, "TPK_FPS_SORTED"), (4, 257, 257, None)])
+def test_fps_returns_sampled_coordinates(B, N, m, env, monkeypatch):
+    """return_xyz: the kernels write xyz[idx] themselves (every kernel variant)."""
+    if env:
+        monkeypatch.setenv(env, "0")
+    x = cu(data.unit_ball(B, N, seed=2100 + N))
+    idx, centres = tpk.furthest_point_sample(x, m, return_xyz=True)
+    np.testing.assert_array_equal(npy(idx), npy(tpk.furthest_point_sample(x, m)))
+    want = torch.gather(x, 1, idx.long().unsqueeze(-1).expand(-1, -1, 3))
+    same_bits(npy(centres), npy(want))
+    # no candidate at all: every sample is point 0
+    tiny = cu(np.full((2, 40, 3), 0.001, np.float32))
+    idx, centres = tpk.furthest_point_sample(tiny, 7, return_xyz=True)
+    assert (npy(idx) == 0).all() and (npy(centres) == np.float32(0.001)).all()
+
+
 def test_fps_all_points_skipped():
     tiny = np.full((2, 40, 3), 0.001, np.float32)
     assert npy(tpk.furthest_point_sample(cu(tiny), 7)).tolist() == [[0] * 7] * 2

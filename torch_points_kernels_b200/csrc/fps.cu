@@ -212,7 +212,8 @@ __device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigne
 template <int PPT, bool CLUSTERED, bool SORTED>
 __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
     fps_onchip_kernel(int n, int m, int log2bs, int flat, const float* __restrict__ xyz_all,
-                      const float4* __restrict__ sorted_all, int32_t* __restrict__ idxs_all)
+                      const float4* __restrict__ sorted_all, int32_t* __restrict__ idxs_all,
+                      float* __restrict__ new_xyz_all)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -324,7 +325,18 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
         cy = __ldg(xyz + 1);
         cz = __ldg(xyz + 2);
     }
-    if (gtid == 0 && m > 0) idxs[0] = 0;
+    // optional second output: the coordinates of the samples, (m, 3) per cloud
+    float* new_xyz = new_xyz_all ? new_xyz_all + static_cast<size_t>(cloud) * m * 3 : nullptr;
+    if (gtid == 0 && m > 0)
+    {
+        idxs[0] = 0;
+        if (new_xyz)
+        {
+            new_xyz[0] = __ldg(xyz + 0);
+            new_xyz[1] = __ldg(xyz + 1);
+            new_xyz[2] = __ldg(xyz + 2);
+        }
+    }
 
     if (CLUSTERED)
     {
@@ -542,7 +554,17 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
         cx = msg.x;
         cy = msg.y;
         cz = msg.z;
-        if (gtid == 0) idxs[j] = msg.key >= 0 ? msg.k : 0;
+        if (gtid == 0)
+        {
+            const bool found = msg.key >= 0;  // otherwise index 0, as the reference's arg-max leaves it
+            idxs[j] = found ? msg.k : 0;
+            if (new_xyz)
+            {
+                new_xyz[3 * j + 0] = found ? msg.x : __ldg(xyz + 0);
+                new_xyz[3 * j + 1] = found ? msg.y : __ldg(xyz + 1);
+                new_xyz[3 * j + 2] = found ? msg.z : __ldg(xyz + 2);
+            }
+        }
     };
 
     int j = 1;
@@ -737,7 +759,8 @@ constexpr int kFpsBigThreads = 512;
 
 __global__ void __launch_bounds__(kFpsBigThreads, 1)
     fps_global_kernel(int n, int m, int log2bs, const float* __restrict__ xyz_all,
-                      float* __restrict__ temp_all, int32_t* __restrict__ idxs_all)
+                      float* __restrict__ temp_all, int32_t* __restrict__ idxs_all,
+                      float* __restrict__ new_xyz_all)
 {
     __shared__ __align__(16) uint4 wmsg_a[64];
     __shared__ __align__(16) uint4 cmsg_a[64];
@@ -768,7 +791,18 @@ __global__ void __launch_bounds__(kFpsBigThreads, 1)
     }
 
     float cx = __ldg(xyz + 0), cy = __ldg(xyz + 1), cz = __ldg(xyz + 2);
-    if (gtid == 0 && m > 0) idxs[0] = 0;
+    // optional second output: the coordinates of the samples, (m, 3) per cloud
+    float* new_xyz = new_xyz_all ? new_xyz_all + static_cast<size_t>(cloud) * m * 3 : nullptr;
+    if (gtid == 0 && m > 0)
+    {
+        idxs[0] = 0;
+        if (new_xyz)
+        {
+            new_xyz[0] = __ldg(xyz + 0);
+            new_xyz[1] = __ldg(xyz + 1);
+            new_xyz[2] = __ldg(xyz + 2);
+        }
+    }
     if (tid == 0)
     {
         mbar_init(smem_u32(mbar + 0), 1);
@@ -907,7 +941,17 @@ __global__ void __launch_bounds__(kFpsBigThreads, 1)
         cx = msg.x;
         cy = msg.y;
         cz = msg.z;
-        if (gtid == 0) idxs[j] = msg.key >= 0 ? msg.k : 0;
+        if (gtid == 0)
+        {
+            const bool found = msg.key >= 0;  // otherwise index 0, as the reference's arg-max leaves it
+            idxs[j] = found ? msg.k : 0;
+            if (new_xyz)
+            {
+                new_xyz[3 * j + 0] = found ? msg.x : __ldg(xyz + 0);
+                new_xyz[3 * j + 1] = found ? msg.y : __ldg(xyz + 1);
+                new_xyz[3 * j + 2] = found ? msg.z : __ldg(xyz + 2);
+            }
+        }
     }
     cluster_sync_all();
 }
@@ -928,7 +972,7 @@ template <int CPL>  // chunks per lane: a warp owns 32 * CPL chunks
 __global__ void __launch_bounds__(kFpsBigThreads, 1)
     fps_pruned_kernel(int n, int m, int log2bs, const float* __restrict__ xyz_all,
                       const float4* __restrict__ sorted_all, float* __restrict__ temp_all,
-                      int32_t* __restrict__ idxs_all)
+                      int32_t* __restrict__ idxs_all, float* __restrict__ new_xyz_all)
 {
     __shared__ __align__(16) uint4 wmsg_a[64];
     __shared__ __align__(16) uint4 cmsg_a[64];
@@ -1019,7 +1063,18 @@ __global__ void __launch_bounds__(kFpsBigThreads, 1)
     }
 
     float cx = __ldg(xyz + 0), cy = __ldg(xyz + 1), cz = __ldg(xyz + 2);
-    if (gtid == 0 && m > 0) idxs[0] = 0;
+    // optional second output: the coordinates of the samples, (m, 3) per cloud
+    float* new_xyz = new_xyz_all ? new_xyz_all + static_cast<size_t>(cloud) * m * 3 : nullptr;
+    if (gtid == 0 && m > 0)
+    {
+        idxs[0] = 0;
+        if (new_xyz)
+        {
+            new_xyz[0] = __ldg(xyz + 0);
+            new_xyz[1] = __ldg(xyz + 1);
+            new_xyz[2] = __ldg(xyz + 2);
+        }
+    }
     if (tid == 0)
     {
         mbar_init(smem_u32(mbar + 0), 1);
@@ -1218,13 +1273,23 @@ __global__ void __launch_bounds__(kFpsBigThreads, 1)
         cx = msg.x;
         cy = msg.y;
         cz = msg.z;
-        if (gtid == 0) idxs[j] = msg.key >= 0 ? msg.k : 0;
+        if (gtid == 0)
+        {
+            const bool found = msg.key >= 0;  // otherwise index 0, as the reference's arg-max leaves it
+            idxs[j] = found ? msg.k : 0;
+            if (new_xyz)
+            {
+                new_xyz[3 * j + 0] = found ? msg.x : __ldg(xyz + 0);
+                new_xyz[3 * j + 1] = found ? msg.y : __ldg(xyz + 1);
+                new_xyz[3 * j + 2] = found ? msg.z : __ldg(xyz + 2);
+            }
+        }
     }
     cluster_sync_all();
 }
 
 int fps_launch_global(int b, int n, int m, int log2bs, const float* xyz, float* temp,
-                      int32_t* idxs, cudaStream_t stream)
+                      int32_t* idxs, float* new_xyz, cudaStream_t stream)
 {
     auto kernel = fps_global_kernel;
     prefer_max_shared(kernel);
@@ -1247,7 +1312,7 @@ int fps_launch_global(int b, int n, int m, int log2bs, const float* xyz, float* 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     count_launches(1);
-    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, xyz, temp, idxs);
+    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, xyz, temp, idxs, new_xyz);
     if (err != cudaSuccess)
     {
         set_error("fps launch (large clouds): %s", cudaGetErrorString(err));
@@ -1261,7 +1326,7 @@ constexpr long long kFpsPrunedMaxPoints = 256ll * 32 * 4 * kFpsChunk;
 
 template <int CPL>
 int fps_launch_pruned_t(int b, int n, int m, int log2bs, const float* xyz, const float4* sorted, float* temp,
-                        int32_t* idxs, cudaStream_t stream)
+                        int32_t* idxs, float* new_xyz, cudaStream_t stream)
 {
     auto kernel = fps_pruned_kernel<CPL>;
     prefer_max_shared(kernel);
@@ -1284,7 +1349,7 @@ int fps_launch_pruned_t(int b, int n, int m, int log2bs, const float* xyz, const
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     count_launches(1);
-    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, xyz, sorted, temp, idxs);
+    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, xyz, sorted, temp, idxs, new_xyz);
     if (err != cudaSuccess)
     {
         set_error("fps launch (large clouds, sorted): %s", cudaGetErrorString(err));
@@ -1295,16 +1360,16 @@ int fps_launch_pruned_t(int b, int n, int m, int log2bs, const float* xyz, const
 
 // scratch: the sorted copy (16 bytes per point), then the running minima (4 bytes per point)
 int fps_launch_pruned(int b, int n, int m, int log2bs, const float* xyz, void* scratch, int32_t* idxs,
-                      cudaStream_t stream)
+                      float* new_xyz, cudaStream_t stream)
 {
     float4* sorted = static_cast<float4*>(scratch);
     float* temp = reinterpret_cast<float*>(sorted + static_cast<size_t>(b) * n);
     const int rc = fps_launch_sort(b, n, xyz, sorted, stream);
     if (rc != TPK_OK) return rc;
     const long long per_lane = (static_cast<long long>(n) + 256ll * 32 * kFpsChunk - 1) / (256ll * 32 * kFpsChunk);
-    if (per_lane <= 1) return fps_launch_pruned_t<1>(b, n, m, log2bs, xyz, sorted, temp, idxs, stream);
-    if (per_lane <= 2) return fps_launch_pruned_t<2>(b, n, m, log2bs, xyz, sorted, temp, idxs, stream);
-    return fps_launch_pruned_t<4>(b, n, m, log2bs, xyz, sorted, temp, idxs, stream);
+    if (per_lane <= 1) return fps_launch_pruned_t<1>(b, n, m, log2bs, xyz, sorted, temp, idxs, new_xyz, stream);
+    if (per_lane <= 2) return fps_launch_pruned_t<2>(b, n, m, log2bs, xyz, sorted, temp, idxs, new_xyz, stream);
+    return fps_launch_pruned_t<4>(b, n, m, log2bs, xyz, sorted, temp, idxs, new_xyz, stream);
 }
 
 struct FpsConfig
@@ -1376,7 +1441,7 @@ bool fps_pick_config(int n, int m, FpsConfig* out)
 
 template <int PPT, bool CLUSTERED, bool SORTED>
 int fps_launch_t(const FpsConfig& c, int b, int n, int m, int log2bs, const float* xyz,
-                 const float4* sorted, int32_t* idxs, cudaStream_t stream)
+                 const float4* sorted, int32_t* idxs, float* new_xyz, cudaStream_t stream)
 {
     auto kernel = fps_onchip_kernel<PPT, CLUSTERED, SORTED>;
     prefer_max_shared(kernel);
@@ -1418,7 +1483,7 @@ int fps_launch_t(const FpsConfig& c, int b, int n, int m, int log2bs, const floa
     const char* flat_env = getenv("TPK_FPS_FLAT");
     const int flat = (c.nranks > 1 && c.nranks * (c.nthreads / 32) <= 32 && !(flat_env && flat_env[0] == '0')) ? 1 : 0;
     count_launches(1);
-    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, flat, xyz, sorted, idxs);
+    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, flat, xyz, sorted, idxs, new_xyz);
     if (err != cudaSuccess)
     {
         set_error("fps launch (cluster %d x %d threads x %d points): %s", c.nranks, c.nthreads,
@@ -1430,16 +1495,16 @@ int fps_launch_t(const FpsConfig& c, int b, int n, int m, int log2bs, const floa
 
 template <bool CLUSTERED, bool SORTED>
 int fps_launch_s(const FpsConfig& c, int b, int n, int m, int log2bs, const float* xyz,
-                 const float4* sorted, int32_t* idxs, cudaStream_t stream)
+                 const float4* sorted, int32_t* idxs, float* new_xyz, cudaStream_t stream)
 {
     switch (c.ppt)
     {
-    case 1: return fps_launch_t<1, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
-    case 2: return fps_launch_t<2, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
-    case 4: return fps_launch_t<4, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
-    case 8: return fps_launch_t<8, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
-    case 16: return fps_launch_t<16, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
-    case 32: return fps_launch_t<32, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
+    case 1: return fps_launch_t<1, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, new_xyz, stream);
+    case 2: return fps_launch_t<2, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, new_xyz, stream);
+    case 4: return fps_launch_t<4, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, new_xyz, stream);
+    case 8: return fps_launch_t<8, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, new_xyz, stream);
+    case 16: return fps_launch_t<16, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, new_xyz, stream);
+    case 32: return fps_launch_t<32, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, new_xyz, stream);
     default: break;
     }
     set_error("fps: unsupported points per thread %d", c.ppt);
@@ -1475,8 +1540,8 @@ extern "C" int64_t tpk_fps_scratch_bytes(int b, int n, int m)
     return static_cast<int64_t>(b) * n * (fps_large_sorted(n) ? 20 : 4);
 }
 
-extern "C" int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz, void* scratch,
-                                           int32_t* idxs, void* stream)
+extern "C" int tpk_furthest_point_sampling_xyz(int b, int n, int m, const float* xyz, void* scratch,
+                                               int32_t* idxs, float* new_xyz, void* stream)
 {
     using namespace tpk;
     TPK_REQUIRE(b >= 0 && n >= 0 && m >= 0, "fps: negative size (b=%d n=%d m=%d)", b, n, m);
@@ -1499,20 +1564,26 @@ extern "C" int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz
         if (fps_large_sorted(n))
         {
             TPK_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 15u) == 0, "fps: scratch must be 16-byte aligned");
-            return fps_launch_pruned(b, n, m, log2bs, xyz, scratch, idxs, s);
+            return fps_launch_pruned(b, n, m, log2bs, xyz, scratch, idxs, new_xyz, s);
         }
-        return fps_launch_global(b, n, m, log2bs, xyz, static_cast<float*>(scratch), idxs, s);
+        return fps_launch_global(b, n, m, log2bs, xyz, static_cast<float*>(scratch), idxs, new_xyz, s);
     }
     if (scratch != nullptr && fps_wants_sorted(n, m) && (reinterpret_cast<uintptr_t>(scratch) & 15u) == 0)
     {
         float4* sorted = static_cast<float4*>(scratch);
         const int rc = fps_launch_sort(b, n, xyz, sorted, s);
         if (rc != TPK_OK) return rc;
-        return c.nranks > 1 ? fps_launch_s<true, true>(c, b, n, m, log2bs, xyz, sorted, idxs, s)
-                            : fps_launch_s<false, true>(c, b, n, m, log2bs, xyz, sorted, idxs, s);
+        return c.nranks > 1 ? fps_launch_s<true, true>(c, b, n, m, log2bs, xyz, sorted, idxs, new_xyz, s)
+                            : fps_launch_s<false, true>(c, b, n, m, log2bs, xyz, sorted, idxs, new_xyz, s);
     }
-    return c.nranks > 1 ? fps_launch_s<true, false>(c, b, n, m, log2bs, xyz, nullptr, idxs, s)
-                        : fps_launch_s<false, false>(c, b, n, m, log2bs, xyz, nullptr, idxs, s);
+    return c.nranks > 1 ? fps_launch_s<true, false>(c, b, n, m, log2bs, xyz, nullptr, idxs, new_xyz, s)
+                        : fps_launch_s<false, false>(c, b, n, m, log2bs, xyz, nullptr, idxs, new_xyz, s);
+}
+
+extern "C" int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz, void* scratch,
+                                           int32_t* idxs, void* stream)
+{
+    return tpk_furthest_point_sampling_xyz(b, n, m, xyz, scratch, idxs, nullptr, stream);
 }
 
 // ------------------------------------------------------------- entry point without scratch
@@ -1571,7 +1642,7 @@ extern "C" int tpk_furthest_point_sampling_static(int b, int n, int m, const flo
     if (log2bs > 9) log2bs = 9;
     // the kernel writes every scratch element it later reads (its first pass sets the
     // running minima), so whatever an earlier call left behind is irrelevant
-    return fps_launch_global(b, n, m, log2bs, xyz, scratch, idxs, static_cast<cudaStream_t>(stream));
+    return fps_launch_global(b, n, m, log2bs, xyz, scratch, idxs, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int tpk_device_status(int* status_out, int reset)

@@ -25,7 +25,7 @@ def _f32(t, name):
     return t
 
 
-def furthest_point_sample(xyz, npoint):
+def furthest_point_sample(xyz, npoint, return_xyz=False):
     r"""
     Iterative furthest point sampling (reference: torchpoints.py:14-37,
     cuda/src/sampling.cpp:8-25).
@@ -36,17 +36,23 @@ def furthest_point_sample(xyz, npoint):
         (B, N, 3) float32 CUDA tensor where N >= npoint
     npoint : int
         number of points in the sampled set
+    return_xyz : bool
+        also return the coordinates of the samples, (B, npoint, 3): the same values as
+        ``xyz.gather(1, idx.long()[..., None].expand(-1, -1, 3))``, written by the sampling
+        kernel itself (an addition to the reference's signature)
 
     Returns
     -------
     torch.Tensor
         (B, npoint) int32 tensor of indices; the first one is always 0
+        (with ``return_xyz``: the tuple (indices, coordinates))
     """
     if npoint > xyz.shape[1]:
         raise ValueError("caanot sample %i points from an input set of %i points" % (npoint, xyz.shape[1]))
     _f32(xyz, "points")
     b, n = xyz.shape[0], xyz.shape[1]
     out = torch.empty((b, npoint), dtype=torch.int32, device=xyz.device)
+    new_xyz = torch.empty((b, npoint, 3), dtype=torch.float32, device=xyz.device) if return_xyz else None
     scratch = None
     with torch.cuda.device(xyz.device):
         need = _lib.lib().tpk_fps_scratch_bytes(b, n, npoint)
@@ -54,9 +60,9 @@ def furthest_point_sample(xyz, npoint):
             raise RuntimeError("furthest_point_sample: clouds of %d points are not supported" % n)
         if need > 0:
             scratch = torch.empty((need,), dtype=torch.uint8, device=xyz.device)
-        _lib.call("tpk_furthest_point_sampling", b, n, npoint, _lib.ptr(xyz), _lib.ptr(scratch),
-                  _lib.ptr(out), _lib.stream_of(xyz))
-    return out
+        _lib.call("tpk_furthest_point_sampling_xyz", b, n, npoint, _lib.ptr(xyz), _lib.ptr(scratch),
+                  _lib.ptr(out), _lib.ptr(new_xyz), _lib.stream_of(xyz))
+    return (out, new_xyz) if return_xyz else out
 
 
 def three_nn(unknown, known):
