@@ -154,6 +154,20 @@ TPK_API int tpk_ball_query_partial_dense(int64_t size_x, int64_t size_y, float r
                                  const float* x, const float* y, const int64_t* batch_x,
                                  const int64_t* batch_y, int64_t* idx, float* dist, void* stream);
 
+/*
+ * The packed query with caller scratch: points are binned on a hashed uniform grid (cells one
+ * radius wide, keyed by segment and cell) and a query looks at the 27 cells around it;
+ * results are identical to tpk_ball_query_partial_dense bit for bit.  scratch:
+ * tpk_ball_query_partial_dense_scratch_bytes(size_x,size_y,radius) bytes, 256-byte aligned;
+ * when that returns 0 (fewer than 4096 points) or scratch is NULL the call is the plain one.
+ * No counterpart in the reference.
+ */
+TPK_API int tpk_ball_query_partial_dense_ws(int64_t size_x, int64_t size_y, float radius, int nsample,
+                                            const float* x, const float* y, const int64_t* batch_x,
+                                            const int64_t* batch_y, int64_t* idx, float* dist, void* scratch,
+                                            int64_t scratch_bytes, void* stream);
+TPK_API int64_t tpk_ball_query_partial_dense_scratch_bytes(int64_t size_x, int64_t size_y, float radius);
+
 /* ---------------------------------------------------------- nearest neighbours ---- */
 
 /*

@@ -67,6 +67,10 @@ def test_scratch_sizes_are_host_arithmetic(monkeypatch):
     assert l.tpk_ball_query_dense_scratch_bytes(2, 256, 64, 32) == 0
     assert l.tpk_ball_query_dense_scratch_bytes(16, 16384, 4096, 32) == 16 * 4096
     assert l.tpk_ball_query_dense_scratch_bytes(2, 300000, 100, 32) > 2 * 300000 * 16
+    # packed ball query: buckets, sorted copy (20 B/point) and one flag per query from 4096 points on
+    assert l.tpk_ball_query_partial_dense_scratch_bytes(1000, 100, 0.1) == 0
+    assert l.tpk_ball_query_partial_dense_scratch_bytes(100000, 5000, 0.1) > 100000 * 20 + 5000
+    assert l.tpk_ball_query_partial_dense_scratch_bytes(100000, 5000, 0.0) == 0
     # three_nn: one flag per unknown point (grid in shared memory), the whole grid for huge known clouds
     assert l.tpk_three_nn_scratch_bytes(2, 256, 64) == 0
     assert l.tpk_three_nn_scratch_bytes(16, 16384, 4096) == 16 * 16384

@@ -330,6 +330,50 @@ def test_ball_query_partial_scene_scale():
     same_bits(npy(d2), od)
 
 
+@pytest.mark.parametrize("case", ["scenes", "crowded", "overlapping_segments", "nonfinite", "far_offsets", "ns1"])
+def test_ball_query_partial_hash_grid_matches_oracle_and_scan(case, monkeypatch):
+    """4096+ packed points go through the hashed grid: same indices and distance bits as the
+    oracle and as the scan of the segments, also for queries the grid hands back (crowded
+    neighbourhoods, non-finite coordinates, coordinates so large that a cell is thinner than their rounding)."""
+    rng = np.random.default_rng(len(case))
+    r, ns = 0.05, 64
+    if case == "scenes":
+        x, y, bx, by = data.packed_planes(n_scenes=6, lo=3000, hi=12000, seed=3002)
+    elif case == "crowded":
+        # hundreds of points inside one ball: more hits than the buffer takes
+        sizes, qsizes = [5000, 3000], [400, 300]
+        x = torch.from_numpy(np.concatenate([rng.normal(0, 0.03, (s, 3)) for s in sizes]).astype(np.float32))
+        y = torch.from_numpy(np.concatenate([rng.normal(0, 0.03, (s, 3)) for s in qsizes]).astype(np.float32))
+        bx = torch.cat([torch.full((s,), i, dtype=torch.long) for i, s in enumerate(sizes)])
+        by = torch.cat([torch.full((s,), i, dtype=torch.long) for i, s in enumerate(qsizes)])
+    else:
+        # every segment fills the same unit cube: neighbours must come from the query's own segment only
+        sizes, qsizes = [3000, 1, 4000, 0, 2500], [200, 3, 300, 5, 0]
+        x = torch.from_numpy(rng.uniform(0, 1, (sum(sizes), 3)).astype(np.float32))
+        y = torch.from_numpy(rng.uniform(0, 1, (sum(qsizes), 3)).astype(np.float32))
+        bx = torch.cat([torch.full((s,), i, dtype=torch.long) for i, s in enumerate(sizes)])
+        by = torch.cat([torch.full((s,), i, dtype=torch.long) for i, s in enumerate(qsizes)])
+        r = 0.08
+        if case == "nonfinite":
+            x[17, 0] = float("inf")
+            x[5000, 2] = float("nan")
+            y[3, 1] = float("nan")
+            y[250, 0] = float("-inf")
+        if case == "far_offsets":
+            x = x + 30000.0
+            y = y + 30000.0
+        if case == "ns1":
+            ns = 1
+    assert _lib.lib().tpk_ball_query_partial_dense_scratch_bytes(x.shape[0], y.shape[0], r) > 0
+    oi, od = orc.ball_query_partial(r, ns, x, y, bx, by)
+    for env in (None, "TPK_BALL_QUERY_SCAN"):
+        if env:
+            monkeypatch.setenv(env, "1")
+        idx, d2 = tpk.ball_query(r, ns, cu(x), cu(y), mode="partial_dense", batch_x=cu(bx), batch_y=cu(by))
+        np.testing.assert_array_equal(npy(idx), oi)
+        same_bits(npy(d2), od)
+
+
 # ------------------------------------------------------------------ three_nn and kNN
 
 @pytest.mark.parametrize("B,n,m", [(4, 4096, 1024), (2, 1000, 2000), (3, 77, 3), (2, 10, 2), (2, 5, 1), (16, 256, 64),

@@ -27,6 +27,8 @@ _SIGNATURES = {
     "tpk_ball_query_dense": [_c_int, _c_int, _c_int, _c_f32, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_ball_query_dense_ws": [_c_int, _c_int, _c_int, _c_f32, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr],
     "tpk_ball_query_partial_dense": [_c_i64, _c_i64, _c_f32, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
+    "tpk_ball_query_partial_dense_ws": [_c_i64, _c_i64, _c_f32, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr,
+                                        _c_i64, _ptr],
     "tpk_three_nn": [_c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_chamfer_dist_f32_ws": [_c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr],
     "tpk_three_nn_ws": [_c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr],
@@ -44,7 +46,8 @@ _SIGNATURES = {
 
 EXPORTS = sorted(list(_SIGNATURES) + ["tpk_version", "tpk_last_error", "tpk_device_status", "tpk_kernel_launches", "tpk_fps_scratch_bytes",
                                        "tpk_fps_static_capacity", "tpk_ball_query_dense_scratch_bytes",
-                                       "tpk_three_nn_scratch_bytes", "tpk_chamfer_dist_scratch_bytes"])
+                                       "tpk_three_nn_scratch_bytes", "tpk_chamfer_dist_scratch_bytes",
+                                       "tpk_ball_query_partial_dense_scratch_bytes"])
 
 
 def lib():
@@ -72,6 +75,8 @@ def lib():
         handle.tpk_fps_scratch_bytes.restype = _c_i64
         handle.tpk_ball_query_dense_scratch_bytes.argtypes = [_c_int, _c_int, _c_int, _c_int]
         handle.tpk_ball_query_dense_scratch_bytes.restype = _c_i64
+        handle.tpk_ball_query_partial_dense_scratch_bytes.argtypes = [_c_i64, _c_i64, _c_f32]
+        handle.tpk_ball_query_partial_dense_scratch_bytes.restype = _c_i64
         handle.tpk_chamfer_dist_scratch_bytes.argtypes = [_c_int, _c_int, _c_int]
         handle.tpk_chamfer_dist_scratch_bytes.restype = _c_i64
         handle.tpk_three_nn_scratch_bytes.argtypes = [_c_int, _c_int, _c_int]

@@ -21,6 +21,12 @@ size_t grid_scratch_bytes(int b, int n, int m);
 int grid_ball_query_dense(int b, int n, int m, float radius, int nsample, const float* new_xyz,
                           const float* xyz, int64_t* idx, float* dist, void* scratch,
                           const unsigned char** need_scan_out, cudaStream_t s);
+// hash_grid.cu
+bool hash_grid_fits(long long size_x, long long size_y);
+size_t hash_grid_scratch_bytes(long long size_x, long long size_y);
+int hash_grid_ball_query(long long size_x, long long size_y, float radius, int nsample, const float* x, const float* y,
+                         const int64_t* batch_x, const int64_t* batch_y, int64_t* idx, float* dist, void* scratch,
+                         const unsigned char** need_out, cudaStream_t s);
 // smem_grid.cu
 bool sg_ball_query_fits(int b, int n, int nsample);
 int sg_ball_query(int b, int n, int m, float radius, int nsample, const float* new_xyz, const float* xyz,
@@ -134,7 +140,7 @@ __global__ void __launch_bounds__(THREADS)
                               const float* __restrict__ x, const float* __restrict__ y,
                               const int64_t* __restrict__ batch_x,
                               const int64_t* __restrict__ batch_y, int64_t* __restrict__ idx_out,
-                              float* __restrict__ dist_out)
+                              float* __restrict__ dist_out, const unsigned char* __restrict__ need)
 {
     __shared__ __align__(16) float smem[2 * kScanTileFloats];
     __shared__ long long s_range[2];
@@ -150,7 +156,8 @@ __global__ void __launch_bounds__(THREADS)
     for (int q = 0; q < Q; ++q)
     {
         const long long j = j0 + q * THREADS + threadIdx.x;
-        valid[q] = j < size_y;
+        // `need` (optional): one byte per centre, 0 = already answered by the grid path
+        valid[q] = j < size_y && (need == nullptr || need[j] != 0);
         const long long row = valid[q] ? j : 0;
         seg[q] = valid[q] ? __ldg(batch_y + row) : 0;
         op.cnt[q] = 0;
@@ -162,8 +169,21 @@ __global__ void __launch_bounds__(THREADS)
         op.drow[q] = dist_out + row * nsample;
     }
 
-    // sorted ids: the CTA's first centre carries its smallest segment id
-    int64_t cur = __ldg(batch_y + j0);
+    // sorted ids: the CTA's first centre still to be answered carries its smallest segment id
+    long long first_valid = 0x7fffffffffffffffll;
+#pragma unroll
+    for (int q = 0; q < Q; ++q)
+        if (valid[q]) first_valid = min(first_valid, j0 + q * THREADS + static_cast<long long>(threadIdx.x));
+    {
+        __shared__ unsigned long long s_first;
+        if (threadIdx.x == 0) s_first = ~0ull;
+        __syncthreads();
+        if (first_valid != 0x7fffffffffffffffll) atomicMin(&s_first, static_cast<unsigned long long>(first_valid));
+        __syncthreads();
+        if (s_first == ~0ull) return;  // nothing left over for this CTA
+        first_valid = static_cast<long long>(s_first);
+    }
+    int64_t cur = __ldg(batch_y + first_valid);
     const unsigned long long kNone = ~0ull;
     while (true)
     {
@@ -319,6 +339,20 @@ extern "C" int tpk_ball_query_dense_ws(int b, int n, int m, float radius, int ns
     return check_launch("ball_query_dense");
 }
 
+static int launch_partial_scan(long long size_x, long long size_y, float radius, int nsample, const float* x,
+                               const float* y, const int64_t* batch_x, const int64_t* batch_y, int64_t* idx,
+                               float* dist, const unsigned char* need, cudaStream_t s)
+{
+    using namespace tpk;
+    int threads, q;
+    pick_shape(size_y, &threads, &q);
+    const long long grid = (size_y + threads * q - 1) / (threads * q);
+    TPK_REQUIRE(grid < (1ll << 31), "ball_query_partial_dense: too many centres");
+    const dim3 g(static_cast<unsigned>(grid));
+    TPK_BQ_DISPATCH(ball_query_partial_kernel, size_x, size_y, radius, nsample, x, y, batch_x, batch_y, idx, dist, need);
+    return check_launch("ball_query_partial_dense");
+}
+
 extern "C" int tpk_ball_query_partial_dense(int64_t size_x, int64_t size_y, float radius,
                                             int nsample, const float* x, const float* y,
                                             const int64_t* batch_x, const int64_t* batch_y,
@@ -330,12 +364,44 @@ extern "C" int tpk_ball_query_partial_dense(int64_t size_x, int64_t size_y, floa
     if (size_y == 0 || nsample == 0) return TPK_OK;
     TPK_REQUIRE(y && batch_y && idx && dist && ((x && batch_x) || size_x == 0),
                 "ball_query_partial_dense: NULL pointer");
+    return launch_partial_scan(size_x, size_y, radius, nsample, x, y, batch_x, batch_y, idx, dist, nullptr,
+                               static_cast<cudaStream_t>(stream));
+}
+
+// TPK_BALL_QUERY_SCAN keeps packed queries on the scan (comparison runs and tests)
+static bool partial_wants_grid(int64_t size_x, int64_t size_y, float radius)
+{
+    return tpk::hash_grid_fits(size_x, size_y) && radius > 0.f && radius < 1.0e18f &&
+           getenv("TPK_BALL_QUERY_SCAN") == nullptr;
+}
+
+extern "C" int64_t tpk_ball_query_partial_dense_scratch_bytes(int64_t size_x, int64_t size_y, float radius)
+{
+    if (!partial_wants_grid(size_x, size_y, radius)) return 0;
+    return static_cast<int64_t>(tpk::hash_grid_scratch_bytes(size_x, size_y));
+}
+
+extern "C" int tpk_ball_query_partial_dense_ws(int64_t size_x, int64_t size_y, float radius, int nsample,
+                                               const float* x, const float* y, const int64_t* batch_x,
+                                               const int64_t* batch_y, int64_t* idx, float* dist, void* scratch,
+                                               int64_t scratch_bytes, void* stream)
+{
+    using namespace tpk;
+    const int64_t want = tpk_ball_query_partial_dense_scratch_bytes(size_x, size_y, radius);
+    if (want == 0 || scratch == nullptr || nsample <= 0)
+        return tpk_ball_query_partial_dense(size_x, size_y, radius, nsample, x, y, batch_x, batch_y, idx, dist, stream);
+    if (scratch_bytes < want)
+    {
+        set_error("ball_query_partial_dense: scratch of %lld bytes given, %lld needed",
+                  static_cast<long long>(scratch_bytes), static_cast<long long>(want));
+        return TPK_ERR_SCRATCH;
+    }
+    TPK_REQUIRE(x && y && batch_x && batch_y && idx && dist, "ball_query_partial_dense: NULL pointer");
+    TPK_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "ball_query_partial_dense: scratch must be 256-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    int threads, q;
-    pick_shape(size_y, &threads, &q);
-    const long long grid = (size_y + threads * q - 1) / (threads * q);
-    TPK_REQUIRE(grid < (1ll << 31), "ball_query_partial_dense: too many centres");
-    const dim3 g(static_cast<unsigned>(grid));
-    TPK_BQ_DISPATCH(ball_query_partial_kernel, size_x, size_y, radius, nsample, x, y, batch_x, batch_y, idx, dist);
-    return check_launch("ball_query_partial_dense");
+    const unsigned char* need = nullptr;
+    const int rc = hash_grid_ball_query(size_x, size_y, radius, nsample, x, y, batch_x, batch_y, idx, dist, scratch, &need, s);
+    if (rc != TPK_OK) return rc;
+    // queries the grid left over (crowded neighbourhoods, non-finite coordinates): index-order scan
+    return launch_partial_scan(size_x, size_y, radius, nsample, x, y, batch_x, batch_y, idx, dist, need, s);
 }

@@ -250,9 +250,17 @@ def ball_query_partial_dense(radius, nsample, x, y, batch_x, batch_y, sort=False
     idx = torch.empty((ny, nsample), dtype=torch.int64, device=y.device)
     dist = torch.empty((ny, nsample), dtype=torch.float32, device=y.device)
     with torch.cuda.device(y.device):
-        _lib.call("tpk_ball_query_partial_dense", x.shape[0], ny, float(radius), int(nsample),
-                  _lib.ptr(x), _lib.ptr(y), _lib.ptr(batch_x), _lib.ptr(batch_y), _lib.ptr(idx),
-                  _lib.ptr(dist), _lib.stream_of(y))
+        need = _lib.lib().tpk_ball_query_partial_dense_scratch_bytes(x.shape[0], ny, float(radius))
+        if need > 0:
+            # hashed uniform grid with scratch (same results as the scan of the segments)
+            scratch = torch.empty((need,), dtype=torch.uint8, device=y.device)
+            _lib.call("tpk_ball_query_partial_dense_ws", x.shape[0], ny, float(radius), int(nsample),
+                      _lib.ptr(x), _lib.ptr(y), _lib.ptr(batch_x), _lib.ptr(batch_y), _lib.ptr(idx),
+                      _lib.ptr(dist), _lib.ptr(scratch), need, _lib.stream_of(y))
+        else:
+            _lib.call("tpk_ball_query_partial_dense", x.shape[0], ny, float(radius), int(nsample),
+                      _lib.ptr(x), _lib.ptr(y), _lib.ptr(batch_x), _lib.ptr(batch_y), _lib.ptr(idx),
+                      _lib.ptr(dist), _lib.stream_of(y))
     return idx, dist
 
 
