@@ -859,10 +859,10 @@ extern "C" int tpk_grouping_grad(int b, int c, int n, int npoint, int nsample,
     const size_t row_bytes = static_cast<size_t>(n) * sizeof(float);
     if (row_bytes <= kRowSmemBudget && getenv("TPK_SCATTER_GLOBAL") == nullptr)
     {
-        // rows per CTA: as many as fit a bit over 100 KB (two CTAs per SM), at most 4,
-        // fewer when that would leave SMs without a CTA
-        // (measured: the atomics want many resident warps more than they want shared indices)
-        size_t budget = 104 * 1024;
+        // rows per CTA: as many as fit 32 KB, at least one, at most 4, fewer when that would
+        // leave SMs without a CTA (measured on the pipeline's shapes: the atomics want many
+        // resident warps more than they want the indices shared between rows)
+        size_t budget = 32 * 1024;
         if (const char* env = getenv("TPK_GROUP_BWD_KB")) budget = static_cast<size_t>(atoi(env)) * 1024;
         int rows = static_cast<int>(budget / row_bytes);
         if (rows < 1) rows = 1;
@@ -933,14 +933,24 @@ extern "C" int tpk_three_interpolate_grad(int b, int c, int n, int m, const floa
                 "three_interpolate_grad: inputs must be 16-byte aligned");
     if (static_cast<size_t>(m) * 4 * 4 <= 64 * 1024 && getenv("TPK_SCATTER_GLOBAL") == nullptr)
     {
-        // 4 rows per CTA (8 when there are plenty of channels); block size follows the
-        // number of points a row has to stream
-        const bool many = static_cast<long long>(b) * c >= 16ll * num_sms() && static_cast<size_t>(m) * 4 * 8 <= 64 * 1024;
-        if (n >= 4096)
-            return many ? launch_interp_bwd_rows<8, 512>(b, c, m, n, grad_out, idx, weight, grad_points, s)
-                        : launch_interp_bwd_rows<4, 512>(b, c, m, n, grad_out, idx, weight, grad_points, s);
-        return many ? launch_interp_bwd_rows<8, 128>(b, c, m, n, grad_out, idx, weight, grad_points, s)
-                    : launch_interp_bwd_rows<4, 128>(b, c, m, n, grad_out, idx, weight, grad_points, s);
+        const bool many = false;
+        if (const char* env = getenv("TPK_INTERP_BWD_CFG"))  // tuning runs: "rows,threads"
+        {
+            int rows = 0, threads = 0;
+            if (sscanf(env, "%d,%d", &rows, &threads) == 2 && static_cast<size_t>(m) * 4 * rows <= 64 * 1024)
+            {
+#define TPK_IB(R, T) if (rows == R && threads == T) return launch_interp_bwd_rows<R, T>(b, c, m, n, grad_out, idx, weight, grad_points, s)
+                TPK_IB(2, 128); TPK_IB(2, 256); TPK_IB(4, 128); TPK_IB(4, 256); TPK_IB(4, 512);
+                TPK_IB(8, 128); TPK_IB(8, 256); TPK_IB(8, 512); TPK_IB(2, 512); TPK_IB(1, 256); TPK_IB(1, 512);
+#undef TPK_IB
+            }
+        }
+        (void)many;
+        // measured on the four pipeline shapes: few rows per CTA and small blocks win (many
+        // resident CTAs hide the latency of the index/weight loads and of the atomics)
+        if (n >= 8192) return launch_interp_bwd_rows<1, 256>(b, c, m, n, grad_out, idx, weight, grad_points, s);
+        if (n >= 2048) return launch_interp_bwd_rows<2, 128>(b, c, m, n, grad_out, idx, weight, grad_points, s);
+        return launch_interp_bwd_rows<4, 128>(b, c, m, n, grad_out, idx, weight, grad_points, s);
     }
     return launch_scatter<true>(b, c, m, n, grad_out, idx, weight, grad_points, s,
                                 "three_interpolate_grad");
