@@ -28,26 +28,6 @@ namespace tpk
 size_t grid_cells_capacity(int n);  // grid_query.cu
 int grid_max_dim(int n);
 
-#ifdef TPK_SG_TIMING
-// Debug builds: slot i holds the longest time (ns) any CTA spent between stamp i - 1 and stamp i.
-__device__ unsigned long long g_sg_stamps[16];
-#define SG_STAMP(i)                                                                        \
-    do                                                                                     \
-    {                                                                                      \
-        __syncthreads();                                                                   \
-        if (threadIdx.x == 0)                                                              \
-        {                                                                                  \
-            unsigned long long t_;                                                         \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                       \
-            if (sg_t_last_ != 0) atomicMax(&g_sg_stamps[i], t_ - sg_t_last_);              \
-            sg_t_last_ = t_;                                                               \
-        }                                                                                  \
-    } while (0)
-#define SG_TIMING_BEGIN() unsigned long long sg_t_last_ = 0
-#else
-#define SG_STAMP(i)
-#define SG_TIMING_BEGIN()
-#endif
 
 namespace
 {
@@ -289,9 +269,6 @@ __device__ __forceinline__ bool sg_nn_search(const SgGrid& g, const int* cells, 
                     }
                     if (xa > xb) continue;
                     const int beg = cells[row + xa], end = cells[row + xb + 1];
-#ifdef TPK_SG_TIMING
-                    atomicAdd(&g_sg_stamps[14], static_cast<unsigned long long>(end - beg));
-#endif
                     // Four candidates per step: the loads and distances are independent; a
                     // candidate that cannot beat the K-th best (one compare) costs nothing more,
                     // the others update the best list in order.
@@ -345,9 +322,6 @@ __device__ __forceinline__ bool sg_nn_search(const SgGrid& g, const int* cells, 
                 }
             }
         px0 = x0; px1 = x1; py0 = y0; py1 = y1; pz0 = z0; pz1 = z1;
-#ifdef TPK_SG_TIMING
-        atomicAdd(&g_sg_stamps[15], 1ull);
-#endif
         if (x0 == 0 && y0 == 0 && z0 == 0 && x1 == g.dx - 1 && y1 == g.dy - 1 && z1 == g.dz - 1) return true;
         // distance to the nearest face of the block with unsearched cells behind it
         float rho = CUDART_INF_F;
@@ -398,13 +372,9 @@ __global__ void __launch_bounds__(kSgThreads, 2)
     const float* unknown = unknown_all + static_cast<size_t>(cloud) * n * 3;
     const size_t qbase = static_cast<size_t>(cloud) * n;
 
-    SG_TIMING_BEGIN();
-    SG_STAMP(8);
     const SgGrid g = sg_make_grid(known, m, 1.0e-30f, max_dim, static_cast<size_t>(cells_cap));
-    SG_STAMP(9);
     int staged = -1;
     if (g.ok) staged = sg_bin(known, m, g, 0, g.dz - 1, cells, spts, m);
-    SG_STAMP(10);
     if (staged < 0)
     {
         if (part == 0)
@@ -443,12 +413,10 @@ __global__ void __launch_bounds__(kSgThreads, 2)
         }
     });
     __syncthreads();
-    SG_STAMP(11);
     const int nq = min(s_nq, qcap);
     sg_block_scan(counts + 1, nkeys);
     for (int i = tid; i < nq; i += kSgThreads) qsorted[atomicAdd(&counts[qkey[i] + 1], 1)] = qj[i];
     __syncthreads();
-    SG_STAMP(12);
 
     for (int i = tid; i < nq; i += kSgThreads)
     {
@@ -469,7 +437,6 @@ __global__ void __launch_bounds__(kSgThreads, 2)
             idx_all[3 * t + 2] = i3 == 0x7fffffff ? 0 : i3;
         }
     }
-    SG_STAMP(13);
 }
 
 // ----------------------------------------------------------- nearest neighbours, by layers
@@ -615,10 +582,7 @@ __global__ void __launch_bounds__(kSgThreads, 2)
 
     const float r1 = radius * 1.00001f + 1.0e-30f;
     const float r2 = __fmul_rn(radius, radius);
-    SG_TIMING_BEGIN();
-    SG_STAMP(0);
     const SgGrid g = sg_make_grid(xyz, n, r1, max_dim, static_cast<size_t>(cells_cap));
-    SG_STAMP(1);
     // too few cells: the scan is as good; a radius that is not a positive finite number: the scan decides
     const bool use = g.ok && radius > 0.f && radius < 1.0e18f && g.dx * g.dy * g.dz >= 64;
     if (!use)
@@ -631,7 +595,6 @@ __global__ void __launch_bounds__(kSgThreads, 2)
     if (own_lo > own_hi) return;
     const int za = max(own_lo - 1, 0), zb = min(own_hi + 1, g.dz - 1);
     const int staged = sg_bin(xyz, n, g, za, zb, cells, spts, pcap);
-    SG_STAMP(2);
 
     SgWarpScratch& ws = wscr[warp];
     for (int base = 0; base < m; base += kSgQueryChunk)
@@ -656,7 +619,6 @@ __global__ void __launch_bounds__(kSgThreads, 2)
         });
         __syncthreads();
         const int nq = s_count;
-        SG_STAMP(3);
         // the next centre's coordinates are requested one centre ahead (they come from L2)
         int j_next = warp < nq ? qlist[warp] : 0;
         float nx = __ldg(new_xyz + 3 * j_next + 0), ny_ = __ldg(new_xyz + 3 * j_next + 1), nz = __ldg(new_xyz + 3 * j_next + 2);
@@ -771,7 +733,6 @@ __global__ void __launch_bounds__(kSgThreads, 2)
             if (lane == 0) need_all[t] = 0;
         }
         __syncthreads();
-        SG_STAMP(4);
     }
 }
 
@@ -1032,12 +993,3 @@ int sg_ball_query(int b, int n, int m, float radius, int nsample, const float* n
 
 }  // namespace tpk
 
-#ifdef TPK_SG_TIMING
-// Debug builds only: phase time stamps (ns) of the middle CTA of the last launches.
-extern "C" __attribute__((visibility("default"))) int tpk_debug_sg_stamps(unsigned long long* out16)
-{
-    static const unsigned long long zeros[16] = {};
-    if (cudaMemcpyFromSymbol(out16, tpk::g_sg_stamps, sizeof(zeros)) != cudaSuccess) return 2;
-    return cudaMemcpyToSymbol(tpk::g_sg_stamps, zeros, sizeof(zeros)) == cudaSuccess ? 0 : 2;
-}
-#endif
