@@ -283,6 +283,24 @@ def test_ball_query_dense_shared_memory_grid_edge_cases(case):
     same_bits(npy(dist), od)
 
 
+@pytest.mark.parametrize("kind", ["ball", "mixture"])
+def test_ball_query_dense_huge_clouds_use_the_hashed_grid(kind, monkeypatch):
+    """Clouds of 2^18+ points: the hashed grid in global scratch, against the oracle, the older
+    bounding-box grid and the scan (crowded centres of the mixture go back to the scan)."""
+    B, N, M, r, ns = 2, 270000, 400, 0.03, 32
+    x = data.unit_ball(B, N, seed=41) if kind == "ball" else data.gaussian_mixture(B, N, seed=42, comps=8)
+    y = x[:, torch.randperm(N, generator=data.gen(43))[:M]].contiguous()
+    need = _lib.lib().tpk_ball_query_dense_scratch_bytes(B, N, M, ns)
+    assert need > B * N * 20
+    oi, od = orc.ball_query_dense(r, ns, x, y)
+    for env in (None, "TPK_BALL_QUERY_GLOBAL_GRID", "TPK_BALL_QUERY_SCAN"):
+        if env:
+            monkeypatch.setenv(env, "1")
+        idx, dist = tpk.ball_query(r, ns, cu(x), cu(y), mode="dense")
+        np.testing.assert_array_equal(npy(idx), oi)
+        same_bits(npy(dist), od)
+
+
 def test_ball_query_dense_boundary_is_strict_partial_is_inclusive():
     x = np.array([[[0, 0, 0], [0.5, 0, 0], [0.25, 0, 0]]], np.float32)
     y = np.array([[[0, 0, 0]]], np.float32)

@@ -27,6 +27,8 @@ size_t hash_grid_scratch_bytes(long long size_x, long long size_y);
 int hash_grid_ball_query(long long size_x, long long size_y, float radius, int nsample, const float* x, const float* y,
                          const int64_t* batch_x, const int64_t* batch_y, int64_t* idx, float* dist, void* scratch,
                          const unsigned char** need_out, cudaStream_t s);
+int hash_grid_ball_query_dense(int b, int n, int m, float radius, int nsample, const float* new_xyz, const float* xyz,
+                               int64_t* idx, float* dist, void* scratch, const unsigned char** need_out, cudaStream_t s);
 // smem_grid.cu
 bool sg_ball_query_fits(int b, int n, int nsample);
 int sg_ball_query(int b, int n, int m, float radius, int nsample, const float* new_xyz, const float* xyz,
@@ -288,11 +290,22 @@ static bool use_smem_grid(int b, int n, int nsample)
     return tpk::sg_ball_query_fits(b, n, nsample) && getenv("TPK_BALL_QUERY_GLOBAL_GRID") == nullptr;
 }
 
+// Clouds the shared-memory grid does not take (2^18 points and more): the hashed grid in
+// global scratch.  TPK_BALL_QUERY_GLOBAL_GRID selects the older bounding-box grid in global
+// memory instead of either (comparison runs and tests of that path).
+static bool use_hash_grid(int b, int n, int m)
+{
+    return n >= 8192 && tpk::hash_grid_fits(static_cast<long long>(b) * n, static_cast<long long>(b) * m) &&
+           getenv("TPK_BALL_QUERY_GLOBAL_GRID") == nullptr;
+}
+
 extern "C" int64_t tpk_ball_query_dense_scratch_bytes(int b, int n, int m, int nsample)
 {
     if (b <= 0 || m <= 0 || nsample <= 0) return 0;
     // shared-memory grid: one flag per centre
     if (use_smem_grid(b, n, nsample)) return (static_cast<int64_t>(b) * m + 255) / 256 * 256;
+    if (use_hash_grid(b, n, m))
+        return static_cast<int64_t>(tpk::hash_grid_scratch_bytes(static_cast<long long>(b) * n, static_cast<long long>(b) * m));
     // the grid in global memory needs clouds worth binning and a hit list that fits shared memory
     if (n < 8192 || nsample > 128) return 0;
     return static_cast<int64_t>(tpk::grid_scratch_bytes(b, n, m));
@@ -322,6 +335,14 @@ extern "C" int tpk_ball_query_dense_ws(int b, int n, int m, float radius, int ns
     {
         need = static_cast<const unsigned char*>(scratch);
         rc = sg_ball_query(b, n, m, radius, nsample, new_xyz, xyz, idx, dist, static_cast<unsigned char*>(scratch), s);
+    }
+    else if (use_hash_grid(b, n, m) && radius > 0.f && radius < 1.0e18f)
+    {
+        rc = hash_grid_ball_query_dense(b, n, m, radius, nsample, new_xyz, xyz, idx, dist, scratch, &need, s);
+    }
+    else if (use_hash_grid(b, n, m))
+    {
+        rc = TPK_OK;  // a radius without a grid: the scan answers every centre
     }
     else
     {

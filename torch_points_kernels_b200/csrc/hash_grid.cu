@@ -1,4 +1,5 @@
-// Packed (partial_dense) ball query on a hashed uniform grid (sm_100a).
+// Ball query on a hashed uniform grid (sm_100a): the packed (partial_dense) layout, and dense
+// clouds too large for the grids in shared memory.
 //
 // The packed layout holds many scenes of different sizes, each with its own extent, so
 // there is no common bounding box to lay a grid over.  Points are instead binned by the
@@ -24,8 +25,7 @@ namespace
 
 constexpr int kHgThreads = 256;
 constexpr int kHgWarps = kHgThreads / 32;
-constexpr int kHgHitCap = 256;        // hits per query the buffer takes
-constexpr int kHgMaxCandidates = 4096;  // above this the early-exit scan is cheaper
+constexpr int kHgHitCap = 512;        // hits per query the buffer takes
 constexpr int kHgCoordLimit = 1 << 20;
 
 __device__ __forceinline__ int hg_cell(float v, float inv_h)
@@ -59,7 +59,7 @@ __device__ __forceinline__ bool hg_finite(float x, float y, float z)
 // Points with non-finite coordinates are not binned (no ball contains them).
 template <bool FILL>
 __global__ void __launch_bounds__(kHgThreads)
-    hg_bin_kernel(long long size_x, float inv_h, uint32_t mask, const float* __restrict__ x,
+    hg_bin_kernel(long long size_x, long long per_cloud, float inv_h, uint32_t mask, const float* __restrict__ x,
                   const int64_t* __restrict__ batch_x, int* __restrict__ counts, float4* __restrict__ sorted,
                   int* __restrict__ sorted_seg)
 {
@@ -67,7 +67,8 @@ __global__ void __launch_bounds__(kHgThreads)
     if (k >= size_x) return;
     const float px = __ldg(x + 3 * k + 0), py = __ldg(x + 3 * k + 1), pz = __ldg(x + 3 * k + 2);
     if (!hg_finite(px, py, pz)) return;
-    const long long seg = __ldg(batch_x + k);
+    // packed layout: the segment id of the point; dense layout (batch_x == NULL): its cloud
+    const long long seg = batch_x ? __ldg(batch_x + k) : k / per_cloud;
     const uint32_t bkt = hg_bucket(seg, hg_cell(px, inv_h), hg_cell(py, inv_h), hg_cell(pz, inv_h), mask);
     const int pos = atomicAdd(counts + bkt + 1, 1);
     if (FILL)
@@ -163,10 +164,16 @@ struct HgWarpScratch
     int hit_pos[kHgHitCap];       // its slot in the sorted copy
     int run_end[32];              // inclusive prefix of the 27 bucket lengths
     int run_shift[32];            // slot of candidate v of run r = run_shift[r] + v
+    int first;                    // dense layout: index of the first hit, repeated in unused slots
 };
 
+// DENSE: (b, n, 3) clouds and (b, m, 3) centres instead of packed segments: the segment of a
+// query is its cloud, the test is the dense kernel's (strict, ball_query_gpu.cu:35-36),
+// indices are local to the cloud and unused slots repeat the first hit.
+template <bool DENSE>
 __global__ void __launch_bounds__(kHgThreads)
-    hg_query_kernel(long long size_y, float radius, int nsample, float inv_h, uint32_t mask,
+    hg_query_kernel(long long size_y, long long per_cloud_x, long long per_cloud_y, float radius, int nsample, int max_candidates,
+                    float inv_h, uint32_t mask,
                     const float* __restrict__ y, const int64_t* __restrict__ batch_y, const int* __restrict__ counts,
                     const float4* __restrict__ sorted, const int* __restrict__ sorted_seg,
                     int64_t* __restrict__ idx_out, float* __restrict__ dist_out, unsigned char* __restrict__ need)
@@ -185,7 +192,7 @@ __global__ void __launch_bounds__(kHgThreads)
             if (lane == 0) need[j] = 1;
             continue;
         }
-        const long long seg = __ldg(batch_y + j);
+        const long long seg = DENSE ? j / per_cloud_y : __ldg(batch_y + j);
         // the ball, enlarged by the rounding of the exact test and of q +- r, must stay inside the
         // three cells per axis around the query's cell; it does unless q sits on a cell face
         const float pad = radius * 1.00001f + 1.0e-30f;
@@ -218,7 +225,7 @@ __global__ void __launch_bounds__(kHgThreads)
             if (lane >= o) incl += v;
         }
         const int total = __shfl_sync(kFullMask, incl, 31);
-        if (total > kHgMaxCandidates)
+        if (total > max_candidates)  // crowded: the scan, which stops at the nsample-th hit, is cheaper
         {
             if (lane == 0) need[j] = 1;
             continue;
@@ -238,9 +245,9 @@ __global__ void __launch_bounds__(kHgThreads)
             const int p = valid ? ws.run_shift[r] + v : 0;
             const float4 c = __ldg(sorted + p);
             const int cseg = __ldg(sorted_seg + p);
-            // the packed kernel's arithmetic (ball_query_gpu.cu:78-82) and its inclusive test
-            const float d = sumsq_loop(qx - c.x, qy - c.y, qz - c.z);
-            const bool hit = valid && cseg == static_cast<int>(seg) && d <= r2;
+            // the packed kernel's arithmetic (ball_query_gpu.cu:78-82) and its inclusive test, or the dense one's
+            const float d = DENSE ? sumsq_abc(qx - c.x, qy - c.y, qz - c.z) : sumsq_loop(qx - c.x, qy - c.y, qz - c.z);
+            const bool hit = valid && cseg == static_cast<int>(seg) && (DENSE ? d < r2 : d <= r2);
             const uint32_t bal = __ballot_sync(kFullMask, hit);
             if (hit)
             {
@@ -261,6 +268,8 @@ __global__ void __launch_bounds__(kHgThreads)
         __syncwarp();
         int64_t* orow = idx_out + j * nsample;
         float* drow = dist_out + j * nsample;
+        const long long base = DENSE ? seg * per_cloud_x : 0;  // dense indices are local to the cloud
+        __syncwarp();
         for (int h0 = 0; h0 < nh; h0 += 32)
         {
             const int h = h0 + lane;
@@ -272,14 +281,17 @@ __global__ void __launch_bounds__(kHgThreads)
                 if (rank < nsample)
                 {
                     const float4 c = __ldg(sorted + ws.hit_pos[h]);
-                    orow[rank] = static_cast<int64_t>(e);
-                    drow[rank] = sumsq_loop(qx - c.x, qy - c.y, qz - c.z);
+                    orow[rank] = static_cast<int64_t>(e) - base;
+                    drow[rank] = DENSE ? sumsq_abc(qx - c.x, qy - c.y, qz - c.z) : sumsq_loop(qx - c.x, qy - c.y, qz - c.z);
+                    if (rank == 0) ws.first = static_cast<int>(static_cast<long long>(e) - base);
                 }
             }
         }
+        __syncwarp();
+        const int64_t fill = DENSE ? (nh ? static_cast<int64_t>(ws.first) : 0) : -1;
         for (int s = min(nh, nsample) + lane; s < nsample; s += 32)
         {
-            orow[s] = -1;
+            orow[s] = fill;
             drow[s] = -1.0f;
         }
         if (lane == 0) need[j] = 0;
@@ -312,9 +324,11 @@ size_t hash_grid_scratch_bytes(long long size_x, long long size_y)
 }
 
 // Answers the queries the grid is good for; *need_out: one byte per query, 1 = left to the scan.
-int hash_grid_ball_query(long long size_x, long long size_y, float radius, int nsample, const float* x, const float* y,
-                         const int64_t* batch_x, const int64_t* batch_y, int64_t* idx, float* dist, void* scratch,
-                         const unsigned char** need_out, cudaStream_t s)
+// Packed layout: batch_x / batch_y give the segments.  Dense layout (both NULL): size_x = b * n,
+// size_y = b * m, per_cloud_x = n, per_cloud_y = m.
+static int hash_grid_run(long long size_x, long long size_y, long long per_cloud_x, long long per_cloud_y, float radius,
+                         int nsample, const float* x, const float* y, const int64_t* batch_x, const int64_t* batch_y,
+                         int64_t* idx, float* dist, void* scratch, const unsigned char** need_out, cudaStream_t s)
 {
     const uint32_t h = hg_buckets(size_x);
     const uint32_t mask = h - 1u;
@@ -340,19 +354,52 @@ int hash_grid_ball_query(long long size_x, long long size_y, float radius, int n
         return TPK_ERR_CUDA;
     }
     const unsigned gp = static_cast<unsigned>((size_x + kHgThreads - 1) / kHgThreads);
-    count_launches(1), hg_bin_kernel<false><<<gp, kHgThreads, 0, s>>>(size_x, inv_h, mask, x, batch_x, counts, sorted, sorted_seg);
+    count_launches(1), hg_bin_kernel<false><<<gp, kHgThreads, 0, s>>>(size_x, per_cloud_x, inv_h, mask, x, batch_x, counts, sorted, sorted_seg);
     count_launches(1), hg_scan_blocks_kernel<<<nblocks, 1024, 0, s>>>(counts, ncount, totals);
     count_launches(1), hg_scan_totals_kernel<<<1, 1024, 0, s>>>(totals, nblocks);
     count_launches(1), hg_scan_add_kernel<<<nblocks, 1024, 0, s>>>(counts, ncount, totals);
-    count_launches(1), hg_bin_kernel<true><<<gp, kHgThreads, 0, s>>>(size_x, inv_h, mask, x, batch_x, counts, sorted, sorted_seg);
+    count_launches(1), hg_bin_kernel<true><<<gp, kHgThreads, 0, s>>>(size_x, per_cloud_x, inv_h, mask, x, batch_x, counts, sorted, sorted_seg);
+    // above this many candidates around a query the early-exit scan is cheaper (the rule of the
+    // other grids for dense clouds; packed segments have no common size)
+    int max_cand = 16384;
+    if (batch_y == nullptr)
+    {
+        const double v = 2.0 * sqrt(6.45 * static_cast<double>(per_cloud_x) * nsample);
+        max_cand = v < 4096.0 ? 4096 : (v > 1.0e6 ? 1000000 : static_cast<int>(v));
+    }
     long long gq = (size_y + kHgWarps - 1) / kHgWarps;
     const long long cap = 32ll * num_sms();
     if (gq > cap) gq = cap;
-    prefer_max_shared(hg_query_kernel);
-    count_launches(1), hg_query_kernel<<<static_cast<unsigned>(gq), kHgThreads, 0, s>>>(size_y, radius, nsample, inv_h, mask, y, batch_y,
-                                                                     counts, sorted, sorted_seg, idx, dist, need);
+    if (batch_y == nullptr)
+    {
+        prefer_max_shared(hg_query_kernel<true>);
+        count_launches(1), hg_query_kernel<true><<<static_cast<unsigned>(gq), kHgThreads, 0, s>>>(
+            size_y, per_cloud_x, per_cloud_y, radius, nsample, max_cand, inv_h, mask, y, batch_y, counts, sorted, sorted_seg, idx, dist, need);
+    }
+    else
+    {
+        prefer_max_shared(hg_query_kernel<false>);
+        count_launches(1), hg_query_kernel<false><<<static_cast<unsigned>(gq), kHgThreads, 0, s>>>(
+            size_y, per_cloud_x, per_cloud_y, radius, nsample, max_cand, inv_h, mask, y, batch_y, counts, sorted, sorted_seg, idx, dist, need);
+    }
     *need_out = need;
     return check_launch("ball_query hash grid");
+}
+
+int hash_grid_ball_query(long long size_x, long long size_y, float radius, int nsample, const float* x, const float* y,
+                         const int64_t* batch_x, const int64_t* batch_y, int64_t* idx, float* dist, void* scratch,
+                         const unsigned char** need_out, cudaStream_t s)
+{
+    return hash_grid_run(size_x, size_y, 1, 1, radius, nsample, x, y, batch_x, batch_y, idx, dist, scratch, need_out, s);
+}
+
+// Dense clouds (b, n, 3) / centres (b, m, 3) on the hashed grid (for clouds too large for the
+// grids in shared memory).
+int hash_grid_ball_query_dense(int b, int n, int m, float radius, int nsample, const float* new_xyz, const float* xyz,
+                               int64_t* idx, float* dist, void* scratch, const unsigned char** need_out, cudaStream_t s)
+{
+    return hash_grid_run(static_cast<long long>(b) * n, static_cast<long long>(b) * m, n, m, radius, nsample, xyz, new_xyz,
+                         nullptr, nullptr, idx, dist, scratch, need_out, s);
 }
 
 }  // namespace tpk
