@@ -125,7 +125,7 @@ class Pipeline:
         fps_idx, fps_ready = [], []
         with torch.cuda.stream(s_fps):
             for l, m in enumerate(LEVELS["npoint"]):
-                # indices and the sampled coordinates from the same kernel (no gather pass)
+                # indices and the sampled coordinates from one library call
                 idx, centres = timed("fps_l%d" % (l + 1), lambda: tpk.furthest_point_sample(pts[l], m, return_xyz=True))
                 fps_idx.append(hand_over(idx, cur))
                 pts.append(hand_over(centres, s_geo))

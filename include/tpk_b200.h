@@ -80,9 +80,9 @@ TPK_API int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz, v
                                 int32_t* idxs, void* stream);
 
 /*
- * The same, also writing the coordinates of the samples: new_xyz (b,m,3) f32, i.e.
- * xyz[b, idxs[b, j], :] (what callers otherwise gather from idxs in a second pass); NULL
- * skips it.  No counterpart in the reference.
+ * The same, followed by a gather of the coordinates of the samples: new_xyz (b,m,3) f32,
+ * i.e. xyz[b, idxs[b, j], :] (what callers otherwise do with several tensor operations);
+ * NULL skips it.  No counterpart in the reference.
  */
 TPK_API int tpk_furthest_point_sampling_xyz(int b, int n, int m, const float* xyz, void* scratch,
                                     int32_t* idxs, float* new_xyz, void* stream);

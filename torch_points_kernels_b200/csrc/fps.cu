@@ -212,8 +212,7 @@ __device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigne
 template <int PPT, bool CLUSTERED, bool SORTED>
 __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
     fps_onchip_kernel(int n, int m, int log2bs, int flat, const float* __restrict__ xyz_all,
-                      const float4* __restrict__ sorted_all, int32_t* __restrict__ idxs_all,
-                      float* __restrict__ new_xyz_all)
+                      const float4* __restrict__ sorted_all, int32_t* __restrict__ idxs_all)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -325,18 +324,7 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
         cy = __ldg(xyz + 1);
         cz = __ldg(xyz + 2);
     }
-    // optional second output: the coordinates of the samples, (m, 3) per cloud
-    float* new_xyz = new_xyz_all ? new_xyz_all + static_cast<size_t>(cloud) * m * 3 : nullptr;
-    if (gtid == 0 && m > 0)
-    {
-        idxs[0] = 0;
-        if (new_xyz)
-        {
-            new_xyz[0] = __ldg(xyz + 0);
-            new_xyz[1] = __ldg(xyz + 1);
-            new_xyz[2] = __ldg(xyz + 2);
-        }
-    }
+    if (gtid == 0 && m > 0) idxs[0] = 0;
 
     if (CLUSTERED)
     {
@@ -554,17 +542,7 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
         cx = msg.x;
         cy = msg.y;
         cz = msg.z;
-        if (gtid == 0)
-        {
-            const bool found = msg.key >= 0;  // otherwise index 0, as the reference's arg-max leaves it
-            idxs[j] = found ? msg.k : 0;
-            if (new_xyz)
-            {
-                new_xyz[3 * j + 0] = found ? msg.x : __ldg(xyz + 0);
-                new_xyz[3 * j + 1] = found ? msg.y : __ldg(xyz + 1);
-                new_xyz[3 * j + 2] = found ? msg.z : __ldg(xyz + 2);
-            }
-        }
+        if (gtid == 0) idxs[j] = msg.key >= 0 ? msg.k : 0;
     };
 
     int j = 1;
@@ -759,8 +737,7 @@ constexpr int kFpsBigThreads = 512;
 
 __global__ void __launch_bounds__(kFpsBigThreads, 1)
     fps_global_kernel(int n, int m, int log2bs, const float* __restrict__ xyz_all,
-                      float* __restrict__ temp_all, int32_t* __restrict__ idxs_all,
-                      float* __restrict__ new_xyz_all)
+                      float* __restrict__ temp_all, int32_t* __restrict__ idxs_all)
 {
     __shared__ __align__(16) uint4 wmsg_a[64];
     __shared__ __align__(16) uint4 cmsg_a[64];
@@ -791,18 +768,7 @@ __global__ void __launch_bounds__(kFpsBigThreads, 1)
     }
 
     float cx = __ldg(xyz + 0), cy = __ldg(xyz + 1), cz = __ldg(xyz + 2);
-    // optional second output: the coordinates of the samples, (m, 3) per cloud
-    float* new_xyz = new_xyz_all ? new_xyz_all + static_cast<size_t>(cloud) * m * 3 : nullptr;
-    if (gtid == 0 && m > 0)
-    {
-        idxs[0] = 0;
-        if (new_xyz)
-        {
-            new_xyz[0] = __ldg(xyz + 0);
-            new_xyz[1] = __ldg(xyz + 1);
-            new_xyz[2] = __ldg(xyz + 2);
-        }
-    }
+    if (gtid == 0 && m > 0) idxs[0] = 0;
     if (tid == 0)
     {
         mbar_init(smem_u32(mbar + 0), 1);
@@ -941,17 +907,7 @@ __global__ void __launch_bounds__(kFpsBigThreads, 1)
         cx = msg.x;
         cy = msg.y;
         cz = msg.z;
-        if (gtid == 0)
-        {
-            const bool found = msg.key >= 0;  // otherwise index 0, as the reference's arg-max leaves it
-            idxs[j] = found ? msg.k : 0;
-            if (new_xyz)
-            {
-                new_xyz[3 * j + 0] = found ? msg.x : __ldg(xyz + 0);
-                new_xyz[3 * j + 1] = found ? msg.y : __ldg(xyz + 1);
-                new_xyz[3 * j + 2] = found ? msg.z : __ldg(xyz + 2);
-            }
-        }
+        if (gtid == 0) idxs[j] = msg.key >= 0 ? msg.k : 0;
     }
     cluster_sync_all();
 }
@@ -972,7 +928,7 @@ template <int CPL>  // chunks per lane: a warp owns 32 * CPL chunks
 __global__ void __launch_bounds__(kFpsBigThreads, 1)
     fps_pruned_kernel(int n, int m, int log2bs, const float* __restrict__ xyz_all,
                       const float4* __restrict__ sorted_all, float* __restrict__ temp_all,
-                      int32_t* __restrict__ idxs_all, float* __restrict__ new_xyz_all)
+                      int32_t* __restrict__ idxs_all)
 {
     __shared__ __align__(16) uint4 wmsg_a[64];
     __shared__ __align__(16) uint4 cmsg_a[64];
@@ -1063,18 +1019,7 @@ __global__ void __launch_bounds__(kFpsBigThreads, 1)
     }
 
     float cx = __ldg(xyz + 0), cy = __ldg(xyz + 1), cz = __ldg(xyz + 2);
-    // optional second output: the coordinates of the samples, (m, 3) per cloud
-    float* new_xyz = new_xyz_all ? new_xyz_all + static_cast<size_t>(cloud) * m * 3 : nullptr;
-    if (gtid == 0 && m > 0)
-    {
-        idxs[0] = 0;
-        if (new_xyz)
-        {
-            new_xyz[0] = __ldg(xyz + 0);
-            new_xyz[1] = __ldg(xyz + 1);
-            new_xyz[2] = __ldg(xyz + 2);
-        }
-    }
+    if (gtid == 0 && m > 0) idxs[0] = 0;
     if (tid == 0)
     {
         mbar_init(smem_u32(mbar + 0), 1);
@@ -1273,23 +1218,13 @@ __global__ void __launch_bounds__(kFpsBigThreads, 1)
         cx = msg.x;
         cy = msg.y;
         cz = msg.z;
-        if (gtid == 0)
-        {
-            const bool found = msg.key >= 0;  // otherwise index 0, as the reference's arg-max leaves it
-            idxs[j] = found ? msg.k : 0;
-            if (new_xyz)
-            {
-                new_xyz[3 * j + 0] = found ? msg.x : __ldg(xyz + 0);
-                new_xyz[3 * j + 1] = found ? msg.y : __ldg(xyz + 1);
-                new_xyz[3 * j + 2] = found ? msg.z : __ldg(xyz + 2);
-            }
-        }
+        if (gtid == 0) idxs[j] = msg.key >= 0 ? msg.k : 0;
     }
     cluster_sync_all();
 }
 
 int fps_launch_global(int b, int n, int m, int log2bs, const float* xyz, float* temp,
-                      int32_t* idxs, float* new_xyz, cudaStream_t stream)
+                      int32_t* idxs, cudaStream_t stream)
 {
     auto kernel = fps_global_kernel;
     prefer_max_shared(kernel);
@@ -1312,7 +1247,7 @@ int fps_launch_global(int b, int n, int m, int log2bs, const float* xyz, float* 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     count_launches(1);
-    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, xyz, temp, idxs, new_xyz);
+    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, xyz, temp, idxs);
     if (err != cudaSuccess)
     {
         set_error("fps launch (large clouds): %s", cudaGetErrorString(err));
@@ -1326,7 +1261,7 @@ constexpr long long kFpsPrunedMaxPoints = 256ll * 32 * 4 * kFpsChunk;
 
 template <int CPL>
 int fps_launch_pruned_t(int b, int n, int m, int log2bs, const float* xyz, const float4* sorted, float* temp,
-                        int32_t* idxs, float* new_xyz, cudaStream_t stream)
+                        int32_t* idxs, cudaStream_t stream)
 {
     auto kernel = fps_pruned_kernel<CPL>;
     prefer_max_shared(kernel);
@@ -1349,7 +1284,7 @@ int fps_launch_pruned_t(int b, int n, int m, int log2bs, const float* xyz, const
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     count_launches(1);
-    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, xyz, sorted, temp, idxs, new_xyz);
+    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, xyz, sorted, temp, idxs);
     if (err != cudaSuccess)
     {
         set_error("fps launch (large clouds, sorted): %s", cudaGetErrorString(err));
@@ -1360,16 +1295,16 @@ int fps_launch_pruned_t(int b, int n, int m, int log2bs, const float* xyz, const
 
 // scratch: the sorted copy (16 bytes per point), then the running minima (4 bytes per point)
 int fps_launch_pruned(int b, int n, int m, int log2bs, const float* xyz, void* scratch, int32_t* idxs,
-                      float* new_xyz, cudaStream_t stream)
+                      cudaStream_t stream)
 {
     float4* sorted = static_cast<float4*>(scratch);
     float* temp = reinterpret_cast<float*>(sorted + static_cast<size_t>(b) * n);
     const int rc = fps_launch_sort(b, n, xyz, sorted, stream);
     if (rc != TPK_OK) return rc;
     const long long per_lane = (static_cast<long long>(n) + 256ll * 32 * kFpsChunk - 1) / (256ll * 32 * kFpsChunk);
-    if (per_lane <= 1) return fps_launch_pruned_t<1>(b, n, m, log2bs, xyz, sorted, temp, idxs, new_xyz, stream);
-    if (per_lane <= 2) return fps_launch_pruned_t<2>(b, n, m, log2bs, xyz, sorted, temp, idxs, new_xyz, stream);
-    return fps_launch_pruned_t<4>(b, n, m, log2bs, xyz, sorted, temp, idxs, new_xyz, stream);
+    if (per_lane <= 1) return fps_launch_pruned_t<1>(b, n, m, log2bs, xyz, sorted, temp, idxs, stream);
+    if (per_lane <= 2) return fps_launch_pruned_t<2>(b, n, m, log2bs, xyz, sorted, temp, idxs, stream);
+    return fps_launch_pruned_t<4>(b, n, m, log2bs, xyz, sorted, temp, idxs, stream);
 }
 
 struct FpsConfig
@@ -1441,7 +1376,7 @@ bool fps_pick_config(int n, int m, FpsConfig* out)
 
 template <int PPT, bool CLUSTERED, bool SORTED>
 int fps_launch_t(const FpsConfig& c, int b, int n, int m, int log2bs, const float* xyz,
-                 const float4* sorted, int32_t* idxs, float* new_xyz, cudaStream_t stream)
+                 const float4* sorted, int32_t* idxs, cudaStream_t stream)
 {
     auto kernel = fps_onchip_kernel<PPT, CLUSTERED, SORTED>;
     prefer_max_shared(kernel);
@@ -1483,7 +1418,7 @@ int fps_launch_t(const FpsConfig& c, int b, int n, int m, int log2bs, const floa
     const char* flat_env = getenv("TPK_FPS_FLAT");
     const int flat = (c.nranks > 1 && c.nranks * (c.nthreads / 32) <= 32 && !(flat_env && flat_env[0] == '0')) ? 1 : 0;
     count_launches(1);
-    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, flat, xyz, sorted, idxs, new_xyz);
+    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, flat, xyz, sorted, idxs);
     if (err != cudaSuccess)
     {
         set_error("fps launch (cluster %d x %d threads x %d points): %s", c.nranks, c.nthreads,
@@ -1495,16 +1430,16 @@ int fps_launch_t(const FpsConfig& c, int b, int n, int m, int log2bs, const floa
 
 template <bool CLUSTERED, bool SORTED>
 int fps_launch_s(const FpsConfig& c, int b, int n, int m, int log2bs, const float* xyz,
-                 const float4* sorted, int32_t* idxs, float* new_xyz, cudaStream_t stream)
+                 const float4* sorted, int32_t* idxs, cudaStream_t stream)
 {
     switch (c.ppt)
     {
-    case 1: return fps_launch_t<1, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, new_xyz, stream);
-    case 2: return fps_launch_t<2, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, new_xyz, stream);
-    case 4: return fps_launch_t<4, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, new_xyz, stream);
-    case 8: return fps_launch_t<8, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, new_xyz, stream);
-    case 16: return fps_launch_t<16, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, new_xyz, stream);
-    case 32: return fps_launch_t<32, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, new_xyz, stream);
+    case 1: return fps_launch_t<1, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
+    case 2: return fps_launch_t<2, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
+    case 4: return fps_launch_t<4, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
+    case 8: return fps_launch_t<8, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
+    case 16: return fps_launch_t<16, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
+    case 32: return fps_launch_t<32, CLUSTERED, SORTED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream);
     default: break;
     }
     set_error("fps: unsupported points per thread %d", c.ppt);
@@ -1540,8 +1475,8 @@ extern "C" int64_t tpk_fps_scratch_bytes(int b, int n, int m)
     return static_cast<int64_t>(b) * n * (fps_large_sorted(n) ? 20 : 4);
 }
 
-extern "C" int tpk_furthest_point_sampling_xyz(int b, int n, int m, const float* xyz, void* scratch,
-                                               int32_t* idxs, float* new_xyz, void* stream)
+extern "C" int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz, void* scratch,
+                                           int32_t* idxs, void* stream)
 {
     using namespace tpk;
     TPK_REQUIRE(b >= 0 && n >= 0 && m >= 0, "fps: negative size (b=%d n=%d m=%d)", b, n, m);
@@ -1564,26 +1499,56 @@ extern "C" int tpk_furthest_point_sampling_xyz(int b, int n, int m, const float*
         if (fps_large_sorted(n))
         {
             TPK_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 15u) == 0, "fps: scratch must be 16-byte aligned");
-            return fps_launch_pruned(b, n, m, log2bs, xyz, scratch, idxs, new_xyz, s);
+            return fps_launch_pruned(b, n, m, log2bs, xyz, scratch, idxs, s);
         }
-        return fps_launch_global(b, n, m, log2bs, xyz, static_cast<float*>(scratch), idxs, new_xyz, s);
+        return fps_launch_global(b, n, m, log2bs, xyz, static_cast<float*>(scratch), idxs, s);
     }
     if (scratch != nullptr && fps_wants_sorted(n, m) && (reinterpret_cast<uintptr_t>(scratch) & 15u) == 0)
     {
         float4* sorted = static_cast<float4*>(scratch);
         const int rc = fps_launch_sort(b, n, xyz, sorted, s);
         if (rc != TPK_OK) return rc;
-        return c.nranks > 1 ? fps_launch_s<true, true>(c, b, n, m, log2bs, xyz, sorted, idxs, new_xyz, s)
-                            : fps_launch_s<false, true>(c, b, n, m, log2bs, xyz, sorted, idxs, new_xyz, s);
+        return c.nranks > 1 ? fps_launch_s<true, true>(c, b, n, m, log2bs, xyz, sorted, idxs, s)
+                            : fps_launch_s<false, true>(c, b, n, m, log2bs, xyz, sorted, idxs, s);
     }
-    return c.nranks > 1 ? fps_launch_s<true, false>(c, b, n, m, log2bs, xyz, nullptr, idxs, new_xyz, s)
-                        : fps_launch_s<false, false>(c, b, n, m, log2bs, xyz, nullptr, idxs, new_xyz, s);
+    return c.nranks > 1 ? fps_launch_s<true, false>(c, b, n, m, log2bs, xyz, nullptr, idxs, s)
+                        : fps_launch_s<false, false>(c, b, n, m, log2bs, xyz, nullptr, idxs, s);
 }
 
-extern "C" int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz, void* scratch,
-                                           int32_t* idxs, void* stream)
+// Coordinates of the samples, new_xyz[b, j, :] = xyz[b, idxs[b, j], :].  A separate pass of a
+// few microseconds: written from inside the sampling kernels the four stores per round sat on
+// the critical path of every round (measured 5 % of the whole call).
+namespace tpk
 {
-    return tpk_furthest_point_sampling_xyz(b, n, m, xyz, scratch, idxs, nullptr, stream);
+namespace
+{
+__global__ void __launch_bounds__(256)
+    fps_gather_xyz_kernel(long long total, int n, int m, const float* __restrict__ xyz, const int32_t* __restrict__ idxs,
+                          float* __restrict__ new_xyz)
+{
+    const long long t = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    if (t >= total) return;
+    const long long cloud = t / m;
+    const float* src = xyz + (cloud * n + __ldg(idxs + t)) * 3;
+    new_xyz[3 * t + 0] = __ldg(src + 0);
+    new_xyz[3 * t + 1] = __ldg(src + 1);
+    new_xyz[3 * t + 2] = __ldg(src + 2);
+}
+}  // namespace
+}  // namespace tpk
+
+extern "C" int tpk_furthest_point_sampling_xyz(int b, int n, int m, const float* xyz, void* scratch,
+                                               int32_t* idxs, float* new_xyz, void* stream)
+{
+    using namespace tpk;
+    const int rc = tpk_furthest_point_sampling(b, n, m, xyz, scratch, idxs, stream);
+    if (rc != TPK_OK || new_xyz == nullptr || b == 0 || m == 0) return rc;
+    const long long total = static_cast<long long>(b) * m;
+    const long long grid = (total + 255) / 256;
+    TPK_REQUIRE(grid < (1ll << 31), "fps: too many samples");
+    count_launches(1), fps_gather_xyz_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        total, n, m, xyz, idxs, new_xyz);
+    return check_launch("fps gather");
 }
 
 // ------------------------------------------------------------- entry point without scratch
@@ -1642,7 +1607,7 @@ extern "C" int tpk_furthest_point_sampling_static(int b, int n, int m, const flo
     if (log2bs > 9) log2bs = 9;
     // the kernel writes every scratch element it later reads (its first pass sets the
     // running minima), so whatever an earlier call left behind is irrelevant
-    return fps_launch_global(b, n, m, log2bs, xyz, scratch, idxs, nullptr, static_cast<cudaStream_t>(stream));
+    return fps_launch_global(b, n, m, log2bs, xyz, scratch, idxs, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int tpk_device_status(int* status_out, int reset)

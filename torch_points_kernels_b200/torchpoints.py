@@ -38,8 +38,8 @@ def furthest_point_sample(xyz, npoint, return_xyz=False):
         number of points in the sampled set
     return_xyz : bool
         also return the coordinates of the samples, (B, npoint, 3): the same values as
-        ``xyz.gather(1, idx.long()[..., None].expand(-1, -1, 3))``, written by the sampling
-        kernel itself (an addition to the reference's signature)
+        ``xyz.gather(1, idx.long()[..., None].expand(-1, -1, 3))``, gathered by one small kernel
+        behind the sampling kernel (an addition to the reference's signature)
 
     Returns
     -------
