@@ -895,7 +895,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--in-flight", type=int, default=6, help="CUDA graphs (steps) replayed in rotation, each on its own stream")
+    ap.add_argument("--in-flight", type=int, default=8, help="CUDA graphs (steps) replayed in rotation, each on its own stream")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from Python instead of replaying CUDA graphs")
     args = ap.parse_args()
     if args.impl == "b200" and not args.only and args.workload == "sa_fp_pipeline":
