@@ -54,7 +54,8 @@ class Pipeline:
       s_geo  : everything else that only needs coordinates (ball query, three_nn, weights),
                level by level behind the FPS events;
       s_feat : the feature work (grouping and interpolation, forward and backward) behind
-               the s_geo events.
+               the s_geo events, one sub-stream per level (the levels' feature kernels are
+               independent of one another), joined on s_feat.
     With pipelined=True consecutive steps are not joined: the geometry of step i+1 (which
     depends on nothing but its input coordinates) runs while the feature work of step i is
     still in flight, as it would behind a prefetching data loader."""
@@ -72,6 +73,9 @@ class Pipeline:
         self.nstep = 0
         self.s_geo = torch.cuda.Stream(dev)
         self.s_feat = torch.cuda.Stream(dev)
+        # the feature kernels of the four levels do not depend on one another: one stream each,
+        # joined on s_feat
+        self.s_feat_level = [torch.cuda.Stream(dev) for _ in range(4)]
         self.s_copy = torch.cuda.Stream(dev)
         g = torch.Generator(device=dev).manual_seed(seed + 7)
         # upstream gradients: produced on the device by the layers above in a real model
@@ -121,6 +125,14 @@ class Pipeline:
                     t.record_stream(st)
             return t
 
+        def level_stream(l):
+            # Under graph capture the feature kernels of each level get a branch of their own.
+            # Launched eagerly they share s_feat: tensors allocated on four more streams make
+            # the caching allocator grow four more pools, which costs more than the overlap gives.
+            if not overlap:
+                return cur
+            return self.s_feat_level[l] if self.keep is not None else s_feat
+
         pts = [xyz]
         fps_idx, fps_ready = [], []
         with torch.cuda.stream(s_fps):
@@ -145,27 +157,35 @@ class Pipeline:
                 dist, idx3 = timed("three_nn_l%d" % (l + 1), lambda: tpk.three_nn(pts[l], pts[l + 1]))
                 w = 1.0 / (dist + 1e-8)
                 w = (w / w.sum(dim=2, keepdim=True)).contiguous()
-                geo.append((hand_over(nbr, s_feat), hand_over(idx3, s_feat), hand_over(w, s_feat)))
+                s_lvl = level_stream(l)
+                geo.append((hand_over(nbr, s_lvl), hand_over(idx3, s_lvl), hand_over(w, s_lvl)))
                 ev = torch.cuda.Event()
                 ev.record(s_geo)
                 geo_ready.append(ev)
 
         grads_sa, grads_fp = [], []
-        with torch.cuda.stream(s_feat):
-            for l in range(4):
+        for l in range(4):
+            s_lvl = level_stream(l)
+            with torch.cuda.stream(s_lvl):
                 if overlap:
-                    s_feat.wait_event(geo_ready[l])
+                    if s_lvl is not s_feat:
+                        s_lvl.wait_stream(s_feat)  # the inputs' readiness, as s_feat saw it at the start of the step
+                    s_lvl.wait_event(geo_ready[l])
                 nbr, idx3, w = geo[l]
                 f = sa_feat[l].requires_grad_(True)
                 grouped = timed("grouping_fwd_l%d" % (l + 1), lambda: tpk.grouping_operation(f, nbr))
                 timed("grouping_bwd_l%d" % (l + 1), lambda: grouped.backward(self.g_grouped[l]))
-                grads_sa.append(hand_over(f.grad, cur))
+                grads_sa.append(hand_over(f.grad, cur, s_feat))
                 f.grad = None
                 ff = fp_feat[l].requires_grad_(True)
                 up = timed("interp_fwd_l%d" % (l + 1), lambda: tpk.three_interpolate(ff, idx3, w))
                 timed("interp_bwd_l%d" % (l + 1), lambda: up.backward(self.g_up[l]))
-                grads_fp.append(hand_over(ff.grad, cur))
+                grads_fp.append(hand_over(ff.grad, cur, s_feat))
                 ff.grad = None
+        with torch.cuda.stream(s_feat):
+            if overlap and self.keep is not None:
+                for st in self.s_feat_level:
+                    s_feat.wait_stream(st)
             done = torch.cuda.Event()
             done.record(s_feat)
         if overlap and not pipelined:
@@ -447,6 +467,8 @@ def run_b200(args, rank, world, local_rank):
             ins[0].record_stream(pipe.s_geo)
             for t in ins[1:]:
                 t.record_stream(pipe.s_feat)
+                for st in pipe.s_feat_level:
+                    t.record_stream(st)
             fps_idx, g_sa, g_fp, _ = pipe.step(*split(ins), pipelined=True, ready=ready)
             bufs = out_bufs[i % 3]
             with torch.cuda.stream(pipe.s_feat):
