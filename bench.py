@@ -704,7 +704,7 @@ def run_workload(args):
     fps_large   B=8 clouds x N=2^20: FPS to --npoint (default 65536) + dense ball query"""
     import torch_points_kernels_b200 as tpk
     from torch_points_kernels_b200 import chamfer_dist as cd
-    from tests import data
+    from torch_points_kernels_b200 import synthetic as data
 
     dev = torch.device("cuda", 0)
     sm_mhz = 1965.0
@@ -769,7 +769,7 @@ def run_reference_cuda(args):
     except Exception as e:
         print(json.dumps({"impl": "reference_cuda", "unavailable": "points_cuda.so does not load: %s" % e}))
         return
-    from tests import data
+    from torch_points_kernels_b200 import synthetic as data
 
     dev = torch.device("cuda", 0)
     out = {"impl": "reference_cuda", "workload": args.workload, "steps": args.steps, "warmup": args.warmup}

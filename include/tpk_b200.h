@@ -48,10 +48,16 @@ TPK_API int tpk_version(void);
 TPK_API const char* tpk_last_error(void);
 
 /*
- * Sticky device-side status word of the current device: 0, or non-zero after a
- * kernel gave up a bounded wait (a cluster or grid barrier that did not complete).
+ * Sticky device-side status word of the current device: 0, or a combination of
+ *   TPK_STATUS_WAIT_ABANDONED  a kernel gave up a bounded wait (cluster exchange or bulk copy
+ *                              that did not complete within a second); its outputs are invalid;
+ *   TPK_STATUS_BAD_INDEX       a gather/scatter kernel met an index outside its tensor; the
+ *                              element was skipped (gathers write 0 for it) and nothing outside
+ *                              the caller's tensors was touched.
  * Reading it synchronises the device.  `reset` != 0 clears it after reading.
  */
+#define TPK_STATUS_WAIT_ABANDONED 1
+#define TPK_STATUS_BAD_INDEX 2
 TPK_API int tpk_device_status(int* status_out, int reset);
 
 /*
@@ -71,13 +77,15 @@ TPK_API int64_t tpk_kernel_launches(void);
  * (kernel cuda/src/sampling_gpu.cu:16-144), including the zero/1e10 fills of
  * cuda/src/sampling.cpp:14-18.
  *
- * scratch: tpk_fps_scratch_bytes(b,n,m) bytes of device memory (16-byte aligned).  Required
- * for clouds of more than 131072 points (sorted copy + running minima); optional below, where
- * it holds a spatially sorted copy that lets most warps skip most rounds (NULL: the kernel
- * without it, same result).  Content on entry is irrelevant.
+ * scratch: scratch_bytes >= tpk_fps_scratch_bytes(b,n,m) bytes of device memory (16-byte
+ * aligned).  Required for clouds of more than 131072 points (sorted copy + running minima);
+ * optional below, where it holds a spatially sorted copy that lets most of the cloud skip most
+ * rounds (NULL: the kernel without it, same result).  A buffer smaller than
+ * tpk_fps_scratch_bytes returns TPK_ERR_SCRATCH and launches nothing.  Content on entry is
+ * irrelevant.
  */
 TPK_API int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz, void* scratch,
-                                int32_t* idxs, void* stream);
+                                int64_t scratch_bytes, int32_t* idxs, void* stream);
 
 /*
  * The same, followed by a gather of the coordinates of the samples: new_xyz (b,m,3) f32,
@@ -85,7 +93,8 @@ TPK_API int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz, v
  * NULL skips it.  No counterpart in the reference.
  */
 TPK_API int tpk_furthest_point_sampling_xyz(int b, int n, int m, const float* xyz, void* scratch,
-                                    int32_t* idxs, float* new_xyz, void* stream);
+                                    int64_t scratch_bytes, int32_t* idxs, float* new_xyz,
+                                    void* stream);
 TPK_API int64_t tpk_fps_scratch_bytes(int b, int n, int m);
 
 /*

@@ -41,17 +41,33 @@ def test_invalid_arguments_return_status_without_gpu():
     assert b"Not enough points" in l.tpk_last_error()
     assert l.tpk_ball_query_dense(-1, 1, 1, 0.1, 1, None, None, None, None, None) == 1
     assert l.tpk_three_nn(1, 4, 4, None, None, None, None, None) == 1
-    assert l.tpk_furthest_point_sampling(1, 0, 2, None, None, None, None) == 1
+    assert l.tpk_furthest_point_sampling(1, 0, 2, None, None, 0, None, None) == 1
     # empty problems are no-ops
-    assert l.tpk_furthest_point_sampling(0, 10, 2, None, None, None, None) == 0
+    assert l.tpk_furthest_point_sampling(0, 10, 2, None, None, 0, None, None) == 0
     assert l.tpk_grouping(0, 4, 4, 4, 4, None, None, None, None) == 0
+
+
+def test_fps_refuses_short_scratch_without_gpu():
+    """A scratch buffer smaller than tpk_fps_scratch_bytes is refused before anything is launched
+    (the sizes are checked on the host; the pointers are never dereferenced)."""
+    l = _lib.lib()
+    need = l.tpk_fps_scratch_bytes(2, 200000, 48)
+    assert need == 2 * 200000 * 20
+    fake = ctypes.c_void_p(256)  # never dereferenced: the call fails on the size
+    for fn, extra in ((l.tpk_furthest_point_sampling, ()), (l.tpk_furthest_point_sampling_xyz, (None,))):
+        rc = fn(2, 200000, 48, fake, fake, need - 1, fake, *extra, None)
+        assert rc == 4  # TPK_ERR_SCRATCH
+        assert b"scratch of" in l.tpk_last_error()
+    # optional scratch (sorted copy of a cloud that fits on chip) is checked the same way
+    need = l.tpk_fps_scratch_bytes(16, 16384, 4096)
+    assert l.tpk_furthest_point_sampling(16, 16384, 4096, fake, fake, need // 2, fake, None) == 4
+    # and a missing buffer where one is required
+    assert l.tpk_furthest_point_sampling(2, 200000, 48, fake, None, 0, fake, None) == 4
 
 
 def test_scratch_sizes_are_host_arithmetic(monkeypatch):
     """What the callers must allocate: pure host functions, usable without a GPU."""
-    for env in ("TPK_FPS_SORTED", "TPK_FPS_FORCE_GLOBAL", "TPK_BALL_QUERY_GLOBAL_GRID", "TPK_THREE_NN_GLOBAL_GRID",
-                "TPK_NN_GLOBAL_GRID", "TPK_CHAMFER_SCAN"):
-        monkeypatch.delenv(env, raising=False)
+    monkeypatch.delenv("TPK_B200_TEST", raising=False)
     l = _lib.lib()
     # FPS: nothing for small clouds or few samples, the sorted copy (16 B/point) for clouds that stay
     # on chip, the sorted copy plus the running minima (20 B/point) above 131072 points
@@ -59,10 +75,13 @@ def test_scratch_sizes_are_host_arithmetic(monkeypatch):
     assert l.tpk_fps_scratch_bytes(4, 16384, 64) == 0
     assert l.tpk_fps_scratch_bytes(16, 16384, 4096) == 16 * 16384 * 16
     assert l.tpk_fps_scratch_bytes(2, 200000, 48) == 2 * 200000 * 20
-    monkeypatch.setenv("TPK_FPS_SORTED", "0")
+    monkeypatch.setenv("TPK_B200_TEST", "fps_unsorted")
     assert l.tpk_fps_scratch_bytes(16, 16384, 4096) == 0
     assert l.tpk_fps_scratch_bytes(2, 200000, 48) == 2 * 200000 * 4
-    monkeypatch.delenv("TPK_FPS_SORTED")
+    monkeypatch.setenv("TPK_B200_TEST", "ball_query_scan,fps_global,fps_config=2:64:8")
+    assert l.tpk_fps_scratch_bytes(2, 1000, 48) == 2 * 1000 * 20
+    assert l.tpk_ball_query_dense_scratch_bytes(16, 16384, 4096, 32) == 0
+    monkeypatch.delenv("TPK_B200_TEST")
     # ball query: one flag per centre with the grid in shared memory, the whole grid for huge clouds
     assert l.tpk_ball_query_dense_scratch_bytes(2, 256, 64, 32) == 0
     assert l.tpk_ball_query_dense_scratch_bytes(16, 16384, 4096, 32) == 16 * 4096

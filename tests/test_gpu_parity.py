@@ -36,14 +36,8 @@ def npy(t):
 
 # ------------------------------------------------------------------------------ FPS
 
-@pytest.fixture
-def fps_env():
-    old = os.environ.get("TPK_FPS_CONFIG")
-    yield
-    if old is None:
-        os.environ.pop("TPK_FPS_CONFIG", None)
-    else:
-        os.environ["TPK_FPS_CONFIG"] = old
+# kernel families of FPS on a cloud that stays on chip: without / with the spatially sorted copy
+FPS_FAMILIES = ["fps_unsorted", "fps_sorted"]
 
 
 def test_fps_known_answer(known_answers):
@@ -54,9 +48,9 @@ def test_fps_known_answer(known_answers):
 
 @pytest.mark.parametrize("B,N,m", [(3, 1000, 200), (2, 4096, 512), (2, 16384, 700), (1, 40000, 150),
                                    (1, 100000, 40), (4, 257, 257), (2, 31, 9), (5, 1, 1), (2, 2, 2)])
-@pytest.mark.parametrize("sorted_copy", ["0", "1"])
-def test_fps_matches_oracle(B, N, m, sorted_copy, monkeypatch):
-    monkeypatch.setenv("TPK_FPS_SORTED", sorted_copy)  # without / with the spatially sorted copy and warp skipping
+@pytest.mark.parametrize("family", FPS_FAMILIES)
+def test_fps_matches_oracle(B, N, m, family, monkeypatch):
+    data.use_paths(monkeypatch, family)
     x = data.unit_ball(B, N, seed=2000 + N)
     got = npy(tpk.furthest_point_sample(cu(x), m))
     np.testing.assert_array_equal(got, orc.fps(x, m))
@@ -66,23 +60,21 @@ def test_fps_matches_oracle(B, N, m, sorted_copy, monkeypatch):
 @pytest.mark.parametrize("cfg", ["1,128,32", "1,512,8", "1,256,16", "2,64,32", "2,512,4", "4,64,16",
                                  "4,256,4", "8,128,4", "8,64,8", "8,512,1", "16,64,4", "16,512,1",
                                  "16,128,2"])
-def test_fps_every_cluster_shape(cfg, fps_env, monkeypatch):
+def test_fps_every_cluster_shape(cfg, monkeypatch):
     """Same cloud through every cluster size / block size (cluster x threads x points per thread),
     with the flat and with the three-stage exchange."""
     x = data.unit_ball(3, 4000, seed=77)
     want = orc.fps(x, 300)
-    os.environ["TPK_FPS_CONFIG"] = cfg
-    for flat in ("1", "0"):
-        for sorted_copy in ("0", "1"):
-            monkeypatch.setenv("TPK_FPS_FLAT", flat)
-            monkeypatch.setenv("TPK_FPS_SORTED", sorted_copy)
+    for tree in (None, "fps_tree"):
+        for family in ("fps_unsorted", "fps_sorted"):
+            data.use_paths(monkeypatch, "fps_config=" + cfg.replace(",", ":"), tree, family)
             got = npy(tpk.furthest_point_sample(cu(x), 300))
             np.testing.assert_array_equal(got, want)
     assert _lib.device_status() == 0
 
 
 @pytest.mark.parametrize("n", [3, 8, 37, 64, 300, 700, 1000, 1500, 2048, 5000])
-def test_fps_tie_break_and_skip_rule(n, fps_env, monkeypatch):
+def test_fps_tie_break_and_skip_rule(n, monkeypatch):
     rng = np.random.default_rng(n)
     pts = np.zeros((2, n, 3), np.float32)
     pts[:, 0] = (1.0, 1.0, 1.0)
@@ -93,28 +85,25 @@ def test_fps_tie_break_and_skip_rule(n, fps_env, monkeypatch):
     m = min(n, 12)
     want = orc.fps(pts, m)
     # with fewer than bs threads per cluster a thread owns several residues of k mod bs
-    for cfg in (None, "1,64,32", "2,64,32", "2,256,16", "4,128,16", "1,128,8", "2,64,4"):
-        if cfg:
-            os.environ["TPK_FPS_CONFIG"] = cfg
-        for sorted_copy in ("0", "1"):
-            monkeypatch.setenv("TPK_FPS_SORTED", sorted_copy)
+    for cfg in (None, "1:64:32", "2:64:32", "2:256:16", "4:128:16", "1:128:8", "2:64:4"):
+        for family in FPS_FAMILIES:
+            data.use_paths(monkeypatch, cfg and "fps_config=" + cfg, family)
             np.testing.assert_array_equal(npy(tpk.furthest_point_sample(cu(pts), m)), want)
 
 
-def test_fps_sorted_copy_is_the_default_for_big_on_chip_clouds():
+def test_fps_sorted_copy_is_the_default_for_big_on_chip_clouds(monkeypatch):
+    data.use_paths(monkeypatch)
     assert _lib.lib().tpk_fps_scratch_bytes(4, 16384, 4096) == 4 * 16384 * 16
     assert _lib.lib().tpk_fps_scratch_bytes(4, 1024, 256) == 0
 
 
 @pytest.mark.parametrize("kind", ["clustered", "lattice", "planar", "nonfinite", "many_skipped"])
-@pytest.mark.parametrize("large_cloud_kernel", [False, True])
-def test_fps_sorted_copy_hard_clouds(kind, large_cloud_kernel, monkeypatch):
+@pytest.mark.parametrize("family", ["fps_sorted", "fps_sorted,fps_global"])
+def test_fps_sorted_copy_hard_clouds(kind, family, monkeypatch):
     """Warp and chunk skipping must never change a result: crowded cells, exact ties everywhere,
     a collapsed axis, coordinates that are not finite, and points the skip rule excludes.
     Both kernels that skip: the register-resident one and the one for large clouds."""
-    monkeypatch.setenv("TPK_FPS_SORTED", "1")
-    if large_cloud_kernel:
-        monkeypatch.setenv("TPK_FPS_FORCE_GLOBAL", "1")
+    data.use_paths(monkeypatch, family)
     rng = np.random.default_rng(len(kind))
     B, n, m = 2, 6000, 400
     if kind == "clustered":
@@ -143,7 +132,7 @@ def test_fps_sorted_copy_hard_clouds(kind, large_cloud_kernel, monkeypatch):
 def test_fps_large_clouds_use_scratch(B, N, m, sorted_copy, monkeypatch):
     """Clouds beyond the on-chip capacity: running minimum in global scratch, with the sorted
     copy and chunk skipping (20 bytes per point) or without (4 bytes per point)."""
-    monkeypatch.setenv("TPK_FPS_SORTED", sorted_copy)
+    data.use_paths(monkeypatch, "fps_unsorted" if sorted_copy == "0" else None)
     assert _lib.lib().tpk_fps_scratch_bytes(B, N, m) == B * N * (20 if sorted_copy == "1" else 4)
     x = data.gaussian_mixture(B, N, seed=5000 + N)
     got = npy(tpk.furthest_point_sample(cu(x), m))
@@ -154,8 +143,7 @@ def test_fps_large_clouds_use_scratch(B, N, m, sorted_copy, monkeypatch):
 @pytest.mark.parametrize("n", [3, 37, 700, 5000, 20000])
 @pytest.mark.parametrize("sorted_copy", ["1", "0"])
 def test_fps_scratch_kernel_tie_break_and_skip_rule(n, sorted_copy, monkeypatch):
-    monkeypatch.setenv("TPK_FPS_FORCE_GLOBAL", "1")
-    monkeypatch.setenv("TPK_FPS_SORTED", sorted_copy)
+    data.use_paths(monkeypatch, "fps_global", "fps_unsorted" if sorted_copy == "0" else None)
     rng = np.random.default_rng(n)
     pts = np.zeros((2, n, 3), np.float32)
     pts[:, 0] = (1.0, 1.0, 1.0)
@@ -170,12 +158,11 @@ def test_fps_scratch_kernel_tie_break_and_skip_rule(n, sorted_copy, monkeypatch)
     np.testing.assert_array_equal(npy(tpk.furthest_point_sample(cu(x), mm)), orc.fps(x, mm))
 
 
-@pytest.mark.parametrize("B,N,m,env", [(3, 1000, 200, None), (2, 16384, 700, None), (2, 16384, 700, "TPK_FPS_SORTED"),
-                                       (1, 150000, 40, None), (1, 150000, 40, "TPK_FPS_SORTED"), (4, 257, 257, None)])
+@pytest.mark.parametrize("B,N,m,env", [(3, 1000, 200, None), (2, 16384, 700, None), (2, 16384, 700, "fps_unsorted"),
+                                       (1, 150000, 40, None), (1, 150000, 40, "fps_unsorted"), (4, 257, 257, None)])
 def test_fps_returns_sampled_coordinates(B, N, m, env, monkeypatch):
-    """return_xyz: the kernels write xyz[idx] themselves (every kernel variant)."""
-    if env:
-        monkeypatch.setenv(env, "0")
+    """return_xyz: the coordinates of the samples (behind every kernel variant)."""
+    data.use_paths(monkeypatch, env)
     x = cu(data.unit_ball(B, N, seed=2100 + N))
     idx, centres = tpk.furthest_point_sample(x, m, return_xyz=True)
     np.testing.assert_array_equal(npy(idx), npy(tpk.furthest_point_sample(x, m)))
@@ -247,9 +234,8 @@ def test_ball_query_dense_grid_path_matches_oracle(case, monkeypatch):
     assert _lib.lib().tpk_ball_query_dense_scratch_bytes(B, N, M, ns) > 0
     oi, od = orc.ball_query_dense(r, ns, x, y)
     # the grid in shared memory (where it fits), the grid in global memory, the plain scan
-    for env in (None, "TPK_BALL_QUERY_GLOBAL_GRID", "TPK_BALL_QUERY_SCAN"):
-        if env:
-            monkeypatch.setenv(env, "1")
+    for env in (None, "ball_query_global_grid", "ball_query_scan"):
+        data.use_paths(monkeypatch, env)
         idx, dist = tpk.ball_query(r, ns, cu(x), cu(y), mode="dense")
         np.testing.assert_array_equal(npy(idx), oi)
         same_bits(npy(dist), od)
@@ -293,9 +279,8 @@ def test_ball_query_dense_huge_clouds_use_the_hashed_grid(kind, monkeypatch):
     need = _lib.lib().tpk_ball_query_dense_scratch_bytes(B, N, M, ns)
     assert need > B * N * 20
     oi, od = orc.ball_query_dense(r, ns, x, y)
-    for env in (None, "TPK_BALL_QUERY_GLOBAL_GRID", "TPK_BALL_QUERY_SCAN"):
-        if env:
-            monkeypatch.setenv(env, "1")
+    for env in (None, "ball_query_global_grid", "ball_query_scan"):
+        data.use_paths(monkeypatch, env)
         idx, dist = tpk.ball_query(r, ns, cu(x), cu(y), mode="dense")
         np.testing.assert_array_equal(npy(idx), oi)
         same_bits(npy(dist), od)
@@ -384,9 +369,8 @@ def test_ball_query_partial_hash_grid_matches_oracle_and_scan(case, monkeypatch)
             ns = 1
     assert _lib.lib().tpk_ball_query_partial_dense_scratch_bytes(x.shape[0], y.shape[0], r) > 0
     oi, od = orc.ball_query_partial(r, ns, x, y, bx, by)
-    for env in (None, "TPK_BALL_QUERY_SCAN"):
-        if env:
-            monkeypatch.setenv(env, "1")
+    for env in (None, "ball_query_scan"):
+        data.use_paths(monkeypatch, env)
         idx, d2 = tpk.ball_query(r, ns, cu(x), cu(y), mode="partial_dense", batch_x=cu(bx), batch_y=cu(by))
         np.testing.assert_array_equal(npy(idx), oi)
         same_bits(npy(d2), od)
@@ -454,9 +438,8 @@ def test_three_nn_grid_path_matches_oracle(name, monkeypatch):
     assert _lib.lib().tpk_three_nn_scratch_bytes(b, n, m) > 0  # the grid path is the one tested
     od2, oi = orc.three_nn(unknown, known)
     # the grid in shared memory (up to 8192 known points), then the grid in global memory
-    for env in (None, "TPK_THREE_NN_GLOBAL_GRID"):
-        if env:
-            monkeypatch.setenv(env, "1")
+    for env in (None, "three_nn_global_grid", "three_nn_scan"):
+        data.use_paths(monkeypatch, env)
         dist, idx = tpk.three_nn(cu(unknown), cu(known))
         np.testing.assert_array_equal(npy(idx), oi)
         same_bits(npy(dist), np.sqrt(od2))
@@ -464,10 +447,9 @@ def test_three_nn_grid_path_matches_oracle(name, monkeypatch):
     assert _lib.device_status() == 0
 
 
-@pytest.mark.parametrize("env", [None, "TPK_THREE_NN_GLOBAL_GRID"])
+@pytest.mark.parametrize("env", [None, "three_nn_global_grid"])
 def test_three_nn_grid_path_nonfinite_falls_back_to_scan(env, monkeypatch):
-    if env:
-        monkeypatch.setenv(env, "1")
+    data.use_paths(monkeypatch, env)
     unknown = data.unit_ball(2, 1500, seed=21).numpy().copy()
     known = data.unit_ball(2, 4096, seed=22).numpy().copy()
     unknown[0, 7, 1] = np.inf
@@ -572,7 +554,7 @@ def test_grouping_forward_backward(B, C, N, P, S, monkeypatch):
     want = orc.grouping_grad(gout, idx, N)
     np.testing.assert_allclose(npy(f.grad), want, rtol=1e-4, atol=1e-4)
     # the global-atomics fallback gives the same sums
-    monkeypatch.setenv("TPK_SCATTER_GLOBAL", "1")
+    data.use_paths(monkeypatch, "scatter_global")
     f2 = cu(feat).requires_grad_(True)
     tpk.grouping_operation(f2, cu(idx)).backward(cu(gout))
     np.testing.assert_allclose(npy(f2.grad), want, rtol=1e-4, atol=1e-4)
@@ -667,9 +649,8 @@ def test_chamfer_grid_path_matches_oracle_and_scan(case, monkeypatch):
     assert _lib.lib().tpk_chamfer_dist_scratch_bytes(B, n, m) > 0
     results = []
     # default (grid in shared memory, by layers above 8192 points), grid in global memory, scan
-    for env in (None, "TPK_NN_GLOBAL_GRID", "TPK_CHAMFER_SCAN"):
-        if env:
-            monkeypatch.setenv(env, "1")
+    for env in (None, "nn_global_grid", "chamfer_scan"):
+        data.use_paths(monkeypatch, env)
         x1, x2 = cu(c1).requires_grad_(True), cu(c2).requires_grad_(True)
         d1, d2 = cd.ChamferFunction.apply(x1, x2)
         torch.autograd.backward([d1, d2], [torch.ones_like(d1), torch.ones_like(d2)])
@@ -686,8 +667,7 @@ def test_chamfer_grid_path_matches_oracle_and_scan(case, monkeypatch):
             np.testing.assert_allclose(results[0][2], other[2], rtol=1e-4, atol=1e-4)
             np.testing.assert_allclose(results[0][3], other[3], rtol=1e-4, atol=1e-4)
     # the indices themselves, through the C ABI: grid + scratch against the plain scan
-    monkeypatch.delenv("TPK_CHAMFER_SCAN")
-    monkeypatch.delenv("TPK_NN_GLOBAL_GRID")
+    data.use_paths(monkeypatch)
     x1, x2 = cu(c1), cu(c2)
     out = []
     for use_ws in (True, False):

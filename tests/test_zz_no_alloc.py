@@ -17,15 +17,23 @@ pytestmark = pytest.mark.gpu
 
 
 def _regular(x, m):
+    """The regular entry point steered onto the same kernel (large-cloud kernel, no sorted copy)
+    through the library's test hook; the scratch is sized by the library for exactly that choice."""
     b, n = x.shape[0], x.shape[1]
     out = torch.empty((b, m), dtype=torch.int32, device=x.device)
-    scratch = torch.empty((b * n,), dtype=torch.float32, device=x.device)
-    os.environ["TPK_FPS_FORCE_GLOBAL"] = "1"   # same kernel family, caller-owned scratch
+    old = os.environ.get("TPK_B200_TEST")
+    os.environ["TPK_B200_TEST"] = "fps_global,fps_unsorted"
     try:
-        _lib.call("tpk_furthest_point_sampling", b, n, m, _lib.ptr(x), _lib.ptr(scratch), _lib.ptr(out),
+        need = _lib.lib().tpk_fps_scratch_bytes(b, n, m)
+        assert need == 4 * b * n
+        scratch = torch.empty((need,), dtype=torch.uint8, device=x.device)
+        _lib.call("tpk_furthest_point_sampling", b, n, m, _lib.ptr(x), _lib.ptr(scratch), need, _lib.ptr(out),
                   _lib.stream_of(x))
     finally:
-        os.environ.pop("TPK_FPS_FORCE_GLOBAL", None)
+        if old is None:
+            os.environ.pop("TPK_B200_TEST", None)
+        else:
+            os.environ["TPK_B200_TEST"] = old
     return out
 
 

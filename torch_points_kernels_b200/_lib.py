@@ -21,8 +21,8 @@ _ptr = ctypes.c_void_p
 
 # name -> argument types, in the order of include/tpk_b200.h
 _SIGNATURES = {
-    "tpk_furthest_point_sampling": [_c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr],
-    "tpk_furthest_point_sampling_xyz": [_c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
+    "tpk_furthest_point_sampling": [_c_int, _c_int, _c_int, _ptr, _ptr, _c_i64, _ptr, _ptr],
+    "tpk_furthest_point_sampling_xyz": [_c_int, _c_int, _c_int, _ptr, _ptr, _c_i64, _ptr, _ptr, _ptr],
     "tpk_furthest_point_sampling_static": [_c_int, _c_int, _c_int, _ptr, _ptr, _ptr],
     "tpk_ball_query_dense": [_c_int, _c_int, _c_int, _c_f32, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_ball_query_dense_ws": [_c_int, _c_int, _c_int, _c_f32, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr],

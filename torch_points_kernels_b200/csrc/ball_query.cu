@@ -283,25 +283,26 @@ extern "C" int tpk_ball_query_dense(int b, int n, int m, float radius, int nsamp
     return check_launch("ball_query_dense");
 }
 
-// TPK_BALL_QUERY_GLOBAL_GRID selects the grid in global memory where the shared-memory grid
-// would be used (comparison runs and tests of that path)
+// the test hook "ball_query_global_grid" selects the grid in global memory where the
+// shared-memory grid would be used
 static bool use_smem_grid(int b, int n, int nsample)
 {
-    return tpk::sg_ball_query_fits(b, n, nsample) && getenv("TPK_BALL_QUERY_GLOBAL_GRID") == nullptr;
+    return tpk::sg_ball_query_fits(b, n, nsample) && !tpk::test_path("ball_query_global_grid");
 }
 
 // Clouds the shared-memory grid does not take (2^18 points and more): the hashed grid in
-// global scratch.  TPK_BALL_QUERY_GLOBAL_GRID selects the older bounding-box grid in global
-// memory instead of either (comparison runs and tests of that path).
+// global scratch.  The test hook "ball_query_global_grid" selects the older bounding-box grid in
+// global memory instead of either.
 static bool use_hash_grid(int b, int n, int m)
 {
     return n >= 8192 && tpk::hash_grid_fits(static_cast<long long>(b) * n, static_cast<long long>(b) * m) &&
-           getenv("TPK_BALL_QUERY_GLOBAL_GRID") == nullptr;
+           !tpk::test_path("ball_query_global_grid");
 }
 
 extern "C" int64_t tpk_ball_query_dense_scratch_bytes(int b, int n, int m, int nsample)
 {
     if (b <= 0 || m <= 0 || nsample <= 0) return 0;
+    if (tpk::test_path("ball_query_scan")) return 0;  // test hook: the index-order scan alone
     // shared-memory grid: one flag per centre
     if (use_smem_grid(b, n, nsample)) return (static_cast<int64_t>(b) * m + 255) / 256 * 256;
     if (use_hash_grid(b, n, m))
@@ -389,11 +390,11 @@ extern "C" int tpk_ball_query_partial_dense(int64_t size_x, int64_t size_y, floa
                                static_cast<cudaStream_t>(stream));
 }
 
-// TPK_BALL_QUERY_SCAN keeps packed queries on the scan (comparison runs and tests)
+// the test hook "ball_query_scan" keeps packed queries on the scan
 static bool partial_wants_grid(int64_t size_x, int64_t size_y, float radius)
 {
     return tpk::hash_grid_fits(size_x, size_y) && radius > 0.f && radius < 1.0e18f &&
-           getenv("TPK_BALL_QUERY_SCAN") == nullptr;
+           !tpk::test_path("ball_query_scan");
 }
 
 extern "C" int64_t tpk_ball_query_partial_dense_scratch_bytes(int64_t size_x, int64_t size_y, float radius)

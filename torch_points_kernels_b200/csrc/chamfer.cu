@@ -268,14 +268,14 @@ extern "C" int tpk_chamfer_dist_f32(int b, int n, const float* xyz1, int m, cons
     return chamfer_dir_f32(b, m, xyz2, n, xyz1, dist2, idx2, nullptr, s);
 }
 
-// The grid pays from about a thousand candidates per cloud on (TPK_CHAMFER_SCAN forces the scan).
-static bool chamfer_wants_grid(int known) { return known >= 1024 && getenv("TPK_CHAMFER_SCAN") == nullptr; }
+// The grid pays from about a thousand candidates per cloud on (the test hook "chamfer_scan" forces the scan).
+static bool chamfer_wants_grid(int known) { return known >= 1024 && !tpk::test_path("chamfer_scan"); }
 
-// TPK_NN_GLOBAL_GRID keeps clouds above 8192 points on the grid in global memory
+// the test hook "nn_global_grid" keeps clouds above 8192 points on the grid in global memory
 // (comparison runs and tests of that path)
 static bool chamfer_by_layers(int b, int queries, int known)
 {
-    return tpk::sg_nn_slab_fits(b, queries, known) && getenv("TPK_NN_GLOBAL_GRID") == nullptr;
+    return tpk::sg_nn_slab_fits(b, queries, known) && !tpk::test_path("nn_global_grid");
 }
 
 // scratch of one direction: one flag per query with the grid in shared memory (whole cloud

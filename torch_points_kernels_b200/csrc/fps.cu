@@ -26,10 +26,10 @@ namespace cg = cooperative_groups;
 
 namespace tpk
 {
+TPK_DEFINE_STATUS_WORD()
+
 namespace
 {
-
-__device__ int g_dev_status = 0;
 
 constexpr int kFpsMaxThreads = 512;
 constexpr int kFpsMaxRanks = 16;
@@ -517,7 +517,7 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
             const uint32_t parity = static_cast<uint32_t>((j - 1) >> 1) & 1u;
             if (!failed && !mbar_wait_bounded(smem_u32(mbar + PAR), parity))
             {
-                if (lane == 0) atomicExch(&g_dev_status, 1);
+                if (lane == 0) atomicOr(&g_dev_status, kStatusWaitAbandoned);
                 failed = true;
             }
             int key3 = INT_MIN, k3 = 0;
@@ -876,7 +876,7 @@ __global__ void __launch_bounds__(kFpsBigThreads, 1)
             const uint32_t parity = static_cast<uint32_t>((j - 1) >> 1) & 1u;
             if (!failed && !mbar_wait_bounded(smem_u32(mbar + par), parity))
             {
-                if (lane == 0) atomicExch(&g_dev_status, 1);
+                if (lane == 0) atomicOr(&g_dev_status, kStatusWaitAbandoned);
                 failed = true;
             }
             int key3 = INT_MIN, k3 = 0;
@@ -1190,7 +1190,7 @@ __global__ void __launch_bounds__(kFpsBigThreads, 1)
             const uint32_t parity = static_cast<uint32_t>((j - 1) >> 1) & 1u;
             if (!failed && !mbar_wait_bounded(smem_u32(mbar + par), parity))
             {
-                if (lane == 0) atomicExch(&g_dev_status, 1);
+                if (lane == 0) atomicOr(&g_dev_status, kStatusWaitAbandoned);
                 failed = true;
             }
             int key3 = INT_MIN, k3 = 0;
@@ -1345,8 +1345,6 @@ bool fps_config_ok(const FpsConfig& e, int n)
 // Picks cluster size, block size and points per thread for n points per cloud: few,
 // fat threads (every warp and every CTA adds a stage to the per-round exchange), and
 // as many CTAs per cloud as keep a CTA's share near 2048-4096 points.
-bool fps_wants_sorted(int n, int m);
-
 bool fps_pick_config(int n, int m, FpsConfig* out)
 {
     FpsConfig c;
@@ -1364,11 +1362,12 @@ bool fps_pick_config(int n, int m, FpsConfig* out)
     c.ppt = round_up_pow2((per_cta + c.nthreads - 1) / c.nthreads);
     if (c.ppt < 1) c.ppt = 1;
     if (!fps_config_ok(c, n)) return false;
-    // override for tuning runs: "nranks,nthreads,ppt"
-    if (const char* env = getenv("TPK_FPS_CONFIG"))
+    // test hook "fps_config=nranks:nthreads:ppt": another cluster shape on the same cloud
+    char text[64];
+    if (test_value("fps_config", text, sizeof(text)))
     {
         FpsConfig e = c;
-        if (sscanf(env, "%d,%d,%d", &e.nranks, &e.nthreads, &e.ppt) == 3 && fps_config_ok(e, n)) c = e;
+        if (sscanf(text, "%d:%d:%d", &e.nranks, &e.nthreads, &e.ppt) == 3 && fps_config_ok(e, n)) c = e;
     }
     *out = c;
     return true;
@@ -1414,9 +1413,8 @@ int fps_launch_t(const FpsConfig& c, int b, int n, int m, int log2bs, const floa
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     // flat exchange whenever the cluster has at most 32 warps (measured 5-8 % faster per round);
-    // TPK_FPS_FLAT=0 selects the three-stage exchange for comparison runs
-    const char* flat_env = getenv("TPK_FPS_FLAT");
-    const int flat = (c.nranks > 1 && c.nranks * (c.nthreads / 32) <= 32 && !(flat_env && flat_env[0] == '0')) ? 1 : 0;
+    // test hook "fps_tree" selects the three-stage exchange
+    const int flat = (c.nranks > 1 && c.nranks * (c.nthreads / 32) <= 32 && !test_path("fps_tree")) ? 1 : 0;
     count_launches(1);
     err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, flat, xyz, sorted, idxs);
     if (err != cudaSuccess)
@@ -1446,37 +1444,48 @@ int fps_launch_s(const FpsConfig& c, int b, int n, int m, int log2bs, const floa
     return TPK_ERR_UNSUPPORTED;
 }
 
-// The sorted copy pays when a cloud has enough warps for most of them to be skipped and
-// enough rounds to earn back the sort.  TPK_FPS_SORTED=0/1 overrides for comparison runs.
-bool fps_wants_sorted(int n, int m)
+// Which kernel family a call takes.  The sorted copy pays when a cloud has enough chunks for
+// most of them to be skipped and enough rounds to earn back the sort.  Test hooks:
+// "fps_global" (large-cloud kernels on any cloud), "fps_unsorted" (no sorted copy anywhere),
+// "fps_sorted" (sorted copy whatever the size).
+enum FpsPath
 {
-    if (const char* env = getenv("TPK_FPS_SORTED")) return env[0] != '0';
-    return n >= 4096 && m >= 128;
+    kFpsOnchip,        // cluster per cloud, registers, no scratch
+    kFpsOnchipSorted,  // cluster per cloud on the sorted copy (16 B/point)
+    kFpsPruned,        // large clouds on the sorted copy (20 B/point)
+    kFpsGlobal         // large clouds, unsorted (4 B/point)
+};
+
+FpsPath fps_pick_path(int n, int m, FpsConfig* c)
+{
+    if (test_path("fps_global") || !fps_pick_config(n, m, c))
+        return (static_cast<long long>(n) <= kFpsPrunedMaxPoints && !test_path("fps_unsorted")) ? kFpsPruned
+                                                                                                  : kFpsGlobal;
+    if (test_path("fps_unsorted")) return kFpsOnchip;
+    const bool worth = test_path("fps_sorted") || (n >= 4096 && m >= 128);
+    return worth ? kFpsOnchipSorted : kFpsOnchip;
 }
 
 }  // namespace
 }  // namespace tpk
 
-// TPK_FPS_SORTED=0 keeps large clouds on the unsorted kernel too (comparison runs, tests)
-static bool fps_large_sorted(int n)
-{
-    const char* env = getenv("TPK_FPS_SORTED");
-    return static_cast<long long>(n) <= tpk::kFpsPrunedMaxPoints && !(env && env[0] == '0');
-}
-
 extern "C" int64_t tpk_fps_scratch_bytes(int b, int n, int m)
 {
     tpk::FpsConfig c;
     if (n <= 0 || b <= 0 || m <= 0) return 0;
-    if (getenv("TPK_FPS_FORCE_GLOBAL") == nullptr && tpk::fps_pick_config(n, m, &c))
-        // optional: the spatially sorted copy, (x, y, z, index) per point
-        return tpk::fps_wants_sorted(n, m) ? static_cast<int64_t>(b) * n * 16 : 0;
+    switch (tpk::fps_pick_path(n, m, &c))
+    {
+    case tpk::kFpsOnchip: return 0;
+    // optional: the spatially sorted copy, (x, y, z, index) per point
+    case tpk::kFpsOnchipSorted: return static_cast<int64_t>(b) * n * 16;
     // large clouds: the running minimum, one float per point, behind the sorted copy if one is used
-    return static_cast<int64_t>(b) * n * (fps_large_sorted(n) ? 20 : 4);
+    case tpk::kFpsPruned: return static_cast<int64_t>(b) * n * 20;
+    default: return static_cast<int64_t>(b) * n * 4;
+    }
 }
 
 extern "C" int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz, void* scratch,
-                                           int32_t* idxs, void* stream)
+                                           int64_t scratch_bytes, int32_t* idxs, void* stream)
 {
     using namespace tpk;
     TPK_REQUIRE(b >= 0 && n >= 0 && m >= 0, "fps: negative size (b=%d n=%d m=%d)", b, n, m);
@@ -1488,22 +1497,31 @@ extern "C" int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz
     int log2bs = floor_log2(n);
     if (log2bs > 9) log2bs = 9;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // a scratch buffer is either absent or large enough for the kernel that will use it
+    const int64_t want = tpk_fps_scratch_bytes(b, n, m);
+    if (scratch != nullptr && scratch_bytes < want)
+    {
+        set_error("fps: scratch of %lld bytes given, %lld needed", static_cast<long long>(scratch_bytes),
+                  static_cast<long long>(want));
+        return TPK_ERR_SCRATCH;
+    }
     FpsConfig c;
-    if (getenv("TPK_FPS_FORCE_GLOBAL") != nullptr || !fps_pick_config(n, m, &c))
+    const FpsPath path = fps_pick_path(n, m, &c);
+    if (path == kFpsPruned || path == kFpsGlobal)
     {
         if (scratch == nullptr)
         {
             set_error("fps: clouds of %d points need tpk_fps_scratch_bytes() bytes of scratch", n);
             return TPK_ERR_SCRATCH;
         }
-        if (fps_large_sorted(n))
+        if (path == kFpsPruned)
         {
             TPK_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 15u) == 0, "fps: scratch must be 16-byte aligned");
             return fps_launch_pruned(b, n, m, log2bs, xyz, scratch, idxs, s);
         }
         return fps_launch_global(b, n, m, log2bs, xyz, static_cast<float*>(scratch), idxs, s);
     }
-    if (scratch != nullptr && fps_wants_sorted(n, m) && (reinterpret_cast<uintptr_t>(scratch) & 15u) == 0)
+    if (path != kFpsOnchip && scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 15u) == 0)
     {
         float4* sorted = static_cast<float4*>(scratch);
         const int rc = fps_launch_sort(b, n, xyz, sorted, s);
@@ -1538,10 +1556,11 @@ __global__ void __launch_bounds__(256)
 }  // namespace tpk
 
 extern "C" int tpk_furthest_point_sampling_xyz(int b, int n, int m, const float* xyz, void* scratch,
-                                               int32_t* idxs, float* new_xyz, void* stream)
+                                               int64_t scratch_bytes, int32_t* idxs, float* new_xyz,
+                                               void* stream)
 {
     using namespace tpk;
-    const int rc = tpk_furthest_point_sampling(b, n, m, xyz, scratch, idxs, stream);
+    const int rc = tpk_furthest_point_sampling(b, n, m, xyz, scratch, scratch_bytes, idxs, stream);
     if (rc != TPK_OK || new_xyz == nullptr || b == 0 || m == 0) return rc;
     const long long total = static_cast<long long>(b) * m;
     const long long grid = (total + 255) / 256;
@@ -1608,22 +1627,4 @@ extern "C" int tpk_furthest_point_sampling_static(int b, int n, int m, const flo
     // the kernel writes every scratch element it later reads (its first pass sets the
     // running minima), so whatever an earlier call left behind is irrelevant
     return fps_launch_global(b, n, m, log2bs, xyz, scratch, idxs, static_cast<cudaStream_t>(stream));
-}
-
-extern "C" int tpk_device_status(int* status_out, int reset)
-{
-    int v = 0;
-    cudaError_t err = cudaMemcpyFromSymbol(&v, tpk::g_dev_status, sizeof(int));
-    if (err == cudaSuccess && reset && v != 0)
-    {
-        const int zero = 0;
-        err = cudaMemcpyToSymbol(tpk::g_dev_status, &zero, sizeof(int));
-    }
-    if (err != cudaSuccess)
-    {
-        tpk::set_error("device status: %s", cudaGetErrorString(err));
-        return TPK_ERR_CUDA;
-    }
-    if (status_out) *status_out = v;
-    return TPK_OK;
 }

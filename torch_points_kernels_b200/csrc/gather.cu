@@ -20,6 +20,8 @@
 
 namespace tpk
 {
+TPK_DEFINE_STATUS_WORD()
+
 namespace
 {
 
@@ -33,6 +35,19 @@ __device__ __forceinline__ float interp3(float p1, float w1, float p2, float w2,
 {
     return __fmaf_rn(p3, w3, __fmaf_rn(p1, w1, __fmul_rn(p2, w2)));
 }
+
+// An index as the kernels use it: the value itself when it addresses an element of a row of
+// `len` elements, -1 otherwise.  An index out of range never reaches a load, a store or an
+// atomic: gathers return 0 for it, scatters drop the contribution, and the sticky status
+// word of the device records it (the reference's torch.gather raises a device assert there).
+__device__ __forceinline__ int checked_index(long long v, int len)
+{
+    if (static_cast<unsigned long long>(v) < static_cast<unsigned long long>(len)) return static_cast<int>(v);
+    atomicOr(&g_dev_status, kStatusBadIndex);
+    return -1;
+}
+__device__ __forceinline__ float gather_or_zero(const float* row, int i) { return i >= 0 ? row[i] : 0.f; }
+__device__ __forceinline__ float ldg_or_zero(const float* row, int i) { return i >= 0 ? __ldg(row + i) : 0.f; }
 
 // ------------------------------------------------------------------ grouping forward
 
@@ -53,17 +68,17 @@ __global__ void __launch_bounds__(kGatherThreads)
     {
         const longlong2 a = __ldg(reinterpret_cast<const longlong2*>(ip));
         const longlong2 b2 = __ldg(reinterpret_cast<const longlong2*>(ip) + 1);
-        i0 = static_cast<int>(a.x);
-        i1 = static_cast<int>(a.y);
-        i2 = static_cast<int>(b2.x);
-        i3 = static_cast<int>(b2.y);
+        i0 = checked_index(a.x, n);
+        i1 = checked_index(a.y, n);
+        i2 = checked_index(b2.x, n);
+        i3 = checked_index(b2.y, n);
     }
     else
     {
-        i0 = static_cast<int>(__ldg(ip));
-        if (pos + 1 < ps) i1 = static_cast<int>(__ldg(ip + 1));
-        if (pos + 2 < ps) i2 = static_cast<int>(__ldg(ip + 2));
-        if (pos + 3 < ps) i3 = static_cast<int>(__ldg(ip + 3));
+        i0 = checked_index(__ldg(ip), n);
+        if (pos + 1 < ps) i1 = checked_index(__ldg(ip + 1), n);
+        if (pos + 2 < ps) i2 = checked_index(__ldg(ip + 2), n);
+        if (pos + 3 < ps) i3 = checked_index(__ldg(ip + 3), n);
     }
     const float* f = features + (static_cast<size_t>(bi) * c + c0) * n;
     float* o = out + (static_cast<size_t>(bi) * c + c0) * ps + pos;
@@ -71,10 +86,10 @@ __global__ void __launch_bounds__(kGatherThreads)
     for (int ch = c0; ch < c1; ++ch, f += n, o += ps)
     {
         float4 v;
-        v.x = __ldg(f + i0);
-        v.y = __ldg(f + i1);
-        v.z = __ldg(f + i2);
-        v.w = __ldg(f + i3);
+        v.x = ldg_or_zero(f, i0);
+        v.y = ldg_or_zero(f, i1);
+        v.z = ldg_or_zero(f, i2);
+        v.w = ldg_or_zero(f, i3);
         if (VEC)
             __stcs(reinterpret_cast<float4*>(o), v);
         else if (full)
@@ -93,7 +108,8 @@ __global__ void __launch_bounds__(kGatherThreads)
 // ------------------------------------------------- grouping forward, rows in shared memory
 
 // Bounded wait for a TMA bulk copy into this CTA's shared memory (parity 0 of a fresh
-// mbarrier).  Gives up after one second; the caller then skips its work.
+// mbarrier).  Gives up after one second; the caller then records it in the device status
+// word and stages the rows with plain loads instead.
 __device__ __forceinline__ bool wait_bulk_copy(uint32_t mbar)
 {
     unsigned long long t0 = 0;
@@ -161,9 +177,11 @@ __global__ void __launch_bounds__(kScatterThreads)
                     : "memory");
             }
         }
-        if (!wait_bulk_copy(bar)) return;
+        // a copy that did not arrive in time is recorded and the rows are staged with plain loads
+        use_tma = __syncthreads_or(wait_bulk_copy(bar) ? 0 : 1) == 0;
+        if (!use_tma && threadIdx.x == 0) atomicOr(&g_dev_status, kStatusWaitAbandoned);
     }
-    else
+    if (!use_tma)
     {
         for (int i = threadIdx.x; i < nrows * n; i += kScatterThreads) rows[i] = __ldg(src + i);
         __syncthreads();
@@ -177,15 +195,17 @@ __global__ void __launch_bounds__(kScatterThreads)
     {
         const longlong2 a = __ldg(reinterpret_cast<const longlong2*>(ib + p));
         const longlong2 b2 = __ldg(reinterpret_cast<const longlong2*>(ib + p) + 1);
-        const int i0 = static_cast<int>(a.x), i1 = static_cast<int>(a.y);
-        const int i2 = static_cast<int>(b2.x), i3 = static_cast<int>(b2.y);
+        const int i0 = checked_index(a.x, n), i1 = checked_index(a.y, n);
+        const int i2 = checked_index(b2.x, n), i3 = checked_index(b2.y, n);
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
         {
             if (r < nrows)
             {
                 const float* row = rows + static_cast<size_t>(r) * n;
-                __stcs(reinterpret_cast<float4*>(ob + r * ps + p), make_float4(row[i0], row[i1], row[i2], row[i3]));
+                __stcs(reinterpret_cast<float4*>(ob + r * ps + p),
+                       make_float4(gather_or_zero(row, i0), gather_or_zero(row, i1), gather_or_zero(row, i2),
+                                   gather_or_zero(row, i3)));
             }
         }
     }
@@ -248,7 +268,7 @@ __global__ void __launch_bounds__(kGatherThreads)
 #pragma unroll
         for (int k = 0; k < 3; ++k)
         {
-            id[t][k] = __ldg(idx + o + k);
+            id[t][k] = checked_index(__ldg(idx + o + k), m);
             w[t][k] = __ldg(weight + o + k);
         }
     }
@@ -260,8 +280,8 @@ __global__ void __launch_bounds__(kGatherThreads)
         float r[4];
 #pragma unroll
         for (int t = 0; t < 4; ++t)
-            r[t] = interp3(__ldg(f + id[t][0]), w[t][0], __ldg(f + id[t][1]), w[t][1],
-                           __ldg(f + id[t][2]), w[t][2]);
+            r[t] = interp3(ldg_or_zero(f, id[t][0]), w[t][0], ldg_or_zero(f, id[t][1]), w[t][1],
+                           ldg_or_zero(f, id[t][2]), w[t][2]);
         if (VEC)
             __stcs(reinterpret_cast<float4*>(o), make_float4(r[0], r[1], r[2], r[3]));
         else
@@ -312,9 +332,10 @@ __global__ void __launch_bounds__(kGatherThreads)
                 "l"(src), "r"(bytes), "r"(bar)
                 : "memory");
         }
-        if (!wait_bulk_copy(bar)) return;
+        use_tma = __syncthreads_or(wait_bulk_copy(bar) ? 0 : 1) == 0;
+        if (!use_tma && threadIdx.x == 0) atomicOr(&g_dev_status, kStatusWaitAbandoned);
     }
-    else
+    if (!use_tma)
     {
         for (int i = threadIdx.x; i < nrows * m; i += kGatherThreads) rows[i] = __ldg(src + i);
         __syncthreads();
@@ -332,7 +353,8 @@ __global__ void __launch_bounds__(kGatherThreads)
         {
             const int4 a = __ldg(reinterpret_cast<const int4*>(idx + o) + t);
             const float4 b4 = __ldg(reinterpret_cast<const float4*>(weight + o) + t);
-            id[4 * t + 0] = a.x; id[4 * t + 1] = a.y; id[4 * t + 2] = a.z; id[4 * t + 3] = a.w;
+            id[4 * t + 0] = checked_index(a.x, m); id[4 * t + 1] = checked_index(a.y, m);
+            id[4 * t + 2] = checked_index(a.z, m); id[4 * t + 3] = checked_index(a.w, m);
             w[4 * t + 0] = b4.x; w[4 * t + 1] = b4.y; w[4 * t + 2] = b4.z; w[4 * t + 3] = b4.w;
         }
         float* op = out + (static_cast<size_t>(bi) * c + c0) * n + j0;
@@ -345,8 +367,8 @@ __global__ void __launch_bounds__(kGatherThreads)
                 float v[4];
 #pragma unroll
                 for (int t = 0; t < 4; ++t)
-                    v[t] = interp3(row[id[3 * t + 0]], w[3 * t + 0], row[id[3 * t + 1]], w[3 * t + 1],
-                                   row[id[3 * t + 2]], w[3 * t + 2]);
+                    v[t] = interp3(gather_or_zero(row, id[3 * t + 0]), w[3 * t + 0], gather_or_zero(row, id[3 * t + 1]),
+                                   w[3 * t + 1], gather_or_zero(row, id[3 * t + 2]), w[3 * t + 2]);
                 __stcs(reinterpret_cast<float4*>(op + static_cast<size_t>(r) * n), make_float4(v[0], v[1], v[2], v[3]));
             }
         }
@@ -394,7 +416,7 @@ int launch_interp_fwd_rows(int b, int c, int m, int n, const float* points, cons
 // indices and weights each).
 template <bool INTERP>
 __global__ void __launch_bounds__(kScatterThreads)
-    scatter_rows_kernel(int c, int row_len, long long src_len, int rows,
+    scatter_rows_kernel(int c, int row_len, long long src_len, int rows, int vec_ok,
                         const float* __restrict__ grad_out, const void* __restrict__ idx_v,
                         const float* __restrict__ weight, float* __restrict__ grad_small)
 {
@@ -407,7 +429,7 @@ __global__ void __launch_bounds__(kScatterThreads)
     __syncthreads();
 
     const float* g = grad_out + (static_cast<size_t>(bi) * c + c0) * src_len;
-    const bool vec = (src_len % 4 == 0);
+    const bool vec = (src_len % 4 == 0) && vec_ok != 0;  // 16-byte loads need aligned inputs
     if (vec)
     {
         for (long long p = static_cast<long long>(threadIdx.x) * 4; p < src_len;
@@ -418,16 +440,16 @@ __global__ void __launch_bounds__(kScatterThreads)
                 const int64_t* ip = static_cast<const int64_t*>(idx_v) + static_cast<size_t>(bi) * src_len + p;
                 const longlong2 a = __ldg(reinterpret_cast<const longlong2*>(ip));
                 const longlong2 b2 = __ldg(reinterpret_cast<const longlong2*>(ip) + 1);
-                const int i0 = static_cast<int>(a.x), i1 = static_cast<int>(a.y);
-                const int i2 = static_cast<int>(b2.x), i3 = static_cast<int>(b2.y);
+                const int i0 = checked_index(a.x, row_len), i1 = checked_index(a.y, row_len);
+                const int i2 = checked_index(b2.x, row_len), i3 = checked_index(b2.y, row_len);
                 for (int r = 0; r < nrows; ++r)
                 {
                     const float4 v = __ldcs(reinterpret_cast<const float4*>(g + r * src_len + p));
                     float* a_r = acc + r * row_len;
-                    atomicAdd(a_r + i0, v.x);
-                    atomicAdd(a_r + i1, v.y);
-                    atomicAdd(a_r + i2, v.z);
-                    atomicAdd(a_r + i3, v.w);
+                    if (i0 >= 0) atomicAdd(a_r + i0, v.x);
+                    if (i1 >= 0) atomicAdd(a_r + i1, v.y);
+                    if (i2 >= 0) atomicAdd(a_r + i2, v.z);
+                    if (i3 >= 0) atomicAdd(a_r + i3, v.w);
                 }
             }
             else
@@ -443,7 +465,8 @@ __global__ void __launch_bounds__(kScatterThreads)
                 {
                     const int4 a = __ldg(reinterpret_cast<const int4*>(ip) + t);
                     const float4 b4 = __ldg(reinterpret_cast<const float4*>(wp) + t);
-                    id[4 * t + 0] = a.x; id[4 * t + 1] = a.y; id[4 * t + 2] = a.z; id[4 * t + 3] = a.w;
+                    id[4 * t + 0] = checked_index(a.x, row_len); id[4 * t + 1] = checked_index(a.y, row_len);
+                    id[4 * t + 2] = checked_index(a.z, row_len); id[4 * t + 3] = checked_index(a.w, row_len);
                     w[4 * t + 0] = b4.x; w[4 * t + 1] = b4.y; w[4 * t + 2] = b4.z; w[4 * t + 3] = b4.w;
                 }
                 for (int r = 0; r < nrows; ++r)
@@ -455,7 +478,7 @@ __global__ void __launch_bounds__(kScatterThreads)
                     for (int t = 0; t < 4; ++t)
 #pragma unroll
                         for (int k = 0; k < 3; ++k)
-                            atomicAdd(a_r + id[3 * t + k], __fmul_rn(gv[t], w[3 * t + k]));
+                            if (id[3 * t + k] >= 0) atomicAdd(a_r + id[3 * t + k], __fmul_rn(gv[t], w[3 * t + k]));
                 }
             }
         }
@@ -466,9 +489,10 @@ __global__ void __launch_bounds__(kScatterThreads)
         {
             if (!INTERP)
             {
-                const int i0 = static_cast<int>(
-                    __ldg(static_cast<const int64_t*>(idx_v) + static_cast<size_t>(bi) * src_len + p));
-                for (int r = 0; r < nrows; ++r) atomicAdd(acc + r * row_len + i0, g[r * src_len + p]);
+                const int i0 = checked_index(
+                    __ldg(static_cast<const int64_t*>(idx_v) + static_cast<size_t>(bi) * src_len + p), row_len);
+                if (i0 >= 0)
+                    for (int r = 0; r < nrows; ++r) atomicAdd(acc + r * row_len + i0, g[r * src_len + p]);
             }
             else
             {
@@ -479,7 +503,10 @@ __global__ void __launch_bounds__(kScatterThreads)
                     const float gv = g[r * src_len + p];
 #pragma unroll
                     for (int k = 0; k < 3; ++k)
-                        atomicAdd(acc + r * row_len + __ldg(ip + k), __fmul_rn(gv, __ldg(weight + o + k)));
+                    {
+                        const int ik = checked_index(__ldg(ip + k), row_len);
+                        if (ik >= 0) atomicAdd(acc + r * row_len + ik, __fmul_rn(gv, __ldg(weight + o + k)));
+                    }
                 }
             }
         }
@@ -535,7 +562,7 @@ __global__ void __launch_bounds__(kScatterThreads)
         {
             if (set + u * NWARPS < nfull)  // warp-uniform
             {
-                id[u] = static_cast<int>(__ldg(ip + u * (NWARPS * 32)));
+                id[u] = checked_index(__ldg(ip + u * (NWARPS * 32)), row_len);
 #pragma unroll
                 for (int r = 0; r < ROWS; ++r) v[u][r] = __ldcs(gp[r] + u * (NWARPS * 32));
             }
@@ -562,7 +589,7 @@ __global__ void __launch_bounds__(kScatterThreads)
                     }
                 }
             }
-            if (mine)
+            if (mine && id[u] >= 0)  // an index out of range (-1) is dropped, with everything folded into it
             {
 #pragma unroll
                 for (int r = 0; r < ROWS; ++r)
@@ -579,10 +606,11 @@ __global__ void __launch_bounds__(kScatterThreads)
         const long long p = nfull * 32 + lane;
         if (p < src_len)
         {
-            const int i0 = static_cast<int>(__ldg(idx + static_cast<size_t>(bi) * src_len + p));
-            for (int r = 0; r < nrows; ++r)
-                atomicAdd(acc + r * row_len + i0,
-                          grad_out[(static_cast<size_t>(bi) * c + c0 + r) * src_len + p]);
+            const int i0 = checked_index(__ldg(idx + static_cast<size_t>(bi) * src_len + p), row_len);
+            if (i0 >= 0)
+                for (int r = 0; r < nrows; ++r)
+                    atomicAdd(acc + r * row_len + i0,
+                              grad_out[(static_cast<size_t>(bi) * c + c0 + r) * src_len + p]);
         }
     }
     __syncthreads();
@@ -655,7 +683,8 @@ __global__ void __launch_bounds__(THREADS)
     for (int j = threadIdx.x; j < n; j += THREADS)
     {
         const size_t o = (static_cast<size_t>(bi) * n + j) * 3;
-        const int i0 = __ldg(idx + o), i1 = __ldg(idx + o + 1), i2 = __ldg(idx + o + 2);
+        const int i0 = checked_index(__ldg(idx + o), m), i1 = checked_index(__ldg(idx + o + 1), m),
+                  i2 = checked_index(__ldg(idx + o + 2), m);
         const float w0 = __ldg(weight + o), w1 = __ldg(weight + o + 1), w2 = __ldg(weight + o + 2);
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
@@ -664,9 +693,9 @@ __global__ void __launch_bounds__(THREADS)
             {
                 const float gv = __ldcs(g + static_cast<size_t>(r) * n + j);
                 float* a = acc + r * m;
-                atomicAdd(a + i0, __fmul_rn(gv, w0));
-                atomicAdd(a + i1, __fmul_rn(gv, w1));
-                atomicAdd(a + i2, __fmul_rn(gv, w2));
+                if (i0 >= 0) atomicAdd(a + i0, __fmul_rn(gv, w0));
+                if (i1 >= 0) atomicAdd(a + i1, __fmul_rn(gv, w1));
+                if (i2 >= 0) atomicAdd(a + i2, __fmul_rn(gv, w2));
             }
         }
     }
@@ -715,14 +744,14 @@ __global__ void __launch_bounds__(kGatherThreads)
     int id[3];
     float w[3] = {1.f, 1.f, 1.f};
     if (!INTERP)
-        id[0] = static_cast<int>(__ldg(static_cast<const int64_t*>(idx_v) + static_cast<size_t>(bi) * src_len + p));
+        id[0] = checked_index(__ldg(static_cast<const int64_t*>(idx_v) + static_cast<size_t>(bi) * src_len + p), row_len);
     else
     {
         const size_t o = (static_cast<size_t>(bi) * src_len + p) * 3;
 #pragma unroll
         for (int k = 0; k < 3; ++k)
         {
-            id[k] = __ldg(static_cast<const int32_t*>(idx_v) + o + k);
+            id[k] = checked_index(__ldg(static_cast<const int32_t*>(idx_v) + o + k), row_len);
             w[k] = __ldg(weight + o + k);
         }
     }
@@ -731,14 +760,19 @@ __global__ void __launch_bounds__(kGatherThreads)
         const float gv = __ldg(grad_out + (static_cast<size_t>(bi) * c + ch) * src_len + p);
         float* dst = grad_small + (static_cast<size_t>(bi) * c + ch) * row_len;
         if (!INTERP)
-            atomicAdd(dst + id[0], gv);
+        {
+            if (id[0] >= 0) atomicAdd(dst + id[0], gv);
+        }
         else
         {
 #pragma unroll
-            for (int k = 0; k < 3; ++k) atomicAdd(dst + id[k], __fmul_rn(gv, w[k]));
+            for (int k = 0; k < 3; ++k)
+                if (id[k] >= 0) atomicAdd(dst + id[k], __fmul_rn(gv, w[k]));
         }
     }
 }
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <bool INTERP>
 int launch_scatter(int b, int c, int row_len, long long src_len, const float* grad_out,
@@ -746,7 +780,7 @@ int launch_scatter(int b, int c, int row_len, long long src_len, const float* gr
                    const char* what)
 {
     const size_t row_bytes = static_cast<size_t>(row_len) * sizeof(float);
-    const bool force_global = getenv("TPK_SCATTER_GLOBAL") != nullptr;
+    const bool force_global = test_path("scatter_global");
     if (row_bytes <= kRowSmemBudget && !force_global)
     {
         int rows = static_cast<int>(kRowSmemBudget / row_bytes);
@@ -769,8 +803,9 @@ int launch_scatter(int b, int c, int row_len, long long src_len, const float* gr
         }
         const long long grid = static_cast<long long>(b) * ((c + rows - 1) / rows);
         TPK_REQUIRE(grid < (1ll << 31), "%s: too many rows", what);
+        const int vec_ok = aligned16(grad_out) && aligned16(idx) && (weight == nullptr || aligned16(weight));
         count_launches(1), kernel<<<static_cast<unsigned>(grid), kScatterThreads, smem, s>>>(
-            c, row_len, src_len, rows, grad_out, idx, weight, grad_small);
+            c, row_len, src_len, rows, vec_ok, grad_out, idx, weight, grad_small);
         return check_launch(what);
     }
     cudaError_t err = cudaMemsetAsync(grad_small, 0, static_cast<size_t>(b) * c * row_bytes, s);
@@ -788,8 +823,6 @@ int launch_scatter(int b, int c, int row_len, long long src_len, const float* gr
     return check_launch(what);
 }
 
-bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-
 }  // namespace
 }  // namespace tpk
 
@@ -804,13 +837,11 @@ extern "C" int tpk_grouping(int b, int c, int n, int npoint, int nsample, const 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const size_t row_bytes = static_cast<size_t>(n) * sizeof(float);
     if (ps % 4 == 0 && aligned16(idx) && aligned16(out) && row_bytes <= kRowSmemBudget && ps >= 4096 &&
-        static_cast<long long>(b) * c <= 65535 && getenv("TPK_GATHER_DIRECT") == nullptr)
+        static_cast<long long>(b) * c <= 65535 && !test_path("gather_direct"))
     {
         // rows per CTA: as many as fit the shared memory of one SM, at most 4 (the indices
         // of a position are loaded once for all rows of the CTA)
-        size_t budget = kRowSmemBudget;
-        if (const char* env = getenv("TPK_GROUP_FWD_KB")) budget = static_cast<size_t>(atoi(env)) * 1024;
-        int rows = static_cast<int>(budget / row_bytes);
+        int rows = static_cast<int>(kRowSmemBudget / row_bytes);
         if (rows < 1) rows = 1;
         if (rows > 4) rows = 4;
         if (rows > c) rows = c;
@@ -855,16 +886,14 @@ extern "C" int tpk_grouping_grad(int b, int c, int n, int npoint, int nsample,
         return TPK_OK;
     }
     TPK_REQUIRE(grad_out && idx, "grouping_grad: NULL pointer");
-    TPK_REQUIRE(aligned16(grad_out) && aligned16(idx), "grouping_grad: inputs must be 16-byte aligned");
     const size_t row_bytes = static_cast<size_t>(n) * sizeof(float);
-    if (row_bytes <= kRowSmemBudget && getenv("TPK_SCATTER_GLOBAL") == nullptr)
+    // (no alignment beyond the elements' own is needed: a view at an odd offset is fine)
+    if (row_bytes <= kRowSmemBudget && !test_path("scatter_global"))
     {
         // rows per CTA: as many as fit 32 KB, at least one, at most 4, fewer when that would
         // leave SMs without a CTA (measured on the pipeline's shapes: the atomics want many
         // resident warps more than they want the indices shared between rows)
-        size_t budget = 32 * 1024;
-        if (const char* env = getenv("TPK_GROUP_BWD_KB")) budget = static_cast<size_t>(atoi(env)) * 1024;
-        int rows = static_cast<int>(budget / row_bytes);
+        int rows = static_cast<int>(32 * 1024 / row_bytes);
         if (rows < 1) rows = 1;
         if (rows > 4) rows = 4;
         if (rows > c) rows = c;
@@ -892,7 +921,7 @@ extern "C" int tpk_three_interpolate(int b, int c, int m, int n, const float* po
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (n % 4 == 0 && aligned16(out) && aligned16(idx) && aligned16(weight) && n >= 1024 &&
         static_cast<size_t>(m) * 4 * 4 <= kRowSmemBudget && static_cast<long long>(b) * c <= 65535 &&
-        getenv("TPK_GATHER_DIRECT") == nullptr)
+        !test_path("gather_direct"))
     {
         if (c >= 8 && static_cast<size_t>(m) * 4 * 8 <= 128 * 1024)
             return launch_interp_fwd_rows<8>(b, c, m, n, points, idx, weight, out, s);
@@ -929,23 +958,8 @@ extern "C" int tpk_three_interpolate_grad(int b, int c, int n, int m, const floa
         return TPK_OK;
     }
     TPK_REQUIRE(grad_out && idx && weight, "three_interpolate_grad: NULL pointer");
-    TPK_REQUIRE(aligned16(grad_out) && aligned16(idx) && aligned16(weight),
-                "three_interpolate_grad: inputs must be 16-byte aligned");
-    if (static_cast<size_t>(m) * 4 * 4 <= 64 * 1024 && getenv("TPK_SCATTER_GLOBAL") == nullptr)
+    if (static_cast<size_t>(m) * 4 * 4 <= 64 * 1024 && !test_path("scatter_global"))
     {
-        const bool many = false;
-        if (const char* env = getenv("TPK_INTERP_BWD_CFG"))  // tuning runs: "rows,threads"
-        {
-            int rows = 0, threads = 0;
-            if (sscanf(env, "%d,%d", &rows, &threads) == 2 && static_cast<size_t>(m) * 4 * rows <= 64 * 1024)
-            {
-#define TPK_IB(R, T) if (rows == R && threads == T) return launch_interp_bwd_rows<R, T>(b, c, m, n, grad_out, idx, weight, grad_points, s)
-                TPK_IB(2, 128); TPK_IB(2, 256); TPK_IB(4, 128); TPK_IB(4, 256); TPK_IB(4, 512);
-                TPK_IB(8, 128); TPK_IB(8, 256); TPK_IB(8, 512); TPK_IB(2, 512); TPK_IB(1, 256); TPK_IB(1, 512);
-#undef TPK_IB
-            }
-        }
-        (void)many;
         // measured on the four pipeline shapes: few rows per CTA and small blocks win (many
         // resident CTAs hide the latency of the index/weight loads and of the atomics)
         if (n >= 8192) return launch_interp_bwd_rows<1, 256>(b, c, m, n, grad_out, idx, weight, grad_points, s);

@@ -362,22 +362,23 @@ extern "C" int tpk_three_nn(int b, int n, int m, const float* unknown, const flo
     return launch_three_nn_scan(b, n, m, unknown, known, dist2, idx, nullptr, static_cast<cudaStream_t>(stream));
 }
 
-// TPK_THREE_NN_GLOBAL_GRID selects the grid in global memory where the shared-memory grid
-// would be used (comparison runs and tests of that path)
+// the test hook "three_nn_global_grid" selects the grid in global memory where the
+// shared-memory grid would be used
 static bool three_nn_smem_grid(int m)
 {
-    return tpk::sg_three_nn_fits(m) && getenv("TPK_THREE_NN_GLOBAL_GRID") == nullptr;
+    return tpk::sg_three_nn_fits(m) && !tpk::test_path("three_nn_global_grid");
 }
 
 // above 8192 known points: the shared-memory grid by layers
 static bool three_nn_by_layers(int b, int n, int m)
 {
-    return tpk::sg_nn_slab_fits(b, n, m) && getenv("TPK_THREE_NN_GLOBAL_GRID") == nullptr;
+    return tpk::sg_nn_slab_fits(b, n, m) && !tpk::test_path("three_nn_global_grid");
 }
 
 extern "C" int64_t tpk_three_nn_scratch_bytes(int b, int n, int m)
 {
     if (b <= 0 || n <= 0) return 0;
+    if (tpk::test_path("three_nn_scan")) return 0;  // test hook: the scan alone
     // shared-memory grid: one flag per unknown point
     if (three_nn_smem_grid(m) || three_nn_by_layers(b, n, m)) return (static_cast<int64_t>(b) * n + 255) / 256 * 256;
     if (m < 4096) return 0;

@@ -17,6 +17,41 @@ void set_error(const char* fmt, ...);
 // stream capture); every launch site calls it.
 void count_launches(int k);
 
+// Test hook: is `name` (or `name=value`) listed in the environment variable TPK_B200_TEST?
+// The only environment variable the library reads; it selects kernels the size heuristics
+// would not pick, for tests that compare kernel families.
+bool test_path(const char* name);
+bool test_value(const char* name, char* out, size_t cap);
+
+// Bits of the sticky device status word reported by tpk_device_status().
+constexpr int kStatusWaitAbandoned = 1;  // a bounded wait (cluster exchange, bulk copy) ran out
+constexpr int kStatusBadIndex = 2;       // an index outside its tensor was skipped
+
+typedef cudaError_t (*StatusReader)(int* value, int reset);
+struct StatusRegistrar
+{
+    explicit StatusRegistrar(StatusReader r);
+};
+
+// Gives the including .cu file its own device status word `g_dev_status` and hooks it into
+// tpk_device_status().  Use once per file, at namespace tpk scope.
+#define TPK_DEFINE_STATUS_WORD()                                                                   \
+    namespace                                                                                      \
+    {                                                                                              \
+    __device__ int g_dev_status = 0;                                                               \
+    cudaError_t read_status_word(int* value, int reset)                                            \
+    {                                                                                              \
+        cudaError_t err = cudaMemcpyFromSymbol(value, g_dev_status, sizeof(int));                  \
+        if (err == cudaSuccess && reset && *value != 0)                                            \
+        {                                                                                          \
+            const int zero = 0;                                                                    \
+            err = cudaMemcpyToSymbol(g_dev_status, &zero, sizeof(int));                            \
+        }                                                                                          \
+        return err;                                                                                \
+    }                                                                                              \
+    StatusRegistrar g_status_registrar(read_status_word);                                          \
+    }
+
 constexpr unsigned kFullMask = 0xffffffffu;
 constexpr int kNumSmsB200 = 148;
 

@@ -5,7 +5,6 @@ torch_points_kernels/torchpoints.py of the reference; every op runs a hand-writt
 sm_100a kernel through the C ABI in include/tpk_b200.h.  Tensors must live on a CUDA
 device: there is no CPU path.
 """
-import os
 from typing import Optional
 
 import torch
@@ -61,7 +60,7 @@ def furthest_point_sample(xyz, npoint, return_xyz=False):
         if need > 0:
             scratch = torch.empty((need,), dtype=torch.uint8, device=xyz.device)
         _lib.call("tpk_furthest_point_sampling_xyz", b, n, npoint, _lib.ptr(xyz), _lib.ptr(scratch),
-                  _lib.ptr(out), _lib.ptr(new_xyz), _lib.stream_of(xyz))
+                  max(need, 0), _lib.ptr(out), _lib.ptr(new_xyz), _lib.stream_of(xyz))
     return (out, new_xyz) if return_xyz else out
 
 
@@ -93,7 +92,7 @@ def three_nn(unknown, known):
     idx = torch.empty((b, n, 3), dtype=torch.int32, device=unknown.device)
     with torch.cuda.device(unknown.device):
         need = _lib.lib().tpk_three_nn_scratch_bytes(b, n, m)
-        if need > 0 and not os.environ.get("TPK_THREE_NN_SCAN"):
+        if need > 0:
             # many known points: uniform-grid search with scratch (same results as the scan)
             scratch = torch.empty((need,), dtype=torch.uint8, device=unknown.device)
             _lib.call("tpk_three_nn_ws", b, n, m, _lib.ptr(unknown), _lib.ptr(known), _lib.ptr(dist2),
@@ -222,7 +221,7 @@ def ball_query_dense(radius, nsample, xyz, new_xyz, batch_xyz=None, batch_new_xy
     dist = torch.empty((b, m, nsample), dtype=torch.float32, device=new_xyz.device)
     with torch.cuda.device(new_xyz.device):
         need = _lib.lib().tpk_ball_query_dense_scratch_bytes(b, n, m, int(nsample))
-        if need > 0 and not os.environ.get("TPK_BALL_QUERY_SCAN"):
+        if need > 0:
             # large clouds: uniform-grid search with scratch (same results as the scan)
             scratch = torch.empty((need,), dtype=torch.uint8, device=new_xyz.device)
             _lib.call("tpk_ball_query_dense_ws", b, n, m, float(radius), int(nsample), _lib.ptr(new_xyz),
