@@ -226,6 +226,26 @@ TPK_API int tpk_knn_partial_dense(int64_t size_s, int64_t size_q, int k, const f
                           const float* query, const int64_t* batch_s, const int64_t* batch_q,
                           int64_t* idx, float* dist2, void* stream);
 
+/*
+ * Both searches with caller scratch: the support points are binned on a hashed uniform grid
+ * (cells keyed by segment or cloud and cell; cell width chosen on the device from the support
+ * points' density) and a query grows a block of cells around itself until its k-th best distance
+ * is provably final; what the grid cannot settle (sparse regions, segments with fewer than k
+ * points, coordinates that are not finite) is answered by the scan.  Results are identical to
+ * tpk_knn_dense / tpk_knn_partial_dense bit for bit, equal distances included.  scratch:
+ * tpk_knn_*_scratch_bytes(...) bytes, 256-byte aligned; when that returns 0 (small problems) or
+ * scratch is NULL the call is the plain one.  The algorithmic counterpart in the reference is its
+ * kd-tree, cpu/src/neighbors.cpp:295-339.
+ */
+TPK_API int tpk_knn_dense_ws(int b, int n, int m, int k, const float* support, const float* query,
+                             int64_t* idx, float* dist2, void* scratch, int64_t scratch_bytes, void* stream);
+TPK_API int64_t tpk_knn_dense_scratch_bytes(int b, int n, int m, int k);
+TPK_API int tpk_knn_partial_dense_ws(int64_t size_s, int64_t size_q, int k, const float* support,
+                                     const float* query, const int64_t* batch_s, const int64_t* batch_q,
+                                     int64_t* idx, float* dist2, void* scratch, int64_t scratch_bytes,
+                                     void* stream);
+TPK_API int64_t tpk_knn_partial_dense_scratch_bytes(int64_t size_s, int64_t size_q, int k);
+
 /* ------------------------------------------------------------- interpolation ---- */
 
 /*

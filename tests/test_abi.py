@@ -148,3 +148,31 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libtpk_b200.so")
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _lib.lib()
+
+
+def test_segment_vectors_are_validated_like_the_reference_cpu_path(known_answers):
+    """The reference's CPU path raises RuntimeError when batch_x and batch_y name different
+    numbers of segments (its own test vector); the same check, plus sortedness, is what the
+    wrappers run under TPK_B200_DEBUG.  The check itself needs no GPU."""
+    ka = known_answers["ball_query_partial_segment_mismatch"]
+    bx, by = torch.tensor(ka["batch_x"]), torch.tensor(ka["batch_y"])
+    with pytest.raises(RuntimeError, match="same number of samples"):
+        _lib.check_segments(bx, by)
+    _lib.check_segments(torch.tensor([0, 0, 1, 1]), torch.tensor([0, 1]))
+    with pytest.raises(RuntimeError, match="sorted"):
+        _lib.check_segments(torch.tensor([0, 1, 0, 1]), torch.tensor([0, 1]))
+    with pytest.raises(RuntimeError, match="sorted"):
+        _lib.check_segments(torch.tensor([0, 1]), torch.tensor([-1, 1]))
+    _lib.check_segments(torch.tensor([], dtype=torch.long), torch.tensor([], dtype=torch.long))
+
+
+def test_test_hook_tokens(monkeypatch):
+    """TPK_B200_TEST is a comma-separated token list; a token only matches whole names."""
+    l = _lib.lib()
+    monkeypatch.setenv("TPK_B200_TEST", "fps_unsortedx,xfps_unsorted")
+    assert l.tpk_fps_scratch_bytes(16, 16384, 4096) == 16 * 16384 * 16
+    monkeypatch.setenv("TPK_B200_TEST", "three_nn_scan,fps_unsorted")
+    assert l.tpk_fps_scratch_bytes(16, 16384, 4096) == 0
+    assert l.tpk_three_nn_scratch_bytes(16, 16384, 4096) == 0
+    monkeypatch.delenv("TPK_B200_TEST")
+    assert l.tpk_three_nn_scratch_bytes(16, 16384, 4096) > 0

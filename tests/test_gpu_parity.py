@@ -34,6 +34,14 @@ def npy(t):
     return t.detach().cpu().numpy()
 
 
+def _guarded(fn):
+    """Runs fn, returns the device status word it left (and clears it)."""
+    assert _lib.device_status() == 0
+    out = fn()
+    torch.cuda.synchronize()
+    return out, _lib.device_status()
+
+
 # ------------------------------------------------------------------------------ FPS
 
 # kernel families of FPS on a cloud that stays on chip: without / with the spatially sorted copy
@@ -504,6 +512,73 @@ def test_knn_partial_matches_per_segment_dense():
     same_bits(npy(d2), od)
 
 
+@pytest.mark.parametrize("B,N,M,k", [(2, 20000, 3000, 16), (1, 6000, 6000, 3), (3, 5000, 700, 64), (2, 9000, 100, 33),
+                                     (1, 50000, 2000, 1)])
+@pytest.mark.parametrize("kind", ["ball", "planes", "clustered"])
+def test_knn_dense_grid_matches_scan_and_oracle(B, N, M, k, kind, monkeypatch):
+    """Clouds large enough for the hashed grid: its answers (and the scan's behind it) against the
+    oracle, and grid against scan bit for bit.  Uniform, planar (the density estimate is
+    volumetric) and clustered clouds with queries far from every point."""
+    g = data.gen(N + k)
+    if kind == "ball":
+        s, q = data.unit_ball(B, N, seed=N + k), data.unit_ball(B, M, seed=M + k)
+    elif kind == "planes":
+        s = torch.rand(B, N, 3, generator=g) * 5
+        s[..., 2] = torch.randint(0, 3, (B, N), generator=g).float() + 0.01 * torch.randn(B, N, generator=g)
+        q = s[:, torch.randperm(N, generator=g)[:M]].contiguous() + 0.001
+    else:
+        s = 0.02 * torch.randn(B, N, 3, generator=g) + torch.randint(0, 3, (B, N, 1), generator=g) * 4.0
+        q = torch.rand(B, M, 3, generator=g) * 10 - 1   # most queries sit in empty space
+    assert _lib.lib().tpk_knn_dense_scratch_bytes(B, N, M, k) > 0
+    idx, d2 = tpk.knn(cu(s), cu(q), k)
+    data.use_paths(monkeypatch, "knn_scan")
+    assert _lib.lib().tpk_knn_dense_scratch_bytes(B, N, M, k) == 0
+    sidx, sd2 = tpk.knn(cu(s), cu(q), k)
+    np.testing.assert_array_equal(npy(idx), npy(sidx))
+    same_bits(npy(d2), npy(sd2))
+    if N * M * B <= 150_000_000:
+        oi, od = orc.knn(s, q, k)
+        np.testing.assert_array_equal(npy(idx), oi)
+        same_bits(npy(d2), od)
+
+
+def test_knn_grid_ties_and_nonfinite(monkeypatch):
+    """Exact distance ties (lattice points: index order among equals) and coordinates that are
+    not finite go through the grid and its fallback with the scan's results."""
+    g = data.gen(3)
+    s = torch.randint(0, 12, (2, 5000, 3), generator=g).float() * 0.25
+    q = torch.randint(0, 12, (2, 400, 3), generator=g).float() * 0.25 + 0.125
+    s[0, 17, 0] = float("inf")
+    s[1, 9, 2] = float("nan")
+    q[0, 3, 1] = float("nan")
+    q[1, 5, 0] = float("-inf")
+    idx, d2 = tpk.knn(cu(s), cu(q), 8)
+    data.use_paths(monkeypatch, "knn_scan")
+    sidx, sd2 = tpk.knn(cu(s), cu(q), 8)
+    np.testing.assert_array_equal(npy(idx), npy(sidx))
+    same_bits(npy(d2), npy(sd2))
+
+
+@pytest.mark.parametrize("k", [16, 40])
+def test_knn_partial_grid_matches_scan_and_oracle(k, monkeypatch):
+    x, y, bx, by = data.packed_planes(n_scenes=5, lo=3000, hi=9000, seed=3005)
+    # a short segment (fewer support points than k), one without queries, one far away
+    x = torch.cat([x, torch.rand(5, 3)]); bx = torch.cat([bx, torch.full((5,), 5)])
+    y = torch.cat([y, torch.rand(2, 3)]); by = torch.cat([by, torch.full((2,), 5)])
+    x = torch.cat([x, torch.rand(30, 3)]); bx = torch.cat([bx, torch.full((30,), 7)])
+    x = torch.cat([x, torch.rand(3000, 3) + 50]); bx = torch.cat([bx, torch.full((3000,), 8)])
+    y = torch.cat([y, torch.rand(40, 3) + 50]); by = torch.cat([by, torch.full((40,), 8)])
+    assert _lib.lib().tpk_knn_partial_dense_scratch_bytes(x.shape[0], y.shape[0], k) > 0
+    idx, d2 = tpk.knn(cu(x), cu(y), k, batch_support=cu(bx), batch_pos=cu(by))
+    oi, od = orc.knn_segmented(x, y, bx, by, k)
+    np.testing.assert_array_equal(npy(idx), oi)
+    same_bits(npy(d2), od)
+    data.use_paths(monkeypatch, "knn_scan")
+    sidx, sd2 = tpk.knn(cu(x), cu(y), k, batch_support=cu(bx), batch_pos=cu(by))
+    np.testing.assert_array_equal(npy(idx), npy(sidx))
+    same_bits(npy(d2), npy(sd2))
+
+
 # --------------------------------------------------------- interpolation and grouping
 
 @pytest.mark.parametrize("B,C,m,n", [(4, 64, 1024, 4096), (2, 7, 33, 1001), (3, 30, 100, 500), (2, 130, 64, 256)])
@@ -757,3 +832,125 @@ def test_empty_and_degenerate_inputs():
     assert (npy(d1) == 0).all() and tuple(d2.shape) == (2, 0)
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
+
+
+# ------------------------------------------------------------- indices that address nothing
+
+@pytest.mark.parametrize("path", [None, "gather_direct"])
+def test_grouping_skips_indices_out_of_range(path, monkeypatch):
+    """An index outside [0, n) reads nothing (the output element is 0) and is recorded in the
+    status word.  The bad values are chosen so that, without the guard, they would still land
+    inside memory this test owns: n is the first element of the next feature row (rows of a
+    CTA are adjacent in shared memory, and the tensor is a slice of a larger allocation), -1
+    the last element of the row before."""
+    data.use_paths(monkeypatch, path)
+    B, C, n, npoint, ns = 2, 8, 4096, 512, 32
+    g = data.gen(11)
+    big = torch.randn(B * C * n + 2 * n, generator=g).to(DEV)
+    feat = big[n:n + B * C * n].view(B, C, n)          # owned memory on both sides of the tensor
+    idx = torch.randint(0, n, (B, npoint, ns), generator=g).to(DEV)
+    good = npy(tpk.grouping_operation(feat, idx))
+    bad = idx.clone()
+    bad[0, 3, 5] = n
+    bad[1, 100, 0] = -1
+    bad[1, 7, 31] = 1 << 40
+    out, status = _guarded(lambda: tpk.grouping_operation(feat, bad))
+    assert status == 2
+    out = npy(out)
+    mask = np.zeros((B, npoint, ns), bool)
+    mask[0, 3, 5] = mask[1, 100, 0] = mask[1, 7, 31] = True
+    assert (out[:, :, :, :][np.broadcast_to(mask[:, None], out.shape)] == 0).all()
+    keep = ~np.broadcast_to(mask[:, None], out.shape)
+    np.testing.assert_array_equal(out[keep], good[keep])
+
+
+@pytest.mark.parametrize("path", [None, "scatter_global"])
+def test_grouping_grad_drops_indices_out_of_range(path, monkeypatch):
+    data.use_paths(monkeypatch, path)
+    B, C, n, npoint, ns = 2, 8, 2048, 256, 32
+    g = data.gen(12)
+    idx = torch.randint(0, n, (B, npoint, ns), generator=g)
+    gout = torch.randn(B, C, npoint, ns, generator=g)
+    bad = idx.clone()
+    bad[0, 3, 5] = n       # the next row of the CTA's shared-memory accumulator
+    bad[1, 100, 0] = -1
+    big = torch.zeros(B * C * n + 2 * n, device=DEV)
+    grad = big[n:n + B * C * n].view(B, C, n)
+    gout_d, bad_d = cu(gout), cu(bad)  # kept alive: the call only sees their addresses
+
+    def run():
+        _lib.call("tpk_grouping_grad", B, C, n, npoint, ns, _lib.ptr(gout_d), _lib.ptr(bad_d), _lib.ptr(grad),
+                  _lib.stream_of(grad))
+        return grad
+    _, status = _guarded(run)
+    assert status == 2
+    # everything but the two dropped contributions, and nothing outside the tensor
+    want_idx = idx.clone().numpy()
+    w = gout.clone().numpy()
+    w[0, :, 3, 5] = 0
+    w[1, :, 100, 0] = 0
+    np.testing.assert_allclose(npy(grad), orc.grouping_grad(w, want_idx, n), rtol=1e-4, atol=1e-4)
+    assert float(big[:n].abs().max()) == 0 and float(big[n + B * C * n:].abs().max()) == 0
+
+
+@pytest.mark.parametrize("path", [None, "gather_direct", "scatter_global"])
+def test_three_interpolate_skips_indices_out_of_range(path, monkeypatch):
+    data.use_paths(monkeypatch, path)
+    B, C, m, n = 2, 16, 512, 2048
+    g = data.gen(13)
+    big = torch.randn(B * C * m + 2 * m, generator=g).to(DEV)
+    feat = big[m:m + B * C * m].view(B, C, m).requires_grad_(True)
+    idx = torch.randint(0, m, (B, n, 3), generator=g).int()
+    w = torch.rand(B, n, 3, generator=g)
+    bad = idx.clone()
+    bad[0, 9, 1] = m
+    bad[1, 1000, 2] = -1
+    out, status = _guarded(lambda: tpk.three_interpolate(feat, cu(bad), cu(w)))
+    assert status == 2
+    w0 = w.clone()
+    w0[0, 9, 1] = 0
+    w0[1, 1000, 2] = 0
+    np.testing.assert_allclose(npy(out), orc.three_interpolate(npy(feat), idx.numpy(), w0.numpy()), rtol=1e-5, atol=1e-6)
+    gout = torch.randn(B, C, n, generator=g)
+    _, status = _guarded(lambda: out.backward(cu(gout)))
+    assert status == 2
+    np.testing.assert_allclose(npy(feat.grad), orc.three_interpolate_grad(gout, idx.numpy(), w0.numpy(), m),
+                               rtol=1e-4, atol=1e-4)
+
+
+def test_debug_mode_raises_on_bad_inputs(monkeypatch):
+    """TPK_B200_DEBUG: segment vectors are validated on the host (as the reference's CPU path
+    does) and a skipped index becomes an exception right after the call."""
+    monkeypatch.setenv("TPK_B200_DEBUG", "1")
+    x = cu(data.unit_ball(1, 100, seed=1)[0])
+    with pytest.raises(RuntimeError, match="same number of samples"):
+        tpk.ball_query(1.0, 2, x, x[:1].contiguous(), mode="PARTIAL_DENSE",
+                       batch_x=cu(torch.tensor([0] * 50 + [1] * 50)), batch_y=cu(torch.tensor([0])))
+    with pytest.raises(RuntimeError, match="sorted"):
+        tpk.knn(x, x[:2].contiguous(), 2, batch_support=cu(torch.tensor([1] * 50 + [0] * 50)),
+                batch_pos=cu(torch.tensor([0, 1])))
+    feat = cu(torch.randn(1, 4, 100))
+    idx = cu(torch.full((1, 8, 4), 100, dtype=torch.long))
+    with pytest.raises(RuntimeError, match="index outside"):
+        tpk.grouping_operation(feat, idx)
+    assert _lib.device_status() == 0
+
+
+def test_backward_accepts_views_at_odd_offsets():
+    """grad_out / idx that are contiguous views starting off a 16-byte boundary work in the
+    backward passes as they do in the forward ones."""
+    g = data.gen(14)
+    B, C, n, npoint, ns = 1, 4, 300, 37, 3
+    idx = torch.randint(0, n, (B * npoint * ns + 1,), generator=g).to(DEV)[1:].view(B, npoint, ns)
+    gout = torch.randn(B * C * npoint * ns + 1, generator=g).to(DEV)[1:].view(B, C, npoint, ns)
+    grad = torch.empty(B, C, n, device=DEV)
+    _lib.call("tpk_grouping_grad", B, C, n, npoint, ns, _lib.ptr(gout), _lib.ptr(idx), _lib.ptr(grad), _lib.stream_of(grad))
+    np.testing.assert_allclose(npy(grad), orc.grouping_grad(npy(gout), npy(idx), n), rtol=1e-4, atol=1e-4)
+    m, nn = 64, 101
+    idx3 = torch.randint(0, m, (B * nn * 3 + 1,), generator=g).int().to(DEV)[1:].view(B, nn, 3)
+    w = torch.rand(B * nn * 3 + 1, generator=g).to(DEV)[1:].view(B, nn, 3)
+    go = torch.randn(B * C * nn + 1, generator=g).to(DEV)[1:].view(B, C, nn)
+    gp = torch.empty(B, C, m, device=DEV)
+    _lib.call("tpk_three_interpolate_grad", B, C, nn, m, _lib.ptr(go), _lib.ptr(idx3), _lib.ptr(w), _lib.ptr(gp),
+              _lib.stream_of(gp))
+    np.testing.assert_allclose(npy(gp), orc.three_interpolate_grad(npy(go), npy(idx3), npy(w), m), rtol=1e-4, atol=1e-4)

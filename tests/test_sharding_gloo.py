@@ -50,6 +50,47 @@ def _worker(rank, world, port, out):
         dist.destroy_process_group()
 
 
+def _worker_backward(rank, world, port, out):
+    """Loss and gradients of the sharded chamfer reduction, per rank, against the
+    single-process mean over the whole batch; plus the final gather of per-rank outputs
+    (5 items over 2 ranks: uneven blocks)."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(6)
+        d1 = torch.rand(5, 40, generator=g)
+        d2 = torch.rand(5, 30, generator=g)
+        # single-process reference: loss and gradient of mean + mean w.r.t. every entry
+        r1, r2 = d1.clone().requires_grad_(True), d2.clone().requires_grad_(True)
+        ((r1 * r1).mean() + (r2 * r2).mean()).backward()
+        lo, hi = sharding.shard_range(5, rank, world)
+        a, b = d1[lo:hi].clone().requires_grad_(True), d2[lo:hi].clone().requires_grad_(True)
+        loss = sharding.reduce_chamfer_loss((a * a).sum(), a.numel(), (b * b).sum(), b.numel())
+        loss.backward()
+        want = float((d1 * d1).mean() + (d2 * d2).mean())
+        gathered = sharding.gather_outputs(d1[lo:hi], n_items=5)
+        out.put((rank, abs(float(loss) - want), float((a.grad - r1.grad[lo:hi]).abs().max()),
+                 float((b.grad - r2.grad[lo:hi]).abs().max()), bool(torch.equal(gathered, d1))))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_chamfer_loss_backward_and_final_gather_two_ranks():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_backward, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for _, dloss, dg1, dg2, same in results:
+        assert dloss < 1e-6 and dg1 < 1e-8 and dg2 < 1e-8 and same
+
+
 def test_chamfer_loss_reduction_two_ranks():
     ctx = mp.get_context("spawn")
     out = ctx.Queue()

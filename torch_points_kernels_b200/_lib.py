@@ -34,6 +34,8 @@ _SIGNATURES = {
     "tpk_three_nn_ws": [_c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr],
     "tpk_knn_dense": [_c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_knn_partial_dense": [_c_i64, _c_i64, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
+    "tpk_knn_dense_ws": [_c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr],
+    "tpk_knn_partial_dense_ws": [_c_i64, _c_i64, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr],
     "tpk_three_interpolate": [_c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_three_interpolate_grad": [_c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_grouping": [_c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr],
@@ -47,7 +49,8 @@ _SIGNATURES = {
 EXPORTS = sorted(list(_SIGNATURES) + ["tpk_version", "tpk_last_error", "tpk_device_status", "tpk_kernel_launches", "tpk_fps_scratch_bytes",
                                        "tpk_fps_static_capacity", "tpk_ball_query_dense_scratch_bytes",
                                        "tpk_three_nn_scratch_bytes", "tpk_chamfer_dist_scratch_bytes",
-                                       "tpk_ball_query_partial_dense_scratch_bytes"])
+                                       "tpk_ball_query_partial_dense_scratch_bytes", "tpk_knn_dense_scratch_bytes",
+                                       "tpk_knn_partial_dense_scratch_bytes"])
 
 
 def lib():
@@ -81,6 +84,10 @@ def lib():
         handle.tpk_chamfer_dist_scratch_bytes.restype = _c_i64
         handle.tpk_three_nn_scratch_bytes.argtypes = [_c_int, _c_int, _c_int]
         handle.tpk_three_nn_scratch_bytes.restype = _c_i64
+        handle.tpk_knn_dense_scratch_bytes.argtypes = [_c_int, _c_int, _c_int, _c_int]
+        handle.tpk_knn_dense_scratch_bytes.restype = _c_i64
+        handle.tpk_knn_partial_dense_scratch_bytes.argtypes = [_c_i64, _c_i64, _c_int]
+        handle.tpk_knn_partial_dense_scratch_bytes.restype = _c_i64
         handle.tpk_fps_static_capacity.argtypes = []
         handle.tpk_fps_static_capacity.restype = _c_i64
         _lib = handle
@@ -122,6 +129,36 @@ def check_float(t, name):
 def check_int(t, name):
     if t.is_floating_point() or t.is_complex() or t.dtype == torch.bool:
         raise RuntimeError("%s must be an int tensor" % name)
+
+
+def debug_checks():
+    """True when TPK_B200_DEBUG is set to anything but 0: the wrappers then validate what the
+    kernels take on trust (segment vectors) at the price of a device-to-host copy, and read
+    the device status word after every call."""
+    return os.environ.get("TPK_B200_DEBUG", "0") not in ("", "0")
+
+
+def check_segments(batch_x, batch_y):
+    """What the reference's CPU path verifies about packed batches (cpu/src/ball_query.cpp:86-88:
+    both vectors name the same number of segments) plus what every implementation assumes
+    (segment ids sorted ascending, non-negative).  Works on tensors of any device; on CUDA
+    tensors it synchronises, which is why the wrappers only call it under TPK_B200_DEBUG."""
+    for t, name in ((batch_x, "batch_x"), (batch_y, "batch_y")):
+        if t.numel() == 0:
+            continue
+        if bool((t[1:] < t[:-1]).any()) or int(t[0]) < 0:
+            raise RuntimeError("%s must hold sorted, non-negative segment ids" % name)
+    if batch_x.numel() and batch_y.numel() and int(batch_x[-1]) != int(batch_y[-1]):
+        raise RuntimeError("Both batches need to have the same number of samples.")
+
+
+def raise_on_device_status(what):
+    """Debug mode: turn a non-zero device status word into an exception right after the call."""
+    v = device_status()
+    if v & 2:
+        raise RuntimeError("%s: an index outside its tensor was skipped" % what)
+    if v & 1:
+        raise RuntimeError("%s: a kernel gave up a bounded wait" % what)
 
 
 def device_status(reset=True):

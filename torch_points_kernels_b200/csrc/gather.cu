@@ -40,11 +40,17 @@ __device__ __forceinline__ float interp3(float p1, float w1, float p2, float w2,
 // `len` elements, -1 otherwise.  An index out of range never reaches a load, a store or an
 // atomic: gathers return 0 for it, scatters drop the contribution, and the sticky status
 // word of the device records it (the reference's torch.gather raises a device assert there).
-__device__ __forceinline__ int checked_index(long long v, int len)
+// `bad` collects the finding in a register; the kernel reports it once, on its way out
+// (report_bad), so that no atomic sits between the loads of the streaming loops.
+__device__ __forceinline__ int checked_index(long long v, int len, bool& bad)
 {
-    if (static_cast<unsigned long long>(v) < static_cast<unsigned long long>(len)) return static_cast<int>(v);
-    atomicOr(&g_dev_status, kStatusBadIndex);
-    return -1;
+    const bool ok = static_cast<unsigned long long>(v) < static_cast<unsigned long long>(len);
+    bad |= !ok;
+    return ok ? static_cast<int>(v) : -1;
+}
+__device__ __forceinline__ void report_bad(bool bad)
+{
+    if (bad) atomicOr(&g_dev_status, kStatusBadIndex);
 }
 __device__ __forceinline__ float gather_or_zero(const float* row, int i) { return i >= 0 ? row[i] : 0.f; }
 __device__ __forceinline__ float ldg_or_zero(const float* row, int i) { return i >= 0 ? __ldg(row + i) : 0.f; }
@@ -62,23 +68,24 @@ __global__ void __launch_bounds__(kGatherThreads)
     const long long pos = (static_cast<long long>(blockIdx.x) * kGatherThreads + threadIdx.x) * 4;
     if (pos >= ps) return;
     const int64_t* ip = idx + static_cast<size_t>(bi) * ps + pos;
+    bool bad = false;
     int i0, i1 = 0, i2 = 0, i3 = 0;
     const bool full = VEC || pos + 3 < ps;
     if (VEC)
     {
         const longlong2 a = __ldg(reinterpret_cast<const longlong2*>(ip));
         const longlong2 b2 = __ldg(reinterpret_cast<const longlong2*>(ip) + 1);
-        i0 = checked_index(a.x, n);
-        i1 = checked_index(a.y, n);
-        i2 = checked_index(b2.x, n);
-        i3 = checked_index(b2.y, n);
+        i0 = checked_index(a.x, n, bad);
+        i1 = checked_index(a.y, n, bad);
+        i2 = checked_index(b2.x, n, bad);
+        i3 = checked_index(b2.y, n, bad);
     }
     else
     {
-        i0 = checked_index(__ldg(ip), n);
-        if (pos + 1 < ps) i1 = checked_index(__ldg(ip + 1), n);
-        if (pos + 2 < ps) i2 = checked_index(__ldg(ip + 2), n);
-        if (pos + 3 < ps) i3 = checked_index(__ldg(ip + 3), n);
+        i0 = checked_index(__ldg(ip), n, bad);
+        if (pos + 1 < ps) i1 = checked_index(__ldg(ip + 1), n, bad);
+        if (pos + 2 < ps) i2 = checked_index(__ldg(ip + 2), n, bad);
+        if (pos + 3 < ps) i3 = checked_index(__ldg(ip + 3), n, bad);
     }
     const float* f = features + (static_cast<size_t>(bi) * c + c0) * n;
     float* o = out + (static_cast<size_t>(bi) * c + c0) * ps + pos;
@@ -103,6 +110,7 @@ __global__ void __launch_bounds__(kGatherThreads)
             if (pos + 2 < ps) o[2] = v.z;
         }
     }
+    report_bad(bad);
 }
 
 // ------------------------------------------------- grouping forward, rows in shared memory
@@ -191,12 +199,13 @@ __global__ void __launch_bounds__(kScatterThreads)
     const long long p1 = min(ps, p0 + chunk);
     const int64_t* ib = idx + static_cast<size_t>(bi) * ps;
     float* ob = out + (static_cast<size_t>(bi) * c + c0) * ps;
+    bool bad = false;
     for (long long p = p0 + static_cast<long long>(threadIdx.x) * 4; p < p1; p += kScatterThreads * 4)
     {
         const longlong2 a = __ldg(reinterpret_cast<const longlong2*>(ib + p));
         const longlong2 b2 = __ldg(reinterpret_cast<const longlong2*>(ib + p) + 1);
-        const int i0 = checked_index(a.x, n), i1 = checked_index(a.y, n);
-        const int i2 = checked_index(b2.x, n), i3 = checked_index(b2.y, n);
+        const int i0 = checked_index(a.x, n, bad), i1 = checked_index(a.y, n, bad);
+        const int i2 = checked_index(b2.x, n, bad), i3 = checked_index(b2.y, n, bad);
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
         {
@@ -209,6 +218,7 @@ __global__ void __launch_bounds__(kScatterThreads)
             }
         }
     }
+    report_bad(bad);
 }
 
 template <int ROWS>
@@ -258,6 +268,7 @@ __global__ void __launch_bounds__(kGatherThreads)
     const int c1 = min(c, c0 + kChanChunk);
     const int j0 = (blockIdx.x * kGatherThreads + threadIdx.x) * 4;
     if (j0 >= n) return;
+    bool bad = false;
     int id[4][3];
     float w[4][3];
 #pragma unroll
@@ -268,7 +279,7 @@ __global__ void __launch_bounds__(kGatherThreads)
 #pragma unroll
         for (int k = 0; k < 3; ++k)
         {
-            id[t][k] = checked_index(__ldg(idx + o + k), m);
+            id[t][k] = checked_index(__ldg(idx + o + k), m, bad);
             w[t][k] = __ldg(weight + o + k);
         }
     }
@@ -291,6 +302,7 @@ __global__ void __launch_bounds__(kGatherThreads)
                 if (j0 + t < n) o[t] = r[t];
         }
     }
+    report_bad(bad);
 }
 
 // --------------------------------------- three_interpolate forward, rows in shared memory
@@ -343,6 +355,7 @@ __global__ void __launch_bounds__(kGatherThreads)
 
     const int j_begin = blockIdx.x * chunk;
     const int j_end = min(n, j_begin + chunk);
+    bool bad = false;
     for (int j0 = j_begin + threadIdx.x * 4; j0 < j_end; j0 += kGatherThreads * 4)
     {
         const size_t o = (static_cast<size_t>(bi) * n + j0) * 3;  // multiple of 12: 16-byte aligned
@@ -353,8 +366,8 @@ __global__ void __launch_bounds__(kGatherThreads)
         {
             const int4 a = __ldg(reinterpret_cast<const int4*>(idx + o) + t);
             const float4 b4 = __ldg(reinterpret_cast<const float4*>(weight + o) + t);
-            id[4 * t + 0] = checked_index(a.x, m); id[4 * t + 1] = checked_index(a.y, m);
-            id[4 * t + 2] = checked_index(a.z, m); id[4 * t + 3] = checked_index(a.w, m);
+            id[4 * t + 0] = checked_index(a.x, m, bad); id[4 * t + 1] = checked_index(a.y, m, bad);
+            id[4 * t + 2] = checked_index(a.z, m, bad); id[4 * t + 3] = checked_index(a.w, m, bad);
             w[4 * t + 0] = b4.x; w[4 * t + 1] = b4.y; w[4 * t + 2] = b4.z; w[4 * t + 3] = b4.w;
         }
         float* op = out + (static_cast<size_t>(bi) * c + c0) * n + j0;
@@ -373,6 +386,7 @@ __global__ void __launch_bounds__(kGatherThreads)
             }
         }
     }
+    report_bad(bad);
 }
 
 template <int ROWS>
@@ -429,6 +443,7 @@ __global__ void __launch_bounds__(kScatterThreads)
     __syncthreads();
 
     const float* g = grad_out + (static_cast<size_t>(bi) * c + c0) * src_len;
+    bool bad = false;
     const bool vec = (src_len % 4 == 0) && vec_ok != 0;  // 16-byte loads need aligned inputs
     if (vec)
     {
@@ -440,8 +455,8 @@ __global__ void __launch_bounds__(kScatterThreads)
                 const int64_t* ip = static_cast<const int64_t*>(idx_v) + static_cast<size_t>(bi) * src_len + p;
                 const longlong2 a = __ldg(reinterpret_cast<const longlong2*>(ip));
                 const longlong2 b2 = __ldg(reinterpret_cast<const longlong2*>(ip) + 1);
-                const int i0 = checked_index(a.x, row_len), i1 = checked_index(a.y, row_len);
-                const int i2 = checked_index(b2.x, row_len), i3 = checked_index(b2.y, row_len);
+                const int i0 = checked_index(a.x, row_len, bad), i1 = checked_index(a.y, row_len, bad);
+                const int i2 = checked_index(b2.x, row_len, bad), i3 = checked_index(b2.y, row_len, bad);
                 for (int r = 0; r < nrows; ++r)
                 {
                     const float4 v = __ldcs(reinterpret_cast<const float4*>(g + r * src_len + p));
@@ -465,8 +480,8 @@ __global__ void __launch_bounds__(kScatterThreads)
                 {
                     const int4 a = __ldg(reinterpret_cast<const int4*>(ip) + t);
                     const float4 b4 = __ldg(reinterpret_cast<const float4*>(wp) + t);
-                    id[4 * t + 0] = checked_index(a.x, row_len); id[4 * t + 1] = checked_index(a.y, row_len);
-                    id[4 * t + 2] = checked_index(a.z, row_len); id[4 * t + 3] = checked_index(a.w, row_len);
+                    id[4 * t + 0] = checked_index(a.x, row_len, bad); id[4 * t + 1] = checked_index(a.y, row_len, bad);
+                    id[4 * t + 2] = checked_index(a.z, row_len, bad); id[4 * t + 3] = checked_index(a.w, row_len, bad);
                     w[4 * t + 0] = b4.x; w[4 * t + 1] = b4.y; w[4 * t + 2] = b4.z; w[4 * t + 3] = b4.w;
                 }
                 for (int r = 0; r < nrows; ++r)
@@ -490,7 +505,7 @@ __global__ void __launch_bounds__(kScatterThreads)
             if (!INTERP)
             {
                 const int i0 = checked_index(
-                    __ldg(static_cast<const int64_t*>(idx_v) + static_cast<size_t>(bi) * src_len + p), row_len);
+                    __ldg(static_cast<const int64_t*>(idx_v) + static_cast<size_t>(bi) * src_len + p), row_len, bad);
                 if (i0 >= 0)
                     for (int r = 0; r < nrows; ++r) atomicAdd(acc + r * row_len + i0, g[r * src_len + p]);
             }
@@ -504,7 +519,7 @@ __global__ void __launch_bounds__(kScatterThreads)
 #pragma unroll
                     for (int k = 0; k < 3; ++k)
                     {
-                        const int ik = checked_index(__ldg(ip + k), row_len);
+                        const int ik = checked_index(__ldg(ip + k), row_len, bad);
                         if (ik >= 0) atomicAdd(acc + r * row_len + ik, __fmul_rn(gv, __ldg(weight + o + k)));
                     }
                 }
@@ -514,6 +529,7 @@ __global__ void __launch_bounds__(kScatterThreads)
     __syncthreads();
     float* dst = grad_small + (static_cast<size_t>(bi) * c + c0) * row_len;
     for (int i = threadIdx.x; i < nrows * row_len; i += kScatterThreads) dst[i] = acc[i];
+    report_bad(bad);
 }
 
 // ------------------------------------------------------ grouping backward, shared rows
@@ -544,6 +560,7 @@ __global__ void __launch_bounds__(kScatterThreads)
     __syncthreads();
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    bool bad = false;
     const int seg_first = lane & ~(SEG - 1);
     const long long nfull = src_len / 32;  // whole 32-position sets
     // this lane's element of set `warp`; sets advance by NWARPS per step
@@ -562,7 +579,7 @@ __global__ void __launch_bounds__(kScatterThreads)
         {
             if (set + u * NWARPS < nfull)  // warp-uniform
             {
-                id[u] = checked_index(__ldg(ip + u * (NWARPS * 32)), row_len);
+                id[u] = checked_index(__ldg(ip + u * (NWARPS * 32)), row_len, bad);
 #pragma unroll
                 for (int r = 0; r < ROWS; ++r) v[u][r] = __ldcs(gp[r] + u * (NWARPS * 32));
             }
@@ -606,7 +623,7 @@ __global__ void __launch_bounds__(kScatterThreads)
         const long long p = nfull * 32 + lane;
         if (p < src_len)
         {
-            const int i0 = checked_index(__ldg(idx + static_cast<size_t>(bi) * src_len + p), row_len);
+            const int i0 = checked_index(__ldg(idx + static_cast<size_t>(bi) * src_len + p), row_len, bad);
             if (i0 >= 0)
                 for (int r = 0; r < nrows; ++r)
                     atomicAdd(acc + r * row_len + i0,
@@ -616,6 +633,7 @@ __global__ void __launch_bounds__(kScatterThreads)
     __syncthreads();
     float* dst = grad_small + (static_cast<size_t>(bi) * c + c0) * row_len;
     for (int i = threadIdx.x; i < nrows * row_len; i += kScatterThreads) dst[i] = acc[i];
+    report_bad(bad);
 }
 
 template <int ROWS, int SEG>
@@ -680,11 +698,12 @@ __global__ void __launch_bounds__(THREADS)
     __syncthreads();
 
     const float* g = grad_out + (static_cast<size_t>(bi) * c + c0) * n;
+    bool bad = false;
     for (int j = threadIdx.x; j < n; j += THREADS)
     {
         const size_t o = (static_cast<size_t>(bi) * n + j) * 3;
-        const int i0 = checked_index(__ldg(idx + o), m), i1 = checked_index(__ldg(idx + o + 1), m),
-                  i2 = checked_index(__ldg(idx + o + 2), m);
+        const int i0 = checked_index(__ldg(idx + o), m, bad), i1 = checked_index(__ldg(idx + o + 1), m, bad),
+                  i2 = checked_index(__ldg(idx + o + 2), m, bad);
         const float w0 = __ldg(weight + o), w1 = __ldg(weight + o + 1), w2 = __ldg(weight + o + 2);
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
@@ -703,6 +722,7 @@ __global__ void __launch_bounds__(THREADS)
     __syncthreads();
     float* dst = grad_points + (static_cast<size_t>(bi) * c + c0) * m;
     for (int i = threadIdx.x; i < nrows * m; i += THREADS) dst[i] = acc[i];
+    report_bad(bad);
 }
 
 template <int ROWS, int THREADS>
@@ -741,17 +761,18 @@ __global__ void __launch_bounds__(kGatherThreads)
     const int c1 = min(c, c0 + kChanChunk);
     const long long p = static_cast<long long>(blockIdx.x) * kGatherThreads + threadIdx.x;
     if (p >= src_len) return;
+    bool bad = false;
     int id[3];
     float w[3] = {1.f, 1.f, 1.f};
     if (!INTERP)
-        id[0] = checked_index(__ldg(static_cast<const int64_t*>(idx_v) + static_cast<size_t>(bi) * src_len + p), row_len);
+        id[0] = checked_index(__ldg(static_cast<const int64_t*>(idx_v) + static_cast<size_t>(bi) * src_len + p), row_len, bad);
     else
     {
         const size_t o = (static_cast<size_t>(bi) * src_len + p) * 3;
 #pragma unroll
         for (int k = 0; k < 3; ++k)
         {
-            id[k] = checked_index(__ldg(static_cast<const int32_t*>(idx_v) + o + k), row_len);
+            id[k] = checked_index(__ldg(static_cast<const int32_t*>(idx_v) + o + k), row_len, bad);
             w[k] = __ldg(weight + o + k);
         }
     }
@@ -770,6 +791,7 @@ __global__ void __launch_bounds__(kGatherThreads)
                 if (id[k] >= 0) atomicAdd(dst + id[k], __fmul_rn(gv, w[k]));
         }
     }
+    report_bad(bad);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -167,7 +167,7 @@ template <int THREADS, int Q>
 __global__ void __launch_bounds__(THREADS)
     knn_dense_kernel(int n, int m, int k, int tiles_per_cloud, const float* __restrict__ support,
                      const float* __restrict__ query, int64_t* __restrict__ idx,
-                     float* __restrict__ dist2)
+                     float* __restrict__ dist2, const unsigned char* __restrict__ need)
 {
     extern __shared__ __align__(16) float dyn_smem[];
     float* tile = dyn_smem;
@@ -184,13 +184,22 @@ __global__ void __launch_bounds__(THREADS)
     for (int q = 0; q < Q; ++q)
     {
         const int j = qtile * (THREADS * Q) + q * THREADS + threadIdx.x;
-        op.act[q] = j < m;
+        // `need` (optional): one byte per query, 0 = already answered by the grid path
+        op.act[q] = j < m && (need == nullptr || need[static_cast<size_t>(cloud) * m + j] != 0);
         const size_t row = static_cast<size_t>(cloud) * m + (op.act[q] ? j : 0);
         op.qx[q] = op.act[q] ? __ldg(query + row * 3 + 0) : 0.f;
         op.qy[q] = op.act[q] ? __ldg(query + row * 3 + 1) : 0.f;
         op.qz[q] = op.act[q] ? __ldg(query + row * 3 + 2) : 0.f;
         op.thr[q] = CUDART_INF_F;
         op.cnt[q] = 0;
+    }
+    if (need != nullptr)
+    {
+        // nothing left over for this CTA (the usual case behind the grid kernel)
+        bool any = false;
+#pragma unroll
+        for (int q = 0; q < Q; ++q) any |= op.act[q];
+        if (!__syncthreads_or(any ? 1 : 0)) return;
     }
     scan_candidates<THREADS, Q>(support + static_cast<size_t>(cloud) * n * 3, n, tile, op.qx, op.qy, op.qz, op);
 #pragma unroll
@@ -208,7 +217,7 @@ __global__ void __launch_bounds__(THREADS)
     knn_partial_kernel(long long size_s, long long size_q, int k,
                        const float* __restrict__ support, const float* __restrict__ query,
                        const int64_t* __restrict__ batch_s, const int64_t* __restrict__ batch_q,
-                       int64_t* __restrict__ idx, float* __restrict__ dist2)
+                       int64_t* __restrict__ idx, float* __restrict__ dist2, const unsigned char* __restrict__ need)
 {
     extern __shared__ __align__(16) float dyn_smem[];
     __shared__ long long s_range[2];
@@ -229,7 +238,8 @@ __global__ void __launch_bounds__(THREADS)
     for (int q = 0; q < Q; ++q)
     {
         const long long j = j0 + q * THREADS + threadIdx.x;
-        valid[q] = j < size_q;
+        // `need` (optional): one byte per query, 0 = already answered by the grid path
+        valid[q] = j < size_q && (need == nullptr || need[j] != 0);
         const long long row = valid[q] ? j : 0;
         seg[q] = valid[q] ? __ldg(batch_q + row) : 0;
         op.qx[q] = valid[q] ? __ldg(query + row * 3 + 0) : 0.f;
@@ -239,8 +249,17 @@ __global__ void __launch_bounds__(THREADS)
         op.cnt[q] = 0;
         base[q] = 0;
     }
-    int64_t cur = __ldg(batch_q + j0);
     const unsigned long long kNone = ~0ull;
+    // the first segment any query of this CTA still needs (segment ids are non-negative)
+    if (threadIdx.x == 0) s_next = kNone;
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < Q; ++q)
+        if (valid[q]) atomicMin(&s_next, static_cast<unsigned long long>(seg[q]));
+    __syncthreads();
+    if (s_next == kNone) return;  // nothing left over for this CTA
+    int64_t cur = static_cast<int64_t>(s_next);
+    __syncthreads();
     while (true)
     {
         if (threadIdx.x == 0)
@@ -447,8 +466,19 @@ extern "C" int tpk_three_nn_ws(int b, int n, int m, const float* unknown, const 
         }                                                                                          \
     } while (0)
 
-extern "C" int tpk_knn_dense(int b, int n, int m, int k, const float* support, const float* query,
-                             int64_t* idx, float* dist2, void* stream)
+namespace tpk
+{
+// hash_grid.cu
+bool hash_grid_fits(long long size_x, long long size_y);
+size_t hash_grid_knn_scratch_bytes(long long size_s, long long size_q);
+int hash_grid_knn(long long size_s, long long size_q, long long per_cloud_s, long long per_cloud_q, int k,
+                  const float* support, const float* query, const int64_t* batch_s, const int64_t* batch_q, int64_t* idx,
+                  float* dist2, void* scratch, const unsigned char** need_out, cudaStream_t s);
+}  // namespace tpk
+
+// `need` (optional, device): one byte per query, 0 = already answered, skip it
+static int knn_dense_scan(int b, int n, int m, int k, const float* support, const float* query, int64_t* idx,
+                          float* dist2, const unsigned char* need, void* stream)
 {
     using namespace tpk;
     TPK_REQUIRE(b >= 0 && n >= 0 && m >= 0, "knn: negative size (b=%d n=%d m=%d)", b, n, m);
@@ -466,14 +496,56 @@ extern "C" int tpk_knn_dense(int b, int n, int m, int k, const float* support, c
     const long long grid = static_cast<long long>(b) * tiles;
     TPK_REQUIRE(grid < (1ll << 31), "knn: too many queries");
     const dim3 g(static_cast<unsigned>(grid));
-    TPK_KNN_DISPATCH(knn_dense_kernel, n, m, k, tiles, support, query, idx, dist2);
+    TPK_KNN_DISPATCH(knn_dense_kernel, n, m, k, tiles, support, query, idx, dist2, need);
     return check_launch("knn_dense");
 }
 
-extern "C" int tpk_knn_partial_dense(int64_t size_s, int64_t size_q, int k, const float* support,
-                                     const float* query, const int64_t* batch_s,
-                                     const int64_t* batch_q, int64_t* idx, float* dist2,
-                                     void* stream)
+extern "C" int tpk_knn_dense(int b, int n, int m, int k, const float* support, const float* query,
+                             int64_t* idx, float* dist2, void* stream)
+{
+    return knn_dense_scan(b, n, m, k, support, query, idx, dist2, nullptr, stream);
+}
+
+// The hashed grid pays from a few thousand support points per cloud on; the test hook
+// "knn_scan" keeps every query on the scan.
+static bool knn_dense_wants_grid(int b, int n, int m)
+{
+    return n >= 2048 && tpk::hash_grid_fits(static_cast<long long>(b) * n, static_cast<long long>(b) * m) &&
+           !tpk::test_path("knn_scan");
+}
+
+extern "C" int64_t tpk_knn_dense_scratch_bytes(int b, int n, int m, int k)
+{
+    if (b <= 0 || n <= 0 || m <= 0 || k <= 0 || !knn_dense_wants_grid(b, n, m)) return 0;
+    return static_cast<int64_t>(tpk::hash_grid_knn_scratch_bytes(static_cast<long long>(b) * n, static_cast<long long>(b) * m));
+}
+
+extern "C" int tpk_knn_dense_ws(int b, int n, int m, int k, const float* support, const float* query, int64_t* idx,
+                                float* dist2, void* scratch, int64_t scratch_bytes, void* stream)
+{
+    using namespace tpk;
+    const int64_t want = tpk_knn_dense_scratch_bytes(b, n, m, k);
+    if (want == 0 || scratch == nullptr) return tpk_knn_dense(b, n, m, k, support, query, idx, dist2, stream);
+    if (scratch_bytes < want)
+    {
+        set_error("knn: scratch of %lld bytes given, %lld needed", static_cast<long long>(scratch_bytes),
+                  static_cast<long long>(want));
+        return TPK_ERR_SCRATCH;
+    }
+    TPK_REQUIRE(k >= 1 && k <= TPK_KNN_MAX_K, "knn: k=%d outside 1..%d", k, TPK_KNN_MAX_K);
+    TPK_REQUIRE(k <= n, "Not enough points in support to find %d neighboors", k);
+    TPK_REQUIRE(support && query && idx && dist2, "knn: NULL pointer");
+    TPK_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "knn: scratch must be 256-byte aligned");
+    const unsigned char* need = nullptr;
+    const int rc = hash_grid_knn(static_cast<long long>(b) * n, static_cast<long long>(b) * m, n, m, k, support, query,
+                                 nullptr, nullptr, idx, dist2, scratch, &need, static_cast<cudaStream_t>(stream));
+    if (rc != TPK_OK) return rc;
+    return knn_dense_scan(b, n, m, k, support, query, idx, dist2, need, stream);
+}
+
+static int knn_partial_scan(int64_t size_s, int64_t size_q, int k, const float* support, const float* query,
+                            const int64_t* batch_s, const int64_t* batch_q, int64_t* idx, float* dist2,
+                            const unsigned char* need, void* stream)
 {
     using namespace tpk;
     TPK_REQUIRE(size_s >= 0 && size_q >= 0, "knn_partial_dense: negative size");
@@ -491,6 +563,50 @@ extern "C" int tpk_knn_partial_dense(int64_t size_s, int64_t size_q, int k, cons
     const long long grid = (size_q + threads * q - 1) / (threads * q);
     TPK_REQUIRE(grid < (1ll << 31), "knn_partial_dense: too many queries");
     const dim3 g(static_cast<unsigned>(grid));
-    TPK_KNN_DISPATCH(knn_partial_kernel, size_s, size_q, k, support, query, batch_s, batch_q, idx, dist2);
+    TPK_KNN_DISPATCH(knn_partial_kernel, size_s, size_q, k, support, query, batch_s, batch_q, idx, dist2, need);
     return check_launch("knn_partial_dense");
+}
+
+extern "C" int tpk_knn_partial_dense(int64_t size_s, int64_t size_q, int k, const float* support,
+                                     const float* query, const int64_t* batch_s,
+                                     const int64_t* batch_q, int64_t* idx, float* dist2,
+                                     void* stream)
+{
+    return knn_partial_scan(size_s, size_q, k, support, query, batch_s, batch_q, idx, dist2, nullptr, stream);
+}
+
+static bool knn_partial_wants_grid(int64_t size_s, int64_t size_q)
+{
+    return tpk::hash_grid_fits(size_s, size_q) && !tpk::test_path("knn_scan");
+}
+
+extern "C" int64_t tpk_knn_partial_dense_scratch_bytes(int64_t size_s, int64_t size_q, int k)
+{
+    if (k <= 0 || !knn_partial_wants_grid(size_s, size_q)) return 0;
+    return static_cast<int64_t>(tpk::hash_grid_knn_scratch_bytes(size_s, size_q));
+}
+
+extern "C" int tpk_knn_partial_dense_ws(int64_t size_s, int64_t size_q, int k, const float* support,
+                                        const float* query, const int64_t* batch_s, const int64_t* batch_q,
+                                        int64_t* idx, float* dist2, void* scratch, int64_t scratch_bytes,
+                                        void* stream)
+{
+    using namespace tpk;
+    const int64_t want = tpk_knn_partial_dense_scratch_bytes(size_s, size_q, k);
+    if (want == 0 || scratch == nullptr)
+        return tpk_knn_partial_dense(size_s, size_q, k, support, query, batch_s, batch_q, idx, dist2, stream);
+    if (scratch_bytes < want)
+    {
+        set_error("knn_partial_dense: scratch of %lld bytes given, %lld needed", static_cast<long long>(scratch_bytes),
+                  static_cast<long long>(want));
+        return TPK_ERR_SCRATCH;
+    }
+    TPK_REQUIRE(k >= 1 && k <= TPK_KNN_MAX_K, "knn: k=%d outside 1..%d", k, TPK_KNN_MAX_K);
+    TPK_REQUIRE(query && batch_q && idx && dist2 && support && batch_s, "knn_partial_dense: NULL pointer");
+    TPK_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "knn_partial_dense: scratch must be 256-byte aligned");
+    const unsigned char* need = nullptr;
+    const int rc = hash_grid_knn(size_s, size_q, 1, 1, k, support, query, batch_s, batch_q, idx, dist2, scratch, &need,
+                                 static_cast<cudaStream_t>(stream));
+    if (rc != TPK_OK) return rc;
+    return knn_partial_scan(size_s, size_q, k, support, query, batch_s, batch_q, idx, dist2, need, stream);
 }

@@ -39,8 +39,15 @@ def knn(pos_support, pos, k, batch_support=None, batch_pos=None):
         idx = torch.empty((b, m, k), dtype=torch.int64, device=pos.device)
         dist2 = torch.empty((b, m, k), dtype=torch.float32, device=pos.device)
         with torch.cuda.device(pos.device):
-            _lib.call("tpk_knn_dense", b, n, m, int(k), _lib.ptr(pos_support), _lib.ptr(pos),
-                      _lib.ptr(idx), _lib.ptr(dist2), _lib.stream_of(pos))
+            need = _lib.lib().tpk_knn_dense_scratch_bytes(b, n, m, int(k))
+            if need > 0:
+                # large clouds: hashed uniform grid with scratch (same results as the scan)
+                scratch = torch.empty((need,), dtype=torch.uint8, device=pos.device)
+                _lib.call("tpk_knn_dense_ws", b, n, m, int(k), _lib.ptr(pos_support), _lib.ptr(pos),
+                          _lib.ptr(idx), _lib.ptr(dist2), _lib.ptr(scratch), need, _lib.stream_of(pos))
+            else:
+                _lib.call("tpk_knn_dense", b, n, m, int(k), _lib.ptr(pos_support), _lib.ptr(pos),
+                          _lib.ptr(idx), _lib.ptr(dist2), _lib.stream_of(pos))
         return idx, dist2
 
     assert pos_support.dim() == 2 and pos.dim() == 2
@@ -52,11 +59,20 @@ def knn(pos_support, pos, k, batch_support=None, batch_pos=None):
             raise RuntimeError("%s must be an int64 tensor" % name)
     batch_support = batch_support.contiguous()
     batch_pos = batch_pos.contiguous()
+    if _lib.debug_checks():
+        _lib.check_segments(batch_support, batch_pos)
     m = pos.shape[0]
     idx = torch.empty((m, k), dtype=torch.int64, device=pos.device)
     dist2 = torch.empty((m, k), dtype=torch.float32, device=pos.device)
     with torch.cuda.device(pos.device):
-        _lib.call("tpk_knn_partial_dense", pos_support.shape[0], m, int(k), _lib.ptr(pos_support),
-                  _lib.ptr(pos), _lib.ptr(batch_support), _lib.ptr(batch_pos), _lib.ptr(idx),
-                  _lib.ptr(dist2), _lib.stream_of(pos))
+        need = _lib.lib().tpk_knn_partial_dense_scratch_bytes(pos_support.shape[0], m, int(k))
+        if need > 0:
+            scratch = torch.empty((need,), dtype=torch.uint8, device=pos.device)
+            _lib.call("tpk_knn_partial_dense_ws", pos_support.shape[0], m, int(k), _lib.ptr(pos_support),
+                      _lib.ptr(pos), _lib.ptr(batch_support), _lib.ptr(batch_pos), _lib.ptr(idx),
+                      _lib.ptr(dist2), _lib.ptr(scratch), need, _lib.stream_of(pos))
+        else:
+            _lib.call("tpk_knn_partial_dense", pos_support.shape[0], m, int(k), _lib.ptr(pos_support),
+                      _lib.ptr(pos), _lib.ptr(batch_support), _lib.ptr(batch_pos), _lib.ptr(idx),
+                      _lib.ptr(dist2), _lib.stream_of(pos))
     return idx, dist2

@@ -4,7 +4,8 @@ Every op on the path is independent per cloud (dense layout), per segment (packe
 layout) or per pair (chamfer), so ranks take contiguous blocks of clouds and no kernel
 needs a collective.  The only exchange is the scalar chamfer loss: two partial sums and
 two counts per rank, all-reduced with torch.distributed (NCCL on GPUs, gloo in the CPU
-tests).  The reference has no multi-device code at all.
+tests); `gather_outputs` assembles per-rank results on every rank where a caller wants the
+whole batch.  The reference has no multi-device code at all.
 """
 import torch
 import torch.distributed as dist
@@ -40,18 +41,36 @@ def balanced_blocks(costs, world_size):
     return bounds
 
 
+class _AllReduceSum(torch.autograd.Function):
+    """Sum over the ranks of `group`.  Every rank ends up with the same value and calls
+    backward on its own copy, so the gradient of that copy w.r.t. this rank's addend is the
+    incoming gradient itself (no second collective)."""
+
+    @staticmethod
+    def forward(ctx, t, group):
+        out = t.clone()
+        dist.all_reduce(out, op=dist.ReduceOp.SUM, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        return grad, None
+
+
 def reduce_chamfer_loss(sum1, count1, sum2, count2, group=None):
     """mean(dist1) + mean(dist2) over the clouds of ALL ranks from per-rank partial sums.
 
     sum1/sum2: 0-dim tensors (sum of this rank's dist1 / dist2 entries), count1/count2:
     number of entries behind them.  Matches the reference's single-device
-    ``torch.mean(dist1) + torch.mean(dist2)`` (chamfer_dist.py:54) on the concatenated batch.
+    ``torch.mean(dist1) + torch.mean(dist2)`` (chamfer_dist.py:54) on the concatenated batch,
+    and so do the gradients: backward() on the returned loss gives every rank the gradient
+    of the whole batch's loss w.r.t. its own pairs.
     """
     buf = torch.stack([sum1.double(), sum2.double(),
                        torch.as_tensor(float(count1), dtype=torch.float64, device=sum1.device),
                        torch.as_tensor(float(count2), dtype=torch.float64, device=sum1.device)])
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
+        buf = _AllReduceSum.apply(buf, group)
     return (buf[0] / buf[2] + buf[1] / buf[3]).to(sum1.dtype)
 
 
@@ -62,3 +81,30 @@ def chamfer_dist_sharded(xyz1, xyz2, group=None):
 
     dist1, dist2 = ChamferFunction.apply(xyz1, xyz2)
     return reduce_chamfer_loss(dist1.sum(), dist1.numel(), dist2.sum(), dist2.numel(), group)
+
+
+def gather_outputs(t, n_items=None, group=None):
+    """The "final gather": per-rank outputs (first dimension = this rank's items, blocks as
+    shard_range hands them out) assembled into the whole batch's tensor on every rank with one
+    all_gather_into_tensor.  Ranks whose block is one item shorter are padded for the
+    collective and trimmed afterwards.  n_items: items of the whole batch (default: the
+    blocks are equal, world_size x this rank's)."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return t
+    world = dist.get_world_size(group)
+    if n_items is None:
+        n_items = t.shape[0] * world
+    per = -(-int(n_items) // world)
+    send = t.contiguous()
+    if send.shape[0] < per:
+        pad = torch.zeros((per - send.shape[0],) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+        send = torch.cat([send, pad])
+    out = torch.empty((world * per,) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+    dist.all_gather_into_tensor(out, send, group=group)
+    if per * world == n_items:
+        return out
+    parts = []
+    for r in range(world):
+        lo, hi = shard_range(n_items, r, world)
+        parts.append(out[r * per:r * per + (hi - lo)])
+    return torch.cat(parts)

@@ -103,6 +103,20 @@ def three_nn(unknown, known):
     return torch.sqrt(dist2), idx
 
 
+def three_interpolate_backward(grad_out, idx, weight, m):
+    """Gradient of three_interpolate w.r.t. its features: (B, c, n) -> (B, c, m), the scatter-add
+    of grad_out * weight (reference: cuda/src/interpolate_gpu.cu:122-152).  What
+    ThreeInterpolate.backward runs; callable on its own."""
+    grad_out = grad_out.contiguous()
+    _f32(grad_out, "grad_out")
+    B, c, n = grad_out.size()
+    grad_features = torch.empty((B, c, m), dtype=torch.float32, device=grad_out.device)
+    with torch.cuda.device(grad_out.device):
+        _lib.call("tpk_three_interpolate_grad", B, c, n, m, _lib.ptr(grad_out), _lib.ptr(idx),
+                  _lib.ptr(weight), _lib.ptr(grad_features), _lib.stream_of(grad_out))
+    return grad_features
+
+
 class ThreeInterpolate(Function):
     """Weighted sum of three gathered feature columns (reference: torchpoints.py:67-106)."""
 
@@ -122,19 +136,14 @@ class ThreeInterpolate(Function):
         with torch.cuda.device(features.device):
             _lib.call("tpk_three_interpolate", B, c, m, n, _lib.ptr(features), _lib.ptr(idx),
                       _lib.ptr(weight), _lib.ptr(out), _lib.stream_of(features))
+            if _lib.debug_checks():
+                _lib.raise_on_device_status("three_interpolate")
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
         idx, weight, m = ctx.three_interpolate_for_backward
-        grad_out = grad_out.contiguous()
-        _f32(grad_out, "grad_out")
-        B, c, n = grad_out.size()
-        grad_features = torch.empty((B, c, m), dtype=torch.float32, device=grad_out.device)
-        with torch.cuda.device(grad_out.device):
-            _lib.call("tpk_three_interpolate_grad", B, c, n, m, _lib.ptr(grad_out), _lib.ptr(idx),
-                      _lib.ptr(weight), _lib.ptr(grad_features), _lib.stream_of(grad_out))
-        return grad_features, None, None
+        return three_interpolate_backward(grad_out, idx, weight, m), None, None
 
 
 def three_interpolate(features, idx, weight):
@@ -158,6 +167,20 @@ def three_interpolate(features, idx, weight):
     return ThreeInterpolate.apply(features, idx, weight)
 
 
+def grouping_backward(grad_out, idx, n):
+    """Gradient of grouping_operation w.r.t. its features: (B, c, npoint, nsample) -> (B, c, n),
+    the scatter-add autograd derives for the reference's torch.gather
+    (torch_points_kernels/torchpoints.py:143-146).  What GroupingOperation.backward runs."""
+    grad_out = grad_out.contiguous()
+    _f32(grad_out, "grad_out")
+    B, c, npoint, nsample = grad_out.size()
+    grad_features = torch.empty((B, c, n), dtype=torch.float32, device=grad_out.device)
+    with torch.cuda.device(grad_out.device):
+        _lib.call("tpk_grouping_grad", B, c, n, npoint, nsample, _lib.ptr(grad_out),
+                  _lib.ptr(idx), _lib.ptr(grad_features), _lib.stream_of(grad_out))
+    return grad_features
+
+
 class GroupingOperation(Function):
     """Gather of feature columns by neighbourhood index; backward is a scatter-add."""
 
@@ -175,18 +198,14 @@ class GroupingOperation(Function):
         with torch.cuda.device(features.device):
             _lib.call("tpk_grouping", B, c, n, npoint, nsample, _lib.ptr(features), _lib.ptr(idx),
                       _lib.ptr(out), _lib.stream_of(features))
+            if _lib.debug_checks():
+                _lib.raise_on_device_status("grouping_operation")
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
         idx, n = ctx.grouping_for_backward
-        grad_out = grad_out.contiguous()
-        B, c, npoint, nsample = grad_out.size()
-        grad_features = torch.empty((B, c, n), dtype=torch.float32, device=grad_out.device)
-        with torch.cuda.device(grad_out.device):
-            _lib.call("tpk_grouping_grad", B, c, n, npoint, nsample, _lib.ptr(grad_out),
-                      _lib.ptr(idx), _lib.ptr(grad_features), _lib.stream_of(grad_out))
-        return grad_features, None
+        return grouping_backward(grad_out, idx, n), None
 
 
 def grouping_operation(features, idx):
@@ -245,6 +264,8 @@ def ball_query_partial_dense(radius, nsample, x, y, batch_x, batch_y, sort=False
         raise RuntimeError("batch_x and batch_y must be int64 tensors")
     batch_x = batch_x.contiguous()
     batch_y = batch_y.contiguous()
+    if _lib.debug_checks():
+        _lib.check_segments(batch_x, batch_y)
     ny = y.shape[0]
     idx = torch.empty((ny, nsample), dtype=torch.int64, device=y.device)
     dist = torch.empty((ny, nsample), dtype=torch.float32, device=y.device)
