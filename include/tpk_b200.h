@@ -329,6 +329,90 @@ TPK_API int tpk_chamfer_dist_grad_f64(int b, int n, const double* xyz1, int m, c
                               const double* grad_dist2, double* grad_xyz1, double* grad_xyz2,
                               void* stream);
 
+/* -------------------------------------------------- GRNet ops (next to chamfer) ---- */
+
+/*
+ * Point cloud -> density grid by trilinear weights.  ptcloud (b,n_pts,3), already scaled to grid
+ * units; the grid spans [min, max] per axis (integers passed as float, as the reference does):
+ * len = max - min + 1 vertices.  -> grid (b, len_x*len_y*len_z), fully written (starts from
+ * zero inside the call); grid_pt_weights (b,n_pts,8,3) and grid_pt_indexes (b,n_pts,8) int32 are
+ * the eight vertices' axis weights 1 - |x - x0| and flat indices, kept for the backward pass.
+ * A vertex outside the grid gets index -1 and contributes nothing (the reference writes out of
+ * bounds there) and sets TPK_STATUS_BAD_INDEX.  f32 and f64, as the reference dispatches both.
+ * Replaces gridding_kernel_warpper, cuda/src/gridding_gpu.cu:163-197 (kernel :28-161).
+ */
+TPK_API int tpk_gridding_f32(int b, int n_pts, float min_x, float max_x, float min_y, float max_y, float min_z,
+                             float max_z, const float* ptcloud, float* grid, float* grid_pt_weights,
+                             int32_t* grid_pt_indexes, void* stream);
+TPK_API int tpk_gridding_f64(int b, int n_pts, float min_x, float max_x, float min_y, float max_y, float min_z,
+                             float max_z, const double* ptcloud, double* grid, double* grid_pt_weights,
+                             int32_t* grid_pt_indexes, void* stream);
+
+/*
+ * grad_ptcloud (b,n_pts,3) from grad_grid (b,n_grid_vertices): per axis the sum over the eight
+ * vertices of +-grad * (the other two weights), in the reference's order (bit-identical).
+ * Replaces gridding_grad_kernel_warpper, cuda/src/gridding_gpu.cu:306-333 (kernel :199-304).
+ */
+TPK_API int tpk_gridding_grad_f32(int b, int n_pts, int64_t n_grid_vertices, const float* grid_pt_weights,
+                                  const int32_t* grid_pt_indexes, const float* grad_grid, float* grad_ptcloud,
+                                  void* stream);
+TPK_API int tpk_gridding_grad_f64(int b, int n_pts, int64_t n_grid_vertices, const double* grid_pt_weights,
+                                  const int32_t* grid_pt_indexes, const double* grad_grid, double* grad_ptcloud,
+                                  void* stream);
+
+/*
+ * Features of the (2*neighborhood_size)^3 grid vertices around every point.  ptcloud (b,n_pts,3)
+ * in grid units, cubic_features (b,channels,scale,scale,scale) -> point_features
+ * (b,n_pts,n_vertices,channels), fully written (0 for vertices outside the grid), and
+ * grid_pt_indexes (b,n_pts,n_vertices) int32 (-1 outside the grid).
+ * Replaces cubic_feature_sampling_kernel_wrapper, cuda/src/cubic_feature_sampling_gpu.cu:99-128.
+ */
+TPK_API int tpk_cubic_feature_sampling_f32(int b, int n_pts, int channels, int scale, int neighborhood_size,
+                                           const float* ptcloud, const float* cubic_features,
+                                           float* point_features, int32_t* grid_pt_indexes, void* stream);
+TPK_API int tpk_cubic_feature_sampling_f64(int b, int n_pts, int channels, int scale, int neighborhood_size,
+                                           const double* ptcloud, const double* cubic_features,
+                                           double* point_features, int32_t* grid_pt_indexes, void* stream);
+
+/*
+ * Scatter-add of grad_point_features into grad_cubic_features (b,channels,scale^3), fully written;
+ * grad_ptcloud (b,n_pts,3) is zero (floor and ceil are flat); either output may be NULL.
+ * Replaces cubic_feature_sampling_grad_kernel_wrapper, cubic_feature_sampling_gpu.cu:179-213.
+ */
+TPK_API int tpk_cubic_feature_sampling_grad_f32(int b, int n_pts, int channels, int scale, int neighborhood_size,
+                                                const float* grad_point_features, const int32_t* grid_pt_indexes,
+                                                float* grad_ptcloud, float* grad_cubic_features, void* stream);
+TPK_API int tpk_cubic_feature_sampling_grad_f64(int b, int n_pts, int channels, int scale, int neighborhood_size,
+                                                const double* grad_point_features, const int32_t* grid_pt_indexes,
+                                                double* grad_ptcloud, double* grad_cubic_features, void* stream);
+
+/* ------------------------------------------- clustering and instance metrics ---- */
+
+/*
+ * `rounds` rounds of label propagation for region growing.  neighbours (n,nsample) int64: the
+ * lists a partial_dense ball query of the points against themselves returns (-1 ends a list);
+ * labels (n) int32, initialised by the caller to 0..n-1.  A round pushes every point's label to
+ * the points it lists (minimum wins) and shortens label chains.  *changed (device int32, zeroed
+ * by the caller) is set to 1 by any round that changed a label: repeat until it stays 0.  At the
+ * fixed point labels[v] is the smallest index that reaches v along the lists, which is the seed
+ * of the cluster the reference's sequential traversal puts v in
+ * (torch_points_kernels/cluster.py:8-37).
+ */
+TPK_API int tpk_grow_labels_step(int64_t n, int nsample, const int64_t* neighbours, int32_t* labels,
+                                 int32_t* changed, int rounds, void* stream);
+
+/*
+ * IoU of every proposal with every ground-truth instance of its sample; proposals_iou
+ * (n_proposals,total_gt_instances) f32 is fully written (0 for other samples' instances).
+ * Arguments as instance_iou_kernel_wrapper, cuda/src/metrics_gpu.cu:50-62 (kernel :9-43), plus
+ * n_points (length of instance_labels and batch) so that indices can be checked.
+ */
+TPK_API int tpk_instance_iou(int n_proposals, int64_t total_gt_instances, int64_t max_gt_instances,
+                             int64_t n_points, const int64_t* num_gt_instances, const int64_t* proposals_idx,
+                             const int64_t* proposals_offset, const int64_t* instance_labels,
+                             const int64_t* offset_num_gt_instances, const int64_t* batch,
+                             const int64_t* instance_pointnum, float* proposals_iou, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

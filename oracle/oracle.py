@@ -216,3 +216,77 @@ def chamfer_grad(xyz1, xyz2, idx1, idx2, grad_dist1, grad_dist2):
     lib().orc_chamfer_grad(b, n, _p(x1, _f32p), m, _p(x2, _f32p), _p(i1, _i32p), _p(i2, _i32p),
                            _p(g1, _f32p), _p(g2, _f32p), _p(o1, _f32p), _p(o2, _f32p))
     return o1, o2
+
+
+def grow_proximity(neighbours, min_cluster_size):
+    """neighbours (N, nsample) int64 -> list of clusters (lists of indices in traversal order),
+    as _grow_proximity_core of the reference returns them."""
+    nb = _np(neighbours, np.int64)
+    n, ns = nb.shape
+    members = np.zeros(max(n, 1), np.int64)
+    offsets = np.zeros(n + 2, np.int64)
+    fn = lib().orc_grow_proximity
+    fn.restype = ctypes.c_int64
+    k = fn(ctypes.c_int64(n), int(ns), _p(nb, _i64p), ctypes.c_int64(int(min_cluster_size)), _p(members, _i64p),
+           _p(offsets, _i64p))
+    return [members[offsets[c]:offsets[c + 1]].tolist() for c in range(int(k))]
+
+
+def instance_iou(num_gt, proposals_idx, proposals_offset, instance_labels, offset_num_gt, batch, instance_pointnum):
+    """The native reference call (cuda/src/metrics.cpp:13-51) on numpy int64 arrays."""
+    arrs = [_np(a, np.int64) for a in (num_gt, proposals_idx, proposals_offset, instance_labels, offset_num_gt, batch,
+                                       instance_pointnum)]
+    nprop = arrs[2].shape[0] - 1
+    total = int(arrs[0].sum())
+    out = np.zeros((nprop, total), np.float32)
+    lib().orc_instance_iou(int(nprop), ctypes.c_int64(total), _p(arrs[0], _i64p), _p(arrs[1], _i64p), _p(arrs[2], _i64p),
+                           _p(arrs[3], _i64p), _p(arrs[4], _i64p), _p(arrs[5], _i64p), _p(arrs[6], _i64p), _p(out, _f32p))
+    return out
+
+
+def gridding(ptcloud, scale):
+    """ptcloud (B, n, 3) f32 in grid units -> grid (B, (2 scale)^3), weights (B, n, 8, 3), indexes (B, n, 8)."""
+    p = _np(ptcloud, np.float32)
+    b, n, _ = p.shape
+    nv = (2 * scale) ** 3
+    grid = np.zeros((b, nv), np.float32)
+    w = np.zeros((b, n, 8, 3), np.float32)
+    ix = np.zeros((b, n, 8), np.int32)
+    f = ctypes.c_float
+    lib().orc_gridding(b, n, f(-scale), f(scale - 1), f(-scale), f(scale - 1), f(-scale), f(scale - 1), _p(p, _f32p),
+                       _p(grid, _f32p), _p(w, _f32p), _p(ix, _i32p))
+    return grid, w, ix
+
+
+def gridding_grad(weights, indexes, grad_grid):
+    w = _np(weights, np.float32)
+    ix = _np(indexes, np.int32)
+    g = _np(grad_grid, np.float32)
+    b, n = ix.shape[0], ix.shape[1]
+    out = np.zeros((b, n, 3), np.float32)
+    lib().orc_gridding_grad(b, n, ctypes.c_int64(g.shape[1]), _p(w, _f32p), _p(ix, _i32p), _p(g, _f32p), _p(out, _f32p))
+    return out
+
+
+def cubic_feature_sampling(ptcloud, cubic_features, neighborhood_size=1):
+    """ptcloud (B, n, 3) f32 in grid units, cubic_features (B, c, s, s, s) -> features (B, n, nv, c), indexes (B, n, nv)."""
+    p = _np(ptcloud, np.float32)
+    cf = _np(cubic_features, np.float32)
+    b, n, _ = p.shape
+    c, s = cf.shape[1], cf.shape[2]
+    nv = (2 * neighborhood_size) ** 3
+    out = np.zeros((b, n, nv, c), np.float32)
+    ix = np.zeros((b, n, nv), np.int32)
+    lib().orc_cubic_feature_sampling(b, n, c, s, int(neighborhood_size), _p(p, _f32p), _p(cf, _f32p), _p(out, _f32p),
+                                     _p(ix, _i32p))
+    return out, ix
+
+
+def cubic_feature_sampling_grad(grad_point_features, indexes, scale, neighborhood_size=1):
+    g = _np(grad_point_features, np.float32)
+    ix = _np(indexes, np.int32)
+    b, n, nv, c = g.shape
+    out = np.zeros((b, c, scale, scale, scale), np.float32)
+    lib().orc_cubic_feature_sampling_grad(b, n, c, int(scale), int(neighborhood_size), _p(g, _f32p), _p(ix, _i32p),
+                                          _p(out, _f32p))
+    return out

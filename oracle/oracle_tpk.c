@@ -519,3 +519,221 @@ void orc_chamfer_grad(int b, int n, const float* xyz1, int m, const float* xyz2,
         free(a2);
     }
 }
+
+/* ------------------------------------------------------------------ region growing
+ *
+ * torch_points_kernels/cluster.py:8-37 (_grow_proximity_core), literally: seeds in index
+ * order, a stack ("queue.pop()" takes the last element), a neighbour list ends at the first
+ * -1.  Writes the members of the clusters that reach min_cluster_size one after the other
+ * into `members`, in the order the traversal met them, and cluster c's range into
+ * offsets[c], offsets[c + 1].  Returns the number of clusters kept.
+ */
+int64_t orc_grow_proximity(int64_t n, int nsample, const int64_t* neighbours, int64_t min_cluster_size,
+                           int64_t* members, int64_t* offsets)
+{
+    unsigned char* visited = (unsigned char*)calloc((size_t)n + 1, 1);
+    int64_t* stack = (int64_t*)malloc(sizeof(int64_t) * ((size_t)n + 1));
+    int64_t* cluster = (int64_t*)malloc(sizeof(int64_t) * ((size_t)n + 1));
+    int64_t nclusters = 0, written = 0;
+    offsets[0] = 0;
+    for (int64_t i = 0; i < n; ++i)
+    {
+        if (visited[i]) continue;
+        int64_t top = 0, size = 0;
+        visited[i] = 1;
+        stack[top++] = i;
+        cluster[size++] = i;
+        while (top > 0)
+        {
+            const int64_t k = stack[--top];
+            for (int s = 0; s < nsample; ++s)
+            {
+                const int64_t nei = neighbours[k * nsample + s];
+                if (nei == -1) break;
+                if (!visited[nei])
+                {
+                    visited[nei] = 1;
+                    stack[top++] = nei;
+                    cluster[size++] = nei;
+                }
+            }
+        }
+        if (size >= min_cluster_size)
+        {
+            for (int64_t j = 0; j < size; ++j) members[written + j] = cluster[j];
+            written += size;
+            offsets[++nclusters] = written;
+        }
+    }
+    free(visited);
+    free(stack);
+    free(cluster);
+    return nclusters;
+}
+
+/* ------------------------------------------------------------------ instance IoU
+ *
+ * cuda/src/metrics_gpu.cu:9-43: per proposal and ground-truth instance of the proposal's
+ * sample, intersection / (float)(|proposal| + |instance| - intersection) + 1e-5, the division
+ * in double, stored as float.  out (n_proposals, total_gt) starts from zero.
+ */
+void orc_instance_iou(int n_proposals, int64_t total_gt, const int64_t* num_gt, const int64_t* proposals_idx,
+                      const int64_t* proposals_offset, const int64_t* instance_labels, const int64_t* offset_num_gt,
+                      const int64_t* batch, const int64_t* instance_pointnum, float* out)
+{
+    for (int64_t i = 0; i < (int64_t)n_proposals * total_gt; ++i) out[i] = 0.f;
+    for (int p = 0; p < n_proposals; ++p)
+    {
+        const int start = (int)proposals_offset[p], end = (int)proposals_offset[p + 1];
+        const int sample = (int)batch[proposals_idx[start]];
+        const int ninst = (int)num_gt[sample];
+        const int inst_off = (int)offset_num_gt[sample];
+        const int proposal_total = end - start;
+        for (int inst = 0; inst < ninst; ++inst)
+        {
+            const int inst_total = (int)instance_pointnum[inst_off + inst];
+            int inter = 0;
+            for (int i = start; i < end; ++i)
+                if ((int)instance_labels[proposals_idx[i]] == inst + 1) inter += 1;
+            out[inst_off + inst + (int64_t)p * total_gt] =
+                (float)((float)inter / ((float)(proposal_total + inst_total - inter) + 1e-5));
+        }
+    }
+}
+
+/* ------------------------------------------------------------------ gridding (float32)
+ *
+ * cuda/src/gridding_gpu.cu:28-161 forward, :199-304 backward.  Vertices outside the grid get
+ * index -1 and are left out (the reference writes out of bounds there).  The forward sums are
+ * taken in double and rounded once (the kernel adds with atomics in arbitrary order); the
+ * backward sums run over the eight vertices in the kernel's order, in float.
+ */
+static float orc_vertex_weight(float x, int x0) { return 1 - fabsf(x - (float)x0); }
+
+void orc_gridding(int b, int n_pts, float min_x, float max_x, float min_y, float max_y, float min_z, float max_z,
+                  const float* ptcloud, float* grid, float* grid_pt_weights, int32_t* grid_pt_indexes)
+{
+    const int len_x = (int)(max_x - min_x + 1), len_y = (int)(max_y - min_y + 1), len_z = (int)(max_z - min_z + 1);
+    const int64_t nv = (int64_t)len_x * len_y * len_z;
+    double* acc = (double*)calloc((size_t)nv + 1, sizeof(double));
+    for (int bi = 0; bi < b; ++bi)
+    {
+        for (int64_t i = 0; i < nv; ++i) acc[i] = 0.0;
+        for (int j = 0; j < n_pts; ++j)
+        {
+            const size_t t = (size_t)bi * n_pts + j;
+            const float p[3] = {ptcloud[t * 3 + 0], ptcloud[t * 3 + 1], ptcloud[t * 3 + 2]};
+            const float mn[3] = {min_x, min_y, min_z};
+            int off[2][3];
+            float w[2][3];
+            for (int a = 0; a < 3; ++a)
+            {
+                int lower = (int)floorf(p[a]), upper = (int)ceilf(p[a]);
+                if (lower == upper) upper += 1;
+                off[0][a] = (int)(lower - mn[a]);
+                off[1][a] = (int)(upper - mn[a]);
+                w[0][a] = orc_vertex_weight(p[a], lower);
+                w[1][a] = orc_vertex_weight(p[a], upper);
+            }
+            for (int v = 0; v < 8; ++v)
+            {
+                const int ux = (v >> 2) & 1, uy = (v >> 1) & 1, uz = v & 1;
+                const int ox = off[ux][0], oy = off[uy][1], oz = off[uz][2];
+                const int inside = ox >= 0 && ox < len_x && oy >= 0 && oy < len_y && oz >= 0 && oz < len_z;
+                const int index = inside ? (ox * len_y + oy) * len_z + oz : -1;
+                grid_pt_indexes[t * 8 + v] = index;
+                grid_pt_weights[t * 24 + v * 3 + 0] = w[ux][0];
+                grid_pt_weights[t * 24 + v * 3 + 1] = w[uy][1];
+                grid_pt_weights[t * 24 + v * 3 + 2] = w[uz][2];
+                if (inside)
+                {
+                    const float prod = (w[ux][0] * w[uy][1]) * w[uz][2];
+                    acc[index] += (double)prod;
+                }
+            }
+        }
+        for (int64_t i = 0; i < nv; ++i) grid[(size_t)bi * nv + i] = (float)acc[i];
+    }
+    free(acc);
+}
+
+void orc_gridding_grad(int b, int n_pts, int64_t n_grid_vertices, const float* grid_pt_weights,
+                       const int32_t* grid_pt_indexes, const float* grad_grid, float* grad_ptcloud)
+{
+    for (int bi = 0; bi < b; ++bi)
+        for (int j = 0; j < n_pts; ++j)
+        {
+            const size_t t = (size_t)bi * n_pts + j;
+            float gx = 0, gy = 0, gz = 0;
+            for (int v = 0; v < 8; ++v)
+            {
+                const int index = grid_pt_indexes[t * 8 + v];
+                if (index < 0) continue;
+                const float g = grad_grid[(size_t)bi * n_grid_vertices + index];
+                const float wx = grid_pt_weights[t * 24 + v * 3 + 0], wy = grid_pt_weights[t * 24 + v * 3 + 1],
+                            wz = grid_pt_weights[t * 24 + v * 3 + 2];
+                const float sx = ((v >> 2) & 1) ? g : -g, sy = ((v >> 1) & 1) ? g : -g, sz = (v & 1) ? g : -g;
+                gx = gx + (sx * wy) * wz;
+                gy = gy + (sy * wx) * wz;
+                gz = gz + (sz * wx) * wy;
+            }
+            grad_ptcloud[t * 3 + 0] = gx;
+            grad_ptcloud[t * 3 + 1] = gy;
+            grad_ptcloud[t * 3 + 2] = gz;
+        }
+}
+
+/* ------------------------------------------------------------------ cubic feature sampling (float32)
+ *
+ * cuda/src/cubic_feature_sampling_gpu.cu:22-97 forward (copies, exact), :130-177 backward
+ * (scatter-add, summed in double here and rounded once).
+ */
+void orc_cubic_feature_sampling(int b, int n_pts, int channels, int scale, int neighborhood_size, const float* ptcloud,
+                                const float* cubic_features, float* point_features, int32_t* grid_pt_indexes)
+{
+    const int ns = neighborhood_size - 1, side = 2 * neighborhood_size, nvert = side * side * side;
+    const int64_t cub = (int64_t)scale * scale * scale;
+    for (int bi = 0; bi < b; ++bi)
+        for (int i = 0; i < n_pts; ++i)
+        {
+            const size_t t = (size_t)bi * n_pts + i;
+            int lo[3];
+            for (int a = 0; a < 3; ++a) lo[a] = (int)floorf(ptcloud[t * 3 + a]);
+            int vertex = 0;
+            for (int j = lo[0] - ns; j < lo[0] - ns + side; ++j)
+                for (int k = lo[1] - ns; k < lo[1] - ns + side; ++k)
+                    for (int m = lo[2] - ns; m < lo[2] - ns + side; ++m)
+                    {
+                        const int outside = j < 0 || j >= scale || k < 0 || k >= scale || m < 0 || m >= scale;
+                        const int index = outside ? -1 : (j * scale + k) * scale + m;
+                        grid_pt_indexes[t * nvert + vertex] = index;
+                        for (int c = 0; c < channels; ++c)
+                            point_features[(t * nvert + vertex) * channels + c] =
+                                outside ? 0.f : cubic_features[((size_t)bi * channels + c) * cub + index];
+                        ++vertex;
+                    }
+        }
+}
+
+void orc_cubic_feature_sampling_grad(int b, int n_pts, int channels, int scale, int neighborhood_size,
+                                     const float* grad_point_features, const int32_t* grid_pt_indexes,
+                                     float* grad_cubic_features)
+{
+    const int side = 2 * neighborhood_size, nvert = side * side * side;
+    const int64_t cub = (int64_t)scale * scale * scale;
+    double* acc = (double*)calloc((size_t)channels * cub + 1, sizeof(double));
+    for (int bi = 0; bi < b; ++bi)
+    {
+        for (int64_t i = 0; i < channels * cub; ++i) acc[i] = 0.0;
+        for (int i = 0; i < n_pts; ++i)
+            for (int j = 0; j < nvert; ++j)
+            {
+                const size_t pv = ((size_t)bi * n_pts + i) * nvert + j;
+                const int index = grid_pt_indexes[pv];
+                if (index < 0) continue;
+                for (int c = 0; c < channels; ++c) acc[c * cub + index] += (double)grad_point_features[pv * channels + c];
+            }
+        for (int64_t i = 0; i < channels * cub; ++i) grad_cubic_features[(size_t)bi * channels * cub + i] = (float)acc[i];
+    }
+    free(acc);
+}

@@ -44,6 +44,16 @@ _SIGNATURES = {
     "tpk_chamfer_dist_f64": [_c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_chamfer_dist_grad_f32": [_c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_chamfer_dist_grad_f64": [_c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
+    "tpk_gridding_f32": [_c_int, _c_int, _c_f32, _c_f32, _c_f32, _c_f32, _c_f32, _c_f32, _ptr, _ptr, _ptr, _ptr, _ptr],
+    "tpk_gridding_f64": [_c_int, _c_int, _c_f32, _c_f32, _c_f32, _c_f32, _c_f32, _c_f32, _ptr, _ptr, _ptr, _ptr, _ptr],
+    "tpk_gridding_grad_f32": [_c_int, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr],
+    "tpk_gridding_grad_f64": [_c_int, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr],
+    "tpk_cubic_feature_sampling_f32": [_c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
+    "tpk_cubic_feature_sampling_f64": [_c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
+    "tpk_cubic_feature_sampling_grad_f32": [_c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
+    "tpk_cubic_feature_sampling_grad_f64": [_c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
+    "tpk_grow_labels_step": [_c_i64, _c_int, _ptr, _ptr, _ptr, _c_int, _ptr],
+    "tpk_instance_iou": [_c_int, _c_i64, _c_i64, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
 }
 
 EXPORTS = sorted(list(_SIGNATURES) + ["tpk_version", "tpk_last_error", "tpk_device_status", "tpk_kernel_launches", "tpk_fps_scratch_bytes",
