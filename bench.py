@@ -398,6 +398,18 @@ def per_kernel_times(pipe, dev, ins):
         gg, gu = pipe.g_grouped[l], pipe.g_up[l]
         kms["grouping_bwd" + tag] = graph_time(lambda: tpk.torchpoints.grouping_backward(gg, nbr, n), dev)
         kms["interp_bwd" + tag] = graph_time(lambda: tpk.torchpoints.three_interpolate_backward(gu, idx3, w, m), dev)
+        # the fused set-abstraction grouping (centres + ball query + relative coordinates + features
+        # in one call) beside the sequence a caller of the separate ops runs for the same tensor
+        fidx = tpk.furthest_point_sample(src, m)
+        kms["sa_group" + tag] = graph_time(lambda: tpk.sa_group(src, f, fidx, r, ns), dev)
+
+        def unfused():
+            c_xyz = torch.gather(src, 1, fidx.long().unsqueeze(-1).expand(-1, -1, 3)).contiguous()
+            nb, _ = tpk.ball_query(r, ns, src, c_xyz, mode="dense")
+            rel = tpk.grouping_operation(src.transpose(1, 2).contiguous(), nb) - c_xyz.transpose(1, 2).unsqueeze(-1)
+            return torch.cat([rel, tpk.grouping_operation(f, nb)], dim=1)
+
+        kms["sa_unfused_sequence" + tag] = graph_time(unfused, dev)
         n_in = src.shape[1]
         if n_in >= 1024:  # ball query on the shared-memory grid: cells one radius wide or wider
             cand["ball_query" + tag] = (grid_candidates(src, centres, r, grid_max_dim(n_in)), src.shape[0] * m)
@@ -811,6 +823,14 @@ def run_b200(args, rank, world, local_rank):
     sm_mhz = clocks.get("sm_mhz") or 1965.0
     fp32_peak_lane_ops = 148 * 128 * sm_mhz * 1e6  # lane-ops / s at the sampled clock
     kernels = {}
+    fused = {}
+    for l in range(1, 5):
+        a, b2 = kms.pop("sa_group_l%d" % l), kms.pop("sa_unfused_sequence_l%d" % l)
+        fused["l%d" % l] = {"sa_group_ms": round(a, 4), "unfused_sequence_ms": round(b2, 4),
+                            "ball_query_plus_grouping_fwd_ms": round(kms["ball_query_l%d" % l] + kms["grouping_fwd_l%d" % l], 4)}
+    fused["what"] = ("sa_group = centres + ball query + relative coordinates + features written as one (B,3+C,M,ns) "
+                     "tensor; unfused_sequence = gather, ball_query, two grouping_operations, subtraction and cat for the "
+                     "same tensor; the third figure is ball query + feature grouping alone (no coordinates, no cat)")
     for name, ms in sorted(kms.items()):
         kind, amount = work[name]
         entry = {"ms": round(ms, 4), "bound": kind}
@@ -876,6 +896,7 @@ def run_b200(args, rank, world, local_rank):
         "roofline": roof,
         "kernels": kernels,
     }
+    line["fused_sa_group"] = fused
     line["verified"] = verified
     line["verified_detail"] = verify_detail
     if ref_cuda is not None:
@@ -1253,6 +1274,7 @@ def run_only(args):
         idx = tpk.furthest_point_sample(pts[i], m)
         pts.append(torch.gather(pts[i], 1, idx.long().unsqueeze(-1).expand(-1, -1, 3)).contiguous())
     m = pts[l + 1].shape[1]
+    fps_idx_l = idx
     r, ns, c = LEVELS["radius"][l], LEVELS["nsample"], LEVELS["channels"][l]
     g = torch.Generator(device=dev).manual_seed(3)
     feat = sa_h[l].to(dev)
@@ -1270,6 +1292,7 @@ def run_only(args):
         "grouping_fwd": lambda: tpk.grouping_operation(feat, nbr),
         "grouping_bwd": lambda: tpk.torchpoints.grouping_backward(g_grouped, nbr, feat.shape[2]),
         "interp_fwd": lambda: tpk.three_interpolate(ffeat, idx3, w),
+        "sa_group": lambda: tpk.sa_group(pts[l], feat, fps_idx_l, r, ns),
         "interp_bwd": lambda: tpk.torchpoints.three_interpolate_backward(g_up, idx3, w, m),
     }
     fn = ops[name]

@@ -286,6 +286,26 @@ TPK_API int tpk_grouping(int b, int c, int n, int npoint, int nsample, const flo
 TPK_API int tpk_grouping_grad(int b, int c, int n, int npoint, int nsample, const float* grad_out,
                       const int64_t* idx, float* grad_features, void* stream);
 
+/* ----------------------------------------------------- fused set abstraction ---- */
+
+/*
+ * The grouping step of a PointNet++ set-abstraction layer in one call: gathers the centres
+ * new_xyz[b,j] = xyz[b, fps_idx[b,j]], runs the dense ball query around them, and writes
+ *   out[b, 0:3, j, s]   = xyz[b, idx[b,j,s], :] - new_xyz[b,j,:]      (relative coordinates)
+ *   out[b, 3:3+c, j, s] = features[b, :, idx[b,j,s]]
+ * i.e. torch.cat([grouping(xyz^T, idx) - new_xyz^T[..., None], grouping(features, idx)], 1)
+ * without materialising the parts, bit-identical to that sequence.  xyz (b,n,3), features (b,c,n)
+ * (NULL with c = 0), fps_idx (b,m) int32 -> new_xyz (b,m,3), idx (b,m,nsample) int64 (the ball
+ * query's result, needed by the backward pass: tpk_grouping_grad on rows 3.. of the gradient),
+ * out (b,3+c,m,nsample).  scratch: tpk_sa_group_scratch_bytes(b,n,m,nsample) bytes, 256-byte
+ * aligned, required.  The unfused sequence in the reference's callers:
+ * torch_points_kernels/torchpoints.py:129-146 (grouping), :171-218 (ball query).
+ */
+TPK_API int tpk_sa_group(int b, int n, int m, int c, float radius, int nsample, const float* xyz,
+                         const float* features, const int32_t* fps_idx, float* new_xyz, int64_t* idx, float* out,
+                         void* scratch, int64_t scratch_bytes, void* stream);
+TPK_API int64_t tpk_sa_group_scratch_bytes(int b, int n, int m, int nsample);
+
 /* ------------------------------------------------------------------- chamfer ---- */
 
 /*

@@ -635,6 +635,34 @@ def test_grouping_forward_backward(B, C, N, P, S, monkeypatch):
     np.testing.assert_allclose(npy(f2.grad), want, rtol=1e-4, atol=1e-4)
 
 
+@pytest.mark.parametrize("B,N,M,C,r", [(2, 16384, 4096, 64, 0.1), (3, 4096, 1024, 7, 0.2), (2, 500, 100, 130, 0.4),
+                                       (1, 70000, 64, 3, 0.05), (2, 1024, 256, 0, 0.3)])
+def test_fused_sa_group_equals_the_unfused_sequence(B, N, M, C, r):
+    """tpk.sa_group against gather + ball_query + two grouping_operations + subtraction + cat,
+    bit for bit, forward; the gradient of the features against grouping's backward."""
+    x = cu(data.unit_ball(B, N, seed=N + C))
+    g = data.gen(N)
+    feat = cu(torch.randn(B, C, N, generator=g)).requires_grad_(True) if C else None
+    fps = tpk.furthest_point_sample(x, M)
+    new_xyz, idx, out = tpk.sa_group(x, feat, fps, r, 32)
+    want_xyz = torch.gather(x, 1, fps.long().unsqueeze(-1).expand(-1, -1, 3)).contiguous()
+    want_idx, _ = tpk.ball_query(r, 32, x, want_xyz, mode="dense")
+    rel = tpk.grouping_operation(x.transpose(1, 2).contiguous(), want_idx) - want_xyz.transpose(1, 2).unsqueeze(-1)
+    same_bits(npy(new_xyz), npy(want_xyz))
+    np.testing.assert_array_equal(npy(idx), npy(want_idx))
+    if C:
+        f2 = feat.detach().clone().requires_grad_(True)
+        want = torch.cat([rel, tpk.grouping_operation(f2, want_idx)], dim=1)
+        same_bits(npy(out), npy(want))
+        gout = cu(torch.randn(out.shape, generator=g))
+        out.backward(gout)
+        want.backward(gout)
+        np.testing.assert_allclose(npy(feat.grad), npy(f2.grad), rtol=1e-4, atol=1e-4)
+    else:
+        same_bits(npy(out), npy(rel))
+    assert _lib.device_status() == 0
+
+
 def test_grouping_golden(golden_dir):
     p = np.load(os.path.join(golden_dir, "plumbing.npz"))
     f = cu(p["gfeat"]).requires_grad_(True)

@@ -12,6 +12,7 @@ from .torchpoints import (  # noqa: F401
     ball_query_partial_dense,
     furthest_point_sample,
     grouping_operation,
+    sa_group,
     three_interpolate,
     three_nn,
     ThreeInterpolate,

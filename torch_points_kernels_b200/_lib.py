@@ -52,6 +52,7 @@ _SIGNATURES = {
     "tpk_cubic_feature_sampling_f64": [_c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_cubic_feature_sampling_grad_f32": [_c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_cubic_feature_sampling_grad_f64": [_c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
+    "tpk_sa_group": [_c_int, _c_int, _c_int, _c_int, _c_f32, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr],
     "tpk_grow_labels_step": [_c_i64, _c_int, _ptr, _ptr, _ptr, _c_int, _ptr],
     "tpk_instance_iou": [_c_int, _c_i64, _c_i64, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
 }
@@ -59,7 +60,7 @@ _SIGNATURES = {
 EXPORTS = sorted(list(_SIGNATURES) + ["tpk_version", "tpk_last_error", "tpk_device_status", "tpk_kernel_launches", "tpk_fps_scratch_bytes",
                                        "tpk_fps_static_capacity", "tpk_ball_query_dense_scratch_bytes",
                                        "tpk_three_nn_scratch_bytes", "tpk_chamfer_dist_scratch_bytes",
-                                       "tpk_ball_query_partial_dense_scratch_bytes", "tpk_knn_dense_scratch_bytes",
+                                       "tpk_ball_query_partial_dense_scratch_bytes", "tpk_knn_dense_scratch_bytes", "tpk_sa_group_scratch_bytes",
                                        "tpk_knn_partial_dense_scratch_bytes"])
 
 
@@ -98,6 +99,8 @@ def lib():
         handle.tpk_knn_dense_scratch_bytes.restype = _c_i64
         handle.tpk_knn_partial_dense_scratch_bytes.argtypes = [_c_i64, _c_i64, _c_int]
         handle.tpk_knn_partial_dense_scratch_bytes.restype = _c_i64
+        handle.tpk_sa_group_scratch_bytes.argtypes = [_c_int, _c_int, _c_int, _c_int]
+        handle.tpk_sa_group_scratch_bytes.restype = _c_i64
         handle.tpk_fps_static_capacity.argtypes = []
         handle.tpk_fps_static_capacity.restype = _c_i64
         _lib = handle

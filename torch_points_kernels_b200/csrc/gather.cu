@@ -59,7 +59,7 @@ __device__ __forceinline__ float ldg_or_zero(const float* row, int i) { return i
 
 template <bool VEC>
 __global__ void __launch_bounds__(kGatherThreads)
-    grouping_fwd_kernel(int c, int n, long long ps, const float* __restrict__ features,
+    grouping_fwd_kernel(int c, int n, long long ps, int out_c, int out_off, const float* __restrict__ features,
                         const int64_t* __restrict__ idx, float* __restrict__ out)
 {
     const int bi = blockIdx.z;
@@ -88,7 +88,9 @@ __global__ void __launch_bounds__(kGatherThreads)
         if (pos + 3 < ps) i3 = checked_index(__ldg(ip + 3), n, bad);
     }
     const float* f = features + (static_cast<size_t>(bi) * c + c0) * n;
-    float* o = out + (static_cast<size_t>(bi) * c + c0) * ps + pos;
+    // row (bi, ch) of the result is row out_off + ch of out_c rows per batch element (the fused
+    // set-abstraction op writes its features behind three coordinate rows)
+    float* o = out + (static_cast<size_t>(bi) * out_c + out_off + c0) * ps + pos;
 #pragma unroll 4
     for (int ch = c0; ch < c1; ++ch, f += n, o += ps)
     {
@@ -149,10 +151,31 @@ __device__ __forceinline__ bool wait_bulk_copy(uint32_t mbar)
 // indices loaded once (two 16-byte loads), ROWS x 4 shared-memory gathers, ROWS 16-byte
 // streaming stores.  Gathering from shared memory instead of L1/L2 removes the
 // sector-per-lane traffic that bounds the direct-gather kernel.
-template <int ROWS>
+// Four consecutive indices of a position run: int64 as the callers pass them, or the 16-bit
+// copy the fused set-abstraction op makes (0xFFFF = out of range).
+constexpr uint16_t kBadIdx16 = 0xFFFFu;
+__device__ __forceinline__ void load_four(const int64_t* p, int n, bool& bad, int& i0, int& i1, int& i2, int& i3)
+{
+    const longlong2 a = __ldg(reinterpret_cast<const longlong2*>(p));
+    const longlong2 b2 = __ldg(reinterpret_cast<const longlong2*>(p) + 1);
+    i0 = checked_index(a.x, n, bad);
+    i1 = checked_index(a.y, n, bad);
+    i2 = checked_index(b2.x, n, bad);
+    i3 = checked_index(b2.y, n, bad);
+}
+__device__ __forceinline__ void load_four(const uint16_t* p, int, bool&, int& i0, int& i1, int& i2, int& i3)
+{
+    const ushort4 a = __ldg(reinterpret_cast<const ushort4*>(p));
+    i0 = a.x == kBadIdx16 ? -1 : a.x;
+    i1 = a.y == kBadIdx16 ? -1 : a.y;
+    i2 = a.z == kBadIdx16 ? -1 : a.z;
+    i3 = a.w == kBadIdx16 ? -1 : a.w;
+}
+
+template <int ROWS, class IdxT>
 __global__ void __launch_bounds__(kScatterThreads)
-    grouping_fwd_rows_kernel(int c, int n, long long ps, long long chunk, int use_tma,
-                             const float* __restrict__ features, const int64_t* __restrict__ idx,
+    grouping_fwd_rows_kernel(int c, int n, long long ps, long long chunk, int use_tma, int out_c, int out_off,
+                             const float* __restrict__ features, const IdxT* __restrict__ idx,
                              float* __restrict__ out)
 {
     extern __shared__ __align__(128) float rows[];
@@ -197,15 +220,13 @@ __global__ void __launch_bounds__(kScatterThreads)
 
     const long long p0 = static_cast<long long>(blockIdx.x) * chunk;
     const long long p1 = min(ps, p0 + chunk);
-    const int64_t* ib = idx + static_cast<size_t>(bi) * ps;
-    float* ob = out + (static_cast<size_t>(bi) * c + c0) * ps;
+    const IdxT* ib = idx + static_cast<size_t>(bi) * ps;
+    float* ob = out + (static_cast<size_t>(bi) * out_c + out_off + c0) * ps;
     bool bad = false;
     for (long long p = p0 + static_cast<long long>(threadIdx.x) * 4; p < p1; p += kScatterThreads * 4)
     {
-        const longlong2 a = __ldg(reinterpret_cast<const longlong2*>(ib + p));
-        const longlong2 b2 = __ldg(reinterpret_cast<const longlong2*>(ib + p) + 1);
-        const int i0 = checked_index(a.x, n, bad), i1 = checked_index(a.y, n, bad);
-        const int i2 = checked_index(b2.x, n, bad), i3 = checked_index(b2.y, n, bad);
+        int i0, i1, i2, i3;
+        load_four(ib + p, n, bad, i0, i1, i2, i3);
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
         {
@@ -221,11 +242,11 @@ __global__ void __launch_bounds__(kScatterThreads)
     report_bad(bad);
 }
 
-template <int ROWS>
-int launch_grouping_fwd_rows(int b, int c, int n, long long ps, const float* features,
-                             const int64_t* idx, float* out, cudaStream_t s)
+template <int ROWS, class IdxT>
+int launch_grouping_fwd_rows(int b, int c, int n, long long ps, int out_c, int out_off, const float* features,
+                             const IdxT* idx, float* out, cudaStream_t s)
 {
-    auto kernel = grouping_fwd_rows_kernel<ROWS>;
+    auto kernel = grouping_fwd_rows_kernel<ROWS, IdxT>;
     prefer_max_shared(kernel);
     const size_t smem = static_cast<size_t>(ROWS) * n * sizeof(float);
     if (smem > 48 * 1024)
@@ -251,7 +272,7 @@ int launch_grouping_fwd_rows(int b, int c, int n, long long ps, const float* fea
     TPK_REQUIRE(groups <= 65535 && nchunks < (1ll << 31), "grouping: grid too large");
     const int use_tma = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(features) & 15u) == 0);
     const dim3 g(static_cast<unsigned>(nchunks), static_cast<unsigned>(groups));
-    count_launches(1), kernel<<<g, kScatterThreads, smem, s>>>(c, n, ps, chunk, use_tma, features, idx, out);
+    count_launches(1), kernel<<<g, kScatterThreads, smem, s>>>(c, n, ps, chunk, use_tma, out_c, out_off, features, idx, out);
     return check_launch("grouping");
 }
 
@@ -848,15 +869,15 @@ int launch_scatter(int b, int c, int row_len, long long src_len, const float* gr
 }  // namespace
 }  // namespace tpk
 
-extern "C" int tpk_grouping(int b, int c, int n, int npoint, int nsample, const float* features,
-                            const int64_t* idx, float* out, void* stream)
+namespace tpk
 {
-    using namespace tpk;
-    TPK_REQUIRE(b >= 0 && c >= 0 && n >= 0 && npoint >= 0 && nsample >= 0, "grouping: negative size");
-    const long long ps = static_cast<long long>(npoint) * nsample;
-    if (b == 0 || c == 0 || ps == 0) return TPK_OK;
-    TPK_REQUIRE(features && idx && out && n > 0, "grouping: NULL pointer or empty feature row");
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
+namespace
+{
+// out[b, out_off + ch, p] = features[b, ch, idx[b, p]] for ch < c, rows of out_c per batch element.
+// idx16 (optional): a 16-bit copy of idx, read instead of it by the row-resident kernel.
+int grouping_forward(int b, int c, int n, long long ps, int out_c, int out_off, const float* features, const int64_t* idx,
+                     const uint16_t* idx16, float* out, cudaStream_t s)
+{
     const size_t row_bytes = static_cast<size_t>(n) * sizeof(float);
     if (ps % 4 == 0 && aligned16(idx) && aligned16(out) && row_bytes <= kRowSmemBudget && ps >= 4096 &&
         static_cast<long long>(b) * c <= 65535 && !test_path("gather_direct"))
@@ -867,23 +888,135 @@ extern "C" int tpk_grouping(int b, int c, int n, int npoint, int nsample, const 
         if (rows < 1) rows = 1;
         if (rows > 4) rows = 4;
         if (rows > c) rows = c;
+#define TPK_GF(R)                                                                                                      \
+    return idx16 ? launch_grouping_fwd_rows<R, uint16_t>(b, c, n, ps, out_c, out_off, features, idx16, out, s)         \
+                 : launch_grouping_fwd_rows<R, int64_t>(b, c, n, ps, out_c, out_off, features, idx, out, s)
         switch (rows)
         {
-        case 1: return launch_grouping_fwd_rows<1>(b, c, n, ps, features, idx, out, s);
-        case 2: return launch_grouping_fwd_rows<2>(b, c, n, ps, features, idx, out, s);
-        case 3: return launch_grouping_fwd_rows<3>(b, c, n, ps, features, idx, out, s);
-        default: return launch_grouping_fwd_rows<4>(b, c, n, ps, features, idx, out, s);
+        case 1: TPK_GF(1);
+        case 2: TPK_GF(2);
+        case 3: TPK_GF(3);
+        default: TPK_GF(4);
         }
+#undef TPK_GF
     }
     const long long gx = (ps + kGatherThreads * 4 - 1) / (kGatherThreads * 4);
     const int gy = (c + kChanChunk - 1) / kChanChunk;
     TPK_REQUIRE(gx < (1ll << 31) && gy <= 65535 && b <= 65535, "grouping: grid too large");
     const dim3 g(static_cast<unsigned>(gx), gy, b);
     if (ps % 4 == 0 && aligned16(idx) && aligned16(out))
-        count_launches(1), grouping_fwd_kernel<true><<<g, kGatherThreads, 0, s>>>(c, n, ps, features, idx, out);
+        count_launches(1), grouping_fwd_kernel<true><<<g, kGatherThreads, 0, s>>>(c, n, ps, out_c, out_off, features, idx, out);
     else
-        count_launches(1), grouping_fwd_kernel<false><<<g, kGatherThreads, 0, s>>>(c, n, ps, features, idx, out);
+        count_launches(1), grouping_fwd_kernel<false><<<g, kGatherThreads, 0, s>>>(c, n, ps, out_c, out_off, features, idx, out);
     return check_launch("grouping");
+}
+
+// ------------------------------------------------------- fused set-abstraction grouping
+//
+// The three coordinate rows of the fused op: out[b, a, p, s] = xyz[b, idx[b, p, s], a] - new_xyz[b, p, a]
+// (what callers compute as grouping_operation(xyz^T, idx) - new_xyz^T[..., None]); also writes the
+// 16-bit copy of idx the feature kernel reads.
+__global__ void __launch_bounds__(kGatherThreads)
+    sa_group_xyz_kernel(long long total, int n, int m, int nsample, int out_c, const float* __restrict__ xyz,
+                        const float* __restrict__ new_xyz, const int64_t* __restrict__ idx, float* __restrict__ out,
+                        uint16_t* __restrict__ idx16)
+{
+    const long long t = static_cast<long long>(blockIdx.x) * kGatherThreads + threadIdx.x;
+    if (t >= total) return;
+    const long long ps = static_cast<long long>(m) * nsample;
+    const long long bi = t / ps, pos = t - bi * ps;
+    const long long centre = bi * m + pos / nsample;
+    bool bad = false;
+    const int i = checked_index(__ldg(idx + t), n, bad);
+    if (idx16) idx16[t] = i < 0 ? kBadIdx16 : static_cast<uint16_t>(i);
+    float* o = out + bi * out_c * ps + pos;
+#pragma unroll
+    for (int a = 0; a < 3; ++a)
+    {
+        const float v = i < 0 ? 0.f : __ldg(xyz + (bi * n + i) * 3 + a);
+        o[a * ps] = __fsub_rn(v, __ldg(new_xyz + centre * 3 + a));
+    }
+    report_bad(bad);
+}
+
+__global__ void __launch_bounds__(kGatherThreads)
+    gather_centres_kernel(long long total, int n, int m, const float* __restrict__ xyz, const int32_t* __restrict__ fps_idx,
+                          float* __restrict__ new_xyz)
+{
+    const long long t = static_cast<long long>(blockIdx.x) * kGatherThreads + threadIdx.x;
+    if (t >= total) return;
+    bool bad = false;
+    const int i = checked_index(__ldg(fps_idx + t), n, bad);
+    const float* src = xyz + ((t / m) * n + (i < 0 ? 0 : i)) * 3;
+    new_xyz[3 * t + 0] = __ldg(src + 0);
+    new_xyz[3 * t + 1] = __ldg(src + 1);
+    new_xyz[3 * t + 2] = __ldg(src + 2);
+    report_bad(bad);
+}
+}  // namespace
+}  // namespace tpk
+
+extern "C" int tpk_grouping(int b, int c, int n, int npoint, int nsample, const float* features,
+                            const int64_t* idx, float* out, void* stream)
+{
+    using namespace tpk;
+    TPK_REQUIRE(b >= 0 && c >= 0 && n >= 0 && npoint >= 0 && nsample >= 0, "grouping: negative size");
+    const long long ps = static_cast<long long>(npoint) * nsample;
+    if (b == 0 || c == 0 || ps == 0) return TPK_OK;
+    TPK_REQUIRE(features && idx && out && n > 0, "grouping: NULL pointer or empty feature row");
+    return grouping_forward(b, c, n, ps, c, 0, features, idx, nullptr, out, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int64_t tpk_sa_group_scratch_bytes(int b, int n, int m, int nsample)
+{
+    if (b <= 0 || n <= 0 || m <= 0 || nsample <= 0) return 0;
+    const int64_t per = static_cast<int64_t>(b) * m * nsample;
+    // ball-query scratch, its distances (the fused op does not return them), the 16-bit indices
+    return (tpk_ball_query_dense_scratch_bytes(b, n, m, nsample) + 255) / 256 * 256 + (per * 4 + 255) / 256 * 256 +
+           (per * 2 + 255) / 256 * 256;
+}
+
+extern "C" int tpk_sa_group(int b, int n, int m, int c, float radius, int nsample, const float* xyz, const float* features,
+                            const int32_t* fps_idx, float* new_xyz, int64_t* idx, float* out, void* scratch,
+                            int64_t scratch_bytes, void* stream)
+{
+    using namespace tpk;
+    TPK_REQUIRE(b >= 0 && n >= 0 && m >= 0 && c >= 0 && nsample >= 0, "sa_group: negative size");
+    if (b == 0 || m == 0 || nsample == 0) return TPK_OK;
+    TPK_REQUIRE(n > 0, "sa_group: empty cloud");
+    TPK_REQUIRE(xyz && fps_idx && new_xyz && idx && out && (features || c == 0), "sa_group: NULL pointer");
+    const int64_t want = tpk_sa_group_scratch_bytes(b, n, m, nsample);
+    if (scratch == nullptr || scratch_bytes < want)
+    {
+        set_error("sa_group: scratch of %lld bytes given, %lld needed", static_cast<long long>(scratch ? scratch_bytes : 0),
+                  static_cast<long long>(want));
+        return TPK_ERR_SCRATCH;
+    }
+    TPK_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "sa_group: scratch must be 256-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int64_t per = static_cast<int64_t>(b) * m * nsample;
+    const int64_t bq_bytes = (tpk_ball_query_dense_scratch_bytes(b, n, m, nsample) + 255) / 256 * 256;
+    unsigned char* p = static_cast<unsigned char*>(scratch);
+    void* bq_scratch = bq_bytes ? p : nullptr;
+    float* dist = reinterpret_cast<float*>(p + bq_bytes);
+    uint16_t* idx16 = n < 65535 ? reinterpret_cast<uint16_t*>(p + bq_bytes + (per * 4 + 255) / 256 * 256) : nullptr;
+
+    // 1. the centres
+    const long long centres = static_cast<long long>(b) * m;
+    TPK_REQUIRE((centres + kGatherThreads - 1) / kGatherThreads < (1ll << 31) && (per + kGatherThreads - 1) / kGatherThreads < (1ll << 31),
+                "sa_group: problem too large for one launch");
+    count_launches(1), gather_centres_kernel<<<static_cast<unsigned>((centres + kGatherThreads - 1) / kGatherThreads), kGatherThreads, 0, s>>>(
+        centres, n, m, xyz, fps_idx, new_xyz);
+    // 2. their neighbourhoods (grid search where the cloud is large enough, the scan otherwise)
+    int rc = tpk_ball_query_dense_ws(b, n, m, radius, nsample, new_xyz, xyz, idx, dist, bq_scratch, bq_bytes, stream);
+    if (rc != TPK_OK) return rc;
+    // 3. relative coordinates (rows 0..2) and the 16-bit indices, then the features (rows 3..)
+    const int out_c = 3 + c;
+    count_launches(1), sa_group_xyz_kernel<<<static_cast<unsigned>((per + kGatherThreads - 1) / kGatherThreads), kGatherThreads, 0, s>>>(
+        per, n, m, nsample, out_c, xyz, new_xyz, idx, out, idx16);
+    rc = check_launch("sa_group");
+    if (rc != TPK_OK || c == 0) return rc;
+    return grouping_forward(b, c, n, static_cast<long long>(m) * nsample, out_c, 3, features, idx, idx16, out, s);
 }
 
 extern "C" int tpk_grouping_grad(int b, int c, int n, int npoint, int nsample,

@@ -228,6 +228,74 @@ def grouping_operation(features, idx):
     return GroupingOperation.apply(features, idx)
 
 
+class SAGroup(Function):
+    """Fused grouping step of a set-abstraction layer (see sa_group)."""
+
+    @staticmethod
+    def forward(ctx, xyz, features, fps_idx, radius, nsample):
+        _f32(xyz, "xyz")
+        _lib.check_contiguous(fps_idx, "fps_idx")
+        _lib.check_cuda(fps_idx, "fps_idx")
+        if fps_idx.dtype != torch.int32:
+            raise RuntimeError("fps_idx must be an int32 tensor (what furthest_point_sample returns)")
+        b, n = xyz.shape[0], xyz.shape[1]
+        m = fps_idx.shape[1]
+        c = 0
+        if features is not None:
+            _f32(features, "features")
+            c = features.shape[1]
+        new_xyz = torch.empty((b, m, 3), dtype=torch.float32, device=xyz.device)
+        idx = torch.empty((b, m, nsample), dtype=torch.int64, device=xyz.device)
+        out = torch.empty((b, 3 + c, m, nsample), dtype=torch.float32, device=xyz.device)
+        with torch.cuda.device(xyz.device):
+            need = _lib.lib().tpk_sa_group_scratch_bytes(b, n, m, int(nsample))
+            scratch = torch.empty((max(need, 1),), dtype=torch.uint8, device=xyz.device)
+            _lib.call("tpk_sa_group", b, n, m, c, float(radius), int(nsample), _lib.ptr(xyz), _lib.ptr(features),
+                      _lib.ptr(fps_idx), _lib.ptr(new_xyz), _lib.ptr(idx), _lib.ptr(out), _lib.ptr(scratch), need,
+                      _lib.stream_of(xyz))
+        ctx.sa_group_for_backward = (idx, n, c)
+        ctx.mark_non_differentiable(new_xyz, idx)
+        return new_xyz, idx, out
+
+    @staticmethod
+    def backward(ctx, _g_new_xyz, _g_idx, grad_out):
+        idx, n, c = ctx.sa_group_for_backward
+        grad_features = None
+        if c > 0:
+            # the feature rows of the gradient; the coordinates get none (indices and centres are
+            # selections, and PointNet++ does not train through the point positions)
+            grad_features = grouping_backward(grad_out[:, 3:].contiguous(), idx, n)
+        return None, grad_features, None, None, None
+
+
+def sa_group(xyz, features, fps_idx, radius, nsample):
+    r"""
+    Grouping step of a PointNet++ set-abstraction layer as one fused call: the sequence
+    ``new_xyz = gather(xyz, fps_idx)``; ``idx, _ = ball_query(radius, nsample, xyz, new_xyz)``;
+    ``cat([grouping_operation(xyz^T, idx) - new_xyz^T[..., None], grouping_operation(features, idx)], 1)``
+    of the reference's callers (torchpoints.py:129-146, 171-218), bit-identical to it, without
+    materialising the intermediate tensors.  No counterpart in the reference.
+
+    Parameters
+    ----------
+    xyz : torch.Tensor
+        (B, N, 3) float32 CUDA tensor
+    features : torch.Tensor or None
+        (B, C, N) float32 features of the points
+    fps_idx : torch.Tensor
+        (B, M) int32 indices of the centres (what furthest_point_sample returns)
+    radius, nsample :
+        the ball query's parameters
+
+    Returns
+    -------
+    new_xyz : (B, M, 3) centres
+    idx : (B, M, nsample) int64 neighbour indices
+    new_features : (B, 3 + C, M, nsample), relative coordinates first; differentiable w.r.t. features
+    """
+    return SAGroup.apply(xyz, features, fps_idx, radius, nsample)
+
+
 def ball_query_dense(radius, nsample, xyz, new_xyz, batch_xyz=None, batch_new_xyz=None, sort=False):
     """Reference: torchpoints.py:149-157 -> cuda/src/ball_query.cpp:15-36."""
     if sort:
