@@ -44,8 +44,9 @@ def _guarded(fn):
 
 # ------------------------------------------------------------------------------ FPS
 
-# kernel families of FPS on a cloud that stays on chip: without / with the spatially sorted copy
-FPS_FAMILIES = ["fps_unsorted", "fps_sorted"]
+# kernel families of FPS on a cloud that stays on chip: without the spatially sorted copy, with it
+# and one sample per exchange, with it and several samples per exchange (the default)
+FPS_FAMILIES = ["fps_unsorted", "fps_sorted,fps_single", "fps_sorted"]
 
 
 def test_fps_known_answer(known_answers):
@@ -74,7 +75,7 @@ def test_fps_every_cluster_shape(cfg, monkeypatch):
     x = data.unit_ball(3, 4000, seed=77)
     want = orc.fps(x, 300)
     for tree in (None, "fps_tree"):
-        for family in ("fps_unsorted", "fps_sorted"):
+        for family in FPS_FAMILIES:
             data.use_paths(monkeypatch, "fps_config=" + cfg.replace(",", ":"), tree, family)
             got = npy(tpk.furthest_point_sample(cu(x), 300))
             np.testing.assert_array_equal(got, want)
@@ -106,11 +107,12 @@ def test_fps_sorted_copy_is_the_default_for_big_on_chip_clouds(monkeypatch):
 
 
 @pytest.mark.parametrize("kind", ["clustered", "lattice", "planar", "nonfinite", "many_skipped"])
-@pytest.mark.parametrize("family", ["fps_sorted", "fps_sorted,fps_global"])
+@pytest.mark.parametrize("family", ["fps_sorted", "fps_sorted,fps_single", "fps_sorted,fps_global"])
 def test_fps_sorted_copy_hard_clouds(kind, family, monkeypatch):
     """Warp and chunk skipping must never change a result: crowded cells, exact ties everywhere,
     a collapsed axis, coordinates that are not finite, and points the skip rule excludes.
-    Both kernels that skip: the register-resident one and the one for large clouds."""
+    All kernels that skip: the register-resident ones (several samples per exchange, one sample
+    per exchange) and the one for large clouds."""
     data.use_paths(monkeypatch, family)
     rng = np.random.default_rng(len(kind))
     B, n, m = 2, 6000, 400
@@ -180,6 +182,31 @@ def test_fps_returns_sampled_coordinates(B, N, m, env, monkeypatch):
     tiny = cu(np.full((2, 40, 3), 0.001, np.float32))
     idx, centres = tpk.furthest_point_sample(tiny, 7, return_xyz=True)
     assert (npy(idx) == 0).all() and (npy(centres) == np.float32(0.001)).all()
+
+
+@pytest.mark.parametrize("kind", ["two_blobs", "duplicates", "line", "shell"])
+@pytest.mark.parametrize("cfg", [None, "8:128:4", "2:512:8", "1:128:32", "16:64:4", "1:512:8"])
+def test_fps_several_samples_per_exchange_hard_cases(kind, cfg, monkeypatch):
+    """The batched kernel accepts a candidate only when it is provably the next sample: clouds
+    where the largest minima sit next to each other (two tight blobs, a line), where many points
+    coincide (equal keys everywhere) and a thin shell, through several cluster shapes."""
+    rng = np.random.default_rng(len(kind))
+    B, n, m = 3, 3000, 1200
+    if kind == "two_blobs":
+        x = (rng.standard_normal((B, n, 3)) * 0.01 + (rng.integers(0, 2, (B, n, 1)) * 3.0)).astype(np.float32)
+    elif kind == "duplicates":
+        base = rng.uniform(-1, 1, (B, 40, 3)).astype(np.float32)
+        x = np.take_along_axis(base, rng.integers(0, 40, (B, n, 1)).repeat(3, 2), 1)
+    elif kind == "line":
+        x = np.zeros((B, n, 3), np.float32)
+        x[..., 0] = rng.uniform(0.1, 5, (B, n))
+    else:
+        d = rng.standard_normal((B, n, 3))
+        x = (d / np.linalg.norm(d, axis=2, keepdims=True) * (1 + 1e-4 * rng.standard_normal((B, n, 1)))).astype(np.float32)
+    want = orc.fps(x, m)
+    data.use_paths(monkeypatch, "fps_sorted", cfg and "fps_config=" + cfg)
+    np.testing.assert_array_equal(npy(tpk.furthest_point_sample(cu(x), m)), want)
+    assert _lib.device_status() == 0
 
 
 def test_fps_all_points_skipped():

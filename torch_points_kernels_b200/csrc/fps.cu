@@ -14,6 +14,7 @@
 // reference's strided scan plus shared-memory tree would keep.  That tie rule is
 // encoded as a rank: with bs = largest power of two <= n (at most 512) the reference
 // prefers the smallest bit-reversed (k mod bs), then the smallest (k div bs).
+#include <atomic>
 #include <climits>
 #include <math_constants.h>
 #include <type_traits>
@@ -553,6 +554,461 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
     }
     if (j < m) round(j, std::integral_constant<int, 1>{});
 
+    // no CTA may leave while a peer can still write into its shared memory
+    if (CLUSTERED) cluster_sync_all();
+}
+
+// ---------------------------------------------------------------- several samples per exchange
+//
+// The sorted kernel above pays one arg-max exchange per sample.  This kernel takes up to eight
+// samples out of one exchange, exactly:
+//
+//   Every warp publishes its best point e1 = {key, index, x, y, z} and the KEY of its second
+//   best point (key2).  Every warp then sorts the warps' best points (key, then tie rank of the
+//   index) and accepts the longest prefix t0, t1, ... in which every t_i
+//     (a) is untouched by the samples accepted before it: !(dist(t_i, t_j) < md(t_i)) for all
+//         j < i, evaluated with the update's own arithmetic, so its running minimum - its key -
+//         is what the sequential algorithm would see after applying t_0..t_{i-1};
+//     (b) beats everything a warp that already gave a sample still holds: key(t_i) > key2 of
+//         those warps (running minima only shrink, so key2 bounds the warp's leftovers);
+//     (c) has a positive key (the list is sorted by key, then by the tie rank of the index, so
+//         equal keys come in the reference's order);
+//     (d) follows only samples with finite coordinates: a sample's own minimum must drop to
+//         zero when it is applied, or the reference would pick it again.
+//   Points of warps that gave no sample are bounded by that warp's e1, which sorts after t_i.
+//   So t_i is the largest running minimum that remains after t_0..t_{i-1} were applied: the
+//   sample the reference picks next.  Cutting the prefix early is always allowed, which is
+//   what makes the conservative tests (b) and (c) safe.
+//
+// Late in a run the largest running minima sit in different holes of the cloud, so almost
+// every candidate passes: about five samples per exchange at 16384 points, with the update,
+// the warp arg-max and the cluster exchange paid once for all of them.  Applying several
+// samples is one pass over the warp's points with a minimum per sample in reach; the order
+// of the minima does not matter.  Requires the sorted copy and at most 32 warps per cloud.
+#ifdef TPK_FPS_PROFILE
+// development builds only: per warp of cloud 0, cycles in the four phases of an exchange, number
+// of exchanges and of exchanges in which the warp recomputed its entry
+__device__ long long g_fps_prof[32][12];
+#endif
+constexpr int kFpsBatchMax = 8;       // samples per exchange
+constexpr int kBatchMsgBytes = 24;    // {x, y, z, key2} + key + index
+
+// One warp's entry into a peer's tables: coordinates and key2 (what the acceptance test reads
+// with one load), the key into a compact table of its own (the ranking reads 32 keys with eight
+// loads), and the point's index.
+__device__ __forceinline__ void st_async_batch(uint32_t addr_c, uint32_t addr_key, uint32_t addr_k, uint32_t mbar,
+                                               const uint4& c, uint32_t key, uint32_t k)
+{
+    asm volatile(
+        "st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::
+            "r"(addr_c), "r"(c.x), "r"(c.y), "r"(c.z), "r"(c.w), "r"(mbar)
+        : "memory");
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::
+                     "r"(addr_key), "r"(key), "r"(mbar)
+                 : "memory");
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::
+                     "r"(addr_k), "r"(k), "r"(mbar)
+                 : "memory");
+}
+
+template <int PPT, int MAXT, bool CLUSTERED>
+__global__ void __launch_bounds__(MAXT, 1)
+    fps_batched_kernel(int n, int m, int log2bs, const float* __restrict__ xyz_all,
+                       const float4* __restrict__ sorted_all, int32_t* __restrict__ idxs_all)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nthreads = blockDim.x, nwarps = nthreads >> 5;
+    const int nranks = CLUSTERED ? static_cast<int>(cluster_nctarank()) : 1;
+    const int rank = CLUSTERED ? static_cast<int>(cluster_ctarank()) : 0;
+    const int cloud = blockIdx.x / nranks;
+    const int gtid = rank * nthreads + tid;
+    const int nslots = nranks * nwarps;  // at most 32: one slot per warp of the cluster
+    const int my_slot = rank * nwarps + warp;
+
+    // shared memory: slot tables of both parities (32 x {16, 4, 4} B each), 2 mbarriers, per warp
+    // the sorted candidates of an exchange (8 x 24 B) and the warp's own entry, then the CTA's points
+    uint4* tab_c = reinterpret_cast<uint4*>(smem_raw);        // [2][32] {x, y, z, key2}
+    int* tab_key = reinterpret_cast<int*>(tab_c + 64);        // [2][32] key
+    int* tab_k = tab_key + 64;                                // [2][32] index of the point
+    uint64_t* mbar = reinterpret_cast<uint64_t*>(tab_k + 64);
+    uint4* sort_c = reinterpret_cast<uint4*>(mbar + 2);       // [16 warps][8] {x, y, z, key2}
+    uint2* sort_k = reinterpret_cast<uint2*>(sort_c + 16 * kFpsBatchMax);  // [16 warps][8] {key, index}
+    uint4* own_c = reinterpret_cast<uint4*>(sort_k + 16 * kFpsBatchMax);   // [16 warps]
+    uint2* own_k = reinterpret_cast<uint2*>(own_c + 16);                   // [16 warps] {key, index}
+    float4* sxyz = reinterpret_cast<float4*>(own_k + 16);
+    uint4* my_sort_c = sort_c + warp * kFpsBatchMax;
+    uint2* my_sort_k = sort_k + warp * kFpsBatchMax;
+
+    const float* xyz = xyz_all + static_cast<size_t>(cloud) * n * 3;
+    int32_t* idxs = idxs_all + static_cast<size_t>(cloud) * m;
+
+    float px[PPT], py[PPT], pz[PPT], md[PPT];
+    float bminx = CUDART_INF_F, bminy = CUDART_INF_F, bminz = CUDART_INF_F;
+    float bmaxx = -CUDART_INF_F, bmaxy = -CUDART_INF_F, bmaxz = -CUDART_INF_F;
+#pragma unroll
+    for (int p = 0; p < PPT; ++p)
+    {
+        // slot of the sorted copy: warp-contiguous, lanes interleaved
+        const int slot = ((rank * nwarps + warp) * PPT + p) * 32 + lane;
+        float x = 0.f, y = 0.f, z = 0.f;
+        int k = n;
+        bool valid = false;
+        if (slot < n)
+        {
+            const float4 v = __ldg(sorted_all + static_cast<size_t>(cloud) * n + slot);
+            x = v.x;
+            y = v.y;
+            z = v.z;
+            k = __float_as_int(v.w);
+            const float mag = sumsq_abc(x, y, z);
+            valid = !(static_cast<double>(mag) <= 1e-3);
+            bminx = fminf(bminx, x);
+            bminy = fminf(bminy, y);
+            bminz = fminf(bminz, z);
+            bmaxx = fmaxf(bmaxx, x);
+            bmaxy = fmaxf(bmaxy, y);
+            bmaxz = fmaxf(bmaxz, z);
+        }
+        px[p] = x;
+        py[p] = y;
+        pz[p] = z;
+        md[p] = valid ? 1e10f : -1.0f;  // negative: never a candidate (fminf keeps it negative)
+        sxyz[p * nthreads + tid] = make_float4(x, y, z, __int_as_float(k));
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1)
+    {
+        bminx = fminf(bminx, __shfl_xor_sync(kFullMask, bminx, o));
+        bminy = fminf(bminy, __shfl_xor_sync(kFullMask, bminy, o));
+        bminz = fminf(bminz, __shfl_xor_sync(kFullMask, bminz, o));
+        bmaxx = fmaxf(bmaxx, __shfl_xor_sync(kFullMask, bmaxx, o));
+        bmaxy = fmaxf(bmaxy, __shfl_xor_sync(kFullMask, bmaxy, o));
+        bmaxz = fmaxf(bmaxz, __shfl_xor_sync(kFullMask, bmaxz, o));
+    }
+    if (gtid == 0 && m > 0) idxs[0] = 0;
+    // the list of samples to apply next (the same in every warp), in the warp's sort scratch:
+    // at first the cloud's point 0
+    if (lane == 0)
+    {
+        float cx = 0.f, cy = 0.f, cz = 0.f;
+        if (n > 0)
+        {
+            cx = __ldg(xyz + 0);
+            cy = __ldg(xyz + 1);
+            cz = __ldg(xyz + 2);
+        }
+        my_sort_c[0] = make_uint4(__float_as_uint(cx), __float_as_uint(cy), __float_as_uint(cz), 0u);
+        my_sort_k[0] = make_uint2(0u, 0u);
+        own_c[warp] = make_uint4(0u, 0u, 0u, 0x80000000u);
+        own_k[warp] = make_uint2(0x80000000u, 0u);
+    }
+    // slots no warp owns sort behind every real entry (key INT_MIN), in both tables
+    if (tid < 64 && (tid & 31) >= nslots)
+    {
+        tab_c[tid] = make_uint4(0u, 0u, 0u, 0x80000000u);
+        tab_key[tid] = static_cast<int>(0x80000000u);
+        tab_k[tid] = 0;
+    }
+    if (CLUSTERED)
+    {
+        if (tid == 0)
+        {
+            mbar_init(smem_u32(mbar + 0), 1);
+            mbar_init(smem_u32(mbar + 1), 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        cluster_sync_all();
+    }
+    else
+    {
+        __syncthreads();
+    }
+    // remote addresses of this warp's slot in CTA `lane` of the cluster, parity 0; parity 1 lies
+    // 32 entries (one barrier) further in the same shared window
+    uint32_t rem_c = 0, rem_key = 0, rem_k = 0, rem_bar = 0;
+    if (CLUSTERED && lane < nranks)
+    {
+        rem_c = mapa_cluster(smem_u32(tab_c + my_slot), lane);
+        rem_key = mapa_cluster(smem_u32(tab_key + my_slot), lane);
+        rem_k = mapa_cluster(smem_u32(tab_k + my_slot), lane);
+        rem_bar = mapa_cluster(smem_u32(mbar), lane);
+    }
+    const float4* my_xyz = sxyz + tid;
+    // the warp's entry of the last exchange it recomputed lives in own_c / own_k; infinite bound:
+    // the first pass never skips
+    float skip_above = CUDART_INF_F;
+    bool failed = false;
+    int nb = 1;   // samples to apply
+    int j = 1;    // next output position
+#ifdef TPK_FPS_PROFILE
+    long long prof[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+    long long t0 = clock64(), t1;
+#define TPK_STAMP(i) (t1 = clock64(), prof[i] += t1 - t0, t0 = t1)
+#else
+#define TPK_STAMP(i) ((void)0)
+#endif
+
+    for (int exch = 0; j < m; ++exch)
+    {
+        const int par = exch & 1;
+        if (CLUSTERED && tid == 0)
+            mbar_arrive_expect_tx(smem_u32(mbar + par), static_cast<uint32_t>(nslots * kBatchMsgBytes));
+
+        // ---- 1. apply the samples in reach of the warp's box
+        // lane i tests sample i against the warp's box (the box is the same in every lane): one vote
+        // for all samples
+        // every lane holds all candidates of the list (loads in flight together; entries beyond nb
+        // are stale and unused)
+        uint4 sc[kFpsBatchMax];
+#pragma unroll
+        for (int i = 0; i < kFpsBatchMax; ++i) sc[i] = my_sort_c[i];
+        bool in_reach = false;
+        {
+            const uint4 sl = my_sort_c[lane < kFpsBatchMax ? lane : 0];
+            const float cx = __uint_as_float(sl.x), cy = __uint_as_float(sl.y), cz = __uint_as_float(sl.z);
+            const float ex = fmaxf(fmaxf(bminx - cx, cx - bmaxx), 0.f);
+            const float ey = fmaxf(fmaxf(bminy - cy, cy - bmaxy), 0.f);
+            const float ez = fmaxf(fmaxf(bminz - cz, cz - bmaxz), 0.f);
+            const float lb = __fmaf_rn(ez, ez, __fmaf_rn(ex, ex, __fmul_rn(ey, ey)));
+            in_reach = lane < nb && !(__fmul_rn(lb, 0.9999f) > skip_above);
+        }
+        const uint32_t todo = __ballot_sync(kFullMask, in_reach);
+        const bool touched = todo != 0u;
+#pragma unroll
+        for (int i = 0; i < kFpsBatchMax; ++i)
+        {
+            if ((todo >> i) & 1u)  // warp-uniform
+            {
+                const float cx = __uint_as_float(sc[i].x), cy = __uint_as_float(sc[i].y), cz = __uint_as_float(sc[i].z);
+                if constexpr (PPT >= 2)
+                {
+                    const unsigned long long ncx = pack2(-cx, -cx), ncy = pack2(-cy, -cy), ncz = pack2(-cz, -cz);
+#pragma unroll
+                    for (int p = 0; p < PPT; p += 2)
+                    {
+                        const unsigned long long dx = add2(pack2(px[p], px[p + 1]), ncx);
+                        const unsigned long long dy = add2(pack2(py[p], py[p + 1]), ncy);
+                        const unsigned long long dz = add2(pack2(pz[p], pz[p + 1]), ncz);
+                        float d0, d1;
+                        unpack2(fma2(dz, dz, fma2(dx, dx, mul2(dy, dy))), d0, d1);
+                        md[p] = fminf(d0, md[p]);
+                        md[p + 1] = fminf(d1, md[p + 1]);
+                    }
+                }
+                else
+                {
+                    md[0] = fminf(sumsq_abc(px[0] - cx, py[0] - cy, pz[0] - cz), md[0]);
+                }
+            }
+        }
+        TPK_STAMP(0);
+#ifdef TPK_FPS_PROFILE
+        prof[5] += 1;
+        prof[6] += touched ? 1 : 0;
+#endif
+        if (touched)
+        {
+            // ---- the warp's best point (ties: rank of the original index) and the key of its second best
+            float red[PPT];
+#pragma unroll
+            for (int p = 0; p < PPT; ++p) red[p] = md[p];
+#pragma unroll
+            for (int w = PPT / 2; w >= 1; w >>= 1)
+#pragma unroll
+                for (int p = 0; p < w; ++p) red[p] = fmaxf(red[p], red[p + w]);
+            const float best = red[0];
+            const int key = __float_as_int(best);
+            const int wkey = __reduce_max_sync(kFullMask, key);
+            uint32_t eq = 0;
+#pragma unroll
+            for (int p = 0; p < PPT; ++p) eq |= (md[p] == best) ? (1u << p) : 0u;
+            int bp = __ffs(eq) - 1;
+            if (key == wkey && wkey >= 0 && (eq & (eq - 1u)) != 0u)
+            {
+                uint32_t best_rank = 0xFFFFFFFFu;
+                for (uint32_t e = eq; e != 0u; e &= e - 1u)
+                {
+                    const int p = __ffs(e) - 1;
+                    const uint32_t r = fps_rank(__float_as_int(my_xyz[p * nthreads].w), log2bs);
+                    if (r < best_rank)
+                    {
+                        best_rank = r;
+                        bp = p;
+                    }
+                }
+            }
+            if (bp < 0) bp = 0;
+            const float4 mine = my_xyz[bp * nthreads];
+            // second best of the warp: a lane that holds the best counts the best of its other
+            // points (the vote below does not wait for this reduction, nor it for the vote)
+            float alt = -2.0f;
+#pragma unroll
+            for (int p = 0; p < PPT; ++p) alt = fmaxf(alt, p == bp ? -2.0f : md[p]);
+            int key2 = __reduce_max_sync(kFullMask, __float_as_int(key == wkey ? alt : best));
+            uint32_t ball = __ballot_sync(kFullMask, key == wkey);
+            if (__popc(ball) > 1 && wkey >= 0)
+            {
+                key2 = wkey;  // another lane holds an equal minimum
+                const uint32_t r = key == wkey ? fps_rank(__float_as_int(mine.w), log2bs) : 0xFFFFFFFFu;
+                const uint32_t wr = __reduce_min_sync(kFullMask, r);
+                ball = __ballot_sync(kFullMask, key == wkey && r == wr);
+            }
+            const int h1 = __ffs(ball) - 1;
+            // the holder publishes through shared memory: every warp-wide instruction on this path
+            // costs about a hundred cycles, a store and a load do not
+            if (lane == h1)
+            {
+                own_c[warp] = make_uint4(__float_as_uint(mine.x), __float_as_uint(mine.y), __float_as_uint(mine.z),
+                                         static_cast<uint32_t>(key2));
+                own_k[warp] = make_uint2(static_cast<uint32_t>(wkey), __float_as_uint(mine.w));
+            }
+            __syncwarp();
+            // no skipping on tiny bounds, where a computed distance may have lost precision
+            skip_above = fmaxf(__int_as_float(wkey), 1.0e-30f);
+        }
+
+        TPK_STAMP(1);
+        // ---- 2. publish the warp's entry to every CTA of the cluster
+        if (CLUSTERED)
+        {
+            if (lane < nranks)
+            {
+                const uint4 oc = own_c[warp];
+                const uint2 ok2 = own_k[warp];
+                st_async_batch(rem_c + par * 32 * 16, rem_key + par * 32 * 4, rem_k + par * 32 * 4, rem_bar + par * 8, oc,
+                               ok2.x, ok2.y);
+            }
+            const uint32_t parity = static_cast<uint32_t>(exch >> 1) & 1u;
+            if (!failed && !mbar_wait_bounded(smem_u32(mbar + par), parity))
+            {
+                if (lane == 0) atomicOr(&g_dev_status, kStatusWaitAbandoned);
+                failed = true;
+            }
+        }
+        else
+        {
+            if (lane == 0)
+            {
+                const uint2 ok2 = own_k[warp];
+                tab_c[par * 32 + my_slot] = own_c[warp];
+                tab_key[par * 32 + my_slot] = static_cast<int>(ok2.x);
+                tab_k[par * 32 + my_slot] = static_cast<int>(ok2.y);
+            }
+            __syncthreads();
+        }
+
+        TPK_STAMP(2);
+        // ---- 3. the samples this exchange yields (every warp computes the same list)
+        // Position of every slot's entry in the exact order of the picks: key descending, then the
+        // tie rank of the point's index, then the slot.  Every lane walks the 32 keys of the table
+        // (broadcast loads, no warp-wide instruction; unowned slots hold INT_MIN).
+        const uint4 ec = tab_c[par * 32 + lane];
+        const int key_l = tab_key[par * 32 + lane];
+        const int k_l = tab_k[par * 32 + lane];
+        int4 kq[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) kq[q] = reinterpret_cast<const int4*>(tab_key + par * 32)[q];
+#ifdef TPK_FPS_PROFILE
+        if (key_l == 0x7fffffff || kq[7].w == 0x7fffffff || kq[0].x == 0x7fffffff) prof[4] += 1;
+        TPK_STAMP(8);
+#endif
+        // integer arithmetic on the comparison results, no short-circuit operators: the compiler
+        // turns those into a branch per step, which costs more than the step
+        int pos = 0, same = 0;
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+        {
+            const int ks[4] = {kq[q].x, kq[q].y, kq[q].z, kq[q].w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+            {
+                const int s = 4 * q + c;
+                pos += ks[c] > key_l ? 1 : 0;
+                same += ks[c] == key_l ? 1 : 0;
+            }
+        }
+        const bool tie = same > 1;  // the lane's own slot is the one match; without ties pos is exact
+#ifdef TPK_FPS_PROFILE
+        if (pos == 77) prof[4] += 1;
+        TPK_STAMP(7);
+        if (__any_sync(kFullMask, tie && key_l >= 0)) prof[4] += 1000;
+#endif
+        if (tie && key_l >= 0)  // rare: equal keys of real entries, the ranks of the indices decide
+        {
+            const uint32_t rl = fps_rank(k_l, log2bs);
+            pos = 0;
+            for (int s = 0; s < 32; ++s)
+            {
+                const int ks = tab_key[par * 32 + s];
+                bool before = ks > key_l;
+                if (ks == key_l && s != lane)
+                {
+                    const uint32_t rs = fps_rank(tab_k[par * 32 + s], log2bs);
+                    before = rs < rl || (rs == rl && s < lane);
+                }
+                pos += before ? 1 : 0;
+            }
+        }
+        TPK_STAMP(9);
+        __syncwarp();  // the list of the previous exchange has been read by every lane
+        if (lane < nslots && pos < kFpsBatchMax)
+        {
+            my_sort_c[pos] = ec;
+            my_sort_k[pos] = make_uint2(static_cast<uint32_t>(key_l), static_cast<uint32_t>(k_l));
+        }
+        __syncwarp();
+        TPK_STAMP(10);
+        const int ncand = nslots < kFpsBatchMax ? nslots : kFpsBatchMax;
+        // every lane runs the test (lanes without a candidate on entry 0): no branch, and the
+        // loads do not wait for one another
+        bool ok;
+        {
+            const int tl = lane < ncand ? lane : 0;
+            const uint4 tc = my_sort_c[tl];
+            const float tx = __uint_as_float(tc.x), ty = __uint_as_float(tc.y), tz = __uint_as_float(tc.z);
+            const int tkey = static_cast<int>(my_sort_k[tl].x);
+            const float tmd = __int_as_float(tkey);
+            uint4 ss[kFpsBatchMax - 1];
+#pragma unroll
+            for (int s = 0; s < kFpsBatchMax - 1; ++s) ss[s] = my_sort_c[s < ncand ? s : 0];
+            // (c) a positive key: at zero every remaining point coincides with a sample, samples of
+            // this exchange included, and only the first pick of an exchange knows their order
+            int okw = (tkey > 0 ? 1 : 0) & (lane < ncand ? 1 : 0);
+#pragma unroll
+            for (int s = 0; s < kFpsBatchMax - 1; ++s)
+            {
+                const float sx = __uint_as_float(ss[s].x), sy = __uint_as_float(ss[s].y), sz = __uint_as_float(ss[s].z);
+                // (a) untouched by sample s, with the update's arithmetic (x + (-c) rounds like x - c)
+                const float d = sumsq_abc(tx - sx, ty - sy, tz - sz);
+                // (b) above whatever the warp that gave sample s still holds; (d) sample s drops to
+                // zero once applied to itself, which needs finite coordinates (inf - inf and NaN
+                // leave its minimum where it is, and the reference then picks it again)
+                const float self = sumsq_abc(sx - sx, sy - sy, sz - sz);
+                const int pass = (d < tmd ? 0 : 1) & (tkey > static_cast<int>(ss[s].w) ? 1 : 0) & (self == 0.f ? 1 : 0);
+                okw &= (s >= lane ? 1 : 0) | pass;
+            }
+            ok = okw != 0 || lane == 0;  // the first pick of an exchange is exact by construction
+        }
+        TPK_STAMP(11);
+        const uint32_t okmask = __ballot_sync(kFullMask, ok);
+        nb = __ffs(~okmask) - 1;  // length of the accepted prefix (lane 0 always accepts)
+        if (nb > m - j) nb = m - j;
+        if (gtid == 0)
+        {
+            for (int i = 0; i < nb; ++i)
+            {
+                const uint2 sk = my_sort_k[i];
+                idxs[j + i] = static_cast<int>(sk.x) >= 0 ? static_cast<int>(sk.y) : 0;
+            }
+        }
+        j += nb;
+        TPK_STAMP(3);
+    }
+#ifdef TPK_FPS_PROFILE
+    if (lane == 0 && cloud == 0)
+        for (int i = 0; i < 12; ++i) g_fps_prof[my_slot][i] = prof[i];
+#endif
     // no CTA may leave while a peer can still write into its shared memory
     if (CLUSTERED) cluster_sync_all();
 }
@@ -1426,6 +1882,111 @@ int fps_launch_t(const FpsConfig& c, int b, int n, int m, int log2bs, const floa
     return TPK_OK;
 }
 
+size_t fps_batched_smem_bytes(const FpsConfig& c)
+{
+    // slot tables (2 x 32 x 24 B), 2 mbarriers, per-warp sort scratch (16 x 8 x 24 B) and own entry
+    // (16 x 24 B), coordinates
+    return 2 * 32 * 24 + 16 + 16 * kFpsBatchMax * 24 + 16 * 24 + static_cast<size_t>(c.ppt) * c.nthreads * 4 * sizeof(float);
+}
+
+template <int PPT, int MAXT, bool CLUSTERED>
+int fps_launch_batched_t(const FpsConfig& c, int b, int n, int m, int log2bs, const float* xyz, const float4* sorted,
+                         int32_t* idxs, cudaStream_t stream)
+{
+    auto kernel = fps_batched_kernel<PPT, MAXT, CLUSTERED>;
+    prefer_max_shared(kernel);
+    const size_t smem = fps_batched_smem_bytes(c);
+    cudaError_t err;
+    if (smem > 48 * 1024)
+    {
+        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (err != cudaSuccess)
+        {
+            set_error("fps: shared memory attribute: %s", cudaGetErrorString(err));
+            return TPK_ERR_CUDA;
+        }
+    }
+    if (c.nranks > 8)
+    {
+        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (err != cudaSuccess)
+        {
+            set_error("fps: cluster size attribute: %s", cudaGetErrorString(err));
+            return TPK_ERR_CUDA;
+        }
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(b) * c.nranks, 1, 1);
+    cfg.blockDim = dim3(c.nthreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = c.nranks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    count_launches(1);
+    err = cudaLaunchKernelEx(&cfg, kernel, n, m, log2bs, xyz, sorted, idxs);
+    if (err != cudaSuccess)
+    {
+        set_error("fps launch (several samples per exchange, cluster %d x %d threads x %d points): %s", c.nranks,
+                  c.nthreads, c.ppt, cudaGetErrorString(err));
+        return TPK_ERR_CUDA;
+    }
+    return TPK_OK;
+}
+
+template <bool CLUSTERED>
+int fps_launch_batched(const FpsConfig& c, int b, int n, int m, int log2bs, const float* xyz, const float4* sorted,
+                       int32_t* idxs, cudaStream_t stream)
+{
+    // Blocks of four warps get their own build: with 512 threads as the bound the compiler has
+    // 128 registers, too few to keep the loads of a merge in flight together.  The lean build
+    // stays for batches whose CTAs only fit the GPU at once with it (measured on 64 clouds).
+    const bool roomy = c.nthreads <= 128 && static_cast<long long>(b) * c.nranks <= 2ll * num_sms();
+#define TPK_FPS_BATCHED_CASE(P)                                                                                      \
+    case P:                                                                                                          \
+        return roomy                                                                                                 \
+                   ? fps_launch_batched_t<P, 128, CLUSTERED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream)          \
+                   : fps_launch_batched_t<P, fps_max_threads(P), CLUSTERED>(c, b, n, m, log2bs, xyz, sorted, idxs, stream)
+    switch (c.ppt)
+    {
+        TPK_FPS_BATCHED_CASE(1);
+        TPK_FPS_BATCHED_CASE(2);
+        TPK_FPS_BATCHED_CASE(4);
+        TPK_FPS_BATCHED_CASE(8);
+        TPK_FPS_BATCHED_CASE(16);
+        TPK_FPS_BATCHED_CASE(32);
+    default: break;
+    }
+#undef TPK_FPS_BATCHED_CASE
+    set_error("fps: unsupported points per thread %d", c.ppt);
+    return TPK_ERR_UNSUPPORTED;
+}
+
+// The kernel with several samples per exchange takes clusters of at most 32 warps (one slot per
+// warp) and 16 warps per CTA; test hook "fps_single" keeps the one-sample-per-exchange kernel.
+bool fps_wants_batched(const FpsConfig& c)
+{
+    return c.nranks * (c.nthreads / 32) <= 32 && c.nthreads / 32 <= 16 && !test_path("fps_single");
+}
+
+// Cluster shape for that kernel: eight CTAs of four warps fill the 32 slots with the fewest
+// warps per SM (measured best from 4096 to 32768 points per cloud, for 16 and for 64 clouds).
+// Larger clouds keep the shape fps_pick_config chose, and with it the one-sample kernel.
+void fps_batched_config(int n, FpsConfig* c)
+{
+    char text[8];
+    if (test_value("fps_config", text, sizeof(text)) || test_path("fps_single")) return;
+    FpsConfig e;
+    e.nranks = 8;
+    e.nthreads = 128;
+    e.ppt = round_up_pow2((n + 1023) / 1024);
+    if (fps_config_ok(e, n)) *c = e;
+}
+
 template <bool CLUSTERED, bool SORTED>
 int fps_launch_s(const FpsConfig& c, int b, int n, int m, int log2bs, const float* xyz,
                  const float4* sorted, int32_t* idxs, cudaStream_t stream)
@@ -1526,6 +2087,10 @@ extern "C" int tpk_furthest_point_sampling(int b, int n, int m, const float* xyz
         float4* sorted = static_cast<float4*>(scratch);
         const int rc = fps_launch_sort(b, n, xyz, sorted, s);
         if (rc != TPK_OK) return rc;
+        fps_batched_config(n, &c);
+        if (fps_wants_batched(c))
+            return c.nranks > 1 ? fps_launch_batched<true>(c, b, n, m, log2bs, xyz, sorted, idxs, s)
+                                : fps_launch_batched<false>(c, b, n, m, log2bs, xyz, sorted, idxs, s);
         return c.nranks > 1 ? fps_launch_s<true, true>(c, b, n, m, log2bs, xyz, sorted, idxs, s)
                             : fps_launch_s<false, true>(c, b, n, m, log2bs, xyz, sorted, idxs, s);
     }
@@ -1580,7 +2145,9 @@ static __device__ __align__(256) float g_fps_static_scratch[kFpsStaticFloats];
 namespace
 {
 constexpr int kMaxDevices = 64;
-float* g_fps_static_ptr[kMaxDevices] = {};  // device address of the array, per device
+// device address of the array, per device; threads that race on a device's first call all store
+// the same address
+std::atomic<float*> g_fps_static_ptr[kMaxDevices] = {};
 }  // namespace
 
 extern "C" int64_t tpk_fps_static_capacity(void) { return kFpsStaticFloats; }
@@ -1609,7 +2176,7 @@ extern "C" int tpk_furthest_point_sampling_static(int b, int n, int m, const flo
     }
     // In host code the array's name is only a handle; the kernel needs the address the
     // array has on the device that is current now.  Looked up once per device.
-    float* scratch = g_fps_static_ptr[dev];
+    float* scratch = g_fps_static_ptr[dev].load(std::memory_order_acquire);
     if (scratch == nullptr)
     {
         void* p = nullptr;
@@ -1620,7 +2187,7 @@ extern "C" int tpk_furthest_point_sampling_static(int b, int n, int m, const flo
             return TPK_ERR_CUDA;
         }
         scratch = static_cast<float*>(p);
-        g_fps_static_ptr[dev] = scratch;
+        g_fps_static_ptr[dev].store(scratch, std::memory_order_release);
     }
     int log2bs = floor_log2(n);
     if (log2bs > 9) log2bs = 9;
@@ -1628,3 +2195,10 @@ extern "C" int tpk_furthest_point_sampling_static(int b, int n, int m, const flo
     // running minima), so whatever an earlier call left behind is irrelevant
     return fps_launch_global(b, n, m, log2bs, xyz, scratch, idxs, static_cast<cudaStream_t>(stream));
 }
+
+#ifdef TPK_FPS_PROFILE
+extern "C" __attribute__((visibility("default"))) int tpk_fps_profile_read(long long* out)
+{
+    return cudaMemcpyFromSymbol(out, tpk::g_fps_prof, sizeof(long long) * 32 * 12) == cudaSuccess ? 0 : 2;
+}
+#endif

@@ -133,7 +133,11 @@ __device__ __forceinline__ void scan_candidates(const float* __restrict__ cand, 
     }
 
     // pairs that passed the filter and wait for the exact test: entry e of this thread at
-    // [e * THREADS + tid]
+    // [e * THREADS + tid].  An entry is (position << 1) | q in 16 bits, and one filter branch can
+    // park 4 * kScanBatch * Q pairs before the next flush test: both only hold for these limits.
+    static_assert(Q <= 2, "a parked entry keeps the query in one bit");
+    static_assert(kScanBatch <= 2, "a parked entry keeps the tile position in 15 bits and a branch's pairs must fit");
+    static_assert(kPendCap >= 4 * kScanBatch * Q + 8, "parked pairs of one branch must fit behind the flush threshold");
     __shared__ uint16_t s_pend[kPendCap * THREADS];
     uint16_t* pend = s_pend + tid;
     int npend = 0;
