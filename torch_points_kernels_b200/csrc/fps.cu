@@ -574,7 +574,8 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
 //     (c) has a positive key (the list is sorted by key, then by the tie rank of the index, so
 //         equal keys come in the reference's order);
 //     (d) follows only samples with finite coordinates: a sample's own minimum must drop to
-//         zero when it is applied, or the reference would pick it again.
+//         zero when it is applied, or the reference would pick it again (a warp publishes such
+//         a point with the largest key2 there is, so test (b) covers it).
 //   Points of warps that gave no sample are bounded by that warp's e1, which sorts after t_i.
 //   So t_i is the largest running minimum that remains after t_0..t_{i-1} were applied: the
 //   sample the reference picks next.  Cutting the prefix early is always allowed, which is
@@ -585,11 +586,6 @@ __global__ void __launch_bounds__(fps_max_threads(PPT), 1)
 // the warp arg-max and the cluster exchange paid once for all of them.  Applying several
 // samples is one pass over the warp's points with a minimum per sample in reach; the order
 // of the minima does not matter.  Requires the sorted copy and at most 32 warps per cloud.
-#ifdef TPK_FPS_PROFILE
-// development builds only: per warp of cloud 0, cycles in the four phases of an exchange, number
-// of exchanges and of exchanges in which the warp recomputed its entry
-__device__ long long g_fps_prof[32][12];
-#endif
 constexpr int kFpsBatchMax = 8;       // samples per exchange
 constexpr int kBatchMsgBytes = 24;    // {x, y, z, key2} + key + index
 
@@ -741,13 +737,6 @@ __global__ void __launch_bounds__(MAXT, 1)
     bool failed = false;
     int nb = 1;   // samples to apply
     int j = 1;    // next output position
-#ifdef TPK_FPS_PROFILE
-    long long prof[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-    long long t0 = clock64(), t1;
-#define TPK_STAMP(i) (t1 = clock64(), prof[i] += t1 - t0, t0 = t1)
-#else
-#define TPK_STAMP(i) ((void)0)
-#endif
 
     for (int exch = 0; j < m; ++exch)
     {
@@ -802,11 +791,6 @@ __global__ void __launch_bounds__(MAXT, 1)
                 }
             }
         }
-        TPK_STAMP(0);
-#ifdef TPK_FPS_PROFILE
-        prof[5] += 1;
-        prof[6] += touched ? 1 : 0;
-#endif
         if (touched)
         {
             // ---- the warp's best point (ties: rank of the original index) and the key of its second best
@@ -840,6 +824,7 @@ __global__ void __launch_bounds__(MAXT, 1)
             }
             if (bp < 0) bp = 0;
             const float4 mine = my_xyz[bp * nthreads];
+            const bool mine_finite = sumsq_abc(mine.x - mine.x, mine.y - mine.y, mine.z - mine.z) == 0.f;
             // second best of the warp: a lane that holds the best counts the best of its other
             // points (the vote below does not wait for this reduction, nor it for the vote)
             float alt = -2.0f;
@@ -859,6 +844,10 @@ __global__ void __launch_bounds__(MAXT, 1)
             // costs about a hundred cycles, a store and a load do not
             if (lane == h1)
             {
+                // (d): a point with a non-finite coordinate does not drop to zero when it becomes a
+                // sample (inf - inf and NaN leave its minimum where it is) and the reference then
+                // picks it again; the largest key2 there is stops every later candidate
+                if (!mine_finite) key2 = 0x7fffffff;
                 own_c[warp] = make_uint4(__float_as_uint(mine.x), __float_as_uint(mine.y), __float_as_uint(mine.z),
                                          static_cast<uint32_t>(key2));
                 own_k[warp] = make_uint2(static_cast<uint32_t>(wkey), __float_as_uint(mine.w));
@@ -867,8 +856,6 @@ __global__ void __launch_bounds__(MAXT, 1)
             // no skipping on tiny bounds, where a computed distance may have lost precision
             skip_above = fmaxf(__int_as_float(wkey), 1.0e-30f);
         }
-
-        TPK_STAMP(1);
         // ---- 2. publish the warp's entry to every CTA of the cluster
         if (CLUSTERED)
         {
@@ -897,8 +884,6 @@ __global__ void __launch_bounds__(MAXT, 1)
             }
             __syncthreads();
         }
-
-        TPK_STAMP(2);
         // ---- 3. the samples this exchange yields (every warp computes the same list)
         // Position of every slot's entry in the exact order of the picks: key descending, then the
         // tie rank of the point's index, then the slot.  Every lane walks the 32 keys of the table
@@ -909,10 +894,6 @@ __global__ void __launch_bounds__(MAXT, 1)
         int4 kq[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q) kq[q] = reinterpret_cast<const int4*>(tab_key + par * 32)[q];
-#ifdef TPK_FPS_PROFILE
-        if (key_l == 0x7fffffff || kq[7].w == 0x7fffffff || kq[0].x == 0x7fffffff) prof[4] += 1;
-        TPK_STAMP(8);
-#endif
         // integer arithmetic on the comparison results, no short-circuit operators: the compiler
         // turns those into a branch per step, which costs more than the step
         int pos = 0, same = 0;
@@ -929,11 +910,6 @@ __global__ void __launch_bounds__(MAXT, 1)
             }
         }
         const bool tie = same > 1;  // the lane's own slot is the one match; without ties pos is exact
-#ifdef TPK_FPS_PROFILE
-        if (pos == 77) prof[4] += 1;
-        TPK_STAMP(7);
-        if (__any_sync(kFullMask, tie && key_l >= 0)) prof[4] += 1000;
-#endif
         if (tie && key_l >= 0)  // rare: equal keys of real entries, the ranks of the indices decide
         {
             const uint32_t rl = fps_rank(k_l, log2bs);
@@ -950,7 +926,6 @@ __global__ void __launch_bounds__(MAXT, 1)
                 pos += before ? 1 : 0;
             }
         }
-        TPK_STAMP(9);
         __syncwarp();  // the list of the previous exchange has been read by every lane
         if (lane < nslots && pos < kFpsBatchMax)
         {
@@ -958,7 +933,6 @@ __global__ void __launch_bounds__(MAXT, 1)
             my_sort_k[pos] = make_uint2(static_cast<uint32_t>(key_l), static_cast<uint32_t>(k_l));
         }
         __syncwarp();
-        TPK_STAMP(10);
         const int ncand = nslots < kFpsBatchMax ? nslots : kFpsBatchMax;
         // every lane runs the test (lanes without a candidate on entry 0): no branch, and the
         // loads do not wait for one another
@@ -981,16 +955,12 @@ __global__ void __launch_bounds__(MAXT, 1)
                 const float sx = __uint_as_float(ss[s].x), sy = __uint_as_float(ss[s].y), sz = __uint_as_float(ss[s].z);
                 // (a) untouched by sample s, with the update's arithmetic (x + (-c) rounds like x - c)
                 const float d = sumsq_abc(tx - sx, ty - sy, tz - sz);
-                // (b) above whatever the warp that gave sample s still holds; (d) sample s drops to
-                // zero once applied to itself, which needs finite coordinates (inf - inf and NaN
-                // leave its minimum where it is, and the reference then picks it again)
-                const float self = sumsq_abc(sx - sx, sy - sy, sz - sz);
-                const int pass = (d < tmd ? 0 : 1) & (tkey > static_cast<int>(ss[s].w) ? 1 : 0) & (self == 0.f ? 1 : 0);
+                // (b) above whatever the warp that gave sample s still holds; (d) is folded into key2
+                const int pass = (d < tmd ? 0 : 1) & (tkey > static_cast<int>(ss[s].w) ? 1 : 0);
                 okw &= (s >= lane ? 1 : 0) | pass;
             }
             ok = okw != 0 || lane == 0;  // the first pick of an exchange is exact by construction
         }
-        TPK_STAMP(11);
         const uint32_t okmask = __ballot_sync(kFullMask, ok);
         nb = __ffs(~okmask) - 1;  // length of the accepted prefix (lane 0 always accepts)
         if (nb > m - j) nb = m - j;
@@ -1003,12 +973,7 @@ __global__ void __launch_bounds__(MAXT, 1)
             }
         }
         j += nb;
-        TPK_STAMP(3);
     }
-#ifdef TPK_FPS_PROFILE
-    if (lane == 0 && cloud == 0)
-        for (int i = 0; i < 12; ++i) g_fps_prof[my_slot][i] = prof[i];
-#endif
     // no CTA may leave while a peer can still write into its shared memory
     if (CLUSTERED) cluster_sync_all();
 }
@@ -2196,9 +2161,3 @@ extern "C" int tpk_furthest_point_sampling_static(int b, int n, int m, const flo
     return fps_launch_global(b, n, m, log2bs, xyz, scratch, idxs, static_cast<cudaStream_t>(stream));
 }
 
-#ifdef TPK_FPS_PROFILE
-extern "C" __attribute__((visibility("default"))) int tpk_fps_profile_read(long long* out)
-{
-    return cudaMemcpyFromSymbol(out, tpk::g_fps_prof, sizeof(long long) * 32 * 12) == cudaSuccess ? 0 : 2;
-}
-#endif
