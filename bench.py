@@ -504,14 +504,14 @@ def pipeline_work(B, N):
     return w
 
 
-# DRAM bytes (read + write) per launch of the HBM-bound kernels at the bench's shapes, from the
-# ncu captures summarised under profiles/ (taken with 4 clouds, scaled x4 to the bench's 16:
-# traffic grows in proportion to the number of clouds).
+# DRAM bytes (read + write) of one launch of the HBM-bound kernels at the bench's own shape
+# (16 clouds), from one-launch ncu captures of dram__bytes_read.sum and dram__bytes_write.sum;
+# the commands and figures are in the summaries under profiles/.
 NCU_TRAFFIC_BYTES = {
-    "grouping_bwd_l1": 4 * (138470400 + 3958272),
-    "grouping_fwd_l1": 4 * (20982784 + 76009472),
-    "interp_fwd_l1": 4 * (5781248 + 0),
-    "interp_bwd_l1": 4 * (18360064 + 0),
+    "grouping_bwd_l1": 553670144 + 11491584,
+    "grouping_fwd_l1": 84018432 + 476870912,
+    "interp_fwd_l1": 23094784 + 9831680,
+    "interp_bwd_l1": 73415168 + 2494976,
 }
 
 
