@@ -284,6 +284,16 @@ def time_reference_cuda(ref, dev, dev_in, split, pipe, steps, in_flight):
     rounds = max(2, (steps + in_flight - 1) // in_flight)
     for st in streams:
         st.wait_stream(cur)
+    # one untimed step per stream: the allocator's pool of every stream is filled before the clock
+    # starts (without it the number swings between 73 and 118 ms per step)
+    for st in streams:
+        with torch.cuda.stream(st):
+            rp.step()
+    for st in streams:
+        cur.wait_stream(st)
+    torch.cuda.synchronize(dev)
+    for st in streams:
+        st.wait_stream(cur)
     e0.record()
     for _ in range(rounds):
         for st in streams:

@@ -166,6 +166,20 @@ def test_segment_vectors_are_validated_like_the_reference_cpu_path(known_answers
     _lib.check_segments(torch.tensor([], dtype=torch.long), torch.tensor([], dtype=torch.long))
 
 
+def test_grouping_grad_scratch_is_sized_and_checked():
+    """The sorted backward (rows of more than 32 KB) asks for 4 bytes per position, padded to whole
+    tiles, and refuses a shorter buffer before anything is launched; other shapes ask for nothing."""
+    l = _lib.lib()
+    assert l.tpk_grouping_grad_scratch_bytes(16, 64, 16384, 4096, 32) == 16 * 4096 * 32 * 4
+    assert l.tpk_grouping_grad_scratch_bytes(2, 8, 10000, 100, 3) == 2 * 512 * 4   # 300 positions, one tile of 512
+    assert l.tpk_grouping_grad_scratch_bytes(2, 8, 4096, 1024, 32) == 0           # short rows: the atomic kernels
+    assert l.tpk_grouping_grad_scratch_bytes(1, 3, 60000, 500, 16) == 0           # the row does not fit shared memory
+    assert l.tpk_grouping_grad_scratch_bytes(0, 3, 10000, 5, 1) == 0
+    rc = l.tpk_grouping_grad_ws(2, 8, 10000, 100, 3, ctypes.c_void_p(256), ctypes.c_void_p(256), ctypes.c_void_p(256),
+                                ctypes.c_void_p(256), ctypes.c_int64(100), None)
+    assert rc == 4 and b"scratch" in l.tpk_last_error()
+
+
 def test_test_hook_tokens(monkeypatch):
     """TPK_B200_TEST is a comma-separated token list; a token only matches whole names."""
     l = _lib.lib()

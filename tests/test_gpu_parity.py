@@ -655,11 +655,44 @@ def test_grouping_forward_backward(B, C, N, P, S, monkeypatch):
     out.backward(cu(gout))
     want = orc.grouping_grad(gout, idx, N)
     np.testing.assert_allclose(npy(f.grad), want, rtol=1e-4, atol=1e-4)
-    # the global-atomics fallback gives the same sums
-    data.use_paths(monkeypatch, "scatter_global")
-    f2 = cu(feat).requires_grad_(True)
-    tpk.grouping_operation(f2, cu(idx)).backward(cu(gout))
-    np.testing.assert_allclose(npy(f2.grad), want, rtol=1e-4, atol=1e-4)
+    # the shared-memory-atomics kernels and the global-atomics fallback give the same sums
+    for path in ("scatter_atomic", "scatter_global"):
+        data.use_paths(monkeypatch, path)
+        f2 = cu(feat).requires_grad_(True)
+        tpk.grouping_operation(f2, cu(idx)).backward(cu(gout))
+        np.testing.assert_allclose(npy(f2.grad), want, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("B,C,N,P,S,kind", [
+    (2, 64, 16384, 4096, 32, "ball"),      # level-1 shape: eight tiles of 16384 positions
+    (2, 5, 9000, 1000, 32, "ball"),        # two tiles, the second one short
+    (1, 3, 12000, 700, 24, "one"),         # every position adds to the same column: runs longer than a chunk
+    (2, 4, 9000, 600, 30, "sorted"),       # targets already in order
+    (1, 2, 10000, 333, 7, "random"),       # positions not a multiple of four: tiles staged by hand
+    (1, 1, 40000, 5000, 8, "random"),      # a row that fills most of shared memory: shorter tiles
+])
+def test_grouping_backward_sorted_path(B, C, N, P, S, kind):
+    """The gradient through the inverted index (tpk_grouping_grad_ws) against the fp64 sums of the
+    oracle, on index patterns that stress its runs: ball-query padding, one target, sorted targets."""
+    g = data.gen(N + P + S)
+    if kind == "ball":
+        idx = torch.randint(0, N, (B, P, S), generator=g)
+        cnt = torch.randint(1, S + 1, (B, P, 1), generator=g)
+        slot = torch.arange(S).view(1, 1, S)
+        idx = torch.where(slot < cnt, idx, idx[:, :, :1])  # unused slots repeat the first index
+    elif kind == "one":
+        idx = torch.full((B, P, S), 77, dtype=torch.long)
+    elif kind == "sorted":
+        idx = torch.sort(torch.randint(0, N, (B, P * S), generator=g), dim=1).values.view(B, P, S)
+    else:
+        idx = torch.randint(0, N, (B, P, S), generator=g)
+    gout = torch.randn(B, C, P, S, generator=g)
+    assert _lib.lib().tpk_grouping_grad_scratch_bytes(B, C, N, P, S) > 0
+    got = tpk.torchpoints.grouping_backward(cu(gout), cu(idx), N)
+    want = orc.grouping_grad(gout, idx, N)
+    tol = 1e-4 * max(1.0, float(np.abs(want).max()))
+    np.testing.assert_allclose(npy(got), want, rtol=1e-4, atol=tol)
+    assert _lib.device_status() == 0
 
 
 @pytest.mark.parametrize("B,N,M,C,r", [(2, 16384, 4096, 64, 0.1), (3, 4096, 1024, 7, 0.2), (2, 500, 100, 130, 0.4),
@@ -917,6 +950,38 @@ def test_grouping_skips_indices_out_of_range(path, monkeypatch):
     assert (out[:, :, :, :][np.broadcast_to(mask[:, None], out.shape)] == 0).all()
     keep = ~np.broadcast_to(mask[:, None], out.shape)
     np.testing.assert_array_equal(out[keep], good[keep])
+
+
+def test_grouping_grad_sorted_drops_indices_out_of_range():
+    """Same contract through the inverted index: a bad index adds nothing, sets the status bit,
+    and nothing outside the result tensor is written."""
+    B, C, n, npoint, ns = 2, 8, 10000, 256, 32
+    g = data.gen(13)
+    idx = torch.randint(0, n, (B, npoint, ns), generator=g)
+    gout = torch.randn(B, C, npoint, ns, generator=g)
+    bad = idx.clone()
+    bad[0, 3, 5] = n
+    bad[1, 100, 0] = -1
+    bad[1, 255, 31] = 1 << 40
+    big = torch.zeros(B * C * n + 2 * n, device=DEV)
+    grad = big[n:n + B * C * n].view(B, C, n)
+    gout_d, bad_d = cu(gout), cu(bad)
+    need = _lib.lib().tpk_grouping_grad_scratch_bytes(B, C, n, npoint, ns)
+    assert need > 0
+    scratch = torch.empty(need, dtype=torch.uint8, device=DEV)
+
+    def run():
+        _lib.call("tpk_grouping_grad_ws", B, C, n, npoint, ns, _lib.ptr(gout_d), _lib.ptr(bad_d), _lib.ptr(grad),
+                  _lib.ptr(scratch), need, _lib.stream_of(grad))
+        return grad
+    _, status = _guarded(run)
+    assert status == 2
+    w = gout.clone().numpy()
+    w[0, :, 3, 5] = 0
+    w[1, :, 100, 0] = 0
+    w[1, :, 255, 31] = 0
+    np.testing.assert_allclose(npy(grad), orc.grouping_grad(w, idx.numpy(), n), rtol=1e-4, atol=1e-4)
+    assert float(big[:n].abs().max()) == 0 and float(big[n + B * C * n:].abs().max()) == 0
 
 
 @pytest.mark.parametrize("path", [None, "scatter_global"])

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "tpk_three_interpolate_grad": [_c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_grouping": [_c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr],
     "tpk_grouping_grad": [_c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr],
+    "tpk_grouping_grad_ws": [_c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr],
     "tpk_chamfer_dist_f32": [_c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_chamfer_dist_f64": [_c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
     "tpk_chamfer_dist_grad_f32": [_c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
@@ -61,7 +62,7 @@ EXPORTS = sorted(list(_SIGNATURES) + ["tpk_version", "tpk_last_error", "tpk_devi
                                        "tpk_fps_static_capacity", "tpk_ball_query_dense_scratch_bytes",
                                        "tpk_three_nn_scratch_bytes", "tpk_chamfer_dist_scratch_bytes",
                                        "tpk_ball_query_partial_dense_scratch_bytes", "tpk_knn_dense_scratch_bytes", "tpk_sa_group_scratch_bytes",
-                                       "tpk_knn_partial_dense_scratch_bytes"])
+                                       "tpk_knn_partial_dense_scratch_bytes", "tpk_grouping_grad_scratch_bytes"])
 
 
 def lib():
@@ -101,6 +102,8 @@ def lib():
         handle.tpk_knn_partial_dense_scratch_bytes.restype = _c_i64
         handle.tpk_sa_group_scratch_bytes.argtypes = [_c_int, _c_int, _c_int, _c_int]
         handle.tpk_sa_group_scratch_bytes.restype = _c_i64
+        handle.tpk_grouping_grad_scratch_bytes.argtypes = [_c_int, _c_int, _c_int, _c_int, _c_int]
+        handle.tpk_grouping_grad_scratch_bytes.restype = _c_i64
         handle.tpk_fps_static_capacity.argtypes = []
         handle.tpk_fps_static_capacity.restype = _c_i64
         _lib = handle

@@ -904,7 +904,6 @@ __global__ void __launch_bounds__(MAXT, 1)
 #pragma unroll
             for (int c = 0; c < 4; ++c)
             {
-                const int s = 4 * q + c;
                 pos += ks[c] > key_l ? 1 : 0;
                 same += ks[c] == key_l ? 1 : 0;
             }

@@ -176,8 +176,13 @@ def grouping_backward(grad_out, idx, n):
     B, c, npoint, nsample = grad_out.size()
     grad_features = torch.empty((B, c, n), dtype=torch.float32, device=grad_out.device)
     with torch.cuda.device(grad_out.device):
-        _lib.call("tpk_grouping_grad", B, c, n, npoint, nsample, _lib.ptr(grad_out),
-                  _lib.ptr(idx), _lib.ptr(grad_features), _lib.stream_of(grad_out))
+        # scratch for the inverted index (positions sorted by target); 0 bytes = shapes the sorted
+        # kernels do not cover, which take the atomic kernels
+        need = _lib.lib().tpk_grouping_grad_scratch_bytes(B, c, n, npoint, nsample)
+        scratch = torch.empty(need, dtype=torch.uint8, device=grad_out.device) if need > 0 else None
+        _lib.call("tpk_grouping_grad_ws", B, c, n, npoint, nsample, _lib.ptr(grad_out),
+                  _lib.ptr(idx), _lib.ptr(grad_features), _lib.ptr(scratch) if scratch is not None else None,
+                  need, _lib.stream_of(grad_out))
     return grad_features
 
 
