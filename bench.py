@@ -572,6 +572,31 @@ def measured_peaks():
         return 6650.0, "fallback"
 
 
+def bind_near_gpu(dev_index):
+    """Moves this process onto the host cores of the NUMA node its GPU hangs off, before any pinned
+    buffer is allocated (pages land on the node of the thread that first touches them), so that
+    the per-step host-to-device copy does not cross the socket link.  Returns what it did for the
+    JSON line; a container that only sees one node's cores is left as it is."""
+    try:
+        p = torch.cuda.get_device_properties(dev_index)
+        pci = "%04x:%02x:%02x.0" % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)
+        node = int(open("/sys/bus/pci/devices/%s/numa_node" % pci).read())
+        if node < 0:
+            return {"node": None, "note": "the platform reports no NUMA node for the GPU"}
+        cpus = set()
+        for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0)
+        near = cpus & allowed
+        if not near:
+            return {"node": node, "note": "none of the %d cores this process may use is on that node" % len(allowed)}
+        os.sched_setaffinity(0, near)
+        return {"node": node, "cores": len(near), "of_allowed": len(allowed)}
+    except (OSError, ValueError, AttributeError) as e:
+        return {"node": None, "note": "not bound: %s" % e}
+
+
 def run_b200(args, rank, world, local_rank):
     import torch.distributed as dist
 
@@ -580,6 +605,7 @@ def run_b200(args, rank, world, local_rank):
     _lib.lib()  # fail loudly if the CUDA library is missing
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    host_binding = bind_near_gpu(local_rank)
     B, N = B_CLOUDS, N_POINTS
     xyz_h, sa_h, fp_h = make_inputs(B, N, 2000 + rank)
     host = [xyz_h] + sa_h + fp_h
@@ -888,8 +914,8 @@ def run_b200(args, rank, world, local_rank):
                    "steps_in_flight": "up to %d (one CUDA graph each): the geometry kernels of a step (FPS, ball "
                                       "query, three_nn; they depend on its coordinates only) overlap the feature "
                                       "kernels of the steps before; ms_per_step_isolated is the same step with a "
-                                      "join after every step; the FPS chain of one step (sum of kernels.fps_l*) is "
-                                      "longer than ms_per_step: several steps' chains run side by side"
+                                      "join after every step; the FPS chain of one step (sum of kernels.fps_l*) "
+                                      "runs beside the other kernels of the steps around it"
                                       % (args.in_flight if graphs is not None else 3)},
         "e2e": {"value": round(clouds * args.steps / (ms_e2e * 1e-3), 2), "unit": "clouds/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(ms_e2e / args.steps, 4),
@@ -897,7 +923,8 @@ def run_b200(args, rank, world, local_rank):
                 "h2d_only_ms": round(ms_h2d / args.steps, 4),
                 "h2d_only_gbs": round(pinned_flat.numel() / (ms_h2d / args.steps) / 1e6, 1),
                 "h2d_only_what": "the step's pinned input buffer copied to the device once per step on the same "
-                                 "streams, no kernels: the floor the host link sets for e2e.ms_per_step"},
+                                 "streams, no kernels: the floor the host link sets for e2e.ms_per_step",
+                "host_binding": host_binding},
         "gpu_launches": launches,
         "host_enqueue_ms_per_step": round(host_ms, 3),
         "launch_mode": "cuda graphs (one per step, %d in rotation)" % args.in_flight if graphs is not None else "eager",
