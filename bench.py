@@ -68,7 +68,10 @@ class Pipeline:
         self.B, self.N = B, N
         # two FPS streams, used by alternate steps: the chain is latency-bound and leaves the SMs
         # mostly idle, so the chains of two consecutive steps can run side by side
-        self.s_fps_pair = [torch.cuda.Stream(dev), torch.cuda.Stream(dev)]
+        # High priority: a sampling kernel that becomes ready gets the next free SMs instead of
+        # queueing behind the thousands of CTAs of the feature kernels (every later level waits for it)
+        # (measured: 9114 against 9024 clouds/s)
+        self.s_fps_pair = [torch.cuda.Stream(dev, priority=-1), torch.cuda.Stream(dev, priority=-1)]
         self.s_fps = self.s_fps_pair[0]
         self.nstep = 0
         self.s_geo = torch.cuda.Stream(dev)
