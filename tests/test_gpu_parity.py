@@ -663,6 +663,30 @@ def test_grouping_forward_backward(B, C, N, P, S, monkeypatch):
         np.testing.assert_allclose(npy(f2.grad), want, rtol=1e-4, atol=1e-4)
 
 
+def test_rows_of_exactly_48_kb_in_a_fresh_process():
+    """Three rows of 4096 floats are exactly the 48 KB a launch may take without raising the
+    kernel's shared-memory limit - but the kernel's static mbarrier counts too.  In a process
+    that has not run the same kernel on longer rows before, the call must still work."""
+    import subprocess
+    import sys
+    code = (
+        "import torch, torch_points_kernels_b200 as tpk\n"
+        "g = torch.Generator().manual_seed(5)\n"
+        "f = torch.randn(2, 3, 4096, generator=g).cuda(); idx = torch.randint(0, 4096, (2, 1024, 32), generator=g).cuda()\n"
+        "out = tpk.grouping_operation(f, idx)\n"
+        "ref = torch.gather(f, 2, idx.view(2, 1, -1).expand(2, 3, -1)).view(2, 3, 1024, 32)\n"
+        "assert torch.equal(out, ref)\n"
+        "p = torch.randn(2, 3, 4096, generator=g).cuda(); i3 = torch.randint(0, 4096, (2, 9000, 3), generator=g).int().cuda()\n"
+        "w = torch.rand(2, 9000, 3, generator=g).cuda()\n"
+        "up = tpk.three_interpolate(p, i3, w)\n"
+        "want = (torch.gather(p, 2, i3.long().view(2, 1, -1).expand(2, 3, -1)).view(2, 3, 9000, 3) * w.unsqueeze(1)).sum(-1)\n"
+        "assert torch.allclose(up, want, rtol=1e-5, atol=1e-5)\n"
+        "print('ok')\n")
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..")
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
+
+
 @pytest.mark.parametrize("B,C,N,P,S,kind", [
     (2, 64, 16384, 4096, 32, "ball"),      # level-1 shape: eight tiles of 16384 positions
     (2, 5, 9000, 1000, 32, "ball"),        # two tiles, the second one short

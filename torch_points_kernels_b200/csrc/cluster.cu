@@ -134,7 +134,7 @@ extern "C" int tpk_instance_iou(int n_proposals, int64_t total_gt_instances, int
                   static_cast<long long>(max_gt_instances), 200 * 1024 / 4);
         return TPK_ERR_UNSUPPORTED;
     }
-    if (smem > 48 * 1024)
+    if (smem > kDynSmemOptIn)
     {
         err = cudaFuncSetAttribute(instance_iou_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (err != cudaSuccess)

@@ -1129,7 +1129,7 @@ int fps_launch_sort(int b, int n, const float* xyz, float4* sorted, cudaStream_t
     const int bits = fps_sort_bits(n);
     const size_t smem = sizeof(int) << (3 * bits);
     prefer_max_shared(fps_sort_kernel);
-    if (smem > 48 * 1024)
+    if (smem > kDynSmemOptIn)
     {
         cudaError_t err = cudaFuncSetAttribute(fps_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                static_cast<int>(smem));
@@ -1801,7 +1801,7 @@ int fps_launch_t(const FpsConfig& c, int b, int n, int m, int log2bs, const floa
     prefer_max_shared(kernel);
     const size_t smem = fps_smem_bytes(c);
     cudaError_t err;
-    if (smem > 48 * 1024)
+    if (smem > kDynSmemOptIn)
     {
         err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(smem));
@@ -1861,7 +1861,7 @@ int fps_launch_batched_t(const FpsConfig& c, int b, int n, int m, int log2bs, co
     prefer_max_shared(kernel);
     const size_t smem = fps_batched_smem_bytes(c);
     cudaError_t err;
-    if (smem > 48 * 1024)
+    if (smem > kDynSmemOptIn)
     {
         err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (err != cudaSuccess)

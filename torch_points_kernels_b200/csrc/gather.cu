@@ -249,7 +249,7 @@ int launch_grouping_fwd_rows(int b, int c, int n, long long ps, int out_c, int o
     auto kernel = grouping_fwd_rows_kernel<ROWS, IdxT>;
     prefer_max_shared(kernel);
     const size_t smem = static_cast<size_t>(ROWS) * n * sizeof(float);
-    if (smem > 48 * 1024)
+    if (smem > kDynSmemOptIn)
     {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                static_cast<int>(smem));
@@ -417,7 +417,7 @@ int launch_interp_fwd_rows(int b, int c, int m, int n, const float* points, cons
     auto kernel = interp_fwd_rows_kernel<ROWS>;
     prefer_max_shared(kernel);
     const size_t smem = static_cast<size_t>(ROWS) * m * sizeof(float);
-    if (smem > 48 * 1024)
+    if (smem > kDynSmemOptIn)
     {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                static_cast<int>(smem));
@@ -664,7 +664,7 @@ int launch_grouping_bwd_rows_seg(int b, int c, int row_len, long long src_len, c
     auto kernel = grouping_bwd_rows_kernel<ROWS, SEG>;
     prefer_max_shared(kernel);
     const size_t smem = static_cast<size_t>(ROWS) * row_len * sizeof(float);
-    if (smem > 48 * 1024)
+    if (smem > kDynSmemOptIn)
     {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                static_cast<int>(smem));
@@ -753,7 +753,7 @@ int launch_interp_bwd_rows(int b, int c, int m, int n, const float* grad_out, co
     auto kernel = interp_bwd_rows_kernel<ROWS, THREADS>;
     prefer_max_shared(kernel);
     const size_t smem = static_cast<size_t>(ROWS) * m * sizeof(float);
-    if (smem > 48 * 1024)
+    if (smem > kDynSmemOptIn)
     {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                static_cast<int>(smem));
@@ -834,7 +834,7 @@ int launch_scatter(int b, int c, int row_len, long long src_len, const float* gr
         const size_t smem = static_cast<size_t>(rows) * row_bytes;
         auto kernel = scatter_rows_kernel<INTERP>;
         prefer_max_shared(kernel);
-        if (smem > 48 * 1024)
+        if (smem > kDynSmemOptIn)
         {
             cudaError_t err = cudaFuncSetAttribute(
                 kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));

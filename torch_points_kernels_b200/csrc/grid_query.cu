@@ -502,7 +502,7 @@ int grid_ball_query_dense(int b, int n, int m, float radius, int nsample, const 
     const size_t smem = static_cast<size_t>(nsample) * kGridQueryThreads * 8;
     auto qk = grid_query_kernel;
     prefer_max_shared(qk);
-    if (smem > 48 * 1024)
+    if (smem > kDynSmemOptIn)
     {
         cudaError_t err = cudaFuncSetAttribute(qk, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (err != cudaSuccess)

@@ -307,7 +307,7 @@ size_t knn_smem_bytes(int threads, int q, int k)
 template <class K>
 int set_smem(K kernel, size_t bytes, const char* what)
 {
-    if (bytes > 48 * 1024)
+    if (bytes > kDynSmemOptIn)
     {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                static_cast<int>(bytes));

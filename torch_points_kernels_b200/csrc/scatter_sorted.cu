@@ -317,7 +317,7 @@ int launch_sorted(const SortedPlan& p, int b, int c, int n, long long ps, const 
 {
     auto kernel = grouping_bwd_sorted_kernel;
     prefer_max_shared(kernel);
-    if (p.smem > 48 * 1024)
+    if (p.smem > kDynSmemOptIn)
     {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(p.smem));
         if (err != cudaSuccess)
@@ -370,7 +370,7 @@ extern "C" int tpk_grouping_grad_ws(int b, int c, int n, int npoint, int nsample
         auto kernel = grouping_sort_kernel;
         prefer_max_shared(kernel);
         const size_t smem = static_cast<size_t>(n + 1) * sizeof(uint32_t);
-        if (smem > 48 * 1024)
+        if (smem > kDynSmemOptIn)
         {
             cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
             if (err != cudaSuccess)

@@ -768,7 +768,7 @@ int sg_nn(int k, int b, int n, int m, const float* unknown, const float* known, 
     const size_t smem = base + static_cast<size_t>(qcap) * 10;
     auto kernel = k == 1 ? sg_three_nn_kernel<1> : sg_three_nn_kernel<3>;
     prefer_max_shared(kernel);
-    if (smem > 48 * 1024)
+    if (smem > kDynSmemOptIn)
     {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (err != cudaSuccess)
@@ -876,7 +876,7 @@ int sg_nn_slab(int k, int b, int n, int m, const float* unknown, const float* kn
     }
     auto kernel = k == 1 ? sg_nn_slab_kernel<1> : sg_nn_slab_kernel<3>;
     prefer_max_shared(kernel);
-    if (p.smem > 48 * 1024)
+    if (p.smem > kDynSmemOptIn)
     {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(p.smem));
         if (err != cudaSuccess)
@@ -973,7 +973,7 @@ int sg_ball_query(int b, int n, int m, float radius, int nsample, const float* n
     }
     auto kernel = sg_ball_query_kernel;
     prefer_max_shared(kernel);
-    if (p.smem > 48 * 1024)
+    if (p.smem > kDynSmemOptIn)
     {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(p.smem));
         if (err != cudaSuccess)

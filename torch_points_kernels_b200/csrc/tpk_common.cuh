@@ -53,6 +53,11 @@ struct StatusRegistrar
     }
 
 constexpr unsigned kFullMask = 0xffffffffu;
+// Dynamic shared memory from which a launcher raises the kernel's limit
+// (cudaFuncAttributeMaxDynamicSharedMemorySize).  Well below the 48 KB a launch may use without
+// that: the limit counts a kernel's static shared memory too, so a request of exactly 48 KB by a
+// kernel with one static mbarrier fails with "invalid argument" unless the limit was raised.
+constexpr size_t kDynSmemOptIn = 32 * 1024;
 constexpr int kNumSmsB200 = 148;
 
 inline int num_sms()
