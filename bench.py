@@ -521,7 +521,7 @@ def pipeline_work(B, N):
 # (16 clouds), from one-launch ncu captures of dram__bytes_read.sum and dram__bytes_write.sum;
 # the commands and figures are in the summaries under profiles/.
 NCU_TRAFFIC_BYTES = {
-    "grouping_bwd_l1": 553670144 + 11491584,
+    "grouping_bwd_l1": (16794368 + 0) + (546299904 + 52450304),  # sort kernel + summing kernel
     "grouping_fwd_l1": 84018432 + 476870912,
     "interp_fwd_l1": 23094784 + 9831680,
     "interp_bwd_l1": 73415168 + 2494976,
