@@ -1206,18 +1206,36 @@ def run_workload(args, rank=0, world=1, local_rank=0):
         out["collectives"] = "all_reduce(SUM) of 4 doubles per step (loss), all_gather_into_tensor of (pairs, 2, N) f32 (outputs)"
     elif args.workload == "partial":
         x, y, bx, by = data.packed_planes(seed=3000)
-        xd, yd, bxd, byd = x.to(dev), y.to(dev), bx.to(dev), by.to(dev)
-        ms_bq = _time_calls(lambda: tpk.ball_query(0.05, 64, xd, yd, mode="partial_dense", batch_x=bxd, batch_y=byd),
-                            args.steps, args.warmup, dev)
-        ms_knn = _time_calls(lambda: tpk.knn(xd, yd, 16, batch_support=bxd, batch_pos=byd), args.steps, args.warmup, dev)
+        # a contiguous block of scenes per rank, balanced by support points x queries per scene;
+        # neighbour indices are made global again (+ first support point of the block) and the
+        # per-rank results assembled on every rank (lists of different lengths: gather_ragged)
+        s0, s1, px0, px1, py0, py1 = sharding.packed_block(bx, by, rank, world)
+        xd, yd = x[px0:px1].to(dev), y[py0:py1].to(dev)
+        bxd, byd = (bx[px0:px1] - s0).to(dev), (by[py0:py1] - s0).to(dev)
+        box = {}
+
+        def bq_step():
+            nbr, d2 = tpk.ball_query(0.05, 64, xd, yd, mode="partial_dense", batch_x=bxd, batch_y=byd)
+            box["nbr"] = sharding.gather_ragged(torch.where(nbr >= 0, nbr + px0, nbr)) if world > 1 else nbr
+
+        def knn_step():
+            idx, d2 = tpk.knn(xd, yd, 16, batch_support=bxd, batch_pos=byd)
+            box["knn"] = sharding.gather_ragged(idx + px0) if world > 1 else idx
+
+        ms_bq = timed(bq_step, args.steps, args.warmup)
+        ms_knn = timed(knn_step, args.steps, args.warmup)
         nx = torch.bincount(bx).double()
         ny = torch.bincount(by, minlength=nx.numel()).double()
         pairs = float((nx * ny).sum())
         out.update({"metric": "partial_dense_ball_query_queries_per_s", "unit": "queries/s",
                     "value": round(y.shape[0] / (ms_bq * 1e-3), 1), "points": x.shape[0], "queries": y.shape[0],
-                    "ball_query_ms": round(ms_bq, 3), "knn_k16_ms": round(ms_knn, 3),
+                    "scenes_of_rank0": s1 - s0, "ball_query_ms": round(ms_bq, 3), "knn_k16_ms": round(ms_knn, 3),
                     "knn_queries_per_s": round(y.shape[0] / (ms_knn * 1e-3), 1), "brute_force_pairs": pairs,
-                    "knn_brute_force_equiv_fp32_frac": round(6.0 * pairs / (ms_knn * 1e-3) / lanes, 4)})
+                    "knn_brute_force_equiv_fp32_frac": round(6.0 * pairs / (ms_knn * 1e-3) / lanes / world, 4)})
+        if world > 1:
+            out["collectives"] = ("all_gather_into_tensor of the neighbour lists (queries, 64) and (queries, 16) int64, "
+                                  "padded to the longest block, inside the timed calls")
+            out["gathered_rows"] = [int(box["nbr"].shape[0]), int(box["knn"].shape[0])]
     elif args.workload == "fps_large":
         B, N = args.clouds or 8, 1 << 20
         m = args.npoint or 65536

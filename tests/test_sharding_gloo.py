@@ -110,3 +110,41 @@ def test_single_process_reduction_is_a_plain_mean():
     d1, d2 = torch.rand(3, 10), torch.rand(3, 20)
     got = sharding.reduce_chamfer_loss(d1.sum(), d1.numel(), d2.sum(), d2.numel())
     assert abs(float(got) - float(d1.mean() + d2.mean())) < 1e-6
+
+
+def _worker_ragged(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # a packed batch of 5 segments; ranks take blocks balanced by points x queries
+        nx, ny = [40, 10, 10, 10, 30], [4, 1, 1, 1, 3]
+        bx = torch.cat([torch.full((n,), i, dtype=torch.int64) for i, n in enumerate(nx)])
+        by = torch.cat([torch.full((n,), i, dtype=torch.int64) for i, n in enumerate(ny)])
+        s0, s1, px0, px1, py0, py1 = sharding.packed_block(bx, by, rank, world)
+        rows = torch.arange(py0, py1, dtype=torch.int64).view(-1, 1) * 10 + rank   # this rank's per-query result
+        whole = sharding.gather_ragged(rows)
+        out.put((rank, (s0, s1, px0, px1, py0, py1), whole[:, 0].tolist()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_packed_blocks_and_ragged_gather_two_ranks():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_ragged, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(out.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    (_, b0, w0), (_, b1, w1) = res
+    # blocks are contiguous, cover all segments, points and queries, and are balanced by cost
+    assert b0[0] == 0 and b0[1] == b1[0] and b1[1] == 5
+    assert b0[2] == 0 and b0[3] == b1[2] and b1[3] == 100 and b0[4] == 0 and b0[5] == b1[4] and b1[5] == 10
+    assert b0[1] == 1                         # cost 160 of 280 in the first segment
+    # every rank holds every query's row, in query order; the last digit says which rank computed it
+    assert w0 == w1 and [v // 10 for v in w0] == list(range(10))
+    assert [v % 10 for v in w0] == [0] * 4 + [1] * 6

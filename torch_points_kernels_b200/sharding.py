@@ -108,3 +108,39 @@ def gather_outputs(t, n_items=None, group=None):
         lo, hi = shard_range(n_items, r, world)
         parts.append(out[r * per:r * per + (hi - lo)])
     return torch.cat(parts)
+
+
+def gather_ragged(t, group=None):
+    """Per-rank outputs whose first dimension differs between ranks (the queries of a block of
+    packed segments) assembled in rank order on every rank: the lengths travel in one small
+    all_gather, the rows in one all_gather_into_tensor padded to the longest block."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return t
+    world = dist.get_world_size(group)
+    send = t.contiguous()
+    mine = torch.tensor([send.shape[0]], dtype=torch.int64, device=send.device)
+    lens = torch.empty(world, dtype=torch.int64, device=send.device)
+    dist.all_gather_into_tensor(lens, mine, group=group)
+    lens = [int(v) for v in lens.tolist()]
+    per = max(lens)
+    if send.shape[0] < per:
+        pad = torch.zeros((per - send.shape[0],) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+        send = torch.cat([send, pad])
+    out = torch.empty((world * per,) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+    dist.all_gather_into_tensor(out, send, group=group)
+    return torch.cat([out[r * per:r * per + lens[r]] for r in range(world)])
+
+
+def packed_block(batch_x, batch_y, rank, world_size):
+    """The contiguous block of segments rank takes from a packed batch, balanced by the cost of the
+    brute-force search (support points x queries per segment).  batch_x / batch_y: sorted int64
+    segment ids (host or device).  Returns (first segment, one past the last segment, first and
+    one-past-last support point, first and one-past-last query)."""
+    nseg = int(max(int(batch_x[-1]) if batch_x.numel() else -1, int(batch_y[-1]) if batch_y.numel() else -1)) + 1
+    nx = torch.bincount(batch_x.cpu(), minlength=nseg)
+    ny = torch.bincount(batch_y.cpu(), minlength=nseg)
+    bounds = balanced_blocks((nx.double() * ny.double()).tolist(), world_size)
+    s0, s1 = bounds[rank], bounds[rank + 1]
+    cx = torch.cat([torch.zeros(1, dtype=torch.int64), nx.cumsum(0)])
+    cy = torch.cat([torch.zeros(1, dtype=torch.int64), ny.cumsum(0)])
+    return s0, s1, int(cx[s0]), int(cx[s1]), int(cy[s0]), int(cy[s1])
