@@ -62,7 +62,7 @@ def test_random_shapes_agree_across_kernel_families(seed, monkeypatch):
     iters = 120
     for it in range(iters):
         g = torch.Generator().manual_seed(seed * 100003 + it)
-        op = pick(["fps", "ball", "three_nn", "knn", "group", "interp", "chamfer", "sa_group", "ball_partial"])
+        op = pick(["fps", "ball", "three_nn", "knn", "group", "interp", "chamfer", "sa_group", "ball_partial", "fps_big"])
         if op == "fps":
             B, N = size(1, 20), size(1, 40000)
             m = size(1, min(N, 3000))
@@ -72,6 +72,17 @@ def test_random_shapes_agree_across_kernel_families(seed, monkeypatch):
                 hook("fps_unsorted"); b = tpk.furthest_point_sample(x, m)
                 hook("fps_sorted,fps_single"); c = tpk.furthest_point_sample(x, m)
                 return bool(torch.equal(a, b) and torch.equal(a, c))
+            check(op, (B, N, m), f)
+        elif op == "fps_big":
+            # clouds beyond the on-chip kernels: chunk-skipping kernel on the sorted copy against the
+            # kernel that keeps every running minimum in global memory
+            B, N = size(1, 3), size(131073, 400000)
+            m = size(1, 200)
+            x = cloud(B, N, g).to(dev)
+            def f():
+                hook(None); a = tpk.furthest_point_sample(x, m)
+                hook("fps_unsorted"); b = tpk.furthest_point_sample(x, m)
+                return bool(torch.equal(a, b))
             check(op, (B, N, m), f)
         elif op == "ball":
             B, N, M = size(1, 8), size(1, 30000), size(1, 3000)
