@@ -319,6 +319,17 @@ TPK_API int tpk_sa_group(int b, int n, int m, int c, float radius, int nsample, 
                          void* scratch, int64_t scratch_bytes, void* stream);
 TPK_API int64_t tpk_sa_group_scratch_bytes(int b, int n, int m, int nsample);
 
+/*
+ * Gradient of tpk_sa_group with respect to the features: grad_out is the whole
+ * (b, 3 + c, npoint, nsample) gradient of `out`; rows 3.. of every cloud are read in place
+ * (callers of the unfused ops would slice and copy them) and scattered as tpk_grouping_grad_ws
+ * does.  The coordinate rows carry no gradient to the features.  scratch:
+ * tpk_grouping_grad_scratch_bytes(b, c, n, npoint, nsample) bytes, or NULL for the atomic kernels.
+ */
+TPK_API int tpk_sa_group_grad(int b, int c, int n, int npoint, int nsample, const float* grad_out,
+                              const int64_t* idx, float* grad_features, void* scratch, int64_t scratch_bytes,
+                              void* stream);
+
 /* ------------------------------------------------------------------- chamfer ---- */
 
 /*

@@ -451,7 +451,7 @@ int launch_interp_fwd_rows(int b, int c, int m, int n, const float* points, cons
 // indices and weights each).
 template <bool INTERP>
 __global__ void __launch_bounds__(kScatterThreads)
-    scatter_rows_kernel(int c, int row_len, long long src_len, int rows, int vec_ok,
+    scatter_rows_kernel(int c, int row_len, long long src_len, long long gbs, int rows, int vec_ok,
                         const float* __restrict__ grad_out, const void* __restrict__ idx_v,
                         const float* __restrict__ weight, float* __restrict__ grad_small)
 {
@@ -463,7 +463,7 @@ __global__ void __launch_bounds__(kScatterThreads)
     for (int i = threadIdx.x; i < nrows * row_len; i += kScatterThreads) acc[i] = 0.f;
     __syncthreads();
 
-    const float* g = grad_out + (static_cast<size_t>(bi) * c + c0) * src_len;
+    const float* g = grad_out + static_cast<size_t>(bi) * gbs + static_cast<size_t>(c0) * src_len;
     bool bad = false;
     const bool vec = (src_len % 4 == 0) && vec_ok != 0;  // 16-byte loads need aligned inputs
     if (vec)
@@ -566,7 +566,7 @@ __global__ void __launch_bounds__(kScatterThreads)
 // pre-reduction, used when nsample is not a power of two).
 template <int ROWS, int SEG>
 __global__ void __launch_bounds__(kScatterThreads)
-    grouping_bwd_rows_kernel(int c, int row_len, long long src_len,
+    grouping_bwd_rows_kernel(int c, int row_len, long long src_len, long long gbs,
                              const float* __restrict__ grad_out, const int64_t* __restrict__ idx,
                              float* __restrict__ grad_small)
 {
@@ -589,7 +589,7 @@ __global__ void __launch_bounds__(kScatterThreads)
     const float* gp[ROWS];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r)
-        gp[r] = grad_out + (static_cast<size_t>(bi) * c + c0 + (r < nrows ? r : 0)) * src_len + warp * 32 + lane;
+        gp[r] = grad_out + static_cast<size_t>(bi) * gbs + static_cast<size_t>(c0 + (r < nrows ? r : 0)) * src_len + warp * 32 + lane;
 
     for (long long set = warp; set < nfull; set += NWARPS * UNROLL)
     {
@@ -648,7 +648,7 @@ __global__ void __launch_bounds__(kScatterThreads)
             if (i0 >= 0)
                 for (int r = 0; r < nrows; ++r)
                     atomicAdd(acc + r * row_len + i0,
-                              grad_out[(static_cast<size_t>(bi) * c + c0 + r) * src_len + p]);
+                              grad_out[static_cast<size_t>(bi) * gbs + static_cast<size_t>(c0 + r) * src_len + p]);
         }
     }
     __syncthreads();
@@ -658,7 +658,7 @@ __global__ void __launch_bounds__(kScatterThreads)
 }
 
 template <int ROWS, int SEG>
-int launch_grouping_bwd_rows_seg(int b, int c, int row_len, long long src_len, const float* grad_out,
+int launch_grouping_bwd_rows_seg(int b, int c, int row_len, long long src_len, long long gbs, const float* grad_out,
                                  const int64_t* idx, float* grad_small, cudaStream_t s)
 {
     auto kernel = grouping_bwd_rows_kernel<ROWS, SEG>;
@@ -676,13 +676,13 @@ int launch_grouping_bwd_rows_seg(int b, int c, int row_len, long long src_len, c
     }
     const long long grid = static_cast<long long>(b) * ((c + ROWS - 1) / ROWS);
     TPK_REQUIRE(grid < (1ll << 31), "grouping_grad: too many rows");
-    count_launches(1), kernel<<<static_cast<unsigned>(grid), kScatterThreads, smem, s>>>(c, row_len, src_len, grad_out, idx,
+    count_launches(1), kernel<<<static_cast<unsigned>(grid), kScatterThreads, smem, s>>>(c, row_len, src_len, gbs, grad_out, idx,
                                                                     grad_small);
     return check_launch("grouping_grad");
 }
 
 template <int ROWS>
-int launch_grouping_bwd_rows(int b, int c, int row_len, long long src_len, int nsample,
+int launch_grouping_bwd_rows(int b, int c, int row_len, long long src_len, long long gbs, int nsample,
                              const float* grad_out, const int64_t* idx, float* grad_small,
                              cudaStream_t s)
 {
@@ -691,10 +691,10 @@ int launch_grouping_bwd_rows(int b, int c, int row_len, long long src_len, int n
     if (nsample > 1 && (nsample & (nsample - 1)) == 0) seg = nsample < 32 ? nsample : 32;
     switch (seg)
     {
-    case 32: return launch_grouping_bwd_rows_seg<ROWS, 32>(b, c, row_len, src_len, grad_out, idx, grad_small, s);
-    case 16: return launch_grouping_bwd_rows_seg<ROWS, 16>(b, c, row_len, src_len, grad_out, idx, grad_small, s);
-    case 8: return launch_grouping_bwd_rows_seg<ROWS, 8>(b, c, row_len, src_len, grad_out, idx, grad_small, s);
-    default: return launch_grouping_bwd_rows_seg<ROWS, 1>(b, c, row_len, src_len, grad_out, idx, grad_small, s);
+    case 32: return launch_grouping_bwd_rows_seg<ROWS, 32>(b, c, row_len, src_len, gbs, grad_out, idx, grad_small, s);
+    case 16: return launch_grouping_bwd_rows_seg<ROWS, 16>(b, c, row_len, src_len, gbs, grad_out, idx, grad_small, s);
+    case 8: return launch_grouping_bwd_rows_seg<ROWS, 8>(b, c, row_len, src_len, gbs, grad_out, idx, grad_small, s);
+    default: return launch_grouping_bwd_rows_seg<ROWS, 1>(b, c, row_len, src_len, gbs, grad_out, idx, grad_small, s);
     }
 }
 
@@ -773,7 +773,7 @@ int launch_interp_bwd_rows(int b, int c, int m, int n, const float* grad_out, co
 
 template <bool INTERP>
 __global__ void __launch_bounds__(kGatherThreads)
-    scatter_global_kernel(int c, int row_len, long long src_len, const float* __restrict__ grad_out,
+    scatter_global_kernel(int c, int row_len, long long src_len, long long gbs, const float* __restrict__ grad_out,
                           const void* __restrict__ idx_v, const float* __restrict__ weight,
                           float* __restrict__ grad_small)
 {
@@ -799,7 +799,7 @@ __global__ void __launch_bounds__(kGatherThreads)
     }
     for (int ch = c0; ch < c1; ++ch)
     {
-        const float gv = __ldg(grad_out + (static_cast<size_t>(bi) * c + ch) * src_len + p);
+        const float gv = __ldg(grad_out + static_cast<size_t>(bi) * gbs + static_cast<size_t>(ch) * src_len + p);
         float* dst = grad_small + (static_cast<size_t>(bi) * c + ch) * row_len;
         if (!INTERP)
         {
@@ -818,7 +818,7 @@ __global__ void __launch_bounds__(kGatherThreads)
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <bool INTERP>
-int launch_scatter(int b, int c, int row_len, long long src_len, const float* grad_out,
+int launch_scatter(int b, int c, int row_len, long long src_len, long long gbs, const float* grad_out,
                    const void* idx, const float* weight, float* grad_small, cudaStream_t s,
                    const char* what)
 {
@@ -846,9 +846,9 @@ int launch_scatter(int b, int c, int row_len, long long src_len, const float* gr
         }
         const long long grid = static_cast<long long>(b) * ((c + rows - 1) / rows);
         TPK_REQUIRE(grid < (1ll << 31), "%s: too many rows", what);
-        const int vec_ok = aligned16(grad_out) && aligned16(idx) && (weight == nullptr || aligned16(weight));
+        const int vec_ok = aligned16(grad_out) && gbs % 4 == 0 && aligned16(idx) && (weight == nullptr || aligned16(weight));
         count_launches(1), kernel<<<static_cast<unsigned>(grid), kScatterThreads, smem, s>>>(
-            c, row_len, src_len, rows, vec_ok, grad_out, idx, weight, grad_small);
+            c, row_len, src_len, gbs, rows, vec_ok, grad_out, idx, weight, grad_small);
         return check_launch(what);
     }
     cudaError_t err = cudaMemsetAsync(grad_small, 0, static_cast<size_t>(b) * c * row_bytes, s);
@@ -861,7 +861,7 @@ int launch_scatter(int b, int c, int row_len, long long src_len, const float* gr
     TPK_REQUIRE(gx < (1ll << 31) && b <= 65535 && (c + kChanChunk - 1) / kChanChunk <= 65535,
                 "%s: grid too large", what);
     const dim3 g(static_cast<unsigned>(gx), (c + kChanChunk - 1) / kChanChunk, b);
-    count_launches(1), scatter_global_kernel<INTERP><<<g, kGatherThreads, 0, s>>>(c, row_len, src_len, grad_out, idx,
+    count_launches(1), scatter_global_kernel<INTERP><<<g, kGatherThreads, 0, s>>>(c, row_len, src_len, gbs, grad_out, idx,
                                                               weight, grad_small);
     return check_launch(what);
 }
@@ -1019,16 +1019,19 @@ extern "C" int tpk_sa_group(int b, int n, int m, int c, float radius, int nsampl
     return grouping_forward(b, c, n, static_cast<long long>(m) * nsample, out_c, 3, features, idx, idx16, out, s);
 }
 
-extern "C" int tpk_grouping_grad(int b, int c, int n, int npoint, int nsample,
-                                 const float* grad_out, const int64_t* idx, float* grad_features,
-                                 void* stream)
+namespace tpk
 {
-    using namespace tpk;
+// Gradient of grouping with shared-memory (or, for long rows, global) atomics.  Row (bi, ch) of
+// the incoming gradient starts at grad_out + bi * gbs + ch * npoint * nsample: gbs is the batch
+// stride in floats (c * npoint * nsample for a plain (b,c,npoint,nsample) tensor; the fused
+// set-abstraction op passes the feature rows of its (b,3+c,npoint,nsample) gradient).
+int grouping_grad_atomic(int b, int c, int n, int npoint, int nsample, const float* grad_out, long long gbs,
+                         const int64_t* idx, float* grad_features, cudaStream_t s)
+{
     TPK_REQUIRE(b >= 0 && c >= 0 && n >= 0 && npoint >= 0 && nsample >= 0,
                 "grouping_grad: negative size");
     if (b == 0 || c == 0 || n == 0) return TPK_OK;
     TPK_REQUIRE(grad_features, "grouping_grad: NULL pointer");
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
     const long long ps = static_cast<long long>(npoint) * nsample;
     if (ps == 0)
     {
@@ -1055,13 +1058,23 @@ extern "C" int tpk_grouping_grad(int b, int c, int n, int npoint, int nsample,
         while (rows > 1 && static_cast<long long>(b) * ((c + rows - 1) / rows) < 2ll * num_sms()) --rows;
         switch (rows)
         {
-        case 1: return launch_grouping_bwd_rows<1>(b, c, n, ps, nsample, grad_out, idx, grad_features, s);
-        case 2: return launch_grouping_bwd_rows<2>(b, c, n, ps, nsample, grad_out, idx, grad_features, s);
-        case 3: return launch_grouping_bwd_rows<3>(b, c, n, ps, nsample, grad_out, idx, grad_features, s);
-        default: return launch_grouping_bwd_rows<4>(b, c, n, ps, nsample, grad_out, idx, grad_features, s);
+        case 1: return launch_grouping_bwd_rows<1>(b, c, n, ps, gbs, nsample, grad_out, idx, grad_features, s);
+        case 2: return launch_grouping_bwd_rows<2>(b, c, n, ps, gbs, nsample, grad_out, idx, grad_features, s);
+        case 3: return launch_grouping_bwd_rows<3>(b, c, n, ps, gbs, nsample, grad_out, idx, grad_features, s);
+        default: return launch_grouping_bwd_rows<4>(b, c, n, ps, gbs, nsample, grad_out, idx, grad_features, s);
         }
     }
-    return launch_scatter<false>(b, c, n, ps, grad_out, idx, nullptr, grad_features, s, "grouping_grad");
+    return launch_scatter<false>(b, c, n, ps, gbs, grad_out, idx, nullptr, grad_features, s, "grouping_grad");
+}
+}  // namespace tpk
+
+extern "C" int tpk_grouping_grad(int b, int c, int n, int npoint, int nsample,
+                                 const float* grad_out, const int64_t* idx, float* grad_features,
+                                 void* stream)
+{
+    return tpk::grouping_grad_atomic(b, c, n, npoint, nsample, grad_out,
+                                     static_cast<long long>(c) * npoint * nsample, idx, grad_features,
+                                     static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int tpk_three_interpolate(int b, int c, int m, int n, const float* points,
@@ -1121,6 +1134,6 @@ extern "C" int tpk_three_interpolate_grad(int b, int c, int n, int m, const floa
         if (n >= 2048) return launch_interp_bwd_rows<2, 128>(b, c, m, n, grad_out, idx, weight, grad_points, s);
         return launch_interp_bwd_rows<4, 128>(b, c, m, n, grad_out, idx, weight, grad_points, s);
     }
-    return launch_scatter<true>(b, c, m, n, grad_out, idx, weight, grad_points, s,
+    return launch_scatter<true>(b, c, m, n, static_cast<long long>(c) * n, grad_out, idx, weight, grad_points, s,
                                 "three_interpolate_grad");
 }

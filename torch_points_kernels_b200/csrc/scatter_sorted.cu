@@ -201,7 +201,7 @@ __device__ __forceinline__ bool wait_parity_bounded(uint32_t mbar, uint32_t pari
 
 // One CTA per (batch, channel) row.
 __global__ void __launch_bounds__(kSortedThreads, 1)
-    grouping_bwd_sorted_kernel(int n, long long ps, int tile, int chunk, int tiles, int bufs, int use_tma, int c,
+    grouping_bwd_sorted_kernel(int n, long long ps, long long gbs, int tile, int chunk, int tiles, int bufs, int use_tma, int c,
                                const float* __restrict__ grad_out, const uint32_t* __restrict__ entries,
                                float* __restrict__ grad_small)
 {
@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(kSortedThreads, 1)
     const int astr = acc_stride(n), tstr = tile_stride(tile);
     float* acc = smem;            // [astr]
     float* stage = smem + astr;   // [bufs][tstr]
-    const float* g = grad_out + static_cast<size_t>(blockIdx.x) * ps;
+    const float* g = grad_out + static_cast<size_t>(bi) * gbs + static_cast<size_t>(blockIdx.x - bi * c) * ps;
     const uint32_t* ent = entries + static_cast<size_t>(bi) * tiles * tile + static_cast<size_t>(warp) * 32 * chunk + lane;
 
     for (int i = tid; i < astr; i += kSortedThreads) acc[i] = 0.f;
@@ -312,7 +312,7 @@ __global__ void __launch_bounds__(kSortedThreads, 1)
     for (int i = tid; i < n; i += kSortedThreads) dst[i] = acc[i];
 }
 
-int launch_sorted(const SortedPlan& p, int b, int c, int n, long long ps, const float* grad_out, const uint32_t* entries,
+int launch_sorted(const SortedPlan& p, int b, int c, int n, long long ps, long long gbs, const float* grad_out, const uint32_t* entries,
                   float* grad_small, cudaStream_t s)
 {
     auto kernel = grouping_bwd_sorted_kernel;
@@ -328,9 +328,9 @@ int launch_sorted(const SortedPlan& p, int b, int c, int n, long long ps, const 
     }
     const long long grid = static_cast<long long>(b) * c;
     TPK_REQUIRE(grid < (1ll << 31), "grouping_grad: too many rows");
-    const int use_tma = (ps % 4 == 0) && ((reinterpret_cast<uintptr_t>(grad_out) & 15u) == 0);
+    const int use_tma = (ps % 4 == 0) && (gbs % 4 == 0) && ((reinterpret_cast<uintptr_t>(grad_out) & 15u) == 0);
     count_launches(1), kernel<<<static_cast<unsigned>(grid), kSortedThreads, p.smem, s>>>(
-                           n, ps, p.tile, p.chunk, p.tiles, p.bufs, use_tma, c, grad_out, entries, grad_small);
+                           n, ps, gbs, p.tile, p.chunk, p.tiles, p.bufs, use_tma, c, grad_out, entries, grad_small);
     return check_launch("grouping_grad (sorted)");
 }
 
@@ -345,10 +345,15 @@ extern "C" int64_t tpk_grouping_grad_scratch_bytes(int b, int c, int n, int npoi
     return static_cast<int64_t>(b) * p.tiles * p.tile * static_cast<int64_t>(sizeof(uint32_t));
 }
 
-extern "C" int tpk_grouping_grad_ws(int b, int c, int n, int npoint, int nsample, const float* grad_out, const int64_t* idx,
-                                    float* grad_features, void* scratch, int64_t scratch_bytes, void* stream)
+namespace tpk
 {
-    using namespace tpk;
+namespace
+{
+// grad_out rows as in grouping_grad_atomic (gbs = batch stride in floats)
+int grouping_grad_with_scratch(int b, int c, int n, int npoint, int nsample, const float* grad_out, long long gbs,
+                               const int64_t* idx, float* grad_features, void* scratch, int64_t scratch_bytes,
+                               cudaStream_t s)
+{
     TPK_REQUIRE(b >= 0 && c >= 0 && n >= 0 && npoint >= 0 && nsample >= 0, "grouping_grad: negative size");
     const int64_t want = tpk_grouping_grad_scratch_bytes(b, c, n, npoint, nsample);
     if (scratch != nullptr && scratch_bytes < want)
@@ -361,10 +366,9 @@ extern "C" int tpk_grouping_grad_ws(int b, int c, int n, int npoint, int nsample
     const long long ps = static_cast<long long>(npoint) * nsample;
     if (scratch == nullptr || want == 0 || test_path("scatter_atomic") || test_path("scatter_global") ||
         !make_plan(n, ps, &p))
-        return tpk_grouping_grad(b, c, n, npoint, nsample, grad_out, idx, grad_features, stream);
+        return grouping_grad_atomic(b, c, n, npoint, nsample, grad_out, gbs, idx, grad_features, s);
     TPK_REQUIRE(grad_out && idx && grad_features, "grouping_grad: NULL pointer");
     TPK_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 3u) == 0, "grouping_grad: scratch must be 4-byte aligned");
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
     uint32_t* entries = static_cast<uint32_t*>(scratch);
     {
         auto kernel = grouping_sort_kernel;
@@ -385,5 +389,23 @@ extern "C" int tpk_grouping_grad_ws(int b, int c, int n, int npoint, int nsample
         const int rc = check_launch("grouping_grad (sort)");
         if (rc != TPK_OK) return rc;
     }
-    return launch_sorted(p, b, c, n, ps, grad_out, entries, grad_features, s);
+    return launch_sorted(p, b, c, n, ps, gbs, grad_out, entries, grad_features, s);
+}
+}  // namespace
+}  // namespace tpk
+
+extern "C" int tpk_grouping_grad_ws(int b, int c, int n, int npoint, int nsample, const float* grad_out, const int64_t* idx,
+                                    float* grad_features, void* scratch, int64_t scratch_bytes, void* stream)
+{
+    return tpk::grouping_grad_with_scratch(b, c, n, npoint, nsample, grad_out, static_cast<long long>(c) * npoint * nsample, idx,
+                                           grad_features, scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tpk_sa_group_grad(int b, int c, int n, int npoint, int nsample, const float* grad_out, const int64_t* idx,
+                                 float* grad_features, void* scratch, int64_t scratch_bytes, void* stream)
+{
+    // the feature rows of the (b, 3 + c, npoint, nsample) gradient: rows 3.. of every cloud
+    const long long ps = static_cast<long long>(npoint) * nsample;
+    return tpk::grouping_grad_with_scratch(b, c, n, npoint, nsample, grad_out ? grad_out + 3 * ps : nullptr, (3ll + c) * ps, idx,
+                                           grad_features, scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
 }

@@ -52,6 +52,10 @@ struct StatusRegistrar
     StatusRegistrar g_status_registrar(read_status_word);                                          \
     }
 
+// gather.cu: gradient of grouping with atomics; gbs = batch stride of grad_out in floats
+int grouping_grad_atomic(int b, int c, int n, int npoint, int nsample, const float* grad_out, long long gbs,
+                         const int64_t* idx, float* grad_features, cudaStream_t s);
+
 constexpr unsigned kFullMask = 0xffffffffu;
 // Dynamic shared memory from which a launcher raises the kernel's limit
 // (cudaFuncAttributeMaxDynamicSharedMemorySize).  Well below the 48 KB a launch may use without

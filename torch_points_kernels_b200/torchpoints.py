@@ -269,7 +269,16 @@ class SAGroup(Function):
         if c > 0:
             # the feature rows of the gradient; the coordinates get none (indices and centres are
             # selections, and PointNet++ does not train through the point positions)
-            grad_features = grouping_backward(grad_out[:, 3:].contiguous(), idx, n)
+            # read in place (tpk_sa_group_grad takes the whole (B, 3+c, npoint, nsample) gradient)
+            grad_out = grad_out.contiguous()
+            _f32(grad_out, "grad_out")
+            B, _, npoint, nsample = grad_out.size()
+            grad_features = torch.empty((B, c, n), dtype=torch.float32, device=grad_out.device)
+            with torch.cuda.device(grad_out.device):
+                need = _lib.lib().tpk_grouping_grad_scratch_bytes(B, c, n, npoint, nsample)
+                scratch = torch.empty(need, dtype=torch.uint8, device=grad_out.device) if need > 0 else None
+                _lib.call("tpk_sa_group_grad", B, c, n, npoint, nsample, _lib.ptr(grad_out), _lib.ptr(idx),
+                          _lib.ptr(grad_features), _lib.ptr(scratch), need, _lib.stream_of(grad_out))
         return None, grad_features, None, None, None
 
 
