@@ -771,7 +771,9 @@ __global__ void __launch_bounds__(MAXT, 1)
     for (int exch = 0; j < m; ++exch)
     {
         const int par = exch & 1;
-        if (CLUSTERED && tid == 0)
+        // (the CTA's last warp arms the barrier: in the middle CTA of a cluster warp 0 holds the
+        // middle of the Morton order, the warp almost every sample reaches and every exchange waits for)
+        if (CLUSTERED && tid == nthreads - 32)
             mbar_arrive_expect_tx(smem_u32(mbar + par), static_cast<uint32_t>(nslots * kBatchMsgBytes));
 
         // ---- 1. apply the samples to the groups of points they can reach
