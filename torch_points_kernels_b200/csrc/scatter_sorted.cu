@@ -102,21 +102,25 @@ __global__ void __launch_bounds__(kSortedThreads)
     uint32_t* out = entries + (static_cast<size_t>(cloud) * tiles + t) * tile;
     const int nkeys = n + 1;
 
+    // the keys of this thread's positions (p = tid, tid + 512, ...), loaded once with all loads in
+    // flight together and kept in registers for both passes
+    int keys[kMaxChunk];
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < kMaxChunk; ++i)
+    {
+        const int p = tid + i * kSortedThreads;
+        long long v = -1;
+        if (p < len) v = __ldg(ip + p);
+        const bool ok = static_cast<unsigned long long>(v) < static_cast<unsigned long long>(n);
+        bad |= p < len && !ok;
+        keys[i] = ok ? static_cast<int>(v) : n;
+    }
     for (int i = tid; i < nkeys; i += kSortedThreads) cnt[i] = 0u;
     __syncthreads();
-    bool bad = false;
-    for (int p = tid; p < tile; p += kSortedThreads)
-    {
-        int key = n;
-        if (p < len)
-        {
-            const long long v = __ldg(ip + p);
-            const bool ok = static_cast<unsigned long long>(v) < static_cast<unsigned long long>(n);
-            bad |= !ok;
-            if (ok) key = static_cast<int>(v);
-        }
-        atomicAdd(&cnt[key], 1u);
-    }
+#pragma unroll
+    for (int i = 0; i < kMaxChunk; ++i)
+        if (tid + i * kSortedThreads < tile) atomicAdd(&cnt[keys[i]], 1u);
     __syncthreads();
     // exclusive scan of the counters: every thread a run of consecutive keys (odd length, so
     // that the threads of a warp start in different banks)
@@ -156,18 +160,18 @@ __global__ void __launch_bounds__(kSortedThreads)
     __syncthreads();
     // scatter: sorted rank q -> the slot thread q / chunk reads in its step q % chunk
     const int per_warp = 32 * chunk;
-    for (int p = tid; p < tile; p += kSortedThreads)
+#pragma unroll
+    for (int i = 0; i < kMaxChunk; ++i)
     {
-        int key = n;
-        if (p < len)
+        const int p = tid + i * kSortedThreads;
+        if (p < tile)
         {
-            const long long v = __ldg(ip + p);
-            if (static_cast<unsigned long long>(v) < static_cast<unsigned long long>(n)) key = static_cast<int>(v);
+            const int key = keys[i];
+            const uint32_t q = atomicAdd(&cnt[key], 1u);
+            const uint32_t owner = q / chunk, step = q - owner * chunk;
+            const uint32_t slot = (owner >> 5) * per_warp + step * 32u + (owner & 31u);
+            out[slot] = (static_cast<uint32_t>(key) << kPosBits) | static_cast<uint32_t>(key == n ? tile : p);
         }
-        const uint32_t q = atomicAdd(&cnt[key], 1u);
-        const uint32_t owner = q / chunk, step = q - owner * chunk;
-        const uint32_t slot = (owner >> 5) * per_warp + step * 32u + (owner & 31u);
-        out[slot] = (static_cast<uint32_t>(key) << kPosBits) | static_cast<uint32_t>(key == n ? tile : p);
     }
     if (bad) atomicOr(&g_dev_status, kStatusBadIndex);
 }
